@@ -1,0 +1,53 @@
+"""Grouped-query attention through torch SDPA without repeating k/v.
+
+The hot path keeps torch's SDPA (a library call in the reference too, solution/attention.py:
+332-343): one call per kv head, its query heads against stride-0 expanded views of that head's
+k and v, which gives the same products as transformers' repeat_kv path without the copies.
+"""
+
+import torch
+import torch.nn.functional as F
+
+
+def _grouped_sdpa(query, key, value, attention_mask, scaling):
+    kv_heads = key.shape[1]
+    per = query.shape[1] // kv_heads
+    B, _, T, D = query.shape
+    pieces = []
+    for j in range(kv_heads):
+        k = key[:, j:j + 1].expand(B, per, key.shape[2], D)
+        v = value[:, j:j + 1].expand(B, per, value.shape[2], D)
+        pieces.append(F.scaled_dot_product_attention(query[:, j * per:(j + 1) * per], k, v,
+                                                     attn_mask=attention_mask, dropout_p=0.0,
+                                                     scale=scaling))
+    return torch.cat(pieces, 1).transpose(1, 2).contiguous()
+
+
+def patch_qwen2_grouped_sdpa():
+    """transformers' "sdpa" attention for grouped-query models with a boolean 4-D mask goes
+    through `_grouped_sdpa`; everything else keeps the installed implementation."""
+    from transformers.modeling_utils import AttentionInterface
+
+    current = AttentionInterface._global_mapping.get("sdpa")
+    if current is None or getattr(current, "_grouped_sdpa", False):
+        return
+    original = current
+
+    def sdpa_attention_forward(module, query, key, value, attention_mask, dropout=0.0,
+                               scaling=None, is_causal=None, **kwargs):
+        groups = getattr(module, "num_key_value_groups", 1)
+        tensors_ok = all(isinstance(x, torch.Tensor) and x.dim() == 4 and x.is_cuda
+                         for x in (query, key, value))
+        mask_ok = (isinstance(attention_mask, torch.Tensor)
+                   and attention_mask.dtype == torch.bool and attention_mask.dim() == 4)
+        plain = (dropout == 0.0 and kwargs.get("sliding_window") is None
+                 and kwargs.get("position_bias") is None
+                 and not kwargs.get("output_attentions", False))
+        if (groups > 1 and tensors_ok and mask_ok and plain
+                and query.shape[1] == key.shape[1] * groups and key.shape == value.shape):
+            return _grouped_sdpa(query, key, value, attention_mask, scaling), None
+        return original(module, query, key, value, attention_mask, dropout=dropout,
+                        scaling=scaling, is_causal=is_causal, **kwargs)
+
+    sdpa_attention_forward._grouped_sdpa = True
+    AttentionInterface._global_mapping["sdpa"] = sdpa_attention_forward

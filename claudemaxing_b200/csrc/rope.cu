@@ -1,0 +1,158 @@
+// Rotary position embedding of q and k in one launch, forward or the transposed rotation.
+//
+// A thread owns 8 elements of the first half of a head row and the matching 8 of the second half
+// (two 128-bit loads and two 128-bit stores per head). It loads its cos/sin vectors once and walks
+// kHeadsPerThread heads with them, q heads first, then k heads, so cos/sin traffic is amortised
+// over the heads and q and k need a single launch. Inputs are read through their strides (q and k
+// arrive as transposed views of the projection outputs); outputs are contiguous [b, h, t, d].
+// Arithmetic is fp32, as in qwen_rope_kernel of the reference (solution/rope.py:17-43).
+#include "common.cuh"
+
+namespace soup {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kHeadsPerThread = 2;
+
+struct RopeArgs {
+  const void* x[2];   // q, k
+  void* out[2];
+  int64_t sb[2], sh[2], st[2];
+  int heads[2];
+  int xdt[2], odt[2];
+  const void* cos;
+  const void* sin;
+  int64_t cs_b, cs_t;
+  int csdt;
+  int64_t b, t;
+  int d;
+  int backward;
+};
+
+__device__ __forceinline__ void rotate(float x1, float x2, float c1, float c2, float s1, float s2,
+                                       int backward, float& o1, float& o2) {
+  if (backward) {  // g*cos + rotate_half^T(g*sin)
+    o1 = x1 * c1 + x2 * s2;
+    o2 = x2 * c2 - x1 * s1;
+  } else {  // x*cos + [-x2, x1]*sin
+    o1 = x1 * c1 - x2 * s1;
+    o2 = x2 * c2 + x1 * s2;
+  }
+}
+
+__global__ void __launch_bounds__(kThreads) rope_vec_kernel(RopeArgs a) {
+  const int half = a.d >> 1, group = half >> 3;
+  const int64_t tid = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+  if (tid >= a.b * a.t * group) return;
+  const int gi = (int)(tid % group);
+  const int64_t bt = tid / group;
+  const int64_t ti = bt % a.t, bi = bt / a.t;
+  const int64_t cs_row = bi * a.cs_b + ti * a.cs_t + (gi << 3);
+  float c1[8], c2[8], s1[8], s2[8];
+  load8(a.cos, cs_row, a.csdt, c1);
+  load8(a.cos, cs_row + half, a.csdt, c2);
+  load8(a.sin, cs_row, a.csdt, s1);
+  load8(a.sin, cs_row + half, a.csdt, s2);
+  const int total_heads = a.heads[0] + a.heads[1];
+  const int h0 = blockIdx.y * kHeadsPerThread;
+  float x1[kHeadsPerThread][8], x2[kHeadsPerThread][8];
+#pragma unroll
+  for (int u = 0; u < kHeadsPerThread; ++u) {
+    const int h = h0 + u;
+    if (h >= total_heads) break;
+    const int which = h < a.heads[0] ? 0 : 1;
+    const int hh = which ? h - a.heads[0] : h;
+    const int64_t off = bi * a.sb[which] + hh * a.sh[which] + ti * a.st[which] + (gi << 3);
+    load8(a.x[which], off, a.xdt[which], x1[u]);
+    load8(a.x[which], off + half, a.xdt[which], x2[u]);
+  }
+#pragma unroll
+  for (int u = 0; u < kHeadsPerThread; ++u) {
+    const int h = h0 + u;
+    if (h >= total_heads) break;
+    const int which = h < a.heads[0] ? 0 : 1;
+    const int hh = which ? h - a.heads[0] : h;
+    float o1[8], o2[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k)
+      rotate(x1[u][k], x2[u][k], c1[k], c2[k], s1[k], s2[k], a.backward, o1[k], o2[k]);
+    const int64_t orow = ((bi * a.heads[which] + hh) * a.t + ti) * a.d + (gi << 3);
+    store8(a.out[which], orow, a.odt[which], o1);
+    store8(a.out[which], orow + half, a.odt[which], o2);
+  }
+}
+
+// Any head_dim / strides / alignment: one thread per (b, head, t, i < half).
+__global__ void __launch_bounds__(kThreads) rope_scalar_kernel(RopeArgs a) {
+  const int half = a.d >> 1;
+  const int total_heads = a.heads[0] + a.heads[1];
+  const int64_t n = a.b * total_heads * a.t * half;
+  for (int64_t idx = (int64_t)blockIdx.x * kThreads + threadIdx.x; idx < n;
+       idx += (int64_t)gridDim.x * kThreads) {
+    const int i = (int)(idx % half);
+    int64_t r = idx / half;
+    const int64_t ti = r % a.t; r /= a.t;
+    const int h = (int)(r % total_heads);
+    const int64_t bi = r / total_heads;
+    const int which = h < a.heads[0] ? 0 : 1;
+    const int hh = which ? h - a.heads[0] : h;
+    const int64_t off = bi * a.sb[which] + hh * a.sh[which] + ti * a.st[which] + i;
+    const int64_t cs_row = bi * a.cs_b + ti * a.cs_t + i;
+    float o1, o2;
+    rotate(load1(a.x[which], off, a.xdt[which]), load1(a.x[which], off + half, a.xdt[which]),
+           load1(a.cos, cs_row, a.csdt), load1(a.cos, cs_row + half, a.csdt),
+           load1(a.sin, cs_row, a.csdt), load1(a.sin, cs_row + half, a.csdt), a.backward, o1, o2);
+    const int64_t orow = ((bi * a.heads[which] + hh) * a.t + ti) * a.d + i;
+    store1(a.out[which], orow, a.odt[which], o1);
+    store1(a.out[which], orow + half, a.odt[which], o2);
+  }
+}
+
+inline bool mult8(int64_t v) { return (v & 7) == 0; }
+
+}  // namespace
+}  // namespace soup
+
+extern "C" int soup_rope(const void* q, const void* k, const void* cos, const void* sin,
+                         void* q_out, void* k_out, int64_t b, int64_t hq, int64_t hk, int64_t t,
+                         int64_t d, int64_t q_sb, int64_t q_sh, int64_t q_st, int64_t k_sb,
+                         int64_t k_sh, int64_t k_st, int64_t cs_b, int64_t cs_t, int q_dtype,
+                         int k_dtype, int cs_dtype, int q_out_dtype, int k_out_dtype, int backward,
+                         void* stream) {
+  using namespace soup;
+  if (!q) hq = 0;
+  if (!k) hk = 0;
+  if (b == 0 || t == 0 || hq + hk == 0) return SOUP_OK;
+  if (b < 0 || t < 0 || hq < 0 || hk < 0 || d <= 0 || (d & 1))
+    SOUP_FAIL(SOUP_ERR_ARG, "rope: bad shape (head_dim must be even)");
+  if (!cos || !sin || (hq && !q_out) || (hk && !k_out)) SOUP_FAIL(SOUP_ERR_ARG, "rope: null pointer");
+  if (!is_float_dtype(cs_dtype) || (hq && !(is_float_dtype(q_dtype) && is_float_dtype(q_out_dtype))) ||
+      (hk && !(is_float_dtype(k_dtype) && is_float_dtype(k_out_dtype))))
+    SOUP_FAIL(SOUP_ERR_ARG, "rope: unsupported dtype");
+  RopeArgs a;
+  a.x[0] = q; a.x[1] = k; a.out[0] = q_out; a.out[1] = k_out;
+  a.sb[0] = q_sb; a.sh[0] = q_sh; a.st[0] = q_st;
+  a.sb[1] = k_sb; a.sh[1] = k_sh; a.st[1] = k_st;
+  a.heads[0] = (int)hq; a.heads[1] = (int)hk;
+  a.xdt[0] = q_dtype; a.xdt[1] = k_dtype; a.odt[0] = q_out_dtype; a.odt[1] = k_out_dtype;
+  a.cos = cos; a.sin = sin; a.cs_b = cs_b; a.cs_t = cs_t; a.csdt = cs_dtype;
+  a.b = b; a.t = t; a.d = (int)d; a.backward = backward;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  bool vec = (d % 16 == 0) && aligned16(cos) && aligned16(sin) && mult8(cs_b) && mult8(cs_t);
+  if (hq) vec = vec && aligned16(q) && aligned16(q_out) && mult8(q_sb) && mult8(q_sh) && mult8(q_st);
+  if (hk) vec = vec && aligned16(k) && aligned16(k_out) && mult8(k_sb) && mult8(k_sh) && mult8(k_st);
+  if (vec) {
+    const int64_t threads = b * t * (d >> 4);
+    dim3 grid((unsigned)((threads + kThreads - 1) / kThreads),
+              (unsigned)((hq + hk + kHeadsPerThread - 1) / kHeadsPerThread));
+    rope_vec_kernel<<<grid, kThreads, 0, s>>>(a);
+  } else {
+    const int64_t n = b * (hq + hk) * t * (d >> 1);
+    int64_t blocks = (n + kThreads - 1) / kThreads;
+    const int64_t cap = (int64_t)sm_count() * 16;
+    if (blocks > cap) blocks = cap;
+    rope_scalar_kernel<<<(unsigned)blocks, kThreads, 0, s>>>(a);
+  }
+  SOUP_CHECK_LAUNCH("rope");
+  return SOUP_OK;
+}

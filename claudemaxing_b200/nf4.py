@@ -1,0 +1,133 @@
+"""NF4 weight dequantisation (bitsandbytes 4-bit layout, double-quantised absmax) in one kernel.
+
+Drop-in for the reference's solution/nf4.py: `dequantize_nf4(packed, state, dtype=None, out=None)`
+takes anything that looks like a bitsandbytes QuantState (`.absmax .code .blocksize .shape .dtype
+.nested .offset .state2{.absmax .code .blocksize} .quant_type`) and returns the [N, K] weight.
+Layout: byte i holds elements 2i (high nibble) and 2i+1 (low nibble); element j belongs to absmax
+block j // blocksize; nested: absmax[b] = code2[absmax8[b]] * absmax2[b // blocksize2] + offset.
+The code tables are inputs, so the result is bit-identical to the unfused fp32 reference for any
+tables (csrc/nf4.cu). `patch_bnb_nf4_dequant` routes bitsandbytes through it when that package is
+installed and is a no-op otherwise.
+"""
+
+import torch
+
+from . import _lib
+
+_BLOCKSIZES = (32, 64, 128, 256, 512, 1024, 2048, 4096)
+
+
+def _supported(packed, state, dtype):
+    if state is None or not packed.is_cuda or packed.dtype != torch.uint8:
+        return False
+    if getattr(state, "quant_type", None) != "nf4" or dtype not in (torch.float16, torch.float32):
+        return False
+    code = getattr(state, "code", None)
+    if code is None or code.numel() != 16 or code.dtype != torch.float32 or not code.is_cuda:
+        return False
+    if not state.absmax.is_cuda or len(state.shape) != 2 or not packed.is_contiguous():
+        return False
+    if state.blocksize not in _BLOCKSIZES or (state.shape[0] * state.shape[1]) % 2:
+        return False
+    if state.nested:
+        s2 = state.state2
+        return (s2.blocksize > 0 and (s2.blocksize & (s2.blocksize - 1)) == 0
+                and s2.code.dtype == torch.float32 and s2.absmax.dtype == torch.float32
+                and state.absmax.dtype == torch.uint8)
+    return state.absmax.dtype == torch.float32
+
+
+def _offset_tensor(offset, device):
+    if isinstance(offset, torch.Tensor):
+        return offset.to(device=device, dtype=torch.float32).reshape(1)
+    return torch.tensor([float(offset)], dtype=torch.float32, device=device)
+
+
+def dequantize_nf4(packed, state, dtype=None, out=None):
+    """The [N, K] weight of an NF4 QuantState in `dtype` (default: state.dtype)."""
+    dtype = dtype or state.dtype
+    _lib.require_cuda(packed)
+    n = state.shape[0] * state.shape[1]
+    if out is None:
+        out = torch.empty(tuple(state.shape), dtype=dtype, device=packed.device)
+    if n == 0:
+        return out
+    nested = bool(state.nested)
+    if nested:
+        s2 = state.state2
+        code2, absmax2 = s2.code.contiguous(), s2.absmax.contiguous()
+        offset = _offset_tensor(state.offset, packed.device)  # stays on the GPU: no sync
+        bs2 = int(s2.blocksize)
+    else:
+        code2 = absmax2 = offset = None
+        bs2 = 1
+    _lib.call("soup_nf4_dequant", _lib.ptr(packed), _lib.ptr(state.absmax.contiguous()),
+              _lib.ptr(state.code), _lib.ptr(code2), _lib.ptr(absmax2), _lib.ptr(offset),
+              _lib.ptr(out), n, int(state.blocksize), bs2, int(nested),
+              _lib.dtype_code(out.dtype), _lib.stream_of(packed))
+    return out
+
+
+ORIGINALS = {}
+_CODE = {}
+
+
+def _nf4_code(device):
+    """bitsandbytes' own NF4 code table on `device` (needs bitsandbytes)."""
+    if device not in _CODE:
+        import bitsandbytes.functional as bnbF
+
+        _CODE[device] = bnbF.get_4bit_type("nf4", device=device).float()
+    return _CODE[device]
+
+
+def patch_bnb_nf4_dequant():
+    """Route bitsandbytes' NF4 dequantisation (the dequant + F.linear path of gemm_4bit and
+    functional.dequantize_4bit) through `dequantize_nf4`. fp4, bf16, CPU tensors or an `out=`
+    buffer keep bitsandbytes' own code. Without bitsandbytes there is nothing to patch
+    (the reference's patch raises there, solution/nf4.py:94-96)."""
+    if ORIGINALS:
+        return
+    try:
+        import bitsandbytes.functional as bnbF
+        from bitsandbytes.backends.cuda import ops as cuda_ops
+        from bitsandbytes.functional import QuantState
+    except Exception:  # noqa: BLE001
+        return
+    original_fallback = cuda_ops._dequant_linear_fallback
+    original_dequant = bnbF.dequantize_4bit
+    ORIGINALS.update(fallback=original_fallback, dequant=original_dequant)
+
+    def _dequant_linear_fallback(A, B, shapeB, absmax, blocksize, quant_type, bias=None,
+                                 absmax_8bit=None, absmax_code=None, absmax_offset=None):
+        def keep():
+            return original_fallback(A, B, shapeB, absmax, blocksize, quant_type, bias,
+                                     absmax_8bit=absmax_8bit, absmax_code=absmax_code,
+                                     absmax_offset=absmax_offset)
+
+        if (quant_type != "nf4" or A.dtype not in (torch.float16, torch.float32) or not A.is_cuda
+                or (absmax_8bit is not None and (absmax_code is None or absmax_offset is None))):
+            return keep()
+        code = _nf4_code(A.device)
+        if absmax_8bit is not None:  # `absmax` is then the nested state's absmax
+            inner = QuantState(absmax=absmax, code=absmax_code, blocksize=256, dtype=torch.float32)
+            state = QuantState(absmax=absmax_8bit, shape=torch.Size(shapeB), code=code,
+                               blocksize=blocksize, quant_type="nf4", dtype=A.dtype,
+                               offset=absmax_offset, state2=inner)
+        else:
+            state = QuantState(absmax=absmax, shape=torch.Size(shapeB), code=code,
+                               blocksize=blocksize, quant_type="nf4", dtype=A.dtype)
+        if not _supported(B, state, A.dtype):
+            return keep()
+        return torch.nn.functional.linear(A, dequantize_nf4(B, state, A.dtype), bias)
+
+    def dequantize_4bit(A, quant_state=None, absmax=None, out=None, blocksize=None,
+                        quant_type="fp4"):
+        if out is None and quant_state is not None and _supported(A, quant_state,
+                                                                    quant_state.dtype):
+            weight = dequantize_nf4(A, quant_state)
+            return weight.t() if A.shape[0] == 1 else weight  # bitsandbytes' [1, X] packed layout
+        return original_dequant(A, quant_state, absmax, out, blocksize, quant_type)
+
+    cuda_ops._dequant_linear_fallback = _dequant_linear_fallback
+    bnbF.dequantize_4bit = dequantize_4bit

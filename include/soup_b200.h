@@ -1,0 +1,178 @@
+/* libsoup_b200 — C ABI of the B200 (sm_100a) kernels behind the QLoRA training hot path.
+ *
+ * The reference project (arturbaimuratov1-sys/claudemaxing) has no native layer: every entry here
+ * stands where the reference launches one of its Triton kernels from Python, and the comment on
+ * each entry names that launch site (path inside the reference project : line).
+ *
+ * Conventions
+ *  - Every pointer is a device pointer owned by the caller; the library allocates nothing, frees
+ *    nothing and never synchronises the device. Work is enqueued on `stream`.
+ *  - `stream` is a cudaStream_t passed as void* (0 = the legacy default stream).
+ *  - Return value: 0 = enqueued; negative = SOUP_ERR_*; the message is in soup_last_error_string()
+ *    (thread local). Nothing aborts or traps.
+ *  - dtype codes: SOUP_F32, SOUP_F16, SOUP_BF16.
+ *  - All entries are re-entrant: no global scratch, so autograd worker threads may call them
+ *    concurrently on different streams.
+ */
+#ifndef SOUP_B200_H
+#define SOUP_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SOUP_F32 0
+#define SOUP_F16 1
+#define SOUP_BF16 2
+
+#define SOUP_OK 0
+#define SOUP_ERR_ARG (-1)     /* bad shape / dtype / alignment / null pointer */
+#define SOUP_ERR_LAUNCH (-2)  /* the CUDA runtime refused the launch */
+#define SOUP_ERR_DEVICE (-3)  /* wrong device (not sm_100) or driver entry point missing */
+
+/* Library ABI version; bumped when a signature changes. */
+int soup_version(void);
+/* Message of the last failing call on this thread ("" if none). */
+const char* soup_last_error_string(void);
+
+/* NF4 -> fp16/fp32 weight, nested (double-quantised) absmax fused, bit-exact unfused fp32 math.
+ * Replaces nf4_dequant_kernel[grid](...) at solution/nf4.py:78-81 (kernel :26-46).
+ *   packed   uint8 [n_elems/2]; element 2i = high nibble of byte i, 2i+1 = low nibble
+ *   absmax   nested: uint8 [n_elems/blocksize]; else float [n_elems/blocksize]
+ *   code     float [16]   4-bit code table
+ *   code2    float [256]  8-bit map of the nested absmax          (nested only)
+ *   absmax2  float [ceil(n_elems/blocksize/blocksize2)]            (nested only)
+ *   offset   float [1]                                             (nested only)
+ *   out      out_dtype [n_elems]
+ * scale = nested ? code2[absmax[b]] * absmax2[b / blocksize2] + offset : absmax[b]   (mul, then add)
+ * out[j] = round_out_dtype(code[nibble_j] * scale)
+ * Requires: n_elems even, blocksize in {32..4096} power of two, out_dtype F16 or F32. */
+int soup_nf4_dequant(const void* packed, const void* absmax, const float* code, const float* code2,
+                     const float* absmax2, const float* offset, void* out, int64_t n_elems,
+                     int blocksize, int blocksize2, int nested, int out_dtype, void* stream);
+
+/* RMSNorm forward: rstd = 1/sqrt(mean(x^2)+eps); normed = round_x_dtype(x*rstd);
+ * out = round_out_dtype(normed*w). Replaces qwen_rmsnorm_fwd_kernel at solution/rmsnorm.py:180-184
+ * (kernel :28-47).
+ *   low   (nullable) fp16 copy of out [n_rows,n_cols]; when given, slot/small are used too:
+ *   slot  int32 [n_cols], index among the tiny-|w| columns or -1
+ *   small fp16 [n_rows,n_small], normalised value of the tiny-|w| columns */
+int soup_rmsnorm_fwd(const void* x, const void* w, void* out, float* rstd, void* low,
+                     const int32_t* slot, void* small, int64_t n_small, int64_t n_rows,
+                     int64_t n_cols, float eps, int x_dtype, int w_dtype, int out_dtype,
+                     void* stream);
+
+/* Number of fp32 rows of the dw workspace soup_rmsnorm_bwd needs for this shape. */
+int64_t soup_rmsnorm_bwd_partials(int64_t n_rows, int64_t n_cols);
+
+/* RMSNorm backward: dx = (gn - n*mean(gn*n))*rstd with gn = dy*w (rounded to xin dtype unless
+ * saved_output), n = xin*rstd, or (saved_output) n = low/w with the tiny-|w| columns taken from
+ * `small`. Optional dw = sum_rows dy*round_x_dtype(n): needs dw_partial (fp32
+ * [soup_rmsnorm_bwd_partials(), n_cols]) and dw (w_dtype [n_cols]); pass both NULL to skip.
+ * Replaces qwen_rmsnorm_bwd_kernel at solution/rmsnorm.py:205-212 (kernel :51-91) and the
+ * partial.sum(0) that follows it (:213-214). */
+int soup_rmsnorm_bwd(const void* dy, const void* xin, const void* w, const float* rstd, void* dx,
+                     float* dw_partial, void* dw, const int32_t* slot, const void* small,
+                     int64_t n_small, int64_t n_rows, int64_t n_cols, int dy_dtype, int xin_dtype,
+                     int w_dtype, int dx_dtype, int saved_output, void* stream);
+
+/* Rotary embedding of q and k in one launch (forward, or the transposed rotation for backward).
+ * Replaces the two qwen_rope_kernel launches of RoPE.forward / RoPE.backward at
+ * solution/rope.py:54-56 (kernel :17-43). Either of q / k may be NULL (skipped).
+ *   q      [b, hq, t, d] with strides (q_sb, q_sh, q_st, 1) in elements; k likewise with hk
+ *   cos,sin [cb, t, d] contiguous in t,d; batch stride cs_b elements (0 to broadcast)
+ *   q_out  [b, hq, t, d] contiguous, k_out [b, hk, t, d] contiguous
+ * fwd: o1 = x1*c1 - x2*s1, o2 = x2*c2 + x1*s2;  bwd: o1 = x1*c1 + x2*s2, o2 = x2*c2 - x1*s1. */
+int soup_rope(const void* q, const void* k, const void* cos, const void* sin, void* q_out,
+              void* k_out, int64_t b, int64_t hq, int64_t hk, int64_t t, int64_t d, int64_t q_sb,
+              int64_t q_sh, int64_t q_st, int64_t k_sb, int64_t k_sh, int64_t k_st, int64_t cs_b,
+              int64_t cs_t, int q_dtype, int k_dtype, int cs_dtype, int q_out_dtype,
+              int k_out_dtype, int backward, void* stream);
+
+/* out = round_out(round_gate?(silu(gate)) * up). Replaces silu_mul_fwd_persistent at
+ * solution/swiglu_recompute.py:98-100 and :176-178 (kernel :36-48). */
+int soup_silu_mul_fwd(const void* gate, const void* up, void* out, int64_t n, int gate_dtype,
+                      int up_dtype, int out_dtype, int round_silu, void* stream);
+
+/* Recompute backward of silu(gate)*up: dup = dy*silu, dgate = round?(dy*up)*sig*(1+g*(1-sig)).
+ * dgate may alias gate and dup may alias up (each element is read before it is written).
+ * Either output may be NULL (not wanted). Replaces silu_mul_bwd_recompute at
+ * solution/swiglu_recompute.py:122-124 and :203-205 (kernel :51-79). */
+int soup_silu_mul_bwd(const void* dy, const void* gate, const void* up, void* dgate, void* dup,
+                      int64_t n, int dy_dtype, int gate_dtype, int up_dtype, int round_silu,
+                      void* stream);
+
+/* LoRA dropout pack: xd = fp16(keep ? x*scale : 0); bits[r] = sum_l keep[8r+l] << l.
+ * Replaces lora_dropout_pack_kernel at solution/lora.py:64-65 (kernel :30-42).
+ *   x [n] x_dtype, mask bool/uint8 [n], xd fp16 [n], bits uint8 [n/8]; n % 8 == 0 */
+int soup_dropout_pack(const void* x, const uint8_t* mask, void* xd, uint8_t* bits, int64_t n,
+                      float scale, int x_dtype, void* stream);
+
+/* LoRA dropout unpack: xd = fp16(keep ? x16*scale : 0), dx = dx_dtype(keep ? g16*scale : 0).
+ * Replaces lora_dropout_unpack_kernel at solution/lora.py:73-74 (kernel :45-57). */
+int soup_dropout_unpack(const void* x16, const uint8_t* bits, const void* g16, void* xd, void* dx,
+                        int64_t n, float scale, int dx_dtype, void* stream);
+
+/* ---- fused LM head + cross-entropy (tcgen05 / TMEM / TMA) -------------------------------------
+ * Replaces the chunk loop of _FusedHeadLoss.forward, solution/lm_head_loss.py:213-224 (torch.mm,
+ * lm_head_vocab_chunk_kernel :108-160, torch.mm, mul_/add_), over the columns of one weight shard.
+ * State arrays are fp32/int32 [n] and are initialised by the call:
+ *   run_max, run_sum  running max and sum of exp(z - run_max) over the shard's columns
+ *   run_dot           running sum of exp(z - run_max) * z                      (entropy)
+ *   best              global vocabulary index of the first maximum             (accuracy)
+ *   label_logit       the label's logit, where the label falls in this shard   (loss)
+ *   label_lse         the running lse when the label's chunk was processed     (label fix-up)
+ *   dh                fp32 [n,h]: 1024 * sum_v softmax_shard(z)_v * W[v] with the label's -1 in
+ *                     place, against this shard's own log-sum-exp; NULL when want_grad == 0
+ * hidden fp16 [n,h] and weight fp16 [v_shard,h] row-major, 16-byte aligned, h % 8 == 0.
+ * col_offset = global index of the shard's first column. chunk_tiles = 256-column tiles per
+ * chunk (0 = library default). workspace: soup_lmhead_workspace_bytes() bytes, 16-byte aligned. */
+int64_t soup_lmhead_workspace_bytes(int64_t n, int64_t h, int64_t v_shard, int64_t chunk_tiles);
+int soup_lmhead_ce(const void* hidden, const void* weight, const int64_t* target, float* run_max,
+                   float* run_sum, float* run_dot, int* best, float* label_logit,
+                   float* label_lse, float* dh, void* workspace, int64_t workspace_bytes,
+                   int64_t n, int64_t h, int64_t v_shard, int64_t col_offset,
+                   int64_t chunk_tiles, int want_grad, void* stream);
+
+/* Reads back the device status word of the last soup_lmhead_ce on this workspace (synchronises
+ * `stream`): 0 = every bounded wait completed; otherwise the code of the wait that gave up. */
+int soup_lmhead_status(const void* workspace, int64_t n, int64_t v_shard, int64_t chunk_tiles,
+                       int* host_status, void* stream);
+
+/* Vocabulary-parallel merge of per-rank states gathered as [n_ranks, n] arrays (rank order =
+ * ascending vocabulary order; shard_begin int64 [n_ranks + 1] on the device). o_lse = merged
+ * log-sum-exp. No counterpart in the reference, which is single-GPU (solution/lm_head_loss.py:
+ * 426-428 refuses n_gpu > 1); the merge rule is the chunk-to-chunk carry of :119-145. */
+int soup_lmhead_merge(const float* g_max, const float* g_sum, const float* g_dot,
+                      const int* g_best, const float* g_label_logit, const float* g_label_lse,
+                      const int64_t* target, const int64_t* shard_begin, float* o_max,
+                      float* o_sum, float* o_dot, int* o_best, float* o_label_logit,
+                      float* o_label_lse, float* o_lse, int64_t n, int n_ranks, void* stream);
+
+/* Finalisation, solution/lm_head_loss.py:225-237: token_loss = lse - label_logit (0 if ignored),
+ * entropy = lse - run_dot/run_sum, correct = labelled && best == target (all nullable together);
+ * dh (nullable, in place): scaled by exp(local_lse - lse) when local_lse is given, and, where the
+ * label falls in this shard, dh -= W[label] * (1 - exp(label_lse - lse)) * 1024. */
+int soup_lmhead_finish(const float* run_max, const float* run_sum, const float* run_dot,
+                       const int* best, const float* label_logit, const float* label_lse,
+                       const float* local_lse, const int64_t* target, const void* weight,
+                       float* token_loss, float* entropy, int* correct, float* dh, int64_t n,
+                       int64_t h, int64_t v_shard, int64_t col_offset, void* stream);
+
+/* out = out_dtype(dh * scale[0]) — _FusedHeadLoss.backward, solution/lm_head_loss.py:248-254. */
+int soup_lmhead_grad_scale(const float* dh, void* out, const float* scale, int64_t n,
+                           int out_dtype, void* stream);
+
+/* Loss / entropy / correct per row from materialised logits [n_rows, n_cols] (row pitch
+ * row_stride elements). Replaces lm_head_xent_rows_kernel, solution/lm_head_loss.py:168-172
+ * (kernel :54-96) in its WRITE_GRAD = False use. */
+int soup_xent_rows(const void* logits, const int64_t* target, float* loss, float* entropy,
+                   int* correct, int64_t n_rows, int64_t n_cols, int64_t row_stride, int dtype,
+                   void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SOUP_B200_H */
