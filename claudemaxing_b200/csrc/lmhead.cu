@@ -144,6 +144,7 @@ __global__ void __launch_bounds__(kThreadsGemm, 1)
 lmhead_logits_kernel(const __grid_constant__ CUtensorMap map_h,
                      const __grid_constant__ CUtensorMap map_w, const LogitsArgs a) {
   extern __shared__ uint8_t smem_raw[];
+  if (*reinterpret_cast<volatile int*>(a.status) != 0) return;  // an earlier kernel gave up
   constexpr int kStageBytes = kABytes + kB1Bytes;
   const GemmSmem s = carve_smem<kStages1, kStageBytes>(smem_raw);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -399,6 +400,7 @@ __global__ void __launch_bounds__(kThreadsGemm, 1)
 lmhead_grad_kernel(const __grid_constant__ CUtensorMap map_p,
                    const __grid_constant__ CUtensorMap map_w, const GradArgs a) {
   extern __shared__ uint8_t smem_raw[];
+  if (*reinterpret_cast<volatile int*>(a.status) != 0) return;  // an earlier kernel gave up
   constexpr int kStageBytes = kABytes + kB2Bytes;
   const GemmSmem s = carve_smem<kStages2, kStageBytes>(smem_raw);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;

@@ -3,7 +3,7 @@
 // with shared-memory matrix descriptors, tcgen05.ld for the epilogue, and the tensor-map encoder
 // obtained from the driver at run time.
 //
-// Every wait is bounded: after kSpinLimit failed polls the waiter records a code in a status word
+// Every wait is bounded: after kWaitLimitNs without success the waiter records a code in a status word
 // and returns false, and the caller unwinds (frees its tensor memory and exits). Nothing here can
 // spin forever and nothing traps.
 #pragma once
@@ -15,7 +15,7 @@
 namespace soup {
 namespace umma {
 
-constexpr uint32_t kSpinLimit = 1u << 24;  // polls; each poll may itself block for a short time
+constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s: far beyond any healthy wait
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -53,13 +53,25 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Bounded wait. `abort_flag` is a shared-memory word every role of the CTA polls, so that one
-// role giving up releases the others too. Returns false when the wait was abandoned.
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Bounded wait: gives up after kWaitLimitNs of wall time. `abort_flag` is a shared-memory word
+// every role of the CTA polls, so that one role giving up releases the others too. Returns false
+// when the wait was abandoned; the first abandoning waiter records `code` in `status`.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                           int* status, int code) {
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = global_timer_ns();
+  for (uint32_t i = 1;; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 1023u) == 1023u && *abort_flag) return false;
+    if ((i & 63u) == 0u) {
+      if (*abort_flag) return false;
+      if (global_timer_ns() - t0 > kWaitLimitNs) break;
+    }
   }
   *abort_flag = 1;
   if (status) atomicCAS(status, 0, code);

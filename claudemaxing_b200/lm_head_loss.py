@@ -96,7 +96,12 @@ def head_partial(h16, w16, target, col_offset=0, chunk_cols=None, want_grad=True
     dev = h16.device
     state = HeadState(n, dev)
     grad_raw = torch.empty((n, hidden), dtype=torch.float32, device=dev) if want_grad else None
-    if n == 0:
+    if n == 0 or vocab == 0:  # an empty shard contributes nothing: max -inf, sums 0, gradient 0
+        state.run_max.fill_(float("-inf"))
+        for t in state.tensors()[1:]:
+            t.zero_()
+        if grad_raw is not None:
+            grad_raw.zero_()
         return state, grad_raw
     tiles = _chunk_tiles(chunk_cols)
     nbytes = _lib.lib().soup_lmhead_workspace_bytes(n, hidden, vocab, tiles)

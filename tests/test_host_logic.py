@@ -1,0 +1,103 @@
+"""Host-side logic that needs no GPU: the patch surface, label shifting, batch packing, the
+compute-dtype rule, shard bounds, the quantiser against the oracle's."""
+
+import torch
+
+from claudemaxing_b200 import lm_head_loss as L
+from claudemaxing_b200 import parallel, qlora
+
+
+def test_apply_is_idempotent_and_class_level():
+    import claudemaxing_b200 as solution
+    from transformers.models.qwen2 import modeling_qwen2 as m
+
+    solution.apply()
+    first = (m.Qwen2RMSNorm.forward, m.Qwen2MLP.forward, m.apply_rotary_pos_emb,
+             m.Qwen2ForCausalLM.forward)
+    solution.apply()
+    again = (m.Qwen2RMSNorm.forward, m.Qwen2MLP.forward, m.apply_rotary_pos_emb,
+             m.Qwen2ForCausalLM.forward)
+    assert all(a is b for a, b in zip(first, again))
+    assert first[0]._fused_rmsnorm and first[1]._swiglu_recompute and first[2]._fused_rope
+    assert first[3]._fused_head
+
+
+def test_patched_modules_keep_original_behaviour_on_cpu():
+    # the guards send CPU tensors to the installed implementation (third-party callers keep working)
+    import claudemaxing_b200 as solution
+    from transformers import Qwen2Config
+    from transformers.models.qwen2 import modeling_qwen2 as m
+
+    solution.apply()
+    cfg = Qwen2Config(hidden_size=32, intermediate_size=64, num_hidden_layers=1,
+                      num_attention_heads=4, num_key_value_heads=2, vocab_size=50)
+    norm = m.Qwen2RMSNorm(32)
+    x = torch.randn(2, 5, 32)
+    ref = norm.weight * (x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + norm.variance_epsilon))
+    assert torch.allclose(norm(x), ref, atol=1e-6)
+    mlp = m.Qwen2MLP(cfg)
+    assert mlp(x).shape == x.shape
+    q, k = torch.randn(1, 4, 5, 8), torch.randn(1, 2, 5, 8)
+    cos, sin = torch.randn(1, 5, 8), torch.randn(1, 5, 8)
+    oq, ok = m.apply_rotary_pos_emb(q, k, cos, sin)
+    assert oq.shape == q.shape and ok.shape == k.shape
+
+
+def test_shift_labels_left():
+    labels = torch.tensor([[1, 2, 3], [4, -100, 6]])
+    assert L.shift_labels_left(labels).tolist() == [[2, 3, -100], [-100, 6, -100]]
+
+
+def test_head_compute_dtype_rule():
+    h16, h32 = torch.zeros(1, dtype=torch.float16), torch.zeros(1)
+    assert L.head_compute_dtype(h16, h16) == torch.float16
+    assert L.head_compute_dtype(h32, h16) is None
+
+
+def test_pack_tokens_layout():
+    ids = torch.tensor([[5, 6, 7, 0], [8, 9, 0, 0]])
+    mask = torch.tensor([[1, 1, 1, 0], [1, 1, 0, 0]])
+    labels = ids.clone()
+    p = L.pack_tokens(ids, mask, labels)
+    assert p.ids.tolist() == [[5, 6, 7, 8, 9]] and p.pos.tolist() == [[0, 1, 2, 0, 1]]
+    assert p.target.tolist() == [[6, 7, 0, 9, 0]]
+    allowed = p.mask[0, 0]
+    assert allowed.shape == (5, 5) and allowed[2, :3].all() and not allowed[3, :3].any()
+    assert allowed[4, 3] and not allowed[3, 4]
+    assert L.pack_tokens(ids, torch.ones_like(mask), labels) is None  # nothing to drop
+    assert L._chunk_tiles(None) == 0 and L._chunk_tiles(7) == 1 and L._chunk_tiles(8192) == 32
+
+
+def test_shard_bounds_cover_the_vocabulary_in_whole_tiles():
+    for vocab, world in ((151936, 8), (151936, 2), (5000, 4), (300, 4), (256, 1)):
+        b = parallel.shard_bounds(vocab, world)
+        assert b[0] == 0 and b[-1] == vocab and len(b) == world + 1
+        assert all(x <= y for x, y in zip(b, b[1:]))
+        assert all(x % 256 == 0 or x == vocab for x in b)
+    sizes = [y - x for x, y in zip(*(lambda b: (b, b[1:]))(parallel.shard_bounds(151936, 8)))]
+    assert max(sizes) - min(sizes) <= 512
+
+
+def test_quantiser_and_tables_match_the_oracle():
+    from oracle import nf4 as onf4
+
+    assert torch.equal(qlora.normal_float4_levels(), onf4.nf4_code_table())
+    assert torch.equal(qlora.absmax_levels(), onf4.dynamic_map())
+    w = (torch.randn(64, 384, generator=torch.Generator().manual_seed(0)) * 0.02).half()
+    for nested in (True, False):
+        p1, s1 = qlora.quantize_nf4(w, nested=nested)
+        p2, s2 = onf4.quantize_nf4(w, nested=nested)
+        assert torch.equal(p1, p2) and torch.equal(s1.absmax, s2.absmax)
+        if nested:
+            assert torch.equal(s1.state2.absmax, s2.state2.absmax) and torch.equal(s1.offset, s2.offset)
+        deq = onf4.dequantize_nf4(p1, s1)
+        assert (deq.float() - w.float()).abs().max() < 0.2 * w.float().abs().max()
+
+
+def test_nf4_supported_guard():
+    from claudemaxing_b200.nf4 import _supported
+
+    w = torch.zeros(4, 64, dtype=torch.float16)
+    p, s = qlora.quantize_nf4(w)
+    assert not _supported(p, s, torch.float16)  # CPU tensors are not for the kernel
+    assert not _supported(p, None, torch.float16)
