@@ -1,0 +1,501 @@
+"""Benchmark of the QLoRA hot path on B200: fused LM-head + cross-entropy forward+backward.
+
+    python bench.py --gpus N --steps K --warmup W            # this repository's kernels
+    python bench.py --impl reference --gpus N --steps K --warmup W   # the CPU restatement, timed
+
+One "step" is one pass of the hot path over one batch of synthetic input: fused_head_loss forward
+plus backward through the public API (loss, per-row loss/entropy/accuracy, dHidden). The workload
+at N=1 is BASELINE config 1 (2048 packed tokens, hidden 1536, tied fp16 head 151936 x 1536, 10 %
+ignored targets). At N>1 the head is vocabulary-parallel with 2048 tokens per GPU (weak scaling:
+per-GPU GEMM work is constant, the exchange is one all-gather of the per-row states and one
+all-reduce of dHidden). `--workload c5a` selects the fixed 65536-token job instead.
+
+The printed line carries: `value` (tokens/s, inputs resident in HBM), `e2e` (the same through host
+buffers: pinned host -> device copies of hidden and targets and device -> host reads of the loss
+and dHidden inside the timed region), `roofline` (tensor-pipe bound, measured per kernel class with
+CUDA events on the launching stream), `kernels` (the memory-bound kernels of the path in GB/s
+against the measured HBM copy peak, cold L2 by rotating buffer sets) and `cpu_baseline` (the oracle
+on the host cores over a bounded sample of the same workload).
+"""
+
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+HIDDEN, VOCAB, TOKENS_PER_GPU = 1536, 151936, 2048
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            p = json.load(f)
+        return {k: float(p[k]) for k in FALLBACK_PEAKS}, "measured"
+    except Exception:  # noqa: BLE001
+        return dict(FALLBACK_PEAKS), "fallback"
+
+
+def make_inputs(n_tokens, seed=0):
+    """BASELINE config 1 recipe: hidden ~N(0,1) fp16, W ~N(0,0.02) fp16, targets uniform with 10 %
+    set to ignore_index. Generated on the CPU so that oracle and kernels see identical bits."""
+    gen = torch.Generator().manual_seed(seed)
+    hidden = torch.randn(n_tokens, HIDDEN, generator=gen).half()
+    weight = torch.empty(VOCAB, HIDDEN, dtype=torch.float16)
+    for r0 in range(0, VOCAB, 16384):  # slab by slab: no 900 MB fp32 temporary
+        rows = min(16384, VOCAB - r0)
+        weight[r0:r0 + rows] = (torch.randn(rows, HIDDEN, generator=gen) * 0.02).half()
+    target = torch.randint(0, VOCAB, (n_tokens,), generator=gen)
+    target[torch.rand(n_tokens, generator=gen) < 0.1] = -100
+    return hidden, weight, target
+
+
+class ClockSampler:
+    """Polls nvidia-smi for SM clocks and throttle reasons while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.samples, self.proc, self.index = [], None, index
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:  # noqa: BLE001
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) == 6:
+                self.samples.append(parts)
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:  # noqa: BLE001
+                self.proc.kill()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        sm = [float(s[0]) for s in self.samples if s[0].replace(".", "").isdigit()]
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        reasons = [n for i, n in enumerate(names) if any(s[2 + i] == "Active" for s in self.samples)]
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": float(self.samples[0][1]) if self.samples[0][1].isdigit() else None,
+                "reasons": reasons, "samples": len(self.samples)}
+
+
+def cpu_head_tokens_per_s(hidden, weight, target, rows, threads):
+    """The oracle (fp32 matmul + log_softmax + autograd) over `rows` rows of the workload."""
+    from oracle.head_ce import head_ce
+
+    torch.set_num_threads(threads)
+    t0 = time.perf_counter()
+    head_ce(hidden[:rows], weight, target[:rows])
+    return rows / (time.perf_counter() - t0)
+
+
+def run_reference(args, rank):
+    """--impl reference: the CPU restatement of the reference's arithmetic on the host cores."""
+    if rank != 0:
+        return
+    cores = os.cpu_count() or 1
+    hidden, weight, target = make_inputs(TOKENS_PER_GPU)
+    w32 = weight.float()
+    probe = cpu_head_tokens_per_s(hidden, w32, target, 32, cores)
+    budget = 150.0 / max(1, args.steps + args.warmup)  # seconds per step
+    rows = int(max(32, min(TOKENS_PER_GPU, probe * budget * 0.8)) // 32 * 32)
+    for _ in range(args.warmup):
+        cpu_head_tokens_per_s(hidden, w32, target, rows, cores)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_head_tokens_per_s(hidden, w32, target, rows, cores)
+    dt = time.perf_counter() - t0
+    value = rows * args.steps / dt
+    line = {
+        "impl": "reference", "metric": "fused LM-head+CE fwd+bwd tokens/s", "value": value,
+        "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "configs[0]: fused LM-head+CE fwd+bwd, H=1536 V=151936, "
+                               f"{rows}-row sample of the 2048-token batch per step"},
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": "port",
+                         "sample": f"{rows} rows x full vocabulary per step, torch fp32 matmul + "
+                                   "log_softmax + autograd (oracle/head_ce.py)"},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------
+# memory-bound kernels of the path, cold L2 (rotating buffer sets larger than the 126 MB L2)
+# ------------------------------------------------------------------------------------------
+def time_rotating(make_call, n_sets, reps=20):
+    """Median milliseconds of `call(i)` over reps, cycling through n_sets independent buffer sets."""
+    for i in range(min(3, n_sets)):
+        make_call(i % n_sets)
+    torch.cuda.synchronize()
+    times = []
+    for r in range(reps):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        make_call(r % n_sets)
+        b.record()
+        b.synchronize()
+        times.append(a.elapsed_time(b))
+    return statistics.median(times)
+
+
+def kernel_suite(dev, hbm_peak, n_rows=2048):
+    from claudemaxing_b200 import _lib, lora, qlora
+    from claudemaxing_b200.nf4 import dequantize_nf4
+    from claudemaxing_b200.swiglu_recompute import _silu_mul_bwd, _silu_mul_fwd
+
+    out = {}
+    f16, f32 = torch.float16, torch.float32
+
+    def sets_for(nbytes):
+        return max(2, int(400e6 // max(nbytes, 1)) + 1)
+
+    def record(name, ms, nbytes, launches=1):
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        out[name] = {"ms": round(ms, 5), "gb_s": round(gbs, 1), "frac_of_measured_hbm": round(gbs / hbm_peak, 3),
+                     "algorithmic_bytes": int(nbytes), "launches": launches}
+
+    # NF4 dequant: the seven projection shapes of one Qwen2.5-1.5B layer, 28 distinct layers
+    shapes = [(1536, 1536), (256, 1536), (256, 1536), (1536, 1536), (8960, 1536), (8960, 1536),
+              (1536, 8960)]
+    code, code2 = qlora.normal_float4_levels().to(dev), qlora.absmax_levels().to(dev)
+    layers = []
+    gen = torch.Generator(device=dev).manual_seed(1)
+    for _ in range(28):
+        layer = []
+        for (o, i) in shapes:
+            n = o * i
+            packed = torch.randint(0, 256, (n // 2, 1), dtype=torch.uint8, device=dev, generator=gen)
+            absmax8 = torch.randint(0, 256, (n // 64,), dtype=torch.uint8, device=dev, generator=gen)
+            inner = qlora.QuantState(torch.rand(-(-n // 64 // 256), device=dev, generator=gen) * 0.01,
+                                     (n // 64,), code2, 256, f32)
+            st = qlora.QuantState(absmax8, (o, i), code, 64, f16,
+                                  offset=torch.tensor([0.02], device=dev), state2=inner)
+            layer.append((packed, st))
+        layers.append(layer)
+    outs = [torch.empty(o * i, dtype=f16, device=dev).view(o, i) for (o, i) in shapes]
+    elems = sum(o * i for o, i in shapes)
+
+    def nf4_all():
+        for layer in layers:
+            for (packed, st), buf in zip(layer, outs):
+                dequantize_nf4(packed, st, f16, out=buf)
+
+    for _ in range(2):
+        nf4_all()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    nf4_all()
+    b.record()
+    b.synchronize()
+    record("nf4_dequant_28_layers", a.elapsed_time(b), 2.51587 * elems * 28, launches=28 * 7)
+    big = [(l[4][0], l[4][1]) for l in layers]  # the 8960 x 1536 gate projections, one per layer
+    ms = time_rotating(lambda i: dequantize_nf4(big[i][0], big[i][1], f16, out=outs[4]), len(big))
+    record("nf4_dequant_8960x1536", ms, 2.51587 * 8960 * 1536)
+    del layers, big
+
+    H, I = 1536, 8960
+    # RMSNorm, variant A (fp16 x, fp16 w) and variant B (fp32 x, fp32 w, fp16 copy + side buffer)
+    nA = sets_for(3 * n_rows * H * 2)
+    xa = [torch.randn(n_rows, H, device=dev, dtype=f16) for _ in range(nA)]
+    dya = [torch.randn(n_rows, H, device=dev, dtype=f16) for _ in range(nA)]
+    oa = [torch.empty(n_rows, H, device=dev, dtype=f16) for _ in range(nA)]
+    wa = (torch.rand(H, device=dev) + 0.5).half()
+    rstd = torch.empty(n_rows, device=dev)
+    code_f16 = _lib.F16
+
+    def rms_fwd_a(i):
+        _lib.call("soup_rmsnorm_fwd", xa[i].data_ptr(), wa.data_ptr(), oa[i].data_ptr(), rstd.data_ptr(),
+                  None, None, None, 1, n_rows, H, 1e-6, code_f16, code_f16, code_f16,
+                  torch.cuda.current_stream().cuda_stream)
+
+    def rms_bwd_a(i):
+        _lib.call("soup_rmsnorm_bwd", dya[i].data_ptr(), xa[i].data_ptr(), wa.data_ptr(), rstd.data_ptr(),
+                  oa[i].data_ptr(), None, None, None, None, 1, n_rows, H, code_f16, code_f16,
+                  code_f16, code_f16, 0, torch.cuda.current_stream().cuda_stream)
+
+    record("rmsnorm_fwd_f16", time_rotating(rms_fwd_a, nA), 2 * n_rows * H * 2 + 4 * n_rows + 2 * H)
+    record("rmsnorm_bwd_f16", time_rotating(rms_bwd_a, nA), 3 * n_rows * H * 2 + 4 * n_rows)
+    del xa, dya, oa
+    nB = sets_for(10 * n_rows * H)
+    xb = [torch.randn(n_rows, H, device=dev) for _ in range(nB)]
+    ob = [torch.empty(n_rows, H, device=dev) for _ in range(nB)]
+    lb = [torch.empty(n_rows, H, device=dev, dtype=f16) for _ in range(nB)]
+    wb = torch.rand(H, device=dev) + 0.5
+    tiny = torch.randperm(H, device=dev)[:15]
+    wb[tiny] = 5e-4
+    slots = torch.full((H,), -1, dtype=torch.int32, device=dev)
+    slots[tiny] = torch.arange(15, dtype=torch.int32, device=dev)
+    small = torch.empty(n_rows, 15, device=dev, dtype=f16)
+
+    def rms_fwd_b(i):
+        _lib.call("soup_rmsnorm_fwd", xb[i].data_ptr(), wb.data_ptr(), ob[i].data_ptr(), rstd.data_ptr(),
+                  lb[i].data_ptr(), slots.data_ptr(), small.data_ptr(), 15, n_rows, H, 1e-6, _lib.F32,
+                  _lib.F32, _lib.F32, torch.cuda.current_stream().cuda_stream)
+
+    record("rmsnorm_fwd_f32_with_f16_copy", time_rotating(rms_fwd_b, nB), 10 * n_rows * H + 4 * n_rows)
+    del xb, ob, lb
+
+    # RoPE: packed row [1, n_rows], 12 q heads / 2 kv heads, head_dim 128
+    from claudemaxing_b200.rope import _rotate_pair
+
+    nR = sets_for(2 * 14 * n_rows * 128 * 2)
+    lens = [n_rows // 4, n_rows * 3 // 16, n_rows * 5 // 16, n_rows // 4]
+    pos = torch.cat([torch.arange(x) for x in lens] + [torch.arange(n_rows - sum(lens))])
+    inv = 1.0 / (1e6 ** (torch.arange(0, 128, 2, dtype=f32) / 128))
+    emb = torch.cat((pos.float()[:, None] * inv,) * 2, -1)[None]
+    cos, sin = emb.cos().to(dev, f16), emb.sin().to(dev, f16)
+    qs = [torch.randn(1, n_rows, 12 * 128, device=dev, dtype=f16).view(1, n_rows, 12, 128).transpose(1, 2)
+          for _ in range(nR)]
+    ks = [torch.randn(1, n_rows, 2 * 128, device=dev, dtype=f16).view(1, n_rows, 2, 128).transpose(1, 2)
+          for _ in range(nR)]
+    rope_bytes = 2 * 14 * n_rows * 128 * 2 + 2 * n_rows * 128 * 2
+    record("rope_fwd_q_and_k", time_rotating(lambda i: _rotate_pair(qs[i], ks[i], cos, sin, f16, f16, False), nR),
+           rope_bytes)
+    record("rope_bwd_q_and_k", time_rotating(lambda i: _rotate_pair(qs[i], ks[i], cos, sin, f16, f16, True), nR),
+           rope_bytes)
+    del qs, ks
+
+    # SwiGLU forward and recompute-backward writing over its inputs
+    nS = sets_for(3 * n_rows * I * 2)
+    gs = [torch.randn(n_rows, I, device=dev, dtype=f16) for _ in range(nS)]
+    us = [torch.randn(n_rows, I, device=dev, dtype=f16) for _ in range(nS)]
+    ys = [torch.randn(n_rows, I, device=dev, dtype=f16) for _ in range(nS)]
+    record("silu_mul_fwd", time_rotating(lambda i: _silu_mul_fwd(gs[i], us[i], ys[i], True), nS),
+           3 * n_rows * I * 2)
+    record("silu_mul_bwd_inplace", time_rotating(lambda i: _silu_mul_bwd(ys[i], gs[i], us[i], gs[i], us[i], True), nS),
+           5 * n_rows * I * 2)
+    del gs, us, ys
+
+    # LoRA dropout pack / unpack
+    nD = sets_for(12 * n_rows * H)
+    xs = [torch.randn(n_rows, H, device=dev) for _ in range(nD)]
+    ms_ = [torch.rand(n_rows, H, device=dev) > 0.05 for _ in range(nD)]
+    packed_out = [lora._pack(xs[i], ms_[i], 1 / 0.95) for i in range(nD)]
+    x16 = [x.half() for x in xs]
+    record("dropout_pack", time_rotating(lambda i: lora._pack(xs[i], ms_[i], 1 / 0.95), nD),
+           n_rows * H * (4 + 1 + 2) + n_rows * H // 8)
+    record("dropout_unpack", time_rotating(
+        lambda i: lora._unpack(x16[i], packed_out[i][1], packed_out[i][0], 1 / 0.95, f32), nD),
+        n_rows * H * (2 + 2 + 2 + 4) + n_rows * H // 8)
+    return out
+
+
+# ------------------------------------------------------------------------------------------
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c1", choices=["c1", "c5a"])
+    ap.add_argument("--no-suite", action="store_true", help="skip the memory-bound kernel suite")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+
+    import torch.distributed as dist
+
+    from claudemaxing_b200 import _lib, parallel
+    from claudemaxing_b200.lm_head_loss import GRAD_SCALE, fused_head_loss
+
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    peak, peak_source = peaks()
+
+    n_tokens = 65536 if args.workload == "c5a" else TOKENS_PER_GPU * world
+    hidden_h, weight_h, target_h = make_inputs(n_tokens)
+    bounds = parallel.shard_bounds(VOCAB, world)
+    w_dev = weight_h[bounds[rank]:bounds[rank + 1]].to(dev)
+    hidden_pin, target_pin = hidden_h.pin_memory(), target_h.pin_memory()
+    hidden_dev, target_dev = hidden_pin.to(dev), target_pin.to(dev)
+    dh_pin = torch.empty(n_tokens, HIDDEN, dtype=torch.float16).pin_memory()
+    n_labelled = int((target_h != -100).sum())
+
+    def step(h_dev, t_dev):
+        """fwd+bwd through the public API; returns (loss, dHidden fp16)."""
+        if world == 1:
+            h = h_dev.detach().requires_grad_(True)
+            loss, _ = fused_head_loss(h[None], w_dev, None, target=t_dev[None])
+            loss.backward()
+            return loss.detach(), h.grad
+        res = parallel.vocab_parallel_head(h_dev, w_dev, t_dev, bounds)
+        loss = res["token_loss"].sum() / n_labelled
+        grad = (res["grad_raw"] * (1.0 / (GRAD_SCALE * n_labelled))).half()
+        return loss, grad
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(steps):
+            fn()
+        b.record()
+        barrier()
+        ms = torch.tensor([a.elapsed_time(b)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return ms.item()
+
+    # ---- device-resident region (value)
+    for _ in range(args.warmup):
+        loss, _ = step(hidden_dev, target_dev)
+    with ClockSampler(local_rank) as clocks:
+        total_ms = timed(lambda: step(hidden_dev, target_dev), args.steps)
+    ms_per_step = total_ms / args.steps
+    value = n_tokens / (ms_per_step * 1e-3)
+
+    # ---- end-to-end region: host buffers in, loss and dHidden out, every step
+    def e2e_step():
+        h = hidden_pin.to(dev, non_blocking=True)
+        t = target_pin.to(dev, non_blocking=True)
+        loss, grad = step(h, t)
+        dh_pin.copy_(grad.reshape(n_tokens, HIDDEN), non_blocking=True)
+        return loss.item()
+
+    for _ in range(3):
+        e2e_step()
+    e2e_ms = timed(e2e_step, args.steps) / args.steps
+    h2d = hidden_pin.numel() * 2 + target_pin.numel() * 8
+    d2h = dh_pin.numel() * 2 + 4
+
+    # ---- per-kernel region: event-bracketed launches inside the library
+    sink = (ctypes.c_float * 6)()
+    _lib.lib().soup_lmhead_set_timing(ctypes.cast(sink, ctypes.c_void_p))
+    barrier()
+    for _ in range(args.steps):
+        step(hidden_dev, target_dev)
+    barrier()
+    _lib.lib().soup_lmhead_set_timing(None)
+    k_ms = [sink[i] / args.steps for i in range(3)]
+    k_launch = [int(round(sink[3 + i] / args.steps)) for i in range(3)]
+    v_local = bounds[rank + 1] - bounds[rank]
+    flops_gemm = 2.0 * n_tokens * HIDDEN * v_local  # per GEMM kind, this rank, per step
+    tf = lambda ms: flops_gemm / (ms * 1e-3) / 1e12 if ms > 0 else 0.0  # noqa: E731
+    tensor_peak = peak["bf16_tflops"]
+    logits_tf, grad_tf = tf(k_ms[0]), tf(k_ms[2])
+    roofline = {
+        "kernel": "lmhead_logits_kernel (tcgen05 GEMM + softmax-statistics epilogue)",
+        "bound": "tensor", "achieved": round(logits_tf, 1), "peak": tensor_peak, "unit": "TFLOP/s",
+        "frac": round(logits_tf / tensor_peak, 4), "peak_source": peak_source + " cuBLAS bf16 burst",
+        "frac_of_sustained": round(logits_tf / peak["bf16_tflops_sustained"], 4),
+        "frac_of_nominal_2250": round(logits_tf / 2250.0, 4),
+        "ms_per_launch": round(k_ms[0] / max(k_launch[0], 1), 5), "launches_per_step": k_launch[0],
+        "traffic": None,
+        "grad_kernel": {"achieved": round(grad_tf, 1), "frac": round(grad_tf / tensor_peak, 4),
+                        "ms_per_launch": round(k_ms[2] / max(k_launch[2], 1), 5),
+                        "launches_per_step": k_launch[2]},
+        "row_kernel_ms_per_step": round(k_ms[1], 5),
+        "fused_op": {"achieved": round(2 * flops_gemm / (ms_per_step * 1e-3) / 1e12, 1),
+                     "frac": round(2 * flops_gemm / (ms_per_step * 1e-3) / 1e12 / tensor_peak, 4),
+                     "note": "4*N*H*V_local / whole step time (all kernels, launch gaps included)"},
+    }
+
+    rb, ct = ctypes.c_int64(), ctypes.c_int64()
+    _lib.lib().soup_lmhead_plan(n_tokens, v_local, 0, ctypes.byref(rb), ctypes.byref(ct))
+    row_blocks = -(-n_tokens // rb.value)
+    chunks = -(-(-(-v_local // 256)) // ct.value)
+    launches = 1 + row_blocks * chunks * 3 + 1 + (1 if world == 1 else 1)
+
+    kernels, cpu = None, None
+    if rank == 0 and world == 1:
+        if not args.no_suite:
+            del hidden_dev
+            kernels = kernel_suite(dev, peak["hbm_gbs"])
+        if not args.no_cpu:
+            cores = os.cpu_count() or 1
+            w32 = weight_h.float()
+            probe = cpu_head_tokens_per_s(hidden_h, w32, target_h, 32, cores)
+            rows = int(max(32, min(TOKENS_PER_GPU, probe * 12.0)) // 32 * 32)
+            cpu_v = cpu_head_tokens_per_s(hidden_h, w32, target_h, rows, cores)
+            cpu = {"value": round(cpu_v, 2), "unit": "tokens/s", "cores": cores, "kind": "port",
+                   "sample": f"{rows} of the 2048 rows x full vocabulary, one pass, torch fp32 "
+                             "matmul + log_softmax + autograd (oracle/head_ce.py)"}
+
+    if rank == 0:
+        line = {
+            "metric": "fused LM-head+CE fwd+bwd tokens/s", "value": round(value, 1),
+            "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": round(ms_per_step, 5), "higher_is_better": True,
+            "scaling": "strong" if args.workload == "c5a" else "weak", "vs_baseline": None,
+            "dtype": "f16", "data": "synthetic",
+            "config": {
+                "workload": ("configs[4a]: 65536 tokens" if args.workload == "c5a" else
+                             "configs[0]: fused LM-head+CE fwd+bwd, 2048 packed tokens per GPU") +
+                            f", hidden {HIDDEN}, tied fp16 head {VOCAB} x {HIDDEN}, 10% ignored",
+                "tokens": n_tokens,
+                "parallelism": "single GPU" if world == 1 else
+                               f"vocabulary-parallel x{world}: all-gather of per-row states + all-reduce of dHidden",
+                "l2": "inputs larger than L2: the 467 MB head weight streams from HBM every step",
+                "tflops_per_step_algorithmic": round(4.0 * n_tokens * HIDDEN * VOCAB / 1e12, 4),
+            },
+            "tflops": round(4.0 * n_tokens * HIDDEN * VOCAB / (ms_per_step * 1e-3) / 1e12, 1),
+            "e2e": {"value": round(n_tokens / (e2e_ms * 1e-3), 1), "unit": "tokens/s",
+                    "ms_per_step": round(e2e_ms, 5), "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h},
+            "gpu_launches": launches * args.steps,
+            "gpu_launches_per_step": launches,
+            "clocks": clocks.summary(),
+            "roofline": roofline,
+            "loss": round(float(loss), 6),
+        }
+        if kernels is not None:
+            line["kernels"] = kernels
+        if cpu is not None:
+            line["cpu_baseline"] = cpu
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -26,6 +26,8 @@
 // soup_lmhead_finish applies exp(lse_rank - lse_global) before the caller sums dH across ranks.
 #include <math.h>
 
+#include <vector>
+
 #include "common.cuh"
 #include "umma.cuh"
 
@@ -686,6 +688,33 @@ inline Workspace carve_workspace(void* base, const Plan& p) {
 
 bool g_attr_set[64] = {false};
 
+// Optional per-kernel-class timing for benchmarks: when a sink is set, soup_lmhead_ce brackets each
+// launch with events, synchronises the stream at the end and adds the elapsed milliseconds of the
+// logits / row / grad kernels to sink[0..2] and their launch counts to sink[3..5].
+float* g_timing_sink = nullptr;
+
+struct LaunchTimer {
+  cudaStream_t s;
+  bool on;
+  std::vector<cudaEvent_t> ev[3];
+  explicit LaunchTimer(cudaStream_t stream) : s(stream), on(g_timing_sink != nullptr) {}
+  void begin(int k) { if (on) { cudaEvent_t e; cudaEventCreate(&e); cudaEventRecord(e, s); ev[k].push_back(e); } }
+  void end(int k) { begin(k); }
+  void finish() {
+    if (!on) return;
+    cudaStreamSynchronize(s);
+    for (int k = 0; k < 3; ++k) {
+      for (size_t i = 0; i + 1 < ev[k].size(); i += 2) {
+        float ms = 0.f;
+        cudaEventElapsedTime(&ms, ev[k][i], ev[k][i + 1]);
+        g_timing_sink[k] += ms;
+        g_timing_sink[3 + k] += 1.f;
+      }
+      for (cudaEvent_t e : ev[k]) cudaEventDestroy(e);
+    }
+  }
+};
+
 int ensure_smem_attr() {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -1;
@@ -793,6 +822,7 @@ extern "C" int soup_lmhead_ce(const void* hidden, const void* weight, const int6
       run_max, run_sum, run_dot, best, label_logit, label_lse, (int)n);
   SOUP_CHECK_LAUNCH("lmhead_init_state");
 
+  LaunchTimer timer(s);
   for (int64_t r0 = 0; r0 < n; r0 += plan.row_block) {
     const int rows = (int)((n - r0) < plan.row_block ? (n - r0) : plan.row_block);
     const int rt = (rows + kBM - 1) / kBM;
@@ -815,8 +845,10 @@ extern "C" int soup_lmhead_ce(const void* hidden, const void* weight, const int6
       la.write_e = want_grad;
       la.status = ws.status;
       const int tiles1 = rt * ct;
+      timer.begin(0);
       lmhead_logits_kernel<<<(unsigned)(tiles1 < sms ? tiles1 : sms), kThreadsGemm, kSmem1, s>>>(
           map_h, map_w1, la);
+      timer.end(0);
       SOUP_CHECK_LAUNCH("lmhead_logits");
 
       RowArgs ra;
@@ -838,7 +870,9 @@ extern "C" int soup_lmhead_ce(const void* hidden, const void* weight, const int6
       ra.ct_stride = plan.ct;
       ra.ld_e = ld_e;
       ra.write_p = want_grad;
+      timer.begin(1);
       lmhead_row_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, s>>>(ra);
+      timer.end(1);
       SOUP_CHECK_LAUNCH("lmhead_row");
 
       if (want_grad) {
@@ -852,12 +886,29 @@ extern "C" int soup_lmhead_ce(const void* hidden, const void* weight, const int6
         ga.first = t0 == 0;
         ga.status = ws.status;
         const int tiles2 = rt * (int)((h + kBN2 - 1) / kBN2);
+        timer.begin(2);
         lmhead_grad_kernel<<<(unsigned)(tiles2 < sms ? tiles2 : sms), kThreadsGemm, kSmem2, s>>>(
             map_p, map_w2, ga);
+        timer.end(2);
         SOUP_CHECK_LAUNCH("lmhead_grad");
       }
     }
   }
+  timer.finish();
+  return SOUP_OK;
+}
+
+extern "C" int soup_lmhead_set_timing(float* host_sink6) {
+  soup::g_timing_sink = host_sink6;
+  return SOUP_OK;
+}
+
+extern "C" int soup_lmhead_plan(int64_t n, int64_t v_shard, int64_t chunk_tiles, int64_t* row_block,
+                                int64_t* tiles_per_chunk) {
+  using namespace soup;
+  const Plan p = make_plan(n, v_shard, sm_count(), (int)chunk_tiles);
+  if (row_block) *row_block = p.row_block;
+  if (tiles_per_chunk) *tiles_per_chunk = p.ct;
   return SOUP_OK;
 }
 

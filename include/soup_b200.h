@@ -136,6 +136,17 @@ int soup_lmhead_ce(const void* hidden, const void* weight, const int64_t* target
                    int64_t n, int64_t h, int64_t v_shard, int64_t col_offset,
                    int64_t chunk_tiles, int want_grad, void* stream);
 
+/* Benchmark aid: while a host array of 6 floats is set, every soup_lmhead_ce call brackets its
+ * launches with events, synchronises its stream before returning, and adds the milliseconds of the
+ * logits / row / grad kernels to sink[0..2] and their launch counts to sink[3..5]. NULL switches it
+ * off (the default). Not for use from concurrent threads. No counterpart in the reference (its
+ * harness times kernels from Python, harness/_train.py:44-83). */
+int soup_lmhead_set_timing(float* host_sink6);
+
+/* The tiling soup_lmhead_ce uses for a shape: rows per row block and 256-column tiles per chunk. */
+int soup_lmhead_plan(int64_t n, int64_t v_shard, int64_t chunk_tiles, int64_t* row_block,
+                     int64_t* tiles_per_chunk);
+
 /* Reads back the device status word of the last soup_lmhead_ce on this workspace (synchronises
  * `stream`): 0 = every bounded wait completed; otherwise the code of the wait that gave up. */
 int soup_lmhead_status(const void* workspace, int64_t n, int64_t v_shard, int64_t chunk_tiles,

@@ -70,7 +70,10 @@ def test_nf4_quantiser_matches_oracle_and_roundtrip_is_idempotent():
     w = (torch.randn(512, 1536, generator=torch.Generator().manual_seed(3)) * 0.02).half()
     p_dev, s_dev = qlora.quantize_nf4(w.to(DEV))
     p_cpu, s_cpu = onf4.quantize_nf4(w)
-    assert torch.equal(p_dev.cpu(), p_cpu) and torch.equal(s_dev.absmax.cpu(), s_cpu.absmax)
+    assert torch.equal(p_dev.cpu(), p_cpu)
+    # the nested codes depend on mean(absmax), whose summation order differs between CPU and GPU
+    assert abs(s_dev.offset.item() - s_cpu.offset.item()) < 1e-6
+    assert (s_dev.absmax.cpu() != s_cpu.absmax).float().mean().item() < 0.01
     deq = dequantize_nf4(p_dev, s_dev)
     # quantising the dequantised weight again reproduces the same codes (a fixed point)
     p_again, _ = qlora.quantize_nf4(deq, nested=False)
@@ -153,7 +156,7 @@ def test_rmsnorm_fp16_copy_path_and_tiny_weights():
     assert fp16_copy_of(out.detach().clone()) is None
     out.backward(dy.to(DEV))
     assert rel_norm(xd.grad.cpu(), x64.grad) < 1e-3
-    out.add_(1)  # a changed tensor no longer has a copy
+    out.detach().add_(1)  # a changed tensor (shared version counter) no longer has a copy
     assert fp16_copy_of(out) is None
 
 
