@@ -415,3 +415,63 @@ extern "C" int soup_rmsnorm_bwd(const void* dy, const void* xin, const void* w, 
   }
   return SOUP_OK;
 }
+
+
+// ------------------------------------------------------------------------------------------
+// Backward with the dw workspace inside the library, for callers that cannot allocate.
+// ------------------------------------------------------------------------------------------
+namespace soup {
+namespace {
+
+constexpr int kStaticPartialRows = 640;   // >= 4 CTAs per SM on a 148-SM part (592)
+constexpr int kStaticMaxCols = 4096;
+
+// 640 x 4096 fp32 = 10 MiB of device memory per GPU that loads the library, held until exit.
+static __device__ __align__(256) float g_dw_scratch[kStaticPartialRows * kStaticMaxCols];
+
+// In host code `g_dw_scratch` is only a handle for the runtime, not a device address; the address
+// a kernel can use comes from cudaGetSymbolAddress, asked once per device with that device current.
+float* g_dw_scratch_addr[64] = {nullptr};
+
+int static_scratch(float** out) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -1;
+  if (!g_dw_scratch_addr[dev]) {
+    void* p = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&p, g_dw_scratch);
+    if (e != cudaSuccess || !p) {
+      set_error("rmsnorm_bwd_noalloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+      return -2;
+    }
+    g_dw_scratch_addr[dev] = reinterpret_cast<float*>(p);
+  }
+  *out = g_dw_scratch_addr[dev];
+  return 0;
+}
+
+}  // namespace
+}  // namespace soup
+
+extern "C" int soup_rmsnorm_bwd_noalloc(const void* dy, const void* xin, const void* w,
+                                        const float* rstd, void* dx, void* dw, const int32_t* slot,
+                                        const void* small, int64_t n_small, int64_t n_rows,
+                                        int64_t n_cols, int dy_dtype, int xin_dtype, int w_dtype,
+                                        int dx_dtype, int saved_output, void* stream) {
+  using namespace soup;
+  if (n_cols > kStaticMaxCols)
+    SOUP_FAIL(SOUP_ERR_ARG, "rmsnorm_bwd_noalloc: n_cols %lld exceeds the built-in workspace (max %d); "
+              "use soup_rmsnorm_bwd with a caller-provided workspace", (long long)n_cols, kStaticMaxCols);
+  if (soup_rmsnorm_bwd_partials(n_rows, n_cols) > kStaticPartialRows)
+    SOUP_FAIL(SOUP_ERR_ARG, "rmsnorm_bwd_noalloc: this device needs %lld partial rows, the built-in "
+              "workspace has %d", (long long)soup_rmsnorm_bwd_partials(n_rows, n_cols), kStaticPartialRows);
+  float* scratch = nullptr;
+  if (dw) {
+    const int rc = static_scratch(&scratch);
+    if (rc == -1) SOUP_FAIL(SOUP_ERR_DEVICE, "rmsnorm_bwd_noalloc: no current CUDA device");
+    if (rc != 0) return SOUP_ERR_DEVICE;
+  }
+  // Every partial row the reduce reads is fully rewritten by its CTA first, so nothing in the
+  // workspace has to start at zero even though it keeps the previous call's contents.
+  return soup_rmsnorm_bwd(dy, xin, w, rstd, dx, scratch, dw, slot, small, n_small, n_rows, n_cols,
+                          dy_dtype, xin_dtype, w_dtype, dx_dtype, saved_output, stream);
+}

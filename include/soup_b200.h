@@ -12,7 +12,8 @@
  *    (thread local). Nothing aborts or traps.
  *  - dtype codes: SOUP_F32, SOUP_F16, SOUP_BF16.
  *  - All entries are re-entrant: no global scratch, so autograd worker threads may call them
- *    concurrently on different streams.
+ *    concurrently on different streams. The one exception is soup_rmsnorm_bwd_noalloc, which
+ *    says so in its own comment.
  */
 #ifndef SOUP_B200_H
 #define SOUP_B200_H
@@ -77,6 +78,26 @@ int soup_rmsnorm_bwd(const void* dy, const void* xin, const void* w, const float
                      float* dw_partial, void* dw, const int32_t* slot, const void* small,
                      int64_t n_small, int64_t n_rows, int64_t n_cols, int dy_dtype, int xin_dtype,
                      int w_dtype, int dx_dtype, int saved_output, void* stream);
+
+/* soup_rmsnorm_bwd for callers that cannot allocate device memory. It has no counterpart in the
+ * reference. Same arguments and results as soup_rmsnorm_bwd, minus dw_partial: the fp32 partial
+ * rows of dw live in a 10 MiB array built into the library (640 rows x 4096 columns, resident on
+ * every GPU that loads the library until the process exits). Meant for hosts that bind this
+ * library without a framework allocator behind them (a plain C or C++ trainer that sized all of its
+ * device memory up front), or that cannot afford cudaMalloc's device-wide synchronisation in
+ * the middle of a step. The call allocates and frees nothing.
+ *  - Limits: n_cols <= 4096 and at most 640 partial rows (4 CTAs per SM, 148 SMs need 592);
+ *    anything larger is refused with SOUP_ERR_ARG and the caller should use soup_rmsnorm_bwd.
+ *  - The first call on each device looks the array's device address up (cudaGetSymbolAddress, with
+ *    that device current); make that first call outside any stream capture.
+ *  - All calls on a device share the one array, which keeps the previous call's contents (each call
+ *    rewrites every row it later reads, so nothing needs clearing). Two calls with dw != NULL that
+ *    overlap on the GPU (different streams, no ordering between them) race on it: serialise them. */
+int soup_rmsnorm_bwd_noalloc(const void* dy, const void* xin, const void* w, const float* rstd,
+                             void* dx, void* dw, const int32_t* slot, const void* small,
+                             int64_t n_small, int64_t n_rows, int64_t n_cols, int dy_dtype,
+                             int xin_dtype, int w_dtype, int dx_dtype, int saved_output,
+                             void* stream);
 
 /* Rotary embedding of q and k in one launch (forward, or the transposed rotation for backward).
  * Replaces the two qwen_rope_kernel launches of RoPE.forward / RoPE.backward at
