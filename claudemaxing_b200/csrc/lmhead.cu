@@ -25,6 +25,7 @@
 // and gets state and dH relative to its own lse; soup_lmhead_merge combines the ranks' states and
 // soup_lmhead_finish applies exp(lse_rank - lse_global) before the caller sums dH across ranks.
 #include <math.h>
+#include <stdlib.h>
 
 #include <vector>
 
@@ -52,7 +53,8 @@ constexpr float kEScale = 16384.0f;         // 2^14, E = kEScale * exp(z - tile_
 constexpr float kGradScale = 1024.0f;       // as GRAD_SCALE of the reference
 constexpr int kIgnore = -100;
 
-constexpr int kSmem1 = kStages1 * (kABytes + kB1Bytes) + 1024 + 256;
+constexpr int kStageE = 4 * 2 * 4096;        // per epilogue warp two 32-row x 64-column fp16 boxes
+constexpr int kSmem1 = kStages1 * (kABytes + kB1Bytes) + kStageE + 1024 + 256;
 constexpr int kSmem2 = kStages2 * (kABytes + kB2Bytes) + 1024 + 256;
 
 struct PipeState {
@@ -66,6 +68,7 @@ struct PipeState {
 
 struct GemmSmem {
   uint8_t* tiles;        // 1024-byte aligned
+  uint8_t* extra;        // kernel-specific staging area behind the stages
   uint64_t* full;        // [STAGES]
   uint64_t* empty;       // [STAGES]
   uint64_t* acc_full;    // [2]
@@ -74,12 +77,13 @@ struct GemmSmem {
   int* abort_flag;
 };
 
-template <int STAGES, int STAGE_BYTES>
+template <int STAGES, int STAGE_BYTES, int EXTRA_BYTES = 0>
 __device__ __forceinline__ GemmSmem carve_smem(uint8_t* raw) {
   GemmSmem s;
   const uintptr_t base = (reinterpret_cast<uintptr_t>(raw) + 1023u) & ~static_cast<uintptr_t>(1023u);
   s.tiles = reinterpret_cast<uint8_t*>(base);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(s.tiles + STAGES * STAGE_BYTES);
+  s.extra = s.tiles + STAGES * STAGE_BYTES;  // 1024-byte aligned (stage sizes are multiples of 1024)
+  uint64_t* bars = reinterpret_cast<uint64_t*>(s.tiles + STAGES * STAGE_BYTES + EXTRA_BYTES);
   s.full = bars;
   s.empty = bars + STAGES;
   s.acc_full = bars + 2 * STAGES;
@@ -121,6 +125,139 @@ __device__ __forceinline__ void finish_pipeline(const GemmSmem& s, int warp, uin
   }
 }
 
+// Statistics epilogue of one 128 x 256 logits tile for one thread (= one row). Two sweeps over the
+// accumulator in TMEM, 32 columns at a time, with the load of the next 32 columns issued before the
+// current ones are consumed: sweep 1 finds the row maximum of the tile and its first index, sweep 2
+// forms E = 2^14 * exp(z - max) (the scale folded into the exponent), its sum, the sum of E*z, and
+// writes E as fp16. FULL tiles (all 256 columns inside the vocabulary) skip every validity select.
+constexpr int kEW = 16;  // accumulator columns per tcgen05.ld in the statistics epilogue
+
+template <bool FULL>
+__device__ __forceinline__ void sweep_max(const uint32_t (&r)[kEW], int col0, int n_valid, float& m,
+                                          int& arg) {
+#pragma unroll
+  for (int j = 0; j < kEW; ++j) {
+    const float z = __uint_as_float(r[j]);
+    const int col = col0 + j;
+    if ((FULL || col < n_valid) && z > m) { m = z; arg = col; }
+  }
+}
+
+// `stage_row` points at this thread's 128-byte row of a 32-row x 64-column staging box laid out with
+// the 128-byte swizzle (16-byte piece k of row r lives at piece k ^ (r & 7)); `piece0` is the first
+// of the two 16-byte pieces these 16 columns fill.
+template <bool FULL>
+__device__ __forceinline__ void sweep_exp(const uint32_t (&r)[kEW], int col0, int n_valid,
+                                          bool store_e, uint8_t* stage_row, int row_swz, int piece0,
+                                          float bias, float (&acc)[4]) {
+  uint32_t packed[kEW / 2];
+#pragma unroll
+  for (int j = 0; j < kEW; j += 2) {
+    const float z0 = __uint_as_float(r[j]), z1 = __uint_as_float(r[j + 1]);
+    const int col = col0 + j;
+    float e0 = exp2f(fmaf(z0, kLog2e, bias));
+    float e1 = exp2f(fmaf(z1, kLog2e, bias));
+    if (!FULL) {
+      if (col >= n_valid) e0 = 0.f;
+      if (col + 1 >= n_valid) e1 = 0.f;
+    }
+    acc[0] += e0;
+    acc[1] += e1;
+    acc[2] = fmaf(e0, (FULL || col < n_valid) ? z0 : 0.f, acc[2]);
+    acc[3] = fmaf(e1, (FULL || col + 1 < n_valid) ? z1 : 0.f, acc[3]);
+    __half2 h = __floats2half2_rn(e0, e1);
+    packed[j >> 1] = *reinterpret_cast<uint32_t*>(&h);
+  }
+  if (store_e) {
+#pragma unroll
+    for (int v = 0; v < kEW / 8; ++v) {
+      const int piece = (piece0 + v) ^ row_swz;
+      *reinterpret_cast<uint4*>(stage_row + piece * 16) =
+          make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+    }
+  }
+}
+
+// Statistics epilogue of one 128 x 256 logits tile for one thread (= one row). Two sweeps over the
+// accumulator in TMEM, 16 columns per tcgen05.ld, the next load in flight while the current columns
+// are consumed; the loop bodies are kept small enough to stay in the instruction cache. Sweep 1:
+// row maximum of the tile and its first index. Sweep 2: E = 2^14 * exp(z - max) (scale folded into
+// the exponent), its sum and the sum of E*z; E leaves as fp16 through a swizzled staging box and a
+// TMA store per 64 columns. FULL tiles (all 256 columns inside the vocabulary) skip the validity
+// selects. The label's logit, needed by very few rows of a tile, is fetched in a third, rare sweep.
+template <bool FULL>
+__device__ __noinline__ void tile_statistics(uint32_t taddr, int n_valid, int label_local,
+                                             bool store_e, const CUtensorMap* map_e,
+                                             uint8_t* stage_warp, int e_col0, int e_row0,
+                                             float& m_out, float& sum_out, float& dot_out,
+                                             float& lab_out, int& arg_out, int debug) {
+  constexpr int kLoads = kBN1 / kEW;      // 16
+  constexpr int kPerBox = 64 / kEW;       // loads per 64-column staging box
+  const int lane = threadIdx.x & 31;
+  uint32_t ra[kEW], rb[kEW];
+  float m = -INFINITY;
+  int arg = 0;
+  if (debug & 2) m = 0.f;
+  if (!(debug & 2)) tmem_ld_32x16(taddr, ra);
+#pragma unroll 1
+  for (int i = 0; i < ((debug & 2) ? 0 : kLoads); i += 2) {
+    tmem_ld_wait_on(ra);
+    tmem_ld_32x16(taddr + (i + 1) * kEW, rb);
+    sweep_max<FULL>(ra, i * kEW, n_valid, m, arg);
+    tmem_ld_wait_on(rb);
+    if (i + 2 < kLoads) tmem_ld_32x16(taddr + (i + 2) * kEW, ra);
+    sweep_max<FULL>(rb, (i + 1) * kEW, n_valid, m, arg);
+  }
+  // exp2(z*log2e - m*log2e + 14) = 2^14 * exp(z - m)
+  const float bias = 14.0f - m * kLog2e;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  uint8_t* stage_row = stage_warp + lane * 128;
+  if (!(debug & 4)) tmem_ld_32x16(taddr, ra);
+#pragma unroll 1
+  for (int i = 0; i < ((debug & 4) ? 0 : kLoads); i += 2) {
+    // 64-column boxes alternate between the warp's two staging areas; the area used two boxes ago
+    // must have been read by its TMA store before it is overwritten.
+    const int box_id = i / kPerBox;
+    uint8_t* box = stage_warp + (box_id & 1) * 4096;
+    if (store_e && (i % kPerBox) == 0) {
+      if (lane == 0) tma_store_wait_read<1>();
+      __syncwarp();
+    }
+    tmem_ld_wait_on(ra);
+    tmem_ld_32x16(taddr + (i + 1) * kEW, rb);
+    sweep_exp<FULL>(ra, i * kEW, n_valid, store_e, stage_row + (box_id & 1) * 4096, lane & 7,
+                    (i % kPerBox) * (kEW / 8), bias, acc);
+    tmem_ld_wait_on(rb);
+    if (i + 2 < kLoads) tmem_ld_32x16(taddr + (i + 2) * kEW, ra);
+    sweep_exp<FULL>(rb, (i + 1) * kEW, n_valid, store_e, stage_row + (box_id & 1) * 4096, lane & 7,
+                    ((i + 1) % kPerBox) * (kEW / 8), bias, acc);
+    if (store_e && ((i + 2) % kPerBox) == 0) {
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        tma_store_2d(map_e, box, e_col0 + box_id * 64, e_row0);
+        tma_store_commit();
+      }
+    }
+  }
+  float lab = 0.f;
+  if (__any_sync(0xffffffffu, label_local >= 0)) {  // rare: some row's label falls in this tile
+#pragma unroll 1
+    for (int i = 0; i < kLoads; ++i) {
+      tmem_ld_32x16(taddr + i * kEW, ra);
+      tmem_ld_wait_on(ra);
+#pragma unroll
+      for (int j = 0; j < kEW; ++j)
+        if (i * kEW + j == label_local) lab = __uint_as_float(ra[j]);
+    }
+  }
+  m_out = m;
+  sum_out = (acc[0] + acc[1]) * (1.0f / kEScale);
+  dot_out = (acc[2] + acc[3]) * (1.0f / kEScale);
+  lab_out = lab;
+  arg_out = arg;
+}
+
 // ------------------------------------------------------------------------------------------
 // Logits kernel: tile statistics + E for one chunk of column tiles of one row block.
 // ------------------------------------------------------------------------------------------
@@ -139,18 +276,24 @@ struct LogitsArgs {
   int ct_stride;           // row pitch of tile_stats
   int ld_e;                // row pitch of e_buf in elements
   int write_e;
+  int debug;               // bit 0: skip the statistics sweeps (timing experiments only)
   int* status;
 };
 
 __global__ void __launch_bounds__(kThreadsGemm, 1)
 lmhead_logits_kernel(const __grid_constant__ CUtensorMap map_h,
-                     const __grid_constant__ CUtensorMap map_w, const LogitsArgs a) {
+                     const __grid_constant__ CUtensorMap map_w,
+                     const __grid_constant__ CUtensorMap map_e, const LogitsArgs a) {
   extern __shared__ uint8_t smem_raw[];
   if (*reinterpret_cast<volatile int*>(a.status) != 0) return;  // an earlier kernel gave up
   constexpr int kStageBytes = kABytes + kB1Bytes;
-  const GemmSmem s = carve_smem<kStages1, kStageBytes>(smem_raw);
+  const GemmSmem s = carve_smem<kStages1, kStageBytes, kStageE>(smem_raw);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  if (warp == 0 && lane == 0) { prefetch_tensormap(&map_h); prefetch_tensormap(&map_w); }
+  if (warp == 0 && lane == 0) {
+    prefetch_tensormap(&map_h);
+    prefetch_tensormap(&map_w);
+    prefetch_tensormap(&map_e);
+  }
   init_pipeline<kStages1>(s, warp, lane);
   const uint32_t tmem = *s.tmem_base;
 
@@ -227,52 +370,19 @@ lmhead_logits_kernel(const __grid_constant__ CUtensorMap map_h,
         const long long loc = tg - a.col_offset - tile_col0;
         if (tg != kIgnore && loc >= 0 && loc < n_valid) label_local = (int)loc;
       }
-      // pass 1: tile maximum and its first index
-      float m = -INFINITY;
-      int arg = 0;
-#pragma unroll 1
-      for (int c = 0; c < kBN1 / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(taddr + c * 32, r);
-        tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const float z = __uint_as_float(r[j]);
-          const int col = c * 32 + j;
-          if (col < n_valid && z > m) { m = z; arg = col; }
-        }
-      }
-      // pass 2: exp against the tile maximum, sums, E
-      float sum = 0.f, dot = 0.f, lab = 0.f;
-      const float m2 = m * kLog2e;
-      __half* e_row = a.e_buf + (size_t)row * a.ld_e + tc * kBN1;
-#pragma unroll 1
-      for (int c = 0; c < kBN1 / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(taddr + c * 32, r);
-        tmem_ld_wait();
-        uint32_t packed[16];
-#pragma unroll
-        for (int j = 0; j < 32; j += 2) {
-          const float z0 = __uint_as_float(r[j]), z1 = __uint_as_float(r[j + 1]);
-          const int col = c * 32 + j;
-          float e0 = col < n_valid ? exp2f(fmaf(z0, kLog2e, -m2)) : 0.f;
-          float e1 = col + 1 < n_valid ? exp2f(fmaf(z1, kLog2e, -m2)) : 0.f;
-          sum += e0 + e1;
-          dot = fmaf(e0, col < n_valid ? z0 : 0.f, dot);
-          dot = fmaf(e1, col + 1 < n_valid ? z1 : 0.f, dot);
-          if (col == label_local) lab = z0;
-          if (col + 1 == label_local) lab = z1;
-          __half2 h = __floats2half2_rn(e0 * kEScale, e1 * kEScale);
-          packed[j >> 1] = *reinterpret_cast<uint32_t*>(&h);
-        }
-        if (row_ok && a.write_e) {
-          uint4* dst = reinterpret_cast<uint4*>(e_row + c * 32);
-#pragma unroll
-          for (int v = 0; v < 4; ++v)
-            dst[v] = make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
-        }
-      }
+      float m, sum, dot, lab;
+      int arg;
+      // E leaves through a per-warp staging box and a TMA store (rows past the buffer are clipped).
+      uint8_t* stage_warp = s.extra + (warp - 2) * 8192;
+      const int e_row0 = tr * kBM + q * 32;
+      if (a.debug & 1) {
+        m = 0.f; sum = 1.f; dot = 0.f; lab = 0.f; arg = 0;
+      } else if (n_valid == kBN1)
+        tile_statistics<true>(taddr, n_valid, label_local, a.write_e != 0, &map_e, stage_warp,
+                              tc * kBN1, e_row0, m, sum, dot, lab, arg, a.debug);
+      else
+        tile_statistics<false>(taddr, n_valid, label_local, a.write_e != 0, &map_e, stage_warp,
+                               tc * kBN1, e_row0, m, sum, dot, lab, arg, a.debug);
       // the accumulator buffer is free again
       tc_fence_before_sync();
       __syncwarp();
@@ -283,6 +393,7 @@ lmhead_logits_kernel(const __grid_constant__ CUtensorMap map_h,
         if (label_local >= 0) a.label_logit[row] = lab;
       }
     }
+    if (lane == 0) tma_store_wait_read<0>();  // staging boxes fully read before shared memory goes away
   }
   finish_pipeline(s, warp, tmem);
 }
@@ -809,12 +920,14 @@ extern "C" int soup_lmhead_ce(const void* hidden, const void* weight, const int6
   const int ld_e = plan.ct * kBN1;
   const int total_ct = (int)((v_shard + kBN1 - 1) / kBN1);
 
-  CUtensorMap map_h, map_w1, map_w2, map_p;
+  CUtensorMap map_h, map_w1, map_w2, map_p, map_e;
   if (umma::encode_map_2d_f16(&map_h, hidden, (uint64_t)n, (uint64_t)h, (uint64_t)h, kBM, kBK) ||
       umma::encode_map_2d_f16(&map_w1, weight, (uint64_t)v_shard, (uint64_t)h, (uint64_t)h, kBN1, kBK) ||
       umma::encode_map_2d_f16(&map_w2, weight, (uint64_t)v_shard, (uint64_t)h, (uint64_t)h, kBK, 64) ||
       umma::encode_map_2d_f16(&map_p, ws.e_buf, (uint64_t)plan.row_block, (uint64_t)ld_e,
-                              (uint64_t)ld_e, kBM, kBK))
+                              (uint64_t)ld_e, kBM, kBK) ||
+      umma::encode_map_2d_f16(&map_e, ws.e_buf, (uint64_t)plan.row_block, (uint64_t)ld_e,
+                              (uint64_t)ld_e, 32, 64))
     SOUP_FAIL(SOUP_ERR_DEVICE, "lmhead_ce: cuTensorMapEncodeTiled failed");
 
   cudaMemsetAsync(ws.status, 0, 4, s);
@@ -843,11 +956,15 @@ extern "C" int soup_lmhead_ce(const void* hidden, const void* weight, const int6
       la.ct_stride = plan.ct;
       la.ld_e = ld_e;
       la.write_e = want_grad;
+      {
+        const char* dbg = getenv("SOUP_LMHEAD_DEBUG");
+        la.debug = dbg ? atoi(dbg) : 0;
+      }
       la.status = ws.status;
       const int tiles1 = rt * ct;
       timer.begin(0);
       lmhead_logits_kernel<<<(unsigned)(tiles1 < sms ? tiles1 : sms), kThreadsGemm, kSmem1, s>>>(
-          map_h, map_w1, la);
+          map_h, map_w1, map_e, la);
       timer.end(0);
       SOUP_CHECK_LAUNCH("lmhead_logits");
 
