@@ -399,6 +399,191 @@ lmhead_logits_kernel(const __grid_constant__ CUtensorMap map_h,
 }
 
 // ------------------------------------------------------------------------------------------
+// CTA-pair variants (cta_group::2): the pair owns a 256-row tile, each CTA 128 rows of it, and the
+// B operand is split between the two CTAs, so every shared-memory stage holds half the B bytes of
+// the single-CTA kernel and the operand traffic through the crossbar per flop drops by a third.
+// ------------------------------------------------------------------------------------------
+constexpr int kBHalf1Bytes = (kBN1 / 2) * kBK * 2;   // 16 KB: this CTA's 128 vocabulary columns
+constexpr int kStagesP1 = 6;
+constexpr int kSmemP1 = kStagesP1 * (kABytes + kBHalf1Bytes) + kStageE + 1024 + 256;
+
+struct PairInit {
+  uint32_t tmem;
+  uint32_t rank;
+  bool run;
+};
+
+// Barrier set-up, tensor-memory allocation and the agreement of both CTAs on whether to run at all
+// (an earlier kernel of the call may have given up). Every thread of both CTAs calls this.
+template <int STAGES>
+__device__ __forceinline__ PairInit init_pair(const GemmSmem& s, int warp, int lane, const int* status) {
+  PairInit r;
+  r.rank = cluster_ctarank();
+  if (warp == 0 && lane == 0) {
+    for (int i = 0; i < STAGES; ++i) { mbar_init(&s.full[i], 1); mbar_init(&s.empty[i], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&s.acc_full[i], 1); mbar_init(&s.acc_empty[i], 8); }
+    *s.abort_flag = *reinterpret_cast<const volatile int*>(status) != 0;
+    fence_barrier_init();
+  }
+  __syncthreads();
+  cluster_sync_all();
+  // the leader's view decides for the pair
+  r.run = ld_shared_cluster_s32(mapa_u32(smem_u32(s.abort_flag), 0)) == 0;
+  cluster_sync_all();  // nobody leaves (or rewrites the flag) while the peer may still read it
+  if (!r.run) { r.tmem = 0; return r; }
+  if (warp == 0 && lane == 0) *s.abort_flag = 0;
+  if (warp == 1) {
+    tmem_alloc_pair(s.tmem_base, 512);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  r.tmem = *s.tmem_base;
+  return r;
+}
+
+__device__ __forceinline__ void finish_pair(const GemmSmem& s, int warp, uint32_t tmem) {
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*s.abort_flag) {
+    for (int i = 0; i < 64; ++i) __nanosleep(2000);
+    __syncthreads();
+  }
+  // The leader's MMAs read the peer's shared memory and both CTAs signal each other's barriers:
+  // neither may exit before the other is done.
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc_pair(tmem, 512);
+  }
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreadsGemm, 1)
+lmhead_logits_pair_kernel(const __grid_constant__ CUtensorMap map_h,
+                          const __grid_constant__ CUtensorMap map_w,
+                          const __grid_constant__ CUtensorMap map_e, const LogitsArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  constexpr int kStageBytes = kABytes + kBHalf1Bytes;
+  const GemmSmem s = carve_smem<kStagesP1, kStageBytes, kStageE>(smem_raw);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (warp == 0 && lane == 0) {
+    prefetch_tensormap(&map_h);
+    prefetch_tensormap(&map_w);
+    prefetch_tensormap(&map_e);
+  }
+  const PairInit pi = init_pair<kStagesP1>(s, warp, lane, a.status);
+  if (!pi.run) return;
+  const uint32_t tmem = pi.tmem, rank = pi.rank;
+  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+
+  const int rt = (a.n_rows + 2 * kBM - 1) / (2 * kBM);   // 256-row tiles
+  const int n_tiles = rt * a.ct;
+  const int n_kb = (a.k_dim + kBK - 1) / kBK;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      PipeState p;
+      bool ok = true;
+      for (int tile = pair; tile < n_tiles && ok; tile += n_pairs) {
+        const int tr = tile % rt, tc = tile / rt;
+        const int row0 = a.row0 + tr * 2 * kBM + (int)rank * kBM;
+        const int col0 = a.col0 + tc * kBN1 + (int)rank * (kBN1 / 2);
+        for (int kb = 0; kb < n_kb; ++kb) {
+          ok = mbar_wait(&s.empty[p.stage], p.phase ^ 1u, s.abort_flag, a.status, 31);
+          if (!ok) break;
+          uint8_t* st = s.tiles + p.stage * kStageBytes;
+          // both CTAs' bytes are counted on the leader's barrier
+          const uint32_t full_leader = mapa_u32(smem_u32(&s.full[p.stage]), 0);
+          if (rank == 0) mbar_expect_tx(&s.full[p.stage], 2 * kStageBytes);
+          tma_load_2d_pair(st, &map_h, kb * kBK, row0, full_leader);
+          tma_load_2d_pair(st + kABytes, &map_w, kb * kBK, col0, full_leader);
+          p.advance<kStagesP1>();
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = make_idesc_f16(2 * kBM, kBN1, false, false);
+      PipeState p;
+      bool ok = true;
+      int it = 0;
+      for (int tile = pair; tile < n_tiles && ok; tile += n_pairs, ++it) {
+        const int ab = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1u;
+        ok = mbar_wait(&s.acc_empty[ab], acc_phase ^ 1u, s.abort_flag, a.status, 32);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem + ab * kBN1;
+        for (int kb = 0; kb < n_kb; ++kb) {
+          ok = mbar_wait(&s.full[p.stage], p.phase, s.abort_flag, a.status, 33);
+          if (!ok) break;
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_u32(s.tiles + p.stage * kStageBytes);
+          const uint64_t da = make_smem_desc(a_addr, 16, 1024);
+          const uint64_t db = make_smem_desc(a_addr + kABytes, 16, 1024);
+#pragma unroll
+          for (int k4 = 0; k4 < kBK / 16; ++k4)
+            mma_f16_ss_pair(d_tmem, da + k4 * 2, db + k4 * 2, idesc, (kb | k4) != 0);
+          tc_commit_pair(&s.empty[p.stage], 3);   // frees the stage in both CTAs
+          p.advance<kStagesP1>();
+        }
+        if (ok) tc_commit_pair(&s.acc_full[ab], 3);
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    bool ok = true;
+    int it = 0;
+    for (int tile = pair; tile < n_tiles && ok; tile += n_pairs, ++it) {
+      const int tr = tile % rt, tc = tile / rt;
+      const int ab = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1u;
+      ok = __all_sync(0xffffffffu, mbar_wait(&s.acc_full[ab], acc_phase, s.abort_flag, a.status, 34));
+      if (!ok) break;
+      tc_fence_after_sync();
+      const int e_row0 = tr * 2 * kBM + (int)rank * kBM + q * 32;
+      const int row = e_row0 + lane;
+      const bool row_ok = row < a.n_rows;
+      const int tile_col0 = a.col0 + tc * kBN1;
+      const int n_valid = min(kBN1, a.v_shard - tile_col0);
+      const uint32_t taddr = tmem + (static_cast<uint32_t>(q * 32) << 16) + ab * kBN1;
+      int label_local = -1;
+      if (row_ok) {
+        const long long tg = a.target[row];
+        const long long loc = tg - a.col_offset - tile_col0;
+        if (tg != kIgnore && loc >= 0 && loc < n_valid) label_local = (int)loc;
+      }
+      float m, sum, dot, lab;
+      int arg;
+      uint8_t* stage_warp = s.extra + (warp - 2) * 8192;
+      if (a.debug & 1) {
+        m = 0.f; sum = 1.f; dot = 0.f; lab = 0.f; arg = 0;
+      } else if (n_valid == kBN1)
+        tile_statistics<true>(taddr, n_valid, label_local, a.write_e != 0, &map_e, stage_warp,
+                              tc * kBN1, e_row0, m, sum, dot, lab, arg, a.debug);
+      else
+        tile_statistics<false>(taddr, n_valid, label_local, a.write_e != 0, &map_e, stage_warp,
+                               tc * kBN1, e_row0, m, sum, dot, lab, arg, a.debug);
+      // the accumulator buffer of this CTA is free again: tell the leader's MMA thread
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) {
+        if (rank == 0) mbar_arrive(&s.acc_empty[ab]);
+        else mbar_arrive_cluster(mapa_u32(smem_u32(&s.acc_empty[ab]), 0));
+      }
+      if (row_ok) {
+        a.tile_stats[(size_t)row * a.ct_stride + tc] =
+            make_float4(m, sum, dot, __int_as_float(tile_col0 + arg + a.col_offset));
+        if (label_local >= 0) a.label_logit[row] = lab;
+      }
+    }
+    if (lane == 0) tma_store_wait_read<0>();
+  }
+  finish_pair(s, warp, tmem);
+}
+
+// ------------------------------------------------------------------------------------------
 // Row kernel: one warp per row. Merges the chunk's tile statistics into the running state and
 // rescales E to P in place.
 // ------------------------------------------------------------------------------------------
@@ -421,12 +606,19 @@ struct RowArgs {
   int ct_stride;
   int ld_e;
   int write_p;
+  float* dh;        // nullable: [n_rows, k_dim] gradient to rescale by this chunk's factor
+  int k_dim;
+  int first;        // first chunk: nothing accumulated yet
 };
 
-__global__ void __launch_bounds__(256) lmhead_row_kernel(const RowArgs a) {
-  const int lane = threadIdx.x & 31;
-  const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
-  if (row >= a.n_rows) return;
+constexpr int kRowWarps = 4;          // warps per row in the row kernel
+constexpr int kRowTilesPerWarp = 16;  // register-resident tiles per warp per pass
+
+__global__ void __launch_bounds__(kRowWarps * 32) lmhead_row_kernel(const RowArgs a) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int row = blockIdx.x;
+  // Every warp merges the (at most a few dozen) tile statistics itself: cheaper than a block-wide
+  // exchange, and all warps then hold the same running state and log-sum-exp.
   const float prev_max = a.run_max[row], prev_sum = a.run_sum[row];
   float run_max = prev_max, run_sum = prev_sum, run_dot = a.run_dot[row];
   int best = a.best[row];
@@ -435,12 +627,11 @@ __global__ void __launch_bounds__(256) lmhead_row_kernel(const RowArgs a) {
     const int t = t0 + lane;
     float4 st = make_float4(-INFINITY, 0.f, 0.f, 0.f);
     if (t < a.ct) st = a.tile_stats[(size_t)row * a.ct_stride + t];
-    // warp-wide maximum and the first lane that holds it
     float gmax = st.x;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) gmax = fmaxf(gmax, __shfl_xor_sync(0xffffffffu, gmax, o));
     const unsigned holders = __ballot_sync(0xffffffffu, st.x == gmax);
-    const int first = __ffs(holders) - 1;
+    const int first = __ffs(holders) - 1;  // first lane (lowest tile) that holds the maximum
     const int cand = __shfl_sync(0xffffffffu, __float_as_int(st.w), first);
     if (gmax > run_max) best = cand;
     const float new_max = fmaxf(run_max, gmax);
@@ -453,41 +644,76 @@ __global__ void __launch_bounds__(256) lmhead_row_kernel(const RowArgs a) {
     run_max = new_max;
   }
   const float lse = run_max + logf(run_sum);
+  const float fac = expf(prev_max + logf(prev_sum) - lse);  // exp(-inf) = 0 on the first chunk
   const long long tg = a.target[row];
   const bool labelled = tg != kIgnore;
   const long long local = tg - a.col_offset - a.col0;  // column inside this chunk
   const bool hit = labelled && local >= 0 && local < (long long)a.ct * kBN1 &&
                    a.col0 + local < a.v_shard;
-  if (lane == 0) {
+  // All state of the previous chunk has been read by every warp before anyone overwrites it.
+  __syncthreads();
+  if (threadIdx.x == 0) {
     a.run_max[row] = run_max;
     a.run_sum[row] = run_sum;
     a.run_dot[row] = run_dot;
     a.best[row] = best;
     if (a.write_p) {
-      a.factor[row] = expf(prev_max + logf(prev_sum) - lse);  // exp(-inf) = 0 on the first chunk
+      a.factor[row] = fac;
       if (hit) a.label_lse[row] = lse;
     }
   }
   if (!a.write_p) return;
-  // P = 1024 * exp(z - lse) = E * 2^-14 * 1024 * exp(tile_max - lse); zero for unlabelled rows.
-  __half* e_row = a.e_buf + (size_t)row * a.ld_e;
-  for (int t = 0; t < a.ct; ++t) {
-    const float tmax = a.tile_stats[(size_t)row * a.ct_stride + t].x;
-    const float scale = labelled ? (kGradScale / kEScale) * exp2f((tmax - lse) * kLog2e) : 0.f;
-    uint4* p = reinterpret_cast<uint4*>(e_row + t * kBN1) + lane;  // 32 lanes x 8 = 256 columns
-    uint4 v = *p;
-    uint32_t w[4] = {v.x, v.y, v.z, v.w};
+  if (a.dh && !a.first) {  // rescale what is accumulated to the new log-sum-exp
+    float4* g = reinterpret_cast<float4*>(a.dh + (size_t)row * a.k_dim);
+    const int n4 = a.k_dim >> 2;
+    for (int i0 = threadIdx.x; i0 < n4; i0 += 4 * blockDim.x) {
+      float4 v[4];
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      float2 f = __half22float2(*reinterpret_cast<__half2*>(&w[k]));
-      __half2 h = __floats2half2_rn(f.x * scale, f.y * scale);
-      w[k] = *reinterpret_cast<uint32_t*>(&h);
+      for (int u = 0; u < 4; ++u)
+        if (i0 + u * blockDim.x < n4) v[u] = g[i0 + u * blockDim.x];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (i0 + u * blockDim.x < n4) {
+          v[u].x *= fac; v[u].y *= fac; v[u].z *= fac; v[u].w *= fac;
+          g[i0 + u * blockDim.x] = v[u];
+        }
     }
-    *p = make_uint4(w[0], w[1], w[2], w[3]);
+    for (int i = (a.k_dim & ~3) + threadIdx.x; i < a.k_dim; i += blockDim.x)
+      a.dh[(size_t)row * a.k_dim + i] *= fac;
   }
-  if (hit) {
-    __syncwarp();
-    if (lane == 0) {
+  // P = 1024 * exp(z - lse) = E * 2^-14 * 1024 * exp(tile_max - lse); zero for unlabelled rows.
+  // Warp w owns tiles w, w + 4, ...; their loads are all issued before the first store.
+  __half* e_row = a.e_buf + (size_t)row * a.ld_e;
+  for (int tb = warp; tb < a.ct; tb += kRowWarps * kRowTilesPerWarp) {
+    uint4 v[kRowTilesPerWarp];
+    float scale[kRowTilesPerWarp];
+#pragma unroll
+    for (int u = 0; u < kRowTilesPerWarp; ++u) {
+      const int t = tb + u * kRowWarps;
+      if (t < a.ct) {
+        v[u] = *(reinterpret_cast<const uint4*>(e_row + t * kBN1) + lane);
+        const float tmax = a.tile_stats[(size_t)row * a.ct_stride + t].x;
+        scale[u] = labelled ? (kGradScale / kEScale) * exp2f((tmax - lse) * kLog2e) : 0.f;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kRowTilesPerWarp; ++u) {
+      const int t = tb + u * kRowWarps;
+      if (t < a.ct) {
+        uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          float2 f = __half22float2(*reinterpret_cast<__half2*>(&w[k]));
+          __half2 h = __floats2half2_rn(f.x * scale[u], f.y * scale[u]);
+          w[k] = *reinterpret_cast<uint32_t*>(&h);
+        }
+        *(reinterpret_cast<uint4*>(e_row + t * kBN1) + lane) = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+    }
+  }
+  if (hit) {  // uniform over the CTA (one row per CTA)
+    __syncthreads();
+    if (threadIdx.x == 0) {
       // The label's entry carries p - 1, formed in fp32 and rounded once.
       const float p = expf(a.label_logit[row] - lse);
       e_row[local] = __float2half_rn((p - 1.0f) * kGradScale);
@@ -506,6 +732,8 @@ struct GradArgs {
   int col0;             // first shard column of the chunk (TMA row coordinate into W)
   int n_kb;             // 64-column blocks of the chunk
   int first;            // first chunk: overwrite instead of accumulate
+  int ksplit;           // pair kernel: K (vocabulary) splits per output tile, partial sums added with RED
+  int debug;            // bit 5: skip the epilogue's global traffic (timing experiments only)
   int* status;
 };
 
@@ -598,7 +826,7 @@ lmhead_grad_kernel(const __grid_constant__ CUtensorMap map_p,
         uint32_t r[32];
         tmem_ld_32x32(taddr + c * 32, r);
         tmem_ld_wait();
-        if (row_ok) {
+        if (row_ok && !(a.debug & 32)) {
 #pragma unroll
           for (int j = 0; j < 32; j += 4) {
             const int col = c * 32 + j;
@@ -628,6 +856,163 @@ lmhead_grad_kernel(const __grid_constant__ CUtensorMap map_p,
     }
   }
   finish_pipeline(s, warp, tmem);
+}
+
+// ------------------------------------------------------------------------------------------
+// Gradient kernel, CTA pairs: the pair owns 256 rows x 192 hidden columns; each CTA loads its 128
+// rows of P and 96 of the 192 weight columns (three 32-column boxes, 64-byte swizzle, MN-major).
+// 8 x 8 = 64 pair tiles cover [2048, 1536]. The epilogue transposes each 32 x 32 block of the
+// accumulator through shared memory so that dH is read and written in full 128-byte rows.
+// ------------------------------------------------------------------------------------------
+constexpr int kStageT = 4 * 32 * 33 * 4;             // per epilogue warp a padded 32 x 32 fp32 block
+
+// BN = hidden columns per pair tile, SWZ = swizzle width in bytes of the B boxes (64 or 128; the
+// half of BN one CTA holds must be a whole number of SWZ/2-column boxes).
+template <int BN, int SWZ>
+struct GradPairCfg {
+  static constexpr int kBoxCols = SWZ / 2;
+  static constexpr int kBoxes = BN / 2 / kBoxCols;
+  static constexpr int kBoxBytes = kBK * SWZ;
+  static constexpr int kBHalfBytes = kBoxes * kBoxBytes;
+  static constexpr int kStageBytes = kABytes + kBHalfBytes;
+  static constexpr int kStages = (200 * 1024) / kStageBytes;
+  static constexpr int kSmem = kStages * kStageBytes + kStageT + 1024 + 256;
+  static_assert(kBoxes * kBoxCols * 2 == BN, "half tile must be whole boxes");
+  static_assert(kStageBytes % 1024 == 0, "stages must keep 1024-byte alignment");
+};
+
+template <int BN, int SWZ>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreadsGemm, 1)
+lmhead_grad_pair_kernel(const __grid_constant__ CUtensorMap map_p,
+                        const __grid_constant__ CUtensorMap map_w, const GradArgs a) {
+  using Cfg = GradPairCfg<BN, SWZ>;
+  extern __shared__ uint8_t smem_raw[];
+  constexpr int kStageBytes = Cfg::kStageBytes;
+  constexpr int kStages = Cfg::kStages;
+  const GemmSmem s = carve_smem<kStages, kStageBytes, kStageT>(smem_raw);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (warp == 0 && lane == 0) { prefetch_tensormap(&map_p); prefetch_tensormap(&map_w); }
+  const PairInit pi = init_pair<kStages>(s, warp, lane, a.status);
+  if (!pi.run) return;
+  const uint32_t tmem = pi.tmem, rank = pi.rank;
+  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+
+  const int rt = (a.n_rows + 2 * kBM - 1) / (2 * kBM);
+  const int nt = (a.k_dim + BN - 1) / BN;
+  const int n_tiles = rt * nt;
+  const int n_units = n_tiles * a.ksplit;   // unit = (output tile, K split)
+
+  if (warp == 0) {
+    if (lane == 0) {
+      PipeState p;
+      bool ok = true;
+      for (int unit = pair; unit < n_units && ok; unit += n_pairs) {
+        const int tile = unit % n_tiles, ks = unit / n_tiles;
+        const int tr = tile % rt, tn = tile / rt;
+        const int row0 = tr * 2 * kBM + (int)rank * kBM;
+        const int hcol0 = tn * BN + (int)rank * (BN / 2);
+        const int kb_end = (a.n_kb * (ks + 1)) / a.ksplit;
+        for (int kb = (a.n_kb * ks) / a.ksplit; kb < kb_end; ++kb) {
+          ok = mbar_wait(&s.empty[p.stage], p.phase ^ 1u, s.abort_flag, a.status, 41);
+          if (!ok) break;
+          uint8_t* st = s.tiles + p.stage * kStageBytes;
+          const uint32_t full_leader = mapa_u32(smem_u32(&s.full[p.stage]), 0);
+          if (rank == 0) mbar_expect_tx(&s.full[p.stage], 2 * kStageBytes);
+          tma_load_2d_pair(st, &map_p, kb * kBK, row0, full_leader);
+#pragma unroll
+          for (int j = 0; j < Cfg::kBoxes; ++j)
+            tma_load_2d_pair(st + kABytes + j * Cfg::kBoxBytes, &map_w, hcol0 + j * Cfg::kBoxCols,
+                             a.col0 + kb * kBK, full_leader);
+          p.template advance<kStages>();
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = make_idesc_f16(2 * kBM, BN, false, true);
+      PipeState p;
+      bool ok = true;
+      int it = 0;
+      for (int unit = pair; unit < n_units && ok; unit += n_pairs, ++it) {
+        const int ks = unit / n_tiles;
+        const int ab = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1u;
+        ok = mbar_wait(&s.acc_empty[ab], acc_phase ^ 1u, s.abort_flag, a.status, 42);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem + ab * 256;
+        const int kb_begin = (a.n_kb * ks) / a.ksplit, kb_end = (a.n_kb * (ks + 1)) / a.ksplit;
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
+          ok = mbar_wait(&s.full[p.stage], p.phase, s.abort_flag, a.status, 43);
+          if (!ok) break;
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_u32(s.tiles + p.stage * kStageBytes);
+          const uint64_t da = make_smem_desc(a_addr, 16, 1024);
+          // MN-major B: column groups of one box are kBoxBytes apart (leading offset), 8-k groups
+          // 8*SWZ bytes apart (stride offset); one MMA consumes 16 k = 16*SWZ bytes.
+          const uint64_t db = make_smem_desc(a_addr + kABytes, Cfg::kBoxBytes, 8 * SWZ,
+                                             SWZ == 128 ? 2 : 4);
+#pragma unroll
+          for (int k4 = 0; k4 < kBK / 16; ++k4)
+            mma_f16_ss_pair(d_tmem, da + k4 * 2, db + k4 * ((16 * SWZ) >> 4), idesc,
+                            (kb != kb_begin) || k4 != 0);
+          tc_commit_pair(&s.empty[p.stage], 3);
+          p.template advance<kStages>();
+        }
+        if (ok) tc_commit_pair(&s.acc_full[ab], 3);
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    float* tpose = reinterpret_cast<float*>(s.extra) + (warp - 2) * (32 * 33);
+    bool ok = true;
+    int it = 0;
+    const bool plain_store = a.first && a.ksplit == 1;   // else dH was zeroed / rescaled before
+    for (int unit = pair; unit < n_units && ok; unit += n_pairs, ++it) {
+      const int tile = unit % n_tiles;
+      const int tr = tile % rt, tn = tile / rt;
+      const int ab = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1u;
+      ok = __all_sync(0xffffffffu, mbar_wait(&s.acc_full[ab], acc_phase, s.abort_flag, a.status, 44));
+      if (!ok) break;
+      tc_fence_after_sync();
+      const int row_base = tr * 2 * kBM + (int)rank * kBM + q * 32;   // first of this warp's 32 rows
+      const uint32_t taddr = tmem + (static_cast<uint32_t>(q * 32) << 16) + ab * 256;
+      const int col_base = tn * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + c * 32, r);
+        tmem_ld_wait_on(r);
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) tpose[lane * 33 + j] = __uint_as_float(r[j]);
+        __syncwarp();
+        // dH was already multiplied by this chunk's factor (row kernel), so partial sums are added
+        // with fire-and-forget reductions. With ksplit == 1 one CTA adds to an element per chunk
+        // and the result is deterministic; with K splits the order of the adds is not.
+        const int col = col_base + c * 32 + lane;
+        const bool col_ok = col < a.k_dim && !(a.debug & 32);
+#pragma unroll 8
+        for (int rr = 0; rr < 32; ++rr) {
+          const int row = row_base + rr;
+          if (col_ok && row < a.n_rows) {
+            float* dst = a.dh + (size_t)row * a.k_dim + col;
+            const float acc = tpose[rr * 33 + lane];
+            if (plain_store) *dst = acc;
+            else atomicAdd(dst, acc);
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) {
+        if (rank == 0) mbar_arrive(&s.acc_empty[ab]);
+        else mbar_arrive_cluster(mapa_u32(smem_u32(&s.acc_empty[ab]), 0));
+      }
+    }
+  }
+  finish_pair(s, warp, tmem);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -744,6 +1129,20 @@ __global__ void lmhead_scale_cast_kernel(const float* __restrict__ dh, void* __r
 
 inline int64_t round_up(int64_t v, int64_t m) { return (v + m - 1) / m * m; }
 
+// K splits per gradient tile that minimise the makespan of `tiles` output tiles on `pairs` CTA
+// pairs (each pair runs its units one after another). 1 keeps the result deterministic.
+inline int pick_ksplit(int tiles, int pairs, int n_kb, bool deterministic) {
+  if (deterministic || tiles <= 0) return 1;
+  int best = 1;
+  long best_span = (long)((tiles + pairs - 1) / pairs) * n_kb;
+  for (int ks = 2; ks <= 4; ++ks) {
+    if (n_kb / ks < 8) break;  // too little work per unit to amortise its epilogue
+    const long span = (long)((tiles * ks + pairs - 1) / pairs) * ((n_kb + ks - 1) / ks);
+    if (span * 10 < best_span * 9) { best = ks; best_span = span; }  // needs a 10 % gain
+  }
+  return best;
+}
+
 struct Plan {
   int row_block;   // rows per row block
   int ct;          // column tiles per chunk
@@ -839,6 +1238,13 @@ int ensure_smem_attr() {
   if (cudaFuncSetAttribute(lmhead_grad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            kSmem2) != cudaSuccess)
     return -1;
+  if (cudaFuncSetAttribute(lmhead_logits_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           kSmemP1) != cudaSuccess)
+    return -1;
+  if (cudaFuncSetAttribute(lmhead_grad_pair_kernel<256, 128>,
+                           cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           GradPairCfg<256, 128>::kSmem) != cudaSuccess)
+    return -1;
   g_attr_set[dev] = true;
   return 0;
 }
@@ -865,7 +1271,7 @@ static EncodeTiledFn get_encode_fn() {
 }
 
 int encode_map_2d_f16(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
-                      uint64_t pitch_elems, uint32_t box_rows, uint32_t box_cols) {
+                      uint64_t pitch_elems, uint32_t box_rows, uint32_t box_cols, int swizzle_bytes) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return -1;
   const cuuint64_t dims[2] = {cols, rows};
@@ -874,7 +1280,8 @@ int encode_map_2d_f16(CUtensorMap* map, const void* base, uint64_t rows, uint64_
   const cuuint32_t estr[2] = {1, 1};
   const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims,
                         strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : -(int)r - 1000;
 }
@@ -920,10 +1327,16 @@ extern "C" int soup_lmhead_ce(const void* hidden, const void* weight, const int6
   const int ld_e = plan.ct * kBN1;
   const int total_ct = (int)((v_shard + kBN1 - 1) / kBN1);
 
-  CUtensorMap map_h, map_w1, map_w2, map_p, map_e;
+  CUtensorMap map_h, map_w1, map_w1h, map_w2, map_w2h, map_p, map_e;
+  const char* single_env = getenv("SOUP_LMHEAD_SINGLE_CTA");
+  const bool use_pairs = !(single_env && atoi(single_env) != 0) && (sms % 2 == 0);
+  const char* det_env = getenv("SOUP_LMHEAD_DETERMINISTIC");
+  const bool deterministic = det_env && atoi(det_env) != 0;
   if (umma::encode_map_2d_f16(&map_h, hidden, (uint64_t)n, (uint64_t)h, (uint64_t)h, kBM, kBK) ||
       umma::encode_map_2d_f16(&map_w1, weight, (uint64_t)v_shard, (uint64_t)h, (uint64_t)h, kBN1, kBK) ||
+      umma::encode_map_2d_f16(&map_w1h, weight, (uint64_t)v_shard, (uint64_t)h, (uint64_t)h, kBN1 / 2, kBK) ||
       umma::encode_map_2d_f16(&map_w2, weight, (uint64_t)v_shard, (uint64_t)h, (uint64_t)h, kBK, 64) ||
+      umma::encode_map_2d_f16(&map_w2h, weight, (uint64_t)v_shard, (uint64_t)h, (uint64_t)h, kBK, 32, 64) ||
       umma::encode_map_2d_f16(&map_p, ws.e_buf, (uint64_t)plan.row_block, (uint64_t)ld_e,
                               (uint64_t)ld_e, kBM, kBK) ||
       umma::encode_map_2d_f16(&map_e, ws.e_buf, (uint64_t)plan.row_block, (uint64_t)ld_e,
@@ -931,6 +1344,8 @@ extern "C" int soup_lmhead_ce(const void* hidden, const void* weight, const int6
     SOUP_FAIL(SOUP_ERR_DEVICE, "lmhead_ce: cuTensorMapEncodeTiled failed");
 
   cudaMemsetAsync(ws.status, 0, 4, s);
+  if (use_pairs && want_grad && !deterministic)   // K-split partial sums are added into dH
+    cudaMemsetAsync(dh, 0, (size_t)n * h * sizeof(float), s);
   lmhead_init_state_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(
       run_max, run_sum, run_dot, best, label_logit, label_lse, (int)n);
   SOUP_CHECK_LAUNCH("lmhead_init_state");
@@ -963,8 +1378,15 @@ extern "C" int soup_lmhead_ce(const void* hidden, const void* weight, const int6
       la.status = ws.status;
       const int tiles1 = rt * ct;
       timer.begin(0);
-      lmhead_logits_kernel<<<(unsigned)(tiles1 < sms ? tiles1 : sms), kThreadsGemm, kSmem1, s>>>(
-          map_h, map_w1, map_e, la);
+      if (use_pairs) {
+        const int tiles_p = ((rows + 2 * kBM - 1) / (2 * kBM)) * ct;
+        const int pairs = tiles_p < sms / 2 ? tiles_p : sms / 2;
+        lmhead_logits_pair_kernel<<<(unsigned)(2 * pairs), kThreadsGemm, kSmemP1, s>>>(
+            map_h, map_w1h, map_e, la);
+      } else {
+        lmhead_logits_kernel<<<(unsigned)(tiles1 < sms ? tiles1 : sms), kThreadsGemm, kSmem1, s>>>(
+            map_h, map_w1, map_e, la);
+      }
       timer.end(0);
       SOUP_CHECK_LAUNCH("lmhead_logits");
 
@@ -987,8 +1409,11 @@ extern "C" int soup_lmhead_ce(const void* hidden, const void* weight, const int6
       ra.ct_stride = plan.ct;
       ra.ld_e = ld_e;
       ra.write_p = want_grad;
+      ra.dh = (use_pairs && want_grad) ? dh + r0 * h : nullptr;
+      ra.k_dim = (int)h;
+      ra.first = t0 == 0;
       timer.begin(1);
-      lmhead_row_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, s>>>(ra);
+      lmhead_row_kernel<<<(unsigned)rows, kRowWarps * 32, 0, s>>>(ra);
       timer.end(1);
       SOUP_CHECK_LAUNCH("lmhead_row");
 
@@ -1001,11 +1426,22 @@ extern "C" int soup_lmhead_ce(const void* hidden, const void* weight, const int6
         ga.col0 = t0 * kBN1;
         ga.n_kb = ct * (kBN1 / kBK);
         ga.first = t0 == 0;
+        ga.ksplit = 1;
+        ga.debug = la.debug;
         ga.status = ws.status;
         const int tiles2 = rt * (int)((h + kBN2 - 1) / kBN2);
         timer.begin(2);
-        lmhead_grad_kernel<<<(unsigned)(tiles2 < sms ? tiles2 : sms), kThreadsGemm, kSmem2, s>>>(
-            map_p, map_w2, ga);
+        if (use_pairs) {
+          const int tiles_p = ((rows + 2 * kBM - 1) / (2 * kBM)) * (int)((h + 255) / 256);
+          ga.ksplit = pick_ksplit(tiles_p, sms / 2, ga.n_kb, deterministic);
+          const int units = tiles_p * ga.ksplit;
+          const int pairs = units < sms / 2 ? units : sms / 2;
+          lmhead_grad_pair_kernel<256, 128><<<(unsigned)(2 * pairs), kThreadsGemm,
+                                               GradPairCfg<256, 128>::kSmem, s>>>(map_p, map_w2, ga);
+        } else {
+          lmhead_grad_kernel<<<(unsigned)(tiles2 < sms ? tiles2 : sms), kThreadsGemm, kSmem2, s>>>(
+              map_p, map_w2, ga);
+        }
         timer.end(2);
         SOUP_CHECK_LAUNCH("lmhead_grad");
       }

@@ -217,6 +217,91 @@ __device__ __forceinline__ void tmem_ld_wait_on(uint32_t (&r)[32]) {
                : "memory");
 }
 
+// ---------------------------------------------------------------- CTA pairs (cta_group::2)
+// Two CTAs of a cluster of 2 share one MMA: each brings its own 128 rows of A and half of the B
+// columns, the leader (cluster rank 0) issues tcgen05.mma.cta_group::2, and each CTA receives its
+// 128 rows of D in its own tensor memory. Barriers live at the same shared-memory offset in both
+// CTAs; `mapa` turns a local address into the peer's.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// shared::cluster address of the same shared-memory location in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t mapa_u32(uint32_t local_addr, uint32_t rank) {
+  uint32_t out;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(local_addr), "r"(rank));
+  return out;
+}
+
+__device__ __forceinline__ int ld_shared_cluster_s32(uint32_t cluster_addr) {
+  int v;
+  asm volatile("ld.shared::cluster.s32 %0, [%1];" : "=r"(v) : "r"(cluster_addr) : "memory");
+  return v;
+}
+
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr)
+               : "memory");
+}
+
+// TMA load whose completion bytes are counted on a barrier given by its shared::cluster address
+// (the leader's barrier, also when the peer CTA issues the load into its own shared memory).
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, int32_t c0,
+                                                 int32_t c1, uint32_t bar_cluster_addr) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr),
+      "r"(c0), "r"(c1)
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_result, uint32_t n_cols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                   smem_u32(smem_result)),
+               "r"(n_cols)
+               : "memory");
+}
+
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t tmem_addr, uint32_t n_cols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_addr), "r"(n_cols)
+               : "memory");
+}
+
+// Leader only: D (+)= A * B over both CTAs of the pair (M = 256: 128 rows per CTA).
+__device__ __forceinline__ void mma_f16_ss_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
+                                                uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// Leader only: when all earlier MMAs have completed, arrive on the barrier at this shared-memory
+// offset in every CTA of `cta_mask` (0b11 = both CTAs of the pair).
+__device__ __forceinline__ void tc_commit_pair(uint64_t* bar, uint16_t cta_mask) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64"
+      " [%0], %1;"
+      ::"r"(smem_u32(bar)), "h"(cta_mask)
+      : "memory");
+}
+
 // ---------------------------------------------------------------- descriptors
 // Shared-memory matrix descriptor (64-bit) for a 128-byte-swizzled tile whose 8-row (K-major) or
 // 8-k (MN-major) groups are 1024 bytes apart. Field layout: start address >> 4 in bits [0,14),
@@ -224,13 +309,13 @@ __device__ __forceinline__ void tmem_ld_wait_on(uint32_t (&r)[32]) {
 // in [46,48), swizzle mode in [61,64) (2 = 128-byte swizzle). The tile base must be 1024-byte
 // aligned so that the base-offset field stays 0.
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t lbo_bytes,
-                                                   uint32_t sbo_bytes) {
+                                                   uint32_t sbo_bytes, uint32_t swizzle_code = 2) {
   uint64_t d = 0;
   d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
   d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
   d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
   d |= static_cast<uint64_t>(1) << 46;
-  d |= static_cast<uint64_t>(2) << 61;
+  d |= static_cast<uint64_t>(swizzle_code) << 61;  // 2 = 128-byte, 4 = 64-byte, 6 = 32-byte swizzle
   return d;
 }
 
@@ -245,10 +330,11 @@ __host__ __device__ constexpr uint32_t make_idesc_f16(int m, int n, bool a_mn_ma
 
 // ---------------------------------------------------------------- host: tensor maps
 // Row-major 2-D tensor [rows, cols] of 16-bit elements with row pitch `pitch_elems`; the box is
-// [box_rows, box_cols] with box_cols * 2 == 128 bytes, written to shared memory with the 128-byte
-// swizzle the descriptors above expect. Out-of-range elements read as zero.
+// [box_rows, box_cols] with box_cols * 2 == swizzle_bytes (128 or 64), written to shared memory
+// with that swizzle, as the descriptors above expect. Out-of-range elements read as zero.
 int encode_map_2d_f16(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
-                      uint64_t pitch_elems, uint32_t box_rows, uint32_t box_cols);
+                      uint64_t pitch_elems, uint32_t box_rows, uint32_t box_cols,
+                      int swizzle_bytes = 128);
 
 }  // namespace umma
 }  // namespace soup

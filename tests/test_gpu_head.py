@@ -164,7 +164,10 @@ def test_full_size_linearity_property():
     loss, step, dh = run_ours(h, w, t)
     tl, en = step.token_loss[0].cpu(), step.token_entropy[0].cpu()
     assert tl[3] == tl[1000] == tl[2047] and en[3] == en[1000] == en[2047]
-    assert torch.equal(dh[3], dh[1000]) and torch.equal(dh[3], dh[2047])
+    # K-split partial sums are added in no fixed order: equal up to fp32 summation order
+    scale = dh[3].float().abs().max().item()
+    assert (dh[3].float() - dh[1000].float()).abs().max().item() <= 2e-3 * scale
+    assert (dh[3].float() - dh[2047].float()).abs().max().item() <= 2e-3 * scale
     rows = torch.tensor([0, 3, 127, 128, 999, 2046])
     z = h[rows].double() @ w.double().t()
     lse = torch.logsumexp(z, -1)
