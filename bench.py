@@ -444,7 +444,8 @@ def main():
     _lib.lib().soup_lmhead_plan(n_tokens, v_local, 0, ctypes.byref(rb), ctypes.byref(ct))
     row_blocks = -(-n_tokens // rb.value)
     chunks = -(-(-(-v_local // 256)) // ct.value)
-    launches = 1 + row_blocks * chunks * 3 + 1 + (1 if world == 1 else 1)
+    # init + per row block (3 kernels per chunk + the first chunk's second logits launch) + finish + backward scale
+    launches = 1 + row_blocks * (chunks * 3 + 1) + 1 + 1
 
     kernels, cpu = None, None
     if rank == 0 and world == 1:

@@ -1,29 +1,45 @@
 // Fused LM head + cross-entropy, forward and hidden-state gradient, without the logits in HBM.
 //
-// The vocabulary is walked in chunks of `ct` column tiles (256 columns each). Per chunk, three
+// The vocabulary is walked in chunks of `ct` column tiles (256 columns each). Per chunk three
 // kernels run back to back on the caller's stream; what they exchange stays in the 126 MB L2:
 //
-//   logits kernel  tcgen05 GEMM  S = H[rows,K] * W[cols,K]^T, 128x256 tiles, fp32 in TMEM, TMA-fed
-//                  4-stage pipeline, double-buffered accumulator. The epilogue never writes S: per
-//                  row and tile it keeps (max, sum exp, sum exp*z, first argmax, label logit) and
-//                  writes E = 2^14 * exp(z - tile_max) as fp16 (always a normal number at the top
-//                  of the tile, so nothing a 152K vocabulary needs flushes to zero).
-//   row kernel     merges the tile statistics into the running per-row state (max, sum, dot,
-//                  argmax, label logit), forms the running log-sum-exp, and rescales E in place to
-//                  P = 1024 * softmax against that running lse (the label's entry gets p - 1,
-//                  computed in fp32). Emits factor = exp(lse_before - lse_after).
-//   grad kernel    tcgen05 GEMM  dH = factor * dH + P[rows,cols] * W[cols,K], with W as the
-//                  MN-major operand straight from its row-major storage, 128x192 tiles.
+//   logits kernel  tcgen05 GEMM  S = H[rows,K] * W[cols,K]^T on CTA pairs (cta_group::2): a pair
+//                  owns a 256 x 256 tile, each CTA 128 rows of it and half of the W columns, fp32
+//                  accumulators double-buffered in TMEM, TMA-fed 6-stage ring. The epilogue never
+//                  writes S. In one sweep over the accumulator it forms, against the row's running
+//                  log-sum-exp `ref` of all earlier chunks, e = exp(z - ref), the tile's sum e and
+//                  sum e*z, the tile maximum with its first index, the label's logit, and stores
+//                  P = bf16(e) (label column and unlabelled rows zeroed) through a swizzled staging
+//                  box and a TMA store. bf16 keeps fp32's exponent range, so a logit far above
+//                  everything seen so far cannot overflow P.
+//   row kernel     one warp per row: adds the tile sums to the running state (the state is kept
+//                  normalised: run_max = lse so far, run_sum = 1), and sets the row's multiplier
+//                  exp(ref - base) for this chunk's gradient contribution.
+//   grad kernel    tcgen05 GEMM  dH += mult * P[rows,cols] * W[cols,K] on CTA pairs, 256 x 256
+//                  tiles with the vocabulary (K) dimension split so that all SMs have work; W is
+//                  the MN-major operand straight from its row-major storage. kind::f16 wants the
+//                  same element format for both operands, so this GEMM reads a bf16 copy of W
+//                  (made once per frozen weight by the caller). Partial sums are added with
+//                  fire-and-forget reductions; dH is kept relative to `base`, the lse after the
+//                  first chunk.
 //
-// A last kernel turns the state into loss / entropy / correct and restores the part of the
-// label's -1 that later rescaling removed. The algorithm (running lse, factor, label fix-up,
-// GRAD_SCALE 1024) is the one of _FusedHeadLoss.forward, solution/lm_head_loss.py:192-245 of the
-// reference; only the tiling, the on-chip statistics and the exp-relative-to-tile-max storage
-// are new.
+// The first chunk has no earlier lse: its statistics are taken against the tile maxima in a first
+// launch (two sweeps), merged, and a second launch writes P against the merged lse. A last kernel
+// turns the state into loss / entropy / correct, rescales dH from `base` to the final lse and
+// adds (p_label - 1) * W[label] in fp32.
 //
-// Vocabulary-parallel use: a rank passes its shard of W, the global index of its first column,
-// and gets state and dH relative to its own lse; soup_lmhead_merge combines the ranks' states and
-// soup_lmhead_finish applies exp(lse_rank - lse_global) before the caller sums dH across ranks.
+// Relation to the reference (_FusedHeadLoss.forward, solution/lm_head_loss.py:192-245 with the
+// kernel of :108-160): same single pass over W in column chunks, same carried statistics (max, sum
+// exp, sum exp*z, first argmax, label logit), same GRAD_SCALE convention for the returned
+// gradient. The reference rescales the accumulated gradient by exp(lse_before - lse_after) every
+// chunk and writes softmax against the *new* lse in fp16; here each chunk is written against the
+// lse *before* it (known when its tiles are computed) and the per-chunk multiplier is applied to
+// the chunk's contribution instead, which removes the second pass over the chunk buffer.
+//
+// Vocabulary-parallel use: a rank passes its shard of W and the global index of its first column
+// and gets its state and dH relative to its own `base` (returned in grad_ref);
+// soup_lmhead_merge combines the ranks' states and soup_lmhead_finish rescales by
+// exp(grad_ref - lse_global) before the caller sums dH across ranks.
 #include <math.h>
 #include <stdlib.h>
 
@@ -37,376 +53,71 @@ namespace {
 
 using namespace umma;
 
-constexpr int kBM = 128;         // rows per tile (TMEM lanes)
-constexpr int kBN1 = 256;        // vocabulary columns per logits tile
-constexpr int kBN2 = 192;        // hidden columns per gradient tile
-constexpr int kBK = 64;          // 64 fp16 = one 128-byte swizzle row
-constexpr int kStages1 = 4;
-constexpr int kStages2 = 5;
-constexpr int kABytes = kBM * kBK * 2;      // 16 KB
-constexpr int kB1Bytes = kBN1 * kBK * 2;    // 32 KB
-constexpr int kB2Bytes = kBN2 * kBK * 2;    // 24 KB, three 64-column boxes of 8 KB
-constexpr int kThreadsGemm = 192;           // warp 0 TMA, warp 1 MMA, warps 2-5 epilogue
+constexpr int kBM = 128;          // rows per CTA (TMEM lanes); a pair owns 2 * kBM rows
+constexpr int kBN = 256;          // columns per tile (vocabulary for logits, hidden for gradient)
+constexpr int kBK = 64;           // 64 16-bit elements = one 128-byte swizzle row
+constexpr int kABytes = kBM * kBK * 2;            // 16 KB: this CTA's rows of the A operand
+constexpr int kBHalfBytes = (kBN / 2) * kBK * 2;  // 16 KB: this CTA's half of the B operand
+constexpr int kStageBytes = kABytes + kBHalfBytes;
+constexpr int kStages = 6;
+constexpr int kThreadsGemm = 192;  // warp 0 TMA, warp 1 MMA, warps 2-5 epilogue
 constexpr float kLog2e = 1.4426950408889634f;
-constexpr float kLn2 = 0.6931471805599453f;
-constexpr float kEScale = 16384.0f;         // 2^14, E = kEScale * exp(z - tile_max)
-constexpr float kGradScale = 1024.0f;       // as GRAD_SCALE of the reference
+constexpr float kGradScale = 1024.0f;  // as GRAD_SCALE of the reference
+constexpr float kRebase = 60.0f;       // rebase dH when the multiplier would exceed e^60
 constexpr int kIgnore = -100;
+constexpr int kEW = 16;                // accumulator columns per tcgen05.ld in the epilogues
 
-constexpr int kStageE = 4 * 2 * 4096;        // per epilogue warp two 32-row x 64-column fp16 boxes
-constexpr int kSmem1 = kStages1 * (kABytes + kB1Bytes) + kStageE + 1024 + 256;
-constexpr int kSmem2 = kStages2 * (kABytes + kB2Bytes) + 1024 + 256;
+constexpr int kStageP = 4 * 2 * 4096;          // logits: per epilogue warp two 32 x 64 bf16 boxes
+constexpr int kStageT = 4 * 32 * 33 * 4;       // gradient: per epilogue warp a padded 32 x 32 fp32 block
+constexpr int kSmemLogits = kStages * kStageBytes + kStageP + 1024 + 256;
+constexpr int kSmemGrad = kStages * kStageBytes + kStageT + 1024 + 256;
+
+enum LogitsMode {
+  kModeTileMax = 0,  // statistics against the tile maximum, no P (first chunk, first launch)
+  kModePOnly = 1,    // P against ref, no statistics (first chunk, second launch)
+  kModeCombined = 2  // statistics and P against ref (all later chunks)
+};
 
 struct PipeState {
   int stage = 0;
   uint32_t phase = 0;
-  template <int STAGES>
   __device__ __forceinline__ void advance() {
-    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+    if (++stage == kStages) { stage = 0; phase ^= 1u; }
   }
 };
 
 struct GemmSmem {
   uint8_t* tiles;        // 1024-byte aligned
   uint8_t* extra;        // kernel-specific staging area behind the stages
-  uint64_t* full;        // [STAGES]
-  uint64_t* empty;       // [STAGES]
+  uint64_t* full;        // [kStages]  (used in the leader CTA)
+  uint64_t* empty;       // [kStages]
   uint64_t* acc_full;    // [2]
-  uint64_t* acc_empty;   // [2]
+  uint64_t* acc_empty;   // [2]        (used in the leader CTA)
   uint32_t* tmem_base;
   int* abort_flag;
 };
 
-template <int STAGES, int STAGE_BYTES, int EXTRA_BYTES = 0>
+template <int EXTRA_BYTES>
 __device__ __forceinline__ GemmSmem carve_smem(uint8_t* raw) {
   GemmSmem s;
   const uintptr_t base = (reinterpret_cast<uintptr_t>(raw) + 1023u) & ~static_cast<uintptr_t>(1023u);
   s.tiles = reinterpret_cast<uint8_t*>(base);
-  s.extra = s.tiles + STAGES * STAGE_BYTES;  // 1024-byte aligned (stage sizes are multiples of 1024)
-  uint64_t* bars = reinterpret_cast<uint64_t*>(s.tiles + STAGES * STAGE_BYTES + EXTRA_BYTES);
+  s.extra = s.tiles + kStages * kStageBytes;  // 1024-byte aligned
+  uint64_t* bars = reinterpret_cast<uint64_t*>(s.extra + EXTRA_BYTES);
   s.full = bars;
-  s.empty = bars + STAGES;
-  s.acc_full = bars + 2 * STAGES;
-  s.acc_empty = bars + 2 * STAGES + 2;
-  s.tmem_base = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  s.empty = bars + kStages;
+  s.acc_full = bars + 2 * kStages;
+  s.acc_empty = bars + 2 * kStages + 2;
+  s.tmem_base = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
   s.abort_flag = reinterpret_cast<int*>(s.tmem_base + 1);
   return s;
 }
 
-template <int STAGES>
-__device__ __forceinline__ void init_pipeline(const GemmSmem& s, int warp, int lane) {
-  if (warp == 0 && lane == 0) {
-    for (int i = 0; i < STAGES; ++i) { mbar_init(&s.full[i], 1); mbar_init(&s.empty[i], 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(&s.acc_full[i], 1); mbar_init(&s.acc_empty[i], 4); }
-    *s.abort_flag = 0;
-    fence_barrier_init();
-  }
-  if (warp == 1) {  // one warp owns the tensor-memory allocation (all 512 columns)
-    tmem_alloc(s.tmem_base, 512);
-    tmem_relinquish();
-  }
-  tc_fence_before_sync();
-  __syncthreads();
-  tc_fence_after_sync();
-}
-
-__device__ __forceinline__ void finish_pipeline(const GemmSmem& s, int warp, uint32_t tmem) {
-  tc_fence_before_sync();
-  __syncthreads();
-  if (*s.abort_flag) {
-    // A wait was abandoned: give copies that may still be in flight time to land before the
-    // shared memory is released.
-    for (int i = 0; i < 64; ++i) __nanosleep(2000);
-    __syncthreads();
-  }
-  if (warp == 1) {
-    tc_fence_after_sync();
-    tmem_dealloc(tmem, 512);
-  }
-}
-
-// Statistics epilogue of one 128 x 256 logits tile for one thread (= one row). Two sweeps over the
-// accumulator in TMEM, 32 columns at a time, with the load of the next 32 columns issued before the
-// current ones are consumed: sweep 1 finds the row maximum of the tile and its first index, sweep 2
-// forms E = 2^14 * exp(z - max) (the scale folded into the exponent), its sum, the sum of E*z, and
-// writes E as fp16. FULL tiles (all 256 columns inside the vocabulary) skip every validity select.
-constexpr int kEW = 16;  // accumulator columns per tcgen05.ld in the statistics epilogue
-
-template <bool FULL>
-__device__ __forceinline__ void sweep_max(const uint32_t (&r)[kEW], int col0, int n_valid, float& m,
-                                          int& arg) {
-#pragma unroll
-  for (int j = 0; j < kEW; ++j) {
-    const float z = __uint_as_float(r[j]);
-    const int col = col0 + j;
-    if ((FULL || col < n_valid) && z > m) { m = z; arg = col; }
-  }
-}
-
-// `stage_row` points at this thread's 128-byte row of a 32-row x 64-column staging box laid out with
-// the 128-byte swizzle (16-byte piece k of row r lives at piece k ^ (r & 7)); `piece0` is the first
-// of the two 16-byte pieces these 16 columns fill.
-template <bool FULL>
-__device__ __forceinline__ void sweep_exp(const uint32_t (&r)[kEW], int col0, int n_valid,
-                                          bool store_e, uint8_t* stage_row, int row_swz, int piece0,
-                                          float bias, float (&acc)[4]) {
-  uint32_t packed[kEW / 2];
-#pragma unroll
-  for (int j = 0; j < kEW; j += 2) {
-    const float z0 = __uint_as_float(r[j]), z1 = __uint_as_float(r[j + 1]);
-    const int col = col0 + j;
-    float e0 = exp2f(fmaf(z0, kLog2e, bias));
-    float e1 = exp2f(fmaf(z1, kLog2e, bias));
-    if (!FULL) {
-      if (col >= n_valid) e0 = 0.f;
-      if (col + 1 >= n_valid) e1 = 0.f;
-    }
-    acc[0] += e0;
-    acc[1] += e1;
-    acc[2] = fmaf(e0, (FULL || col < n_valid) ? z0 : 0.f, acc[2]);
-    acc[3] = fmaf(e1, (FULL || col + 1 < n_valid) ? z1 : 0.f, acc[3]);
-    __half2 h = __floats2half2_rn(e0, e1);
-    packed[j >> 1] = *reinterpret_cast<uint32_t*>(&h);
-  }
-  if (store_e) {
-#pragma unroll
-    for (int v = 0; v < kEW / 8; ++v) {
-      const int piece = (piece0 + v) ^ row_swz;
-      *reinterpret_cast<uint4*>(stage_row + piece * 16) =
-          make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
-    }
-  }
-}
-
-// Statistics epilogue of one 128 x 256 logits tile for one thread (= one row). Two sweeps over the
-// accumulator in TMEM, 16 columns per tcgen05.ld, the next load in flight while the current columns
-// are consumed; the loop bodies are kept small enough to stay in the instruction cache. Sweep 1:
-// row maximum of the tile and its first index. Sweep 2: E = 2^14 * exp(z - max) (scale folded into
-// the exponent), its sum and the sum of E*z; E leaves as fp16 through a swizzled staging box and a
-// TMA store per 64 columns. FULL tiles (all 256 columns inside the vocabulary) skip the validity
-// selects. The label's logit, needed by very few rows of a tile, is fetched in a third, rare sweep.
-template <bool FULL>
-__device__ __noinline__ void tile_statistics(uint32_t taddr, int n_valid, int label_local,
-                                             bool store_e, const CUtensorMap* map_e,
-                                             uint8_t* stage_warp, int e_col0, int e_row0,
-                                             float& m_out, float& sum_out, float& dot_out,
-                                             float& lab_out, int& arg_out, int debug) {
-  constexpr int kLoads = kBN1 / kEW;      // 16
-  constexpr int kPerBox = 64 / kEW;       // loads per 64-column staging box
-  const int lane = threadIdx.x & 31;
-  uint32_t ra[kEW], rb[kEW];
-  float m = -INFINITY;
-  int arg = 0;
-  if (debug & 2) m = 0.f;
-  if (!(debug & 2)) tmem_ld_32x16(taddr, ra);
-#pragma unroll 1
-  for (int i = 0; i < ((debug & 2) ? 0 : kLoads); i += 2) {
-    tmem_ld_wait_on(ra);
-    tmem_ld_32x16(taddr + (i + 1) * kEW, rb);
-    sweep_max<FULL>(ra, i * kEW, n_valid, m, arg);
-    tmem_ld_wait_on(rb);
-    if (i + 2 < kLoads) tmem_ld_32x16(taddr + (i + 2) * kEW, ra);
-    sweep_max<FULL>(rb, (i + 1) * kEW, n_valid, m, arg);
-  }
-  // exp2(z*log2e - m*log2e + 14) = 2^14 * exp(z - m)
-  const float bias = 14.0f - m * kLog2e;
-  float acc[4] = {0.f, 0.f, 0.f, 0.f};
-  uint8_t* stage_row = stage_warp + lane * 128;
-  if (!(debug & 4)) tmem_ld_32x16(taddr, ra);
-#pragma unroll 1
-  for (int i = 0; i < ((debug & 4) ? 0 : kLoads); i += 2) {
-    // 64-column boxes alternate between the warp's two staging areas; the area used two boxes ago
-    // must have been read by its TMA store before it is overwritten.
-    const int box_id = i / kPerBox;
-    uint8_t* box = stage_warp + (box_id & 1) * 4096;
-    if (store_e && (i % kPerBox) == 0) {
-      if (lane == 0) tma_store_wait_read<1>();
-      __syncwarp();
-    }
-    tmem_ld_wait_on(ra);
-    tmem_ld_32x16(taddr + (i + 1) * kEW, rb);
-    sweep_exp<FULL>(ra, i * kEW, n_valid, store_e, stage_row + (box_id & 1) * 4096, lane & 7,
-                    (i % kPerBox) * (kEW / 8), bias, acc);
-    tmem_ld_wait_on(rb);
-    if (i + 2 < kLoads) tmem_ld_32x16(taddr + (i + 2) * kEW, ra);
-    sweep_exp<FULL>(rb, (i + 1) * kEW, n_valid, store_e, stage_row + (box_id & 1) * 4096, lane & 7,
-                    ((i + 1) % kPerBox) * (kEW / 8), bias, acc);
-    if (store_e && ((i + 2) % kPerBox) == 0) {
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) {
-        tma_store_2d(map_e, box, e_col0 + box_id * 64, e_row0);
-        tma_store_commit();
-      }
-    }
-  }
-  float lab = 0.f;
-  if (__any_sync(0xffffffffu, label_local >= 0)) {  // rare: some row's label falls in this tile
-#pragma unroll 1
-    for (int i = 0; i < kLoads; ++i) {
-      tmem_ld_32x16(taddr + i * kEW, ra);
-      tmem_ld_wait_on(ra);
-#pragma unroll
-      for (int j = 0; j < kEW; ++j)
-        if (i * kEW + j == label_local) lab = __uint_as_float(ra[j]);
-    }
-  }
-  m_out = m;
-  sum_out = (acc[0] + acc[1]) * (1.0f / kEScale);
-  dot_out = (acc[2] + acc[3]) * (1.0f / kEScale);
-  lab_out = lab;
-  arg_out = arg;
-}
-
 // ------------------------------------------------------------------------------------------
-// Logits kernel: tile statistics + E for one chunk of column tiles of one row block.
+// CTA pairs (cta_group::2): each CTA brings its own 128 rows of A and half of the B columns, so a
+// shared-memory stage holds half the B bytes a single CTA would need; the leader (cluster rank 0)
+// issues the MMAs and each CTA receives its 128 rows of the accumulator in its own tensor memory.
 // ------------------------------------------------------------------------------------------
-struct LogitsArgs {
-  const int64_t* target;   // [n_rows] of this row block
-  __half* e_buf;           // [n_rows, ld_e]
-  float4* tile_stats;      // [n_rows, ct_stride]  (max, sum, dot, argmax bits)
-  float* label_logit;      // [n_rows]
-  int n_rows;              // rows in this row block
-  int row0;                // first row of the block inside the hidden matrix (TMA coordinate)
-  int k_dim;               // hidden size
-  int col0;                // first column of the chunk inside the weight shard
-  int v_shard;             // columns of the weight shard
-  int col_offset;          // global vocabulary index of shard column 0
-  int ct;                  // column tiles in this chunk
-  int ct_stride;           // row pitch of tile_stats
-  int ld_e;                // row pitch of e_buf in elements
-  int write_e;
-  int debug;               // bit 0: skip the statistics sweeps (timing experiments only)
-  int* status;
-};
-
-__global__ void __launch_bounds__(kThreadsGemm, 1)
-lmhead_logits_kernel(const __grid_constant__ CUtensorMap map_h,
-                     const __grid_constant__ CUtensorMap map_w,
-                     const __grid_constant__ CUtensorMap map_e, const LogitsArgs a) {
-  extern __shared__ uint8_t smem_raw[];
-  if (*reinterpret_cast<volatile int*>(a.status) != 0) return;  // an earlier kernel gave up
-  constexpr int kStageBytes = kABytes + kB1Bytes;
-  const GemmSmem s = carve_smem<kStages1, kStageBytes, kStageE>(smem_raw);
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  if (warp == 0 && lane == 0) {
-    prefetch_tensormap(&map_h);
-    prefetch_tensormap(&map_w);
-    prefetch_tensormap(&map_e);
-  }
-  init_pipeline<kStages1>(s, warp, lane);
-  const uint32_t tmem = *s.tmem_base;
-
-  const int rt = (a.n_rows + kBM - 1) / kBM;
-  const int n_tiles = rt * a.ct;
-  const int n_kb = (a.k_dim + kBK - 1) / kBK;
-
-  if (warp == 0) {
-    if (lane == 0) {
-      PipeState p;
-      bool ok = true;
-      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-        const int tr = tile % rt, tc = tile / rt;
-        for (int kb = 0; kb < n_kb; ++kb) {
-          ok = mbar_wait(&s.empty[p.stage], p.phase ^ 1u, s.abort_flag, a.status, 11);
-          if (!ok) break;
-          uint8_t* st = s.tiles + p.stage * kStageBytes;
-          mbar_expect_tx(&s.full[p.stage], kStageBytes);
-          tma_load_2d(st, &map_h, kb * kBK, a.row0 + tr * kBM, &s.full[p.stage]);
-          tma_load_2d(st + kABytes, &map_w, kb * kBK, a.col0 + tc * kBN1, &s.full[p.stage]);
-          p.advance<kStages1>();
-        }
-      }
-    }
-  } else if (warp == 1) {
-    if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc_f16(kBM, kBN1, false, false);
-      PipeState p;
-      bool ok = true;
-      int it = 0;
-      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++it) {
-        const int ab = it & 1;
-        const uint32_t acc_phase = (it >> 1) & 1u;
-        ok = mbar_wait(&s.acc_empty[ab], acc_phase ^ 1u, s.abort_flag, a.status, 12);
-        if (!ok) break;
-        tc_fence_after_sync();
-        const uint32_t d_tmem = tmem + ab * kBN1;
-        for (int kb = 0; kb < n_kb; ++kb) {
-          ok = mbar_wait(&s.full[p.stage], p.phase, s.abort_flag, a.status, 13);
-          if (!ok) break;
-          tc_fence_after_sync();
-          const uint32_t a_addr = smem_u32(s.tiles + p.stage * kStageBytes);
-          const uint64_t da = make_smem_desc(a_addr, 16, 1024);
-          const uint64_t db = make_smem_desc(a_addr + kABytes, 16, 1024);
-#pragma unroll
-          for (int k4 = 0; k4 < kBK / 16; ++k4)
-            mma_f16_ss(d_tmem, da + k4 * 2, db + k4 * 2, idesc, (kb | k4) != 0);
-          tc_commit(&s.empty[p.stage]);
-          p.advance<kStages1>();
-        }
-        if (ok) tc_commit(&s.acc_full[ab]);
-      }
-    }
-  } else {
-    // Epilogue: warp w may touch TMEM lanes [32*(w%4), 32*(w%4)+32).
-    const int q = warp & 3;
-    bool ok = true;
-    int it = 0;
-    for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++it) {
-      const int tr = tile % rt, tc = tile / rt;
-      const int ab = it & 1;
-      const uint32_t acc_phase = (it >> 1) & 1u;
-      ok = __all_sync(0xffffffffu, mbar_wait(&s.acc_full[ab], acc_phase, s.abort_flag, a.status, 14));
-      if (!ok) break;
-      tc_fence_after_sync();
-      const int row = tr * kBM + q * 32 + lane;       // row inside the row block
-      const bool row_ok = row < a.n_rows;
-      const int tile_col0 = a.col0 + tc * kBN1;       // column inside the shard
-      const int n_valid = min(kBN1, a.v_shard - tile_col0);  // >= 1 by construction
-      const uint32_t taddr = tmem + (static_cast<uint32_t>(q * 32) << 16) + ab * kBN1;
-      int label_local = -1;
-      if (row_ok) {
-        const long long tg = a.target[row];
-        const long long loc = tg - a.col_offset - tile_col0;
-        if (tg != kIgnore && loc >= 0 && loc < n_valid) label_local = (int)loc;
-      }
-      float m, sum, dot, lab;
-      int arg;
-      // E leaves through a per-warp staging box and a TMA store (rows past the buffer are clipped).
-      uint8_t* stage_warp = s.extra + (warp - 2) * 8192;
-      const int e_row0 = tr * kBM + q * 32;
-      if (a.debug & 1) {
-        m = 0.f; sum = 1.f; dot = 0.f; lab = 0.f; arg = 0;
-      } else if (n_valid == kBN1)
-        tile_statistics<true>(taddr, n_valid, label_local, a.write_e != 0, &map_e, stage_warp,
-                              tc * kBN1, e_row0, m, sum, dot, lab, arg, a.debug);
-      else
-        tile_statistics<false>(taddr, n_valid, label_local, a.write_e != 0, &map_e, stage_warp,
-                               tc * kBN1, e_row0, m, sum, dot, lab, arg, a.debug);
-      // the accumulator buffer is free again
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&s.acc_empty[ab]);
-      if (row_ok) {
-        a.tile_stats[(size_t)row * a.ct_stride + tc] =
-            make_float4(m, sum, dot, __int_as_float(tile_col0 + arg + a.col_offset));
-        if (label_local >= 0) a.label_logit[row] = lab;
-      }
-    }
-    if (lane == 0) tma_store_wait_read<0>();  // staging boxes fully read before shared memory goes away
-  }
-  finish_pipeline(s, warp, tmem);
-}
-
-// ------------------------------------------------------------------------------------------
-// CTA-pair variants (cta_group::2): the pair owns a 256-row tile, each CTA 128 rows of it, and the
-// B operand is split between the two CTAs, so every shared-memory stage holds half the B bytes of
-// the single-CTA kernel and the operand traffic through the crossbar per flop drops by a third.
-// ------------------------------------------------------------------------------------------
-constexpr int kBHalf1Bytes = (kBN1 / 2) * kBK * 2;   // 16 KB: this CTA's 128 vocabulary columns
-constexpr int kStagesP1 = 6;
-constexpr int kSmemP1 = kStagesP1 * (kABytes + kBHalf1Bytes) + kStageE + 1024 + 256;
-
 struct PairInit {
   uint32_t tmem;
   uint32_t rank;
@@ -415,12 +126,11 @@ struct PairInit {
 
 // Barrier set-up, tensor-memory allocation and the agreement of both CTAs on whether to run at all
 // (an earlier kernel of the call may have given up). Every thread of both CTAs calls this.
-template <int STAGES>
 __device__ __forceinline__ PairInit init_pair(const GemmSmem& s, int warp, int lane, const int* status) {
   PairInit r;
   r.rank = cluster_ctarank();
   if (warp == 0 && lane == 0) {
-    for (int i = 0; i < STAGES; ++i) { mbar_init(&s.full[i], 1); mbar_init(&s.empty[i], 1); }
+    for (int i = 0; i < kStages; ++i) { mbar_init(&s.full[i], 1); mbar_init(&s.empty[i], 1); }
     for (int i = 0; i < 2; ++i) { mbar_init(&s.acc_full[i], 1); mbar_init(&s.acc_empty[i], 8); }
     *s.abort_flag = *reinterpret_cast<const volatile int*>(status) != 0;
     fence_barrier_init();
@@ -447,6 +157,8 @@ __device__ __forceinline__ void finish_pair(const GemmSmem& s, int warp, uint32_
   tc_fence_before_sync();
   __syncthreads();
   if (*s.abort_flag) {
+    // A wait was abandoned: give copies that may still be in flight time to land before the
+    // shared memory is released.
     for (int i = 0; i < 64; ++i) __nanosleep(2000);
     __syncthreads();
   }
@@ -459,24 +171,224 @@ __device__ __forceinline__ void finish_pair(const GemmSmem& s, int warp, uint32_
   }
 }
 
+__device__ __forceinline__ void release_accumulator(const GemmSmem& s, int ab, uint32_t rank, int lane) {
+  tc_fence_before_sync();
+  __syncwarp();
+  if (lane == 0) {
+    if (rank == 0) mbar_arrive(&s.acc_empty[ab]);
+    else mbar_arrive_cluster(mapa_u32(smem_u32(&s.acc_empty[ab]), 0));
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// Logits kernel
+// ------------------------------------------------------------------------------------------
+struct LogitsArgs {
+  const int64_t* target;   // [n_rows] of this row block
+  const float* ref;        // [n_rows] running lse of the earlier chunks (modes POnly / Combined)
+  float4* tile_stats;      // [n_rows, ct_stride]
+                           //   TileMax : (tile max, sum exp(z - max), sum exp(z - max) z, argmax bits)
+                           //   Combined: (tile max, sum exp(z - ref), sum exp(z - ref) z, argmax bits)
+  float* label_logit;      // [n_rows]
+  int n_rows;              // rows in this row block
+  int row0;                // first row of the block inside the hidden matrix (TMA coordinate)
+  int k_dim;               // hidden size
+  int col0;                // first column of the chunk inside the weight shard
+  int v_shard;             // columns of the weight shard
+  int col_offset;          // global vocabulary index of shard column 0
+  int ct;                  // column tiles in this chunk
+  int ct_stride;           // row pitch of tile_stats
+  int mode;                // LogitsMode
+  int store_p;             // write P (gradient wanted)
+  int* status;
+};
+
+// First chunk, first launch: statistics of one 128 x 256 tile for one thread (= one row) against
+// the tile's own maximum. Two sweeps over the accumulator, 16 columns per tcgen05.ld with the next
+// load in flight while the current columns are consumed; loop bodies stay small enough for the
+// instruction cache.
+template <bool FULL>
+__device__ __noinline__ void tile_stats_tilemax(uint32_t taddr, int n_valid, int label_local,
+                                                float& m_out, float& sum_out, float& dot_out,
+                                                float& lab_out, int& arg_out) {
+  constexpr int kLoads = kBN / kEW;
+  uint32_t ra[kEW], rb[kEW];
+  float m = -INFINITY;
+  int arg = 0;
+  auto sweep_max = [&](const uint32_t (&r)[kEW], int col0) {
+#pragma unroll
+    for (int j = 0; j < kEW; ++j) {
+      const float z = __uint_as_float(r[j]);
+      const int col = col0 + j;
+      if ((FULL || col < n_valid) && z > m) { m = z; arg = col; }
+    }
+  };
+  tmem_ld_32x16(taddr, ra);
+#pragma unroll 1
+  for (int i = 0; i < kLoads; i += 2) {
+    tmem_ld_wait_on(ra);
+    tmem_ld_32x16(taddr + (i + 1) * kEW, rb);
+    sweep_max(ra, i * kEW);
+    tmem_ld_wait_on(rb);
+    if (i + 2 < kLoads) tmem_ld_32x16(taddr + (i + 2) * kEW, ra);
+    sweep_max(rb, (i + 1) * kEW);
+  }
+  const float bias = -m * kLog2e;
+  float s0 = 0.f, s1 = 0.f, d0 = 0.f, d1 = 0.f, lab = 0.f;
+  auto sweep_exp = [&](const uint32_t (&r)[kEW], int col0) {
+#pragma unroll
+    for (int j = 0; j < kEW; j += 2) {
+      const float z0 = __uint_as_float(r[j]), z1 = __uint_as_float(r[j + 1]);
+      const int col = col0 + j;
+      float e0 = exp2f(fmaf(z0, kLog2e, bias)), e1 = exp2f(fmaf(z1, kLog2e, bias));
+      if (!FULL) {
+        if (col >= n_valid) e0 = 0.f;
+        if (col + 1 >= n_valid) e1 = 0.f;
+      }
+      s0 += e0;
+      s1 += e1;
+      d0 = fmaf(e0, (FULL || col < n_valid) ? z0 : 0.f, d0);
+      d1 = fmaf(e1, (FULL || col + 1 < n_valid) ? z1 : 0.f, d1);
+    }
+    if (label_local >= col0 && label_local < col0 + kEW) {  // rare
+#pragma unroll
+      for (int j = 0; j < kEW; ++j)
+        if (col0 + j == label_local) lab = __uint_as_float(r[j]);
+    }
+  };
+  tmem_ld_32x16(taddr, ra);
+#pragma unroll 1
+  for (int i = 0; i < kLoads; i += 2) {
+    tmem_ld_wait_on(ra);
+    tmem_ld_32x16(taddr + (i + 1) * kEW, rb);
+    sweep_exp(ra, i * kEW);
+    tmem_ld_wait_on(rb);
+    if (i + 2 < kLoads) tmem_ld_32x16(taddr + (i + 2) * kEW, ra);
+    sweep_exp(rb, (i + 1) * kEW);
+  }
+  m_out = m;
+  sum_out = s0 + s1;
+  dot_out = d0 + d1;
+  lab_out = lab;
+  arg_out = arg;
+}
+
+// All other launches: one sweep against `ref`, the row's log-sum-exp over the earlier chunks.
+// e = exp(z - ref); with STATS the tile's sum e, sum e*z, maximum and first argmax; with store_p
+// P = bf16(e) leaves through the warp's swizzled staging boxes (32 rows x 64 columns, 16-byte piece
+// k of row r at piece k ^ (r & 7)) and one TMA store per box. `keep_mask` is 0 for rows without a
+// label (their gradient is zero) and the label's own column is zeroed: its term is added exactly,
+// in fp32, by the finish kernel.
+template <bool FULL, bool STATS>
+__device__ __noinline__ void tile_ref_pass(uint32_t taddr, int n_valid, int label_local, float ref,
+                                           uint32_t keep_mask, bool store_p, const CUtensorMap* map_p,
+                                           uint8_t* stage_warp, int p_col0, int p_row0, float& m_out,
+                                           float& sum_out, float& dot_out, float& lab_out,
+                                           int& arg_out) {
+  constexpr int kLoads = kBN / kEW;       // 16
+  constexpr int kPerBox = 64 / kEW;       // loads per 64-column staging box
+  const int lane = threadIdx.x & 31;
+  const int row_swz = lane & 7;
+  uint32_t ra[kEW], rb[kEW];
+  float m = -INFINITY, lab = 0.f;
+  int arg = 0;
+  float s0 = 0.f, s1 = 0.f, d0 = 0.f, d1 = 0.f;
+  const float bias = -ref * kLog2e;
+  auto sweep = [&](uint32_t (&r)[kEW], int col0, uint8_t* stage_row, int piece0) {
+    uint32_t packed[kEW / 2];
+    const bool has_label = label_local >= col0 && label_local < col0 + kEW;  // rare
+    if (has_label) {
+#pragma unroll
+      for (int j = 0; j < kEW; ++j)
+        if (col0 + j == label_local) lab = __uint_as_float(r[j]);
+    }
+#pragma unroll
+    for (int j = 0; j < kEW; j += 2) {
+      const float z0 = __uint_as_float(r[j]), z1 = __uint_as_float(r[j + 1]);
+      const int col = col0 + j;
+      float e0 = exp2f(fmaf(z0, kLog2e, bias)), e1 = exp2f(fmaf(z1, kLog2e, bias));
+      if (!FULL) {
+        if (col >= n_valid) e0 = 0.f;
+        if (col + 1 >= n_valid) e1 = 0.f;
+      }
+      if (STATS) {
+        if ((FULL || col < n_valid) && z0 > m) { m = z0; arg = col; }
+        if ((FULL || col + 1 < n_valid) && z1 > m) { m = z1; arg = col + 1; }
+        s0 += e0;
+        s1 += e1;
+        d0 = fmaf(e0, (FULL || col < n_valid) ? z0 : 0.f, d0);
+        d1 = fmaf(e1, (FULL || col + 1 < n_valid) ? z1 : 0.f, d1);
+      }
+      __nv_bfloat162 h = __floats2bfloat162_rn(e0, e1);
+      packed[j >> 1] = *reinterpret_cast<uint32_t*>(&h) & keep_mask;
+    }
+    if (has_label) {  // the label's own column carries no P
+#pragma unroll
+      for (int j = 0; j < kEW; ++j)
+        if (col0 + j == label_local) packed[j >> 1] &= (j & 1) ? 0x0000FFFFu : 0xFFFF0000u;
+    }
+    if (store_p) {
+#pragma unroll
+      for (int v = 0; v < kEW / 8; ++v) {
+        const int piece = (piece0 + v) ^ row_swz;
+        *reinterpret_cast<uint4*>(stage_row + piece * 16) =
+            make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+      }
+    }
+  };
+  tmem_ld_32x16(taddr, ra);
+#pragma unroll 1
+  for (int i = 0; i < kLoads; i += 2) {
+    // 64-column boxes alternate between the warp's two staging areas; the area used two boxes ago
+    // must have been read by its TMA store before it is overwritten.
+    const int box_id = i / kPerBox;
+    uint8_t* box = stage_warp + (box_id & 1) * 4096;
+    if (store_p && (i % kPerBox) == 0) {
+      if (lane == 0) tma_store_wait_read<1>();
+      __syncwarp();
+    }
+    uint8_t* stage_row = box + lane * 128;
+    tmem_ld_wait_on(ra);
+    tmem_ld_32x16(taddr + (i + 1) * kEW, rb);
+    sweep(ra, i * kEW, stage_row, (i % kPerBox) * (kEW / 8));
+    tmem_ld_wait_on(rb);
+    if (i + 2 < kLoads) tmem_ld_32x16(taddr + (i + 2) * kEW, ra);
+    sweep(rb, (i + 1) * kEW, stage_row, ((i + 1) % kPerBox) * (kEW / 8));
+    if (store_p && ((i + 2) % kPerBox) == 0) {
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        tma_store_2d(map_p, box, p_col0 + box_id * 64, p_row0);
+        tma_store_commit();
+      }
+    }
+  }
+  m_out = m;
+  sum_out = s0 + s1;
+  dot_out = d0 + d1;
+  lab_out = lab;
+  arg_out = arg;
+}
+
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreadsGemm, 1)
-lmhead_logits_pair_kernel(const __grid_constant__ CUtensorMap map_h,
-                          const __grid_constant__ CUtensorMap map_w,
-                          const __grid_constant__ CUtensorMap map_e, const LogitsArgs a) {
+lmhead_logits_kernel(const __grid_constant__ CUtensorMap map_h,
+                     const __grid_constant__ CUtensorMap map_w,
+                     const __grid_constant__ CUtensorMap map_p, const LogitsArgs a) {
   extern __shared__ uint8_t smem_raw[];
-  constexpr int kStageBytes = kABytes + kBHalf1Bytes;
-  const GemmSmem s = carve_smem<kStagesP1, kStageBytes, kStageE>(smem_raw);
+  const GemmSmem s = carve_smem<kStageP>(smem_raw);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (warp == 0 && lane == 0) {
     prefetch_tensormap(&map_h);
     prefetch_tensormap(&map_w);
-    prefetch_tensormap(&map_e);
+    prefetch_tensormap(&map_p);
   }
-  const PairInit pi = init_pair<kStagesP1>(s, warp, lane, a.status);
+  const PairInit pi = init_pair(s, warp, lane, a.status);
   if (!pi.run) return;
   const uint32_t tmem = pi.tmem, rank = pi.rank;
   const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
 
+  // Tiles are ordered row-tile-fastest: the row tiles that share a weight tile run together, so
+  // the weight streams from HBM once.
   const int rt = (a.n_rows + 2 * kBM - 1) / (2 * kBM);   // 256-row tiles
   const int n_tiles = rt * a.ct;
   const int n_kb = (a.k_dim + kBK - 1) / kBK;
@@ -488,9 +400,9 @@ lmhead_logits_pair_kernel(const __grid_constant__ CUtensorMap map_h,
       for (int tile = pair; tile < n_tiles && ok; tile += n_pairs) {
         const int tr = tile % rt, tc = tile / rt;
         const int row0 = a.row0 + tr * 2 * kBM + (int)rank * kBM;
-        const int col0 = a.col0 + tc * kBN1 + (int)rank * (kBN1 / 2);
+        const int col0 = a.col0 + tc * kBN + (int)rank * (kBN / 2);
         for (int kb = 0; kb < n_kb; ++kb) {
-          ok = mbar_wait(&s.empty[p.stage], p.phase ^ 1u, s.abort_flag, a.status, 31);
+          ok = mbar_wait(&s.empty[p.stage], p.phase ^ 1u, s.abort_flag, a.status, 11);
           if (!ok) break;
           uint8_t* st = s.tiles + p.stage * kStageBytes;
           // both CTAs' bytes are counted on the leader's barrier
@@ -498,25 +410,25 @@ lmhead_logits_pair_kernel(const __grid_constant__ CUtensorMap map_h,
           if (rank == 0) mbar_expect_tx(&s.full[p.stage], 2 * kStageBytes);
           tma_load_2d_pair(st, &map_h, kb * kBK, row0, full_leader);
           tma_load_2d_pair(st + kABytes, &map_w, kb * kBK, col0, full_leader);
-          p.advance<kStagesP1>();
+          p.advance();
         }
       }
     }
   } else if (warp == 1) {
     if (lane == 0 && rank == 0) {
-      constexpr uint32_t idesc = make_idesc_f16(2 * kBM, kBN1, false, false);
+      constexpr uint32_t idesc = make_idesc_f16(2 * kBM, kBN, kFmtF16, kFmtF16, false, false);
       PipeState p;
       bool ok = true;
       int it = 0;
       for (int tile = pair; tile < n_tiles && ok; tile += n_pairs, ++it) {
         const int ab = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1u;
-        ok = mbar_wait(&s.acc_empty[ab], acc_phase ^ 1u, s.abort_flag, a.status, 32);
+        ok = mbar_wait(&s.acc_empty[ab], acc_phase ^ 1u, s.abort_flag, a.status, 12);
         if (!ok) break;
         tc_fence_after_sync();
-        const uint32_t d_tmem = tmem + ab * kBN1;
+        const uint32_t d_tmem = tmem + ab * kBN;
         for (int kb = 0; kb < n_kb; ++kb) {
-          ok = mbar_wait(&s.full[p.stage], p.phase, s.abort_flag, a.status, 33);
+          ok = mbar_wait(&s.full[p.stage], p.phase, s.abort_flag, a.status, 13);
           if (!ok) break;
           tc_fence_after_sync();
           const uint32_t a_addr = smem_u32(s.tiles + p.stage * kStageBytes);
@@ -526,381 +438,217 @@ lmhead_logits_pair_kernel(const __grid_constant__ CUtensorMap map_h,
           for (int k4 = 0; k4 < kBK / 16; ++k4)
             mma_f16_ss_pair(d_tmem, da + k4 * 2, db + k4 * 2, idesc, (kb | k4) != 0);
           tc_commit_pair(&s.empty[p.stage], 3);   // frees the stage in both CTAs
-          p.advance<kStagesP1>();
+          p.advance();
         }
         if (ok) tc_commit_pair(&s.acc_full[ab], 3);
       }
     }
   } else {
+    // Epilogue: warp w may touch TMEM lanes [32*(w%4), 32*(w%4)+32).
     const int q = warp & 3;
+    uint8_t* stage_warp = s.extra + (warp - 2) * 8192;
     bool ok = true;
     int it = 0;
     for (int tile = pair; tile < n_tiles && ok; tile += n_pairs, ++it) {
       const int tr = tile % rt, tc = tile / rt;
       const int ab = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1u;
-      ok = __all_sync(0xffffffffu, mbar_wait(&s.acc_full[ab], acc_phase, s.abort_flag, a.status, 34));
+      ok = __all_sync(0xffffffffu, mbar_wait(&s.acc_full[ab], acc_phase, s.abort_flag, a.status, 14));
       if (!ok) break;
       tc_fence_after_sync();
-      const int e_row0 = tr * 2 * kBM + (int)rank * kBM + q * 32;
-      const int row = e_row0 + lane;
+      const int p_row0 = tr * 2 * kBM + (int)rank * kBM + q * 32;   // row inside the row block
+      const int row = p_row0 + lane;
       const bool row_ok = row < a.n_rows;
-      const int tile_col0 = a.col0 + tc * kBN1;
-      const int n_valid = min(kBN1, a.v_shard - tile_col0);
-      const uint32_t taddr = tmem + (static_cast<uint32_t>(q * 32) << 16) + ab * kBN1;
+      const int tile_col0 = a.col0 + tc * kBN;                      // column inside the shard
+      const int n_valid = min(kBN, a.v_shard - tile_col0);          // >= 1 by construction
+      const uint32_t taddr = tmem + (static_cast<uint32_t>(q * 32) << 16) + ab * kBN;
       int label_local = -1;
+      bool labelled = false;
+      float ref = 0.f;
       if (row_ok) {
         const long long tg = a.target[row];
+        labelled = tg != kIgnore;
         const long long loc = tg - a.col_offset - tile_col0;
-        if (tg != kIgnore && loc >= 0 && loc < n_valid) label_local = (int)loc;
+        if (labelled && loc >= 0 && loc < n_valid) label_local = (int)loc;
+        if (a.mode != kModeTileMax) ref = a.ref[row];
       }
+      const uint32_t keep_mask = labelled ? 0xFFFFFFFFu : 0u;
       float m, sum, dot, lab;
       int arg;
-      uint8_t* stage_warp = s.extra + (warp - 2) * 8192;
-      if (a.debug & 1) {
-        m = 0.f; sum = 1.f; dot = 0.f; lab = 0.f; arg = 0;
-      } else if (n_valid == kBN1)
-        tile_statistics<true>(taddr, n_valid, label_local, a.write_e != 0, &map_e, stage_warp,
-                              tc * kBN1, e_row0, m, sum, dot, lab, arg, a.debug);
-      else
-        tile_statistics<false>(taddr, n_valid, label_local, a.write_e != 0, &map_e, stage_warp,
-                               tc * kBN1, e_row0, m, sum, dot, lab, arg, a.debug);
-      // the accumulator buffer of this CTA is free again: tell the leader's MMA thread
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) {
-        if (rank == 0) mbar_arrive(&s.acc_empty[ab]);
-        else mbar_arrive_cluster(mapa_u32(smem_u32(&s.acc_empty[ab]), 0));
+      const bool full = n_valid == kBN;
+      if (a.mode == kModeTileMax) {
+        if (full) tile_stats_tilemax<true>(taddr, n_valid, label_local, m, sum, dot, lab, arg);
+        else tile_stats_tilemax<false>(taddr, n_valid, label_local, m, sum, dot, lab, arg);
+      } else if (a.mode == kModeCombined) {
+        if (full)
+          tile_ref_pass<true, true>(taddr, n_valid, label_local, ref, keep_mask, a.store_p != 0,
+                                    &map_p, stage_warp, tc * kBN, p_row0, m, sum, dot, lab, arg);
+        else
+          tile_ref_pass<false, true>(taddr, n_valid, label_local, ref, keep_mask, a.store_p != 0,
+                                     &map_p, stage_warp, tc * kBN, p_row0, m, sum, dot, lab, arg);
+      } else {
+        if (full)
+          tile_ref_pass<true, false>(taddr, n_valid, label_local, ref, keep_mask, true, &map_p,
+                                     stage_warp, tc * kBN, p_row0, m, sum, dot, lab, arg);
+        else
+          tile_ref_pass<false, false>(taddr, n_valid, label_local, ref, keep_mask, true, &map_p,
+                                      stage_warp, tc * kBN, p_row0, m, sum, dot, lab, arg);
       }
-      if (row_ok) {
+      release_accumulator(s, ab, rank, lane);
+      if (row_ok && a.mode != kModePOnly) {
         a.tile_stats[(size_t)row * a.ct_stride + tc] =
             make_float4(m, sum, dot, __int_as_float(tile_col0 + arg + a.col_offset));
         if (label_local >= 0) a.label_logit[row] = lab;
       }
     }
-    if (lane == 0) tma_store_wait_read<0>();
+    if (lane == 0) tma_store_wait_read<0>();  // staging boxes fully read before shared memory goes away
   }
   finish_pair(s, warp, tmem);
 }
 
 // ------------------------------------------------------------------------------------------
-// Row kernel: one warp per row. Merges the chunk's tile statistics into the running state and
-// rescales E to P in place.
+// Row kernel: one warp per row merges the chunk's tile statistics into the running state.
+// The state is kept normalised: run_max = log-sum-exp so far, run_sum = 1, run_dot = sum of
+// softmax-so-far * z. For the gradient it also maintains `base` (the lse dH is relative to) and
+// writes the row's multiplier for this chunk's contribution.
 // ------------------------------------------------------------------------------------------
 struct RowArgs {
-  const int64_t* target;
-  __half* e_buf;
   const float4* tile_stats;
   float* run_max;
   float* run_sum;
   float* run_dot;
   int* best;
-  const float* label_logit;
-  float* label_lse;
-  float* factor;
+  float* best_val;  // [n_rows] largest logit so far (the state itself carries the lse, not the max)
+  float* base;      // [n_rows] lse that dH is relative to (set by the first chunk)
+  float* mult;      // [n_rows] out: exp(ref - base) for the gradient kernel of this chunk
+  float* dh;        // nullable: [n_rows, k_dim], touched only when a row is rebased
   int n_rows;
-  int col0;         // first shard column of the chunk
-  int v_shard;
-  int col_offset;
+  int k_dim;
   int ct;
   int ct_stride;
-  int ld_e;
-  int write_p;
-  float* dh;        // nullable: [n_rows, k_dim] gradient to rescale by this chunk's factor
-  int k_dim;
-  int first;        // first chunk: nothing accumulated yet
+  int mode;         // kModeTileMax (first chunk) or kModeCombined
+  int want_grad;
+  int* status;
 };
 
-constexpr int kRowWarps = 4;          // warps per row in the row kernel
-constexpr int kRowTilesPerWarp = 16;  // register-resident tiles per warp per pass
-
-__global__ void __launch_bounds__(kRowWarps * 32) lmhead_row_kernel(const RowArgs a) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int row = blockIdx.x;
-  // Every warp merges the (at most a few dozen) tile statistics itself: cheaper than a block-wide
-  // exchange, and all warps then hold the same running state and log-sum-exp.
-  const float prev_max = a.run_max[row], prev_sum = a.run_sum[row];
-  float run_max = prev_max, run_sum = prev_sum, run_dot = a.run_dot[row];
+__global__ void __launch_bounds__(256) lmhead_row_kernel(const RowArgs a) {
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= a.n_rows) return;
+  const float ref = a.run_max[row];   // lse so far (-inf before the first chunk)
+  float run_dot = a.run_dot[row];
   int best = a.best[row];
-  // Tiles in ascending column order, so a later tile wins the argmax only if strictly larger.
-  for (int t0 = 0; t0 < a.ct; t0 += 32) {
-    const int t = t0 + lane;
-    float4 st = make_float4(-INFINITY, 0.f, 0.f, 0.f);
-    if (t < a.ct) st = a.tile_stats[(size_t)row * a.ct_stride + t];
-    float gmax = st.x;
+  float best_val = a.mode == kModeTileMax ? -INFINITY : a.best_val[row];
+  float new_lse, new_dot;
+  if (a.mode == kModeTileMax) {
+    // statistics relative to each tile's own maximum: log-sum-exp merge
+    float run_max = -INFINITY, run_sum = 0.f;
+    run_dot = 0.f;
+    for (int t0 = 0; t0 < a.ct; t0 += 32) {
+      const int t = t0 + lane;
+      float4 st = make_float4(-INFINITY, 0.f, 0.f, 0.f);
+      if (t < a.ct) st = a.tile_stats[(size_t)row * a.ct_stride + t];
+      float gmax = st.x;
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) gmax = fmaxf(gmax, __shfl_xor_sync(0xffffffffu, gmax, o));
-    const unsigned holders = __ballot_sync(0xffffffffu, st.x == gmax);
-    const int first = __ffs(holders) - 1;  // first lane (lowest tile) that holds the maximum
-    const int cand = __shfl_sync(0xffffffffu, __float_as_int(st.w), first);
-    if (gmax > run_max) best = cand;
-    const float new_max = fmaxf(run_max, gmax);
-    const float w = t < a.ct ? exp2f((st.x - new_max) * kLog2e) : 0.f;
-    const float part_sum = warp_sum(st.y * w);
-    const float part_dot = warp_sum(st.z * w);
-    const float rescale = exp2f((run_max - new_max) * kLog2e);  // exp(-inf) = 0 on the first chunk
-    run_sum = run_sum * rescale + part_sum;
-    run_dot = run_dot * rescale + part_dot;
-    run_max = new_max;
+      for (int o = 16; o > 0; o >>= 1) gmax = fmaxf(gmax, __shfl_xor_sync(0xffffffffu, gmax, o));
+      const unsigned holders = __ballot_sync(0xffffffffu, st.x == gmax);
+      const int first = __ffs(holders) - 1;  // lowest tile that holds the maximum
+      const int cand = __shfl_sync(0xffffffffu, __float_as_int(st.w), first);
+      if (gmax > best_val) { best_val = gmax; best = cand; }
+      const float new_max = fmaxf(run_max, gmax);
+      const float w = t < a.ct ? exp2f((st.x - new_max) * kLog2e) : 0.f;
+      const float part_sum = warp_sum(st.y * w);
+      const float part_dot = warp_sum(st.z * w);
+      const float rescale = exp2f((run_max - new_max) * kLog2e);  // exp(-inf) = 0 at the start
+      run_sum = run_sum * rescale + part_sum;
+      run_dot = run_dot * rescale + part_dot;
+      run_max = new_max;
+    }
+    new_lse = run_max + logf(run_sum);
+    new_dot = run_dot / run_sum;
+  } else {
+    // statistics relative to ref: the mass so far is exp(ref) * 1
+    float add_sum = 0.f, add_dot = 0.f;
+    for (int t0 = 0; t0 < a.ct; t0 += 32) {
+      const int t = t0 + lane;
+      float4 st = make_float4(-INFINITY, 0.f, 0.f, 0.f);
+      if (t < a.ct) st = a.tile_stats[(size_t)row * a.ct_stride + t];
+      float gmax = st.x;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) gmax = fmaxf(gmax, __shfl_xor_sync(0xffffffffu, gmax, o));
+      const unsigned holders = __ballot_sync(0xffffffffu, st.x == gmax);
+      const int first = __ffs(holders) - 1;
+      const int cand = __shfl_sync(0xffffffffu, __float_as_int(st.w), first);
+      if (gmax > best_val) { best_val = gmax; best = cand; }  // later tiles win only if larger
+      add_sum += warp_sum(st.y);
+      add_dot += warp_sum(st.z);
+    }
+    const float total = 1.0f + add_sum;
+    new_lse = ref + logf(total);
+    new_dot = (run_dot + add_dot) / total;
+    if (!(total < INFINITY) && lane == 0) atomicCAS(a.status, 0, 90);  // exp(z - ref) overflowed
   }
-  const float lse = run_max + logf(run_sum);
-  const float fac = expf(prev_max + logf(prev_sum) - lse);  // exp(-inf) = 0 on the first chunk
-  const long long tg = a.target[row];
-  const bool labelled = tg != kIgnore;
-  const long long local = tg - a.col_offset - a.col0;  // column inside this chunk
-  const bool hit = labelled && local >= 0 && local < (long long)a.ct * kBN1 &&
-                   a.col0 + local < a.v_shard;
-  // All state of the previous chunk has been read by every warp before anyone overwrites it.
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    a.run_max[row] = run_max;
-    a.run_sum[row] = run_sum;
-    a.run_dot[row] = run_dot;
+  float mult = 1.0f;
+  if (a.want_grad) {
+    if (a.mode == kModeTileMax) {
+      if (lane == 0) a.base[row] = new_lse;   // the first chunk's P is written against this lse
+    } else {
+      float base = a.base[row];
+      if (ref - base > kRebase) {
+        // rare: the multiplier exp(ref - base) is getting large; bring dH of this row to ref
+        const float down = expf(base - ref);
+        for (int i = lane; i < a.k_dim; i += 32) a.dh[(size_t)row * a.k_dim + i] *= down;
+        base = ref;
+        __syncwarp();
+        if (lane == 0) a.base[row] = base;
+      }
+      mult = expf(ref - base);
+    }
+  }
+  if (lane == 0) {
+    a.run_max[row] = new_lse;
+    a.run_sum[row] = 1.0f;
+    a.run_dot[row] = new_dot;
     a.best[row] = best;
-    if (a.write_p) {
-      a.factor[row] = fac;
-      if (hit) a.label_lse[row] = lse;
-    }
-  }
-  if (!a.write_p) return;
-  if (a.dh && !a.first) {  // rescale what is accumulated to the new log-sum-exp
-    float4* g = reinterpret_cast<float4*>(a.dh + (size_t)row * a.k_dim);
-    const int n4 = a.k_dim >> 2;
-    for (int i0 = threadIdx.x; i0 < n4; i0 += 4 * blockDim.x) {
-      float4 v[4];
-#pragma unroll
-      for (int u = 0; u < 4; ++u)
-        if (i0 + u * blockDim.x < n4) v[u] = g[i0 + u * blockDim.x];
-#pragma unroll
-      for (int u = 0; u < 4; ++u)
-        if (i0 + u * blockDim.x < n4) {
-          v[u].x *= fac; v[u].y *= fac; v[u].z *= fac; v[u].w *= fac;
-          g[i0 + u * blockDim.x] = v[u];
-        }
-    }
-    for (int i = (a.k_dim & ~3) + threadIdx.x; i < a.k_dim; i += blockDim.x)
-      a.dh[(size_t)row * a.k_dim + i] *= fac;
-  }
-  // P = 1024 * exp(z - lse) = E * 2^-14 * 1024 * exp(tile_max - lse); zero for unlabelled rows.
-  // Warp w owns tiles w, w + 4, ...; their loads are all issued before the first store.
-  __half* e_row = a.e_buf + (size_t)row * a.ld_e;
-  for (int tb = warp; tb < a.ct; tb += kRowWarps * kRowTilesPerWarp) {
-    uint4 v[kRowTilesPerWarp];
-    float scale[kRowTilesPerWarp];
-#pragma unroll
-    for (int u = 0; u < kRowTilesPerWarp; ++u) {
-      const int t = tb + u * kRowWarps;
-      if (t < a.ct) {
-        v[u] = *(reinterpret_cast<const uint4*>(e_row + t * kBN1) + lane);
-        const float tmax = a.tile_stats[(size_t)row * a.ct_stride + t].x;
-        scale[u] = labelled ? (kGradScale / kEScale) * exp2f((tmax - lse) * kLog2e) : 0.f;
-      }
-    }
-#pragma unroll
-    for (int u = 0; u < kRowTilesPerWarp; ++u) {
-      const int t = tb + u * kRowWarps;
-      if (t < a.ct) {
-        uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          float2 f = __half22float2(*reinterpret_cast<__half2*>(&w[k]));
-          __half2 h = __floats2half2_rn(f.x * scale[u], f.y * scale[u]);
-          w[k] = *reinterpret_cast<uint32_t*>(&h);
-        }
-        *(reinterpret_cast<uint4*>(e_row + t * kBN1) + lane) = make_uint4(w[0], w[1], w[2], w[3]);
-      }
-    }
-  }
-  if (hit) {  // uniform over the CTA (one row per CTA)
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      // The label's entry carries p - 1, formed in fp32 and rounded once.
-      const float p = expf(a.label_logit[row] - lse);
-      e_row[local] = __float2half_rn((p - 1.0f) * kGradScale);
-    }
+    a.best_val[row] = best_val;
+    if (a.want_grad) a.mult[row] = mult;
   }
 }
 
 // ------------------------------------------------------------------------------------------
-// Gradient kernel: dH[rows, K] = factor * dH + P[rows, cols] * W[cols, K] for one chunk.
+// Gradient kernel: dH[rows, K] += mult[row] * P[rows, cols] * W[cols, K] for one chunk. A pair owns
+// a 256-row x 256-hidden-column output tile; a work unit is (tile, K split). The epilogue transposes
+// each 32 x 32 block of the accumulator through shared memory so that dH is touched in full
+// 128-byte rows.
 // ------------------------------------------------------------------------------------------
 struct GradArgs {
-  float* dh;            // [n_rows, k_dim] fp32 of this row block
-  const float* factor;  // [n_rows]
+  float* dh;            // [n_rows, k_dim] fp32 of this row block, zeroed before the first chunk
+  const float* mult;    // [n_rows]
   int n_rows;
   int k_dim;            // hidden size (output columns)
   int col0;             // first shard column of the chunk (TMA row coordinate into W)
   int n_kb;             // 64-column blocks of the chunk
-  int first;            // first chunk: overwrite instead of accumulate
-  int ksplit;           // pair kernel: K (vocabulary) splits per output tile, partial sums added with RED
-  int debug;            // bit 5: skip the epilogue's global traffic (timing experiments only)
+  int ksplit;           // K (vocabulary) splits per output tile
   int* status;
 };
 
-__global__ void __launch_bounds__(kThreadsGemm, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreadsGemm, 1)
 lmhead_grad_kernel(const __grid_constant__ CUtensorMap map_p,
                    const __grid_constant__ CUtensorMap map_w, const GradArgs a) {
   extern __shared__ uint8_t smem_raw[];
-  if (*reinterpret_cast<volatile int*>(a.status) != 0) return;  // an earlier kernel gave up
-  constexpr int kStageBytes = kABytes + kB2Bytes;
-  const GemmSmem s = carve_smem<kStages2, kStageBytes>(smem_raw);
+  const GemmSmem s = carve_smem<kStageT>(smem_raw);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (warp == 0 && lane == 0) { prefetch_tensormap(&map_p); prefetch_tensormap(&map_w); }
-  init_pipeline<kStages2>(s, warp, lane);
-  const uint32_t tmem = *s.tmem_base;
-
-  const int rt = (a.n_rows + kBM - 1) / kBM;
-  const int nt = (a.k_dim + kBN2 - 1) / kBN2;
-  const int n_tiles = rt * nt;
-
-  if (warp == 0) {
-    if (lane == 0) {
-      PipeState p;
-      bool ok = true;
-      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-        const int tr = tile % rt, tn = tile / rt;
-        for (int kb = 0; kb < a.n_kb; ++kb) {
-          ok = mbar_wait(&s.empty[p.stage], p.phase ^ 1u, s.abort_flag, a.status, 21);
-          if (!ok) break;
-          uint8_t* st = s.tiles + p.stage * kStageBytes;
-          mbar_expect_tx(&s.full[p.stage], kStageBytes);
-          tma_load_2d(st, &map_p, kb * kBK, tr * kBM, &s.full[p.stage]);
-#pragma unroll
-          for (int j = 0; j < kBN2 / 64; ++j)
-            tma_load_2d(st + kABytes + j * (kBK * 128), &map_w, tn * kBN2 + j * 64,
-                        a.col0 + kb * kBK, &s.full[p.stage]);
-          p.advance<kStages2>();
-        }
-      }
-    }
-  } else if (warp == 1) {
-    if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc_f16(kBM, kBN2, false, true);
-      PipeState p;
-      bool ok = true;
-      int it = 0;
-      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++it) {
-        const int ab = it & 1;
-        const uint32_t acc_phase = (it >> 1) & 1u;
-        ok = mbar_wait(&s.acc_empty[ab], acc_phase ^ 1u, s.abort_flag, a.status, 22);
-        if (!ok) break;
-        tc_fence_after_sync();
-        const uint32_t d_tmem = tmem + ab * 256;
-        for (int kb = 0; kb < a.n_kb; ++kb) {
-          ok = mbar_wait(&s.full[p.stage], p.phase, s.abort_flag, a.status, 23);
-          if (!ok) break;
-          tc_fence_after_sync();
-          const uint32_t a_addr = smem_u32(s.tiles + p.stage * kStageBytes);
-          const uint64_t da = make_smem_desc(a_addr, 16, 1024);
-          // MN-major B: 64-column groups are kBK*128 bytes apart (leading offset), 8-k groups
-          // 1024 bytes apart (stride offset); one MMA consumes 16 k = 2048 bytes.
-          const uint64_t db = make_smem_desc(a_addr + kABytes, kBK * 128, 1024);
-#pragma unroll
-          for (int k4 = 0; k4 < kBK / 16; ++k4)
-            mma_f16_ss(d_tmem, da + k4 * 2, db + k4 * (2048 >> 4), idesc, (kb | k4) != 0);
-          tc_commit(&s.empty[p.stage]);
-          p.advance<kStages2>();
-        }
-        if (ok) tc_commit(&s.acc_full[ab]);
-      }
-    }
-  } else {
-    const int q = warp & 3;
-    bool ok = true;
-    int it = 0;
-    for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++it) {
-      const int tr = tile % rt, tn = tile / rt;
-      const int ab = it & 1;
-      const uint32_t acc_phase = (it >> 1) & 1u;
-      ok = __all_sync(0xffffffffu, mbar_wait(&s.acc_full[ab], acc_phase, s.abort_flag, a.status, 24));
-      if (!ok) break;
-      tc_fence_after_sync();
-      const int row = tr * kBM + q * 32 + lane;
-      const bool row_ok = row < a.n_rows;
-      const float fac = (row_ok && !a.first) ? a.factor[row] : 0.f;
-      const uint32_t taddr = tmem + (static_cast<uint32_t>(q * 32) << 16) + ab * 256;
-      float* out_row = a.dh + (size_t)row * a.k_dim + tn * kBN2;
-      const int n_valid = min(kBN2, a.k_dim - tn * kBN2);
-#pragma unroll 1
-      for (int c = 0; c < kBN2 / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(taddr + c * 32, r);
-        tmem_ld_wait();
-        if (row_ok && !(a.debug & 32)) {
-#pragma unroll
-          for (int j = 0; j < 32; j += 4) {
-            const int col = c * 32 + j;
-            if (col + 3 < n_valid) {
-              float4* dst = reinterpret_cast<float4*>(out_row + col);
-              float4 o = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
-                                     __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-              if (!a.first) {
-                const float4 old = *dst;
-                o.x = fmaf(old.x, fac, o.x); o.y = fmaf(old.y, fac, o.y);
-                o.z = fmaf(old.z, fac, o.z); o.w = fmaf(old.w, fac, o.w);
-              }
-              *dst = o;
-            } else {
-              for (int u = 0; u < 4; ++u)
-                if (col + u < n_valid) {
-                  const float acc = __uint_as_float(r[j + u]);
-                  out_row[col + u] = a.first ? acc : fmaf(out_row[col + u], fac, acc);
-                }
-            }
-          }
-        }
-      }
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&s.acc_empty[ab]);
-    }
-  }
-  finish_pipeline(s, warp, tmem);
-}
-
-// ------------------------------------------------------------------------------------------
-// Gradient kernel, CTA pairs: the pair owns 256 rows x 192 hidden columns; each CTA loads its 128
-// rows of P and 96 of the 192 weight columns (three 32-column boxes, 64-byte swizzle, MN-major).
-// 8 x 8 = 64 pair tiles cover [2048, 1536]. The epilogue transposes each 32 x 32 block of the
-// accumulator through shared memory so that dH is read and written in full 128-byte rows.
-// ------------------------------------------------------------------------------------------
-constexpr int kStageT = 4 * 32 * 33 * 4;             // per epilogue warp a padded 32 x 32 fp32 block
-
-// BN = hidden columns per pair tile, SWZ = swizzle width in bytes of the B boxes (64 or 128; the
-// half of BN one CTA holds must be a whole number of SWZ/2-column boxes).
-template <int BN, int SWZ>
-struct GradPairCfg {
-  static constexpr int kBoxCols = SWZ / 2;
-  static constexpr int kBoxes = BN / 2 / kBoxCols;
-  static constexpr int kBoxBytes = kBK * SWZ;
-  static constexpr int kBHalfBytes = kBoxes * kBoxBytes;
-  static constexpr int kStageBytes = kABytes + kBHalfBytes;
-  static constexpr int kStages = (200 * 1024) / kStageBytes;
-  static constexpr int kSmem = kStages * kStageBytes + kStageT + 1024 + 256;
-  static_assert(kBoxes * kBoxCols * 2 == BN, "half tile must be whole boxes");
-  static_assert(kStageBytes % 1024 == 0, "stages must keep 1024-byte alignment");
-};
-
-template <int BN, int SWZ>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreadsGemm, 1)
-lmhead_grad_pair_kernel(const __grid_constant__ CUtensorMap map_p,
-                        const __grid_constant__ CUtensorMap map_w, const GradArgs a) {
-  using Cfg = GradPairCfg<BN, SWZ>;
-  extern __shared__ uint8_t smem_raw[];
-  constexpr int kStageBytes = Cfg::kStageBytes;
-  constexpr int kStages = Cfg::kStages;
-  const GemmSmem s = carve_smem<kStages, kStageBytes, kStageT>(smem_raw);
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  if (warp == 0 && lane == 0) { prefetch_tensormap(&map_p); prefetch_tensormap(&map_w); }
-  const PairInit pi = init_pair<kStages>(s, warp, lane, a.status);
+  const PairInit pi = init_pair(s, warp, lane, a.status);
   if (!pi.run) return;
   const uint32_t tmem = pi.tmem, rank = pi.rank;
   const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
 
   const int rt = (a.n_rows + 2 * kBM - 1) / (2 * kBM);
-  const int nt = (a.k_dim + BN - 1) / BN;
+  const int nt = (a.k_dim + kBN - 1) / kBN;
   const int n_tiles = rt * nt;
-  const int n_units = n_tiles * a.ksplit;   // unit = (output tile, K split)
+  const int n_units = n_tiles * a.ksplit;
+  constexpr int kBoxBytes = kBK * 128;   // one 64-column x 64-k box of W
 
   if (warp == 0) {
     if (lane == 0) {
@@ -910,26 +658,28 @@ lmhead_grad_pair_kernel(const __grid_constant__ CUtensorMap map_p,
         const int tile = unit % n_tiles, ks = unit / n_tiles;
         const int tr = tile % rt, tn = tile / rt;
         const int row0 = tr * 2 * kBM + (int)rank * kBM;
-        const int hcol0 = tn * BN + (int)rank * (BN / 2);
+        const int hcol0 = tn * kBN + (int)rank * (kBN / 2);
         const int kb_end = (a.n_kb * (ks + 1)) / a.ksplit;
         for (int kb = (a.n_kb * ks) / a.ksplit; kb < kb_end; ++kb) {
-          ok = mbar_wait(&s.empty[p.stage], p.phase ^ 1u, s.abort_flag, a.status, 41);
+          ok = mbar_wait(&s.empty[p.stage], p.phase ^ 1u, s.abort_flag, a.status, 21);
           if (!ok) break;
           uint8_t* st = s.tiles + p.stage * kStageBytes;
           const uint32_t full_leader = mapa_u32(smem_u32(&s.full[p.stage]), 0);
           if (rank == 0) mbar_expect_tx(&s.full[p.stage], 2 * kStageBytes);
           tma_load_2d_pair(st, &map_p, kb * kBK, row0, full_leader);
 #pragma unroll
-          for (int j = 0; j < Cfg::kBoxes; ++j)
-            tma_load_2d_pair(st + kABytes + j * Cfg::kBoxBytes, &map_w, hcol0 + j * Cfg::kBoxCols,
-                             a.col0 + kb * kBK, full_leader);
-          p.template advance<kStages>();
+          for (int j = 0; j < kBN / 2 / 64; ++j)
+            tma_load_2d_pair(st + kABytes + j * kBoxBytes, &map_w, hcol0 + j * 64, a.col0 + kb * kBK,
+                             full_leader);
+          p.advance();
         }
       }
     }
   } else if (warp == 1) {
     if (lane == 0 && rank == 0) {
-      constexpr uint32_t idesc = make_idesc_f16(2 * kBM, BN, false, true);
+      // A = P (K-major) and B = W (MN-major), both bf16: kind::f16 wants one element format for
+      // both operands (a bf16 A with an fp16 B raises an illegal-instruction fault).
+      constexpr uint32_t idesc = make_idesc_f16(2 * kBM, kBN, kFmtBF16, kFmtBF16, false, true);
       PipeState p;
       bool ok = true;
       int it = 0;
@@ -937,27 +687,26 @@ lmhead_grad_pair_kernel(const __grid_constant__ CUtensorMap map_p,
         const int ks = unit / n_tiles;
         const int ab = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1u;
-        ok = mbar_wait(&s.acc_empty[ab], acc_phase ^ 1u, s.abort_flag, a.status, 42);
+        ok = mbar_wait(&s.acc_empty[ab], acc_phase ^ 1u, s.abort_flag, a.status, 22);
         if (!ok) break;
         tc_fence_after_sync();
-        const uint32_t d_tmem = tmem + ab * 256;
+        const uint32_t d_tmem = tmem + ab * kBN;
         const int kb_begin = (a.n_kb * ks) / a.ksplit, kb_end = (a.n_kb * (ks + 1)) / a.ksplit;
         for (int kb = kb_begin; kb < kb_end; ++kb) {
-          ok = mbar_wait(&s.full[p.stage], p.phase, s.abort_flag, a.status, 43);
+          ok = mbar_wait(&s.full[p.stage], p.phase, s.abort_flag, a.status, 23);
           if (!ok) break;
           tc_fence_after_sync();
           const uint32_t a_addr = smem_u32(s.tiles + p.stage * kStageBytes);
           const uint64_t da = make_smem_desc(a_addr, 16, 1024);
-          // MN-major B: column groups of one box are kBoxBytes apart (leading offset), 8-k groups
-          // 8*SWZ bytes apart (stride offset); one MMA consumes 16 k = 16*SWZ bytes.
-          const uint64_t db = make_smem_desc(a_addr + kABytes, Cfg::kBoxBytes, 8 * SWZ,
-                                             SWZ == 128 ? 2 : 4);
+          // MN-major B: the two 64-column boxes are kBoxBytes apart (leading offset), 8-k groups
+          // 1024 bytes apart (stride offset); one MMA consumes 16 k = 2048 bytes.
+          const uint64_t db = make_smem_desc(a_addr + kABytes, kBoxBytes, 1024);
 #pragma unroll
           for (int k4 = 0; k4 < kBK / 16; ++k4)
-            mma_f16_ss_pair(d_tmem, da + k4 * 2, db + k4 * ((16 * SWZ) >> 4), idesc,
+            mma_f16_ss_pair(d_tmem, da + k4 * 2, db + k4 * (2048 >> 4), idesc,
                             (kb != kb_begin) || k4 != 0);
           tc_commit_pair(&s.empty[p.stage], 3);
-          p.template advance<kStages>();
+          p.advance();
         }
         if (ok) tc_commit_pair(&s.acc_full[ab], 3);
       }
@@ -967,84 +716,78 @@ lmhead_grad_pair_kernel(const __grid_constant__ CUtensorMap map_p,
     float* tpose = reinterpret_cast<float*>(s.extra) + (warp - 2) * (32 * 33);
     bool ok = true;
     int it = 0;
-    const bool plain_store = a.first && a.ksplit == 1;   // else dH was zeroed / rescaled before
     for (int unit = pair; unit < n_units && ok; unit += n_pairs, ++it) {
       const int tile = unit % n_tiles;
       const int tr = tile % rt, tn = tile / rt;
       const int ab = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1u;
-      ok = __all_sync(0xffffffffu, mbar_wait(&s.acc_full[ab], acc_phase, s.abort_flag, a.status, 44));
+      ok = __all_sync(0xffffffffu, mbar_wait(&s.acc_full[ab], acc_phase, s.abort_flag, a.status, 24));
       if (!ok) break;
       tc_fence_after_sync();
       const int row_base = tr * 2 * kBM + (int)rank * kBM + q * 32;   // first of this warp's 32 rows
-      const uint32_t taddr = tmem + (static_cast<uint32_t>(q * 32) << 16) + ab * 256;
-      const int col_base = tn * BN;
+      const float my_mult = (row_base + lane < a.n_rows) ? a.mult[row_base + lane] : 0.f;
+      const uint32_t taddr = tmem + (static_cast<uint32_t>(q * 32) << 16) + ab * kBN;
+      const int col_base = tn * kBN;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = 0; c < kBN / 32; ++c) {
         uint32_t r[32];
         tmem_ld_32x32(taddr + c * 32, r);
         tmem_ld_wait_on(r);
         __syncwarp();
 #pragma unroll
-        for (int j = 0; j < 32; ++j) tpose[lane * 33 + j] = __uint_as_float(r[j]);
+        for (int j = 0; j < 32; ++j) tpose[lane * 33 + j] = __uint_as_float(r[j]) * my_mult;
         __syncwarp();
-        // dH was already multiplied by this chunk's factor (row kernel), so partial sums are added
-        // with fire-and-forget reductions. With ksplit == 1 one CTA adds to an element per chunk
-        // and the result is deterministic; with K splits the order of the adds is not.
+        // Fire-and-forget reductions: with one K split exactly one CTA adds to an element per
+        // chunk and the result is deterministic; with several the order of the adds is not.
         const int col = col_base + c * 32 + lane;
-        const bool col_ok = col < a.k_dim && !(a.debug & 32);
+        const bool col_ok = col < a.k_dim;
 #pragma unroll 8
         for (int rr = 0; rr < 32; ++rr) {
           const int row = row_base + rr;
-          if (col_ok && row < a.n_rows) {
-            float* dst = a.dh + (size_t)row * a.k_dim + col;
-            const float acc = tpose[rr * 33 + lane];
-            if (plain_store) *dst = acc;
-            else atomicAdd(dst, acc);
-          }
+          if (col_ok && row < a.n_rows)
+            atomicAdd(a.dh + (size_t)row * a.k_dim + col, tpose[rr * 33 + lane]);
         }
       }
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) {
-        if (rank == 0) mbar_arrive(&s.acc_empty[ab]);
-        else mbar_arrive_cluster(mapa_u32(smem_u32(&s.acc_empty[ab]), 0));
-      }
+      release_accumulator(s, ab, rank, lane);
     }
   }
   finish_pair(s, warp, tmem);
 }
 
 // ------------------------------------------------------------------------------------------
-// Small kernels: state initialisation, merge across ranks, finish.
+// Small kernels: state initialisation, merge across ranks, finish, backward scale.
 // ------------------------------------------------------------------------------------------
 __global__ void lmhead_init_state_kernel(float* run_max, float* run_sum, float* run_dot, int* best,
-                                         float* label_logit, float* label_lse, int n) {
+                                         float* best_val, float* label_logit, float* grad_ref,
+                                         int n) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   run_max[i] = -INFINITY;
   run_sum[i] = 0.f;
   run_dot[i] = 0.f;
   best[i] = 0;
+  best_val[i] = -INFINITY;
   label_logit[i] = 0.f;
-  label_lse[i] = 0.f;
+  grad_ref[i] = 0.f;
 }
 
 // states: [n_ranks, n] each; out: [n]. Ranks are in ascending vocabulary order, so a later rank
-// wins the argmax only if strictly larger.
+// wins the argmax only if strictly larger. Each rank's (max, sum, dot) means: mass = sum * e^max,
+// dot mass = dot * e^max.
 __global__ void lmhead_merge_kernel(const float* g_max, const float* g_sum, const float* g_dot,
-                                    const int* g_best, const float* g_label_logit,
-                                    const float* g_label_lse, const int64_t* target,
+                                    const int* g_best, const float* g_best_val,
+                                    const float* g_label_logit, const int64_t* target,
                                     const int64_t* shard_begin, float* o_max, float* o_sum,
-                                    float* o_dot, int* o_best, float* o_label_logit,
-                                    float* o_label_lse, float* o_lse, int n, int n_ranks) {
+                                    float* o_dot, int* o_best, float* o_best_val,
+                                    float* o_label_logit, float* o_lse, int n, int n_ranks) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
-  float m = -INFINITY;
+  float m = -INFINITY, bv = -INFINITY;
   int best = 0;
   for (int r = 0; r < n_ranks; ++r) {
-    const float v = g_max[(size_t)r * n + i];
-    if (v > m) { m = v; best = g_best[(size_t)r * n + i]; }
+    m = fmaxf(m, g_max[(size_t)r * n + i]);
+    const float v = g_best_val[(size_t)r * n + i];
+    if (v > bv) { bv = v; best = g_best[(size_t)r * n + i]; }
   }
   float sum = 0.f, dot = 0.f;
   for (int r = 0; r < n_ranks; ++r) {
@@ -1052,17 +795,14 @@ __global__ void lmhead_merge_kernel(const float* g_max, const float* g_sum, cons
     sum += g_sum[(size_t)r * n + i] * w;
     dot += g_dot[(size_t)r * n + i] * w;
   }
-  float ll = 0.f, lls = 0.f;
+  float ll = 0.f;
   const long long tg = target[i];
   if (tg != kIgnore) {
     for (int r = 0; r < n_ranks; ++r)
-      if (tg >= shard_begin[r] && tg < shard_begin[r + 1]) {
-        ll = g_label_logit[(size_t)r * n + i];
-        lls = g_label_lse[(size_t)r * n + i];
-      }
+      if (tg >= shard_begin[r] && tg < shard_begin[r + 1]) ll = g_label_logit[(size_t)r * n + i];
   }
-  o_max[i] = m; o_sum[i] = sum; o_dot[i] = dot; o_best[i] = best;
-  o_label_logit[i] = ll; o_label_lse[i] = lls;
+  o_max[i] = m; o_sum[i] = sum; o_dot[i] = dot; o_best[i] = best; o_best_val[i] = bv;
+  o_label_logit[i] = ll;
   o_lse[i] = m + logf(sum);
 }
 
@@ -1072,8 +812,7 @@ struct FinishArgs {
   const float* run_dot;
   const int* best;
   const float* label_logit;
-  const float* label_lse;
-  const float* local_lse;   // nullable: lse of this rank's own shard, for the dH rescale
+  const float* grad_ref;    // lse this rank's dH is relative to (needed when dh is given)
   const int64_t* target;
   const __half* weight;     // this rank's shard [v_shard, k_dim]
   float* token_loss;        // nullable (only the rank that reports writes them)
@@ -1095,17 +834,16 @@ __global__ void __launch_bounds__(256) lmhead_finish_kernel(const FinishArgs a) 
   }
   if (!a.dh) return;
   float* dh_row = a.dh + (size_t)row * a.k_dim;
-  const float scale = a.local_lse ? expf(a.local_lse[row] - lse) : 1.0f;
+  // dH holds sum_v exp(z_v - grad_ref) W_v over the shard's columns except the label's.
+  const float scale = kGradScale * expf(a.grad_ref[row] - lse);
   const long long local = tg - a.col_offset;
   const bool mine = labelled && local >= 0 && local < a.v_shard;
-  // The label's -1 entered the sum in its chunk and was rescaled with it by
-  // exp(lse_at_label_chunk - lse); put the missing part of -W[label] back.
-  const float missing = mine ? (1.0f - expf(a.label_lse[row] - lse)) * kGradScale : 0.f;
+  // the label's term, (p_label - 1) W[label], in fp32 (expm1 keeps it exact when p_label ~ 1)
+  const float label_term = mine ? expm1f(a.label_logit[row] - lse) * kGradScale : 0.f;
   const __half* w_row = a.weight + (size_t)(mine ? local : 0) * a.k_dim;
-  if (scale == 1.0f && !mine) return;
   for (int c = threadIdx.x; c < a.k_dim; c += blockDim.x) {
-    float v = dh_row[c] * scale;
-    if (mine) v -= __half2float(w_row[c]) * missing;
+    float v = labelled ? dh_row[c] * scale : 0.f;
+    if (mine) v = fmaf(__half2float(w_row[c]), label_term, v);
     dh_row[c] = v;
   }
 }
@@ -1148,21 +886,21 @@ struct Plan {
   int ct;          // column tiles per chunk
 };
 
-// Rows per block and column tiles per chunk: the E buffer of one chunk must stay L2 resident
-// (about 40 MB) and rows_tiles * ct should fill whole waves of SMs.
+// Rows per block and column tiles per chunk: the P buffer of one chunk must stay L2 resident
+// (about 40 MB) and row_tiles * ct should fill whole waves of CTA pairs.
 inline Plan make_plan(int64_t n, int64_t v_shard, int sms, int ct_override) {
   Plan p;
   p.row_block = (int)(n < 2048 ? (n < 1 ? 1 : n) : 2048);
-  const int rt = (p.row_block + kBM - 1) / kBM;
-  const int total_ct = (int)((v_shard + kBN1 - 1) / kBN1);
+  const int rt = (p.row_block + 2 * kBM - 1) / (2 * kBM);
+  const int pairs = sms / 2 > 0 ? sms / 2 : 1;
+  const int total_ct = (int)((v_shard + kBN - 1) / kBN);
   int ct = 37;
   if (ct_override > 0) {
     ct = ct_override;
   } else {
-    // largest ct <= 40 with rt*ct a multiple of the SM count, else 37
     int best = -1;
     for (int c = 40; c >= 8; --c)
-      if ((rt * c) % sms == 0) { best = c; break; }
+      if ((rt * c) % pairs == 0) { best = c; break; }
     if (best > 0) ct = best;
   }
   if (ct > total_ct) ct = total_ct;
@@ -1172,9 +910,9 @@ inline Plan make_plan(int64_t n, int64_t v_shard, int sms, int ct_override) {
 }
 
 struct Workspace {
-  __half* e_buf;
-  float4* tile_stats;
-  float* factor;
+  __nv_bfloat16* p_buf;   // [row_block, ct * 256]
+  float4* tile_stats;     // [row_block, ct]
+  float* mult;            // [row_block]
   int* status;
   int64_t bytes;
 };
@@ -1183,12 +921,12 @@ inline Workspace carve_workspace(void* base, const Plan& p) {
   Workspace w;
   uint8_t* b = reinterpret_cast<uint8_t*>(base);
   int64_t off = 0;
-  const int64_t ld_e = (int64_t)p.ct * kBN1;
-  w.e_buf = reinterpret_cast<__half*>(b + off);
-  off += round_up((int64_t)p.row_block * ld_e * 2, 1024);
+  const int64_t ld_p = (int64_t)p.ct * kBN;
+  w.p_buf = reinterpret_cast<__nv_bfloat16*>(b + off);
+  off += round_up((int64_t)p.row_block * ld_p * 2, 1024);
   w.tile_stats = reinterpret_cast<float4*>(b + off);
   off += round_up((int64_t)p.row_block * p.ct * 16, 1024);
-  w.factor = reinterpret_cast<float*>(b + off);
+  w.mult = reinterpret_cast<float*>(b + off);
   off += round_up((int64_t)p.row_block * 4, 1024);
   w.status = reinterpret_cast<int*>(b + off);
   off += 1024;
@@ -1208,8 +946,13 @@ struct LaunchTimer {
   bool on;
   std::vector<cudaEvent_t> ev[3];
   explicit LaunchTimer(cudaStream_t stream) : s(stream), on(g_timing_sink != nullptr) {}
-  void begin(int k) { if (on) { cudaEvent_t e; cudaEventCreate(&e); cudaEventRecord(e, s); ev[k].push_back(e); } }
-  void end(int k) { begin(k); }
+  void mark(int k) {
+    if (!on) return;
+    cudaEvent_t e;
+    cudaEventCreate(&e);
+    cudaEventRecord(e, s);
+    ev[k].push_back(e);
+  }
   void finish() {
     if (!on) return;
     cudaStreamSynchronize(s);
@@ -1233,17 +976,10 @@ int ensure_smem_attr() {
   cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
   if (major != 10) return -2;
   if (cudaFuncSetAttribute(lmhead_logits_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           kSmem1) != cudaSuccess)
+                           kSmemLogits) != cudaSuccess)
     return -1;
   if (cudaFuncSetAttribute(lmhead_grad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           kSmem2) != cudaSuccess)
-    return -1;
-  if (cudaFuncSetAttribute(lmhead_logits_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           kSmemP1) != cudaSuccess)
-    return -1;
-  if (cudaFuncSetAttribute(lmhead_grad_pair_kernel<256, 128>,
-                           cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           GradPairCfg<256, 128>::kSmem) != cudaSuccess)
+                           kSmemGrad) != cudaSuccess)
     return -1;
   g_attr_set[dev] = true;
   return 0;
@@ -1270,19 +1006,18 @@ static EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
-int encode_map_2d_f16(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
-                      uint64_t pitch_elems, uint32_t box_rows, uint32_t box_cols, int swizzle_bytes) {
+int encode_map_2d_16bit(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
+                        uint64_t pitch_elems, uint32_t box_rows, uint32_t box_cols, bool bf16) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return -1;
   const cuuint64_t dims[2] = {cols, rows};
   const cuuint64_t strides[1] = {pitch_elems * 2};
   const cuuint32_t box[2] = {box_cols, box_rows};
   const cuuint32_t estr[2] = {1, 1};
-  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims,
-                        strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                        swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
-                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  const CUresult r = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                        2, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : -(int)r - 1000;
 }
 
@@ -1297,21 +1032,22 @@ extern "C" int64_t soup_lmhead_workspace_bytes(int64_t n, int64_t h, int64_t v_s
   return carve_workspace(nullptr, p).bytes;
 }
 
-extern "C" int soup_lmhead_ce(const void* hidden, const void* weight, const int64_t* target,
-                              float* run_max, float* run_sum, float* run_dot, int* best,
-                              float* label_logit, float* label_lse, float* dh, void* workspace,
-                              int64_t workspace_bytes, int64_t n, int64_t h, int64_t v_shard,
-                              int64_t col_offset, int64_t chunk_tiles, int want_grad,
-                              void* stream) {
+extern "C" int soup_lmhead_ce(const void* hidden, const void* weight, const void* weight_bf16,
+                              const int64_t* target, float* run_max, float* run_sum, float* run_dot, int* best,
+                              float* best_val, float* label_logit, float* grad_ref, float* dh,
+                              void* workspace, int64_t workspace_bytes, int64_t n, int64_t h,
+                              int64_t v_shard, int64_t col_offset, int64_t chunk_tiles,
+                              int want_grad, void* stream) {
   using namespace soup;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (n < 0 || h <= 0 || v_shard <= 0) SOUP_FAIL(SOUP_ERR_ARG, "lmhead_ce: bad shape");
   if (n == 0) return SOUP_OK;
-  if (!hidden || !weight || !target || !run_max || !run_sum || !run_dot || !best || !label_logit ||
-      !label_lse || !workspace || (want_grad && !dh))
+  if (!hidden || !weight || !target || !run_max || !run_sum || !run_dot || !best || !best_val ||
+      !label_logit || !grad_ref || !workspace || (want_grad && (!dh || !weight_bf16)))
     SOUP_FAIL(SOUP_ERR_ARG, "lmhead_ce: null pointer");
   if (h % 8 != 0) SOUP_FAIL(SOUP_ERR_ARG, "lmhead_ce: hidden size must be a multiple of 8 (TMA pitch)");
-  if (!aligned16(hidden) || !aligned16(weight) || !aligned16(workspace) || (dh && !aligned16(dh)))
+  if (!aligned16(hidden) || !aligned16(weight) || !aligned16(workspace) || (dh && !aligned16(dh)) ||
+      (weight_bf16 && !aligned16(weight_bf16)))
     SOUP_FAIL(SOUP_ERR_ARG, "lmhead_ce: pointers must be 16-byte aligned");
   if (n > INT32_MAX / 2 || v_shard > INT32_MAX / 2 || col_offset + v_shard > INT32_MAX)
     SOUP_FAIL(SOUP_ERR_ARG, "lmhead_ce: shape exceeds 32-bit tile coordinates");
@@ -1319,130 +1055,111 @@ extern "C" int soup_lmhead_ce(const void* hidden, const void* weight, const int6
   if (attr == -2) SOUP_FAIL(SOUP_ERR_DEVICE, "lmhead_ce: needs a compute capability 10.x device");
   if (attr != 0) SOUP_FAIL(SOUP_ERR_DEVICE, "lmhead_ce: cannot raise the shared-memory limit");
   const int sms = sm_count();
+  const int max_pairs = sms / 2;
+  if (max_pairs < 1) SOUP_FAIL(SOUP_ERR_DEVICE, "lmhead_ce: needs at least two SMs");
   const Plan plan = make_plan(n, v_shard, sms, (int)chunk_tiles);
   const Workspace ws = carve_workspace(workspace, plan);
   if (workspace_bytes < ws.bytes)
     SOUP_FAIL(SOUP_ERR_ARG, "lmhead_ce: workspace too small (%lld < %lld)",
               (long long)workspace_bytes, (long long)ws.bytes);
-  const int ld_e = plan.ct * kBN1;
-  const int total_ct = (int)((v_shard + kBN1 - 1) / kBN1);
-
-  CUtensorMap map_h, map_w1, map_w1h, map_w2, map_w2h, map_p, map_e;
-  const char* single_env = getenv("SOUP_LMHEAD_SINGLE_CTA");
-  const bool use_pairs = !(single_env && atoi(single_env) != 0) && (sms % 2 == 0);
+  const int ld_p = plan.ct * kBN;
+  const int total_ct = (int)((v_shard + kBN - 1) / kBN);
   const char* det_env = getenv("SOUP_LMHEAD_DETERMINISTIC");
   const bool deterministic = det_env && atoi(det_env) != 0;
-  if (umma::encode_map_2d_f16(&map_h, hidden, (uint64_t)n, (uint64_t)h, (uint64_t)h, kBM, kBK) ||
-      umma::encode_map_2d_f16(&map_w1, weight, (uint64_t)v_shard, (uint64_t)h, (uint64_t)h, kBN1, kBK) ||
-      umma::encode_map_2d_f16(&map_w1h, weight, (uint64_t)v_shard, (uint64_t)h, (uint64_t)h, kBN1 / 2, kBK) ||
-      umma::encode_map_2d_f16(&map_w2, weight, (uint64_t)v_shard, (uint64_t)h, (uint64_t)h, kBK, 64) ||
-      umma::encode_map_2d_f16(&map_w2h, weight, (uint64_t)v_shard, (uint64_t)h, (uint64_t)h, kBK, 32, 64) ||
-      umma::encode_map_2d_f16(&map_p, ws.e_buf, (uint64_t)plan.row_block, (uint64_t)ld_e,
-                              (uint64_t)ld_e, kBM, kBK) ||
-      umma::encode_map_2d_f16(&map_e, ws.e_buf, (uint64_t)plan.row_block, (uint64_t)ld_e,
-                              (uint64_t)ld_e, 32, 64))
+
+  CUtensorMap map_h, map_w_k, map_w_mn, map_p_ld, map_p_st;
+  if (umma::encode_map_2d_16bit(&map_h, hidden, (uint64_t)n, (uint64_t)h, (uint64_t)h, kBM, kBK, false) ||
+      umma::encode_map_2d_16bit(&map_w_k, weight, (uint64_t)v_shard, (uint64_t)h, (uint64_t)h, kBN / 2, kBK, false) ||
+      (want_grad &&
+       umma::encode_map_2d_16bit(&map_w_mn, weight_bf16, (uint64_t)v_shard, (uint64_t)h, (uint64_t)h, kBK, 64, true)) ||
+      umma::encode_map_2d_16bit(&map_p_ld, ws.p_buf, (uint64_t)plan.row_block, (uint64_t)ld_p,
+                                (uint64_t)ld_p, kBM, kBK, true) ||
+      umma::encode_map_2d_16bit(&map_p_st, ws.p_buf, (uint64_t)plan.row_block, (uint64_t)ld_p,
+                                (uint64_t)ld_p, 32, 64, true))
     SOUP_FAIL(SOUP_ERR_DEVICE, "lmhead_ce: cuTensorMapEncodeTiled failed");
 
   cudaMemsetAsync(ws.status, 0, 4, s);
-  if (use_pairs && want_grad && !deterministic)   // K-split partial sums are added into dH
-    cudaMemsetAsync(dh, 0, (size_t)n * h * sizeof(float), s);
+  if (want_grad) cudaMemsetAsync(dh, 0, (size_t)n * h * sizeof(float), s);
   lmhead_init_state_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(
-      run_max, run_sum, run_dot, best, label_logit, label_lse, (int)n);
+      run_max, run_sum, run_dot, best, best_val, label_logit, grad_ref, (int)n);
   SOUP_CHECK_LAUNCH("lmhead_init_state");
 
   LaunchTimer timer(s);
   for (int64_t r0 = 0; r0 < n; r0 += plan.row_block) {
     const int rows = (int)((n - r0) < plan.row_block ? (n - r0) : plan.row_block);
-    const int rt = (rows + kBM - 1) / kBM;
+    const int rt = (rows + 2 * kBM - 1) / (2 * kBM);
     for (int t0 = 0; t0 < total_ct; t0 += plan.ct) {
       const int ct = (total_ct - t0) < plan.ct ? (total_ct - t0) : plan.ct;
+      const bool first = t0 == 0;
       LogitsArgs la;
       la.target = target + r0;
-      la.e_buf = ws.e_buf;
+      la.ref = run_max + r0;
       la.tile_stats = ws.tile_stats;
       la.label_logit = label_logit + r0;
       la.n_rows = rows;
       la.row0 = (int)r0;
       la.k_dim = (int)h;
-      la.col0 = t0 * kBN1;
+      la.col0 = t0 * kBN;
       la.v_shard = (int)v_shard;
       la.col_offset = (int)col_offset;
       la.ct = ct;
       la.ct_stride = plan.ct;
-      la.ld_e = ld_e;
-      la.write_e = want_grad;
-      {
-        const char* dbg = getenv("SOUP_LMHEAD_DEBUG");
-        la.debug = dbg ? atoi(dbg) : 0;
-      }
+      la.store_p = want_grad;
       la.status = ws.status;
       const int tiles1 = rt * ct;
-      timer.begin(0);
-      if (use_pairs) {
-        const int tiles_p = ((rows + 2 * kBM - 1) / (2 * kBM)) * ct;
-        const int pairs = tiles_p < sms / 2 ? tiles_p : sms / 2;
-        lmhead_logits_pair_kernel<<<(unsigned)(2 * pairs), kThreadsGemm, kSmemP1, s>>>(
-            map_h, map_w1h, map_e, la);
-      } else {
-        lmhead_logits_kernel<<<(unsigned)(tiles1 < sms ? tiles1 : sms), kThreadsGemm, kSmem1, s>>>(
-            map_h, map_w1, map_e, la);
-      }
-      timer.end(0);
+      const unsigned grid1 = 2u * (unsigned)(tiles1 < max_pairs ? tiles1 : max_pairs);
+
+      la.mode = first ? kModeTileMax : kModeCombined;
+      timer.mark(0);
+      lmhead_logits_kernel<<<grid1, kThreadsGemm, kSmemLogits, s>>>(map_h, map_w_k, map_p_st, la);
+      timer.mark(0);
       SOUP_CHECK_LAUNCH("lmhead_logits");
 
       RowArgs ra;
-      ra.target = target + r0;
-      ra.e_buf = ws.e_buf;
       ra.tile_stats = ws.tile_stats;
       ra.run_max = run_max + r0;
       ra.run_sum = run_sum + r0;
       ra.run_dot = run_dot + r0;
       ra.best = best + r0;
-      ra.label_logit = label_logit + r0;
-      ra.label_lse = label_lse + r0;
-      ra.factor = ws.factor;
+      ra.best_val = best_val + r0;
+      ra.base = grad_ref + r0;
+      ra.mult = ws.mult;
+      ra.dh = want_grad ? dh + r0 * h : nullptr;
       ra.n_rows = rows;
-      ra.col0 = t0 * kBN1;
-      ra.v_shard = (int)v_shard;
-      ra.col_offset = (int)col_offset;
+      ra.k_dim = (int)h;
       ra.ct = ct;
       ra.ct_stride = plan.ct;
-      ra.ld_e = ld_e;
-      ra.write_p = want_grad;
-      ra.dh = (use_pairs && want_grad) ? dh + r0 * h : nullptr;
-      ra.k_dim = (int)h;
-      ra.first = t0 == 0;
-      timer.begin(1);
-      lmhead_row_kernel<<<(unsigned)rows, kRowWarps * 32, 0, s>>>(ra);
-      timer.end(1);
+      ra.mode = la.mode;
+      ra.want_grad = want_grad;
+      ra.status = ws.status;
+      timer.mark(1);
+      lmhead_row_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, s>>>(ra);
+      timer.mark(1);
       SOUP_CHECK_LAUNCH("lmhead_row");
 
       if (want_grad) {
+        if (first) {  // the first chunk's P, against the lse the row kernel just produced
+          la.mode = kModePOnly;
+          timer.mark(0);
+          lmhead_logits_kernel<<<grid1, kThreadsGemm, kSmemLogits, s>>>(map_h, map_w_k, map_p_st, la);
+          timer.mark(0);
+          SOUP_CHECK_LAUNCH("lmhead_logits");
+        }
         GradArgs ga;
         ga.dh = dh + r0 * h;
-        ga.factor = ws.factor;
+        ga.mult = ws.mult;
         ga.n_rows = rows;
         ga.k_dim = (int)h;
-        ga.col0 = t0 * kBN1;
-        ga.n_kb = ct * (kBN1 / kBK);
-        ga.first = t0 == 0;
-        ga.ksplit = 1;
-        ga.debug = la.debug;
+        ga.col0 = t0 * kBN;
+        ga.n_kb = ct * (kBN / kBK);
         ga.status = ws.status;
-        const int tiles2 = rt * (int)((h + kBN2 - 1) / kBN2);
-        timer.begin(2);
-        if (use_pairs) {
-          const int tiles_p = ((rows + 2 * kBM - 1) / (2 * kBM)) * (int)((h + 255) / 256);
-          ga.ksplit = pick_ksplit(tiles_p, sms / 2, ga.n_kb, deterministic);
-          const int units = tiles_p * ga.ksplit;
-          const int pairs = units < sms / 2 ? units : sms / 2;
-          lmhead_grad_pair_kernel<256, 128><<<(unsigned)(2 * pairs), kThreadsGemm,
-                                               GradPairCfg<256, 128>::kSmem, s>>>(map_p, map_w2, ga);
-        } else {
-          lmhead_grad_kernel<<<(unsigned)(tiles2 < sms ? tiles2 : sms), kThreadsGemm, kSmem2, s>>>(
-              map_p, map_w2, ga);
-        }
-        timer.end(2);
+        const int tiles2 = rt * (int)((h + kBN - 1) / kBN);
+        ga.ksplit = pick_ksplit(tiles2, max_pairs, ga.n_kb, deterministic);
+        const int units = tiles2 * ga.ksplit;
+        const unsigned grid2 = 2u * (unsigned)(units < max_pairs ? units : max_pairs);
+        timer.mark(2);
+        lmhead_grad_kernel<<<grid2, kThreadsGemm, kSmemGrad, s>>>(map_p_ld, map_w_mn, ga);
+        timer.mark(2);
         SOUP_CHECK_LAUNCH("lmhead_grad");
       }
     }
@@ -1478,39 +1195,39 @@ extern "C" int soup_lmhead_status(const void* workspace, int64_t n, int64_t v_sh
 }
 
 extern "C" int soup_lmhead_merge(const float* g_max, const float* g_sum, const float* g_dot,
-                                 const int* g_best, const float* g_label_logit,
-                                 const float* g_label_lse, const int64_t* target,
+                                 const int* g_best, const float* g_best_val,
+                                 const float* g_label_logit, const int64_t* target,
                                  const int64_t* shard_begin, float* o_max, float* o_sum,
-                                 float* o_dot, int* o_best, float* o_label_logit,
-                                 float* o_label_lse, float* o_lse, int64_t n, int n_ranks,
+                                 float* o_dot, int* o_best, float* o_best_val,
+                                 float* o_label_logit, float* o_lse, int64_t n, int n_ranks,
                                  void* stream) {
   using namespace soup;
   if (n == 0) return SOUP_OK;
   if (n < 0 || n_ranks < 1) SOUP_FAIL(SOUP_ERR_ARG, "lmhead_merge: bad shape");
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   lmhead_merge_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(
-      g_max, g_sum, g_dot, g_best, g_label_logit, g_label_lse, target, shard_begin, o_max, o_sum,
-      o_dot, o_best, o_label_logit, o_label_lse, o_lse, (int)n, n_ranks);
+      g_max, g_sum, g_dot, g_best, g_best_val, g_label_logit, target, shard_begin, o_max, o_sum,
+      o_dot, o_best, o_best_val, o_label_logit, o_lse, (int)n, n_ranks);
   SOUP_CHECK_LAUNCH("lmhead_merge");
   return SOUP_OK;
 }
 
 extern "C" int soup_lmhead_finish(const float* run_max, const float* run_sum, const float* run_dot,
-                                  const int* best, const float* label_logit, const float* label_lse,
-                                  const float* local_lse, const int64_t* target, const void* weight,
-                                  float* token_loss, float* entropy, int* correct, float* dh,
-                                  int64_t n, int64_t h, int64_t v_shard, int64_t col_offset,
-                                  void* stream) {
+                                  const int* best, const float* label_logit, const float* grad_ref,
+                                  const int64_t* target, const void* weight, float* token_loss,
+                                  float* entropy, int* correct, float* dh, int64_t n, int64_t h,
+                                  int64_t v_shard, int64_t col_offset, void* stream) {
   using namespace soup;
   if (n == 0) return SOUP_OK;
   if (n < 0 || h <= 0) SOUP_FAIL(SOUP_ERR_ARG, "lmhead_finish: bad shape");
-  if (!run_max || !run_sum || !run_dot || !best || !label_logit || !label_lse || !target)
+  if (!run_max || !run_sum || !run_dot || !best || !label_logit || !target)
     SOUP_FAIL(SOUP_ERR_ARG, "lmhead_finish: null pointer");
-  if (dh && !weight) SOUP_FAIL(SOUP_ERR_ARG, "lmhead_finish: dH needs the weight shard");
+  if (dh && (!weight || !grad_ref))
+    SOUP_FAIL(SOUP_ERR_ARG, "lmhead_finish: dH needs the weight shard and grad_ref");
   if (token_loss && (!entropy || !correct)) SOUP_FAIL(SOUP_ERR_ARG, "lmhead_finish: null output");
   FinishArgs a;
   a.run_max = run_max; a.run_sum = run_sum; a.run_dot = run_dot; a.best = best;
-  a.label_logit = label_logit; a.label_lse = label_lse; a.local_lse = local_lse;
+  a.label_logit = label_logit; a.grad_ref = grad_ref;
   a.target = target; a.weight = reinterpret_cast<const __half*>(weight);
   a.token_loss = token_loss; a.entropy = entropy; a.correct = correct; a.dh = dh;
   a.n_rows = (int)n; a.k_dim = (int)h; a.v_shard = (int)v_shard; a.col_offset = (int)col_offset;

@@ -319,22 +319,25 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t 
   return d;
 }
 
-// Instruction descriptor of tcgen05.mma kind::f16 with fp16 A and B, fp32 accumulator.
-// Bits: [4,6) accumulator format (1 = f32), [7,10) A format (0 = f16), [10,13) B format,
-// [15] A major (0 = K), [16] B major (1 = MN), [17,23) N >> 3, [24,29) M >> 4.
-__host__ __device__ constexpr uint32_t make_idesc_f16(int m, int n, bool a_mn_major, bool b_mn_major) {
-  return (1u << 4) | (0u << 7) | (0u << 10) | ((a_mn_major ? 1u : 0u) << 15) |
+// Instruction descriptor of tcgen05.mma kind::f16 with 16-bit A and B (fp16 or bf16, independently)
+// and an fp32 accumulator. Bits: [4,6) accumulator format (1 = f32), [7,10) A format, [10,13) B
+// format (0 = f16, 1 = bf16), [15] A major (0 = K), [16] B major (1 = MN), [17,23) N >> 3,
+// [24,29) M >> 4.
+constexpr uint32_t kFmtF16 = 0, kFmtBF16 = 1;
+__host__ __device__ constexpr uint32_t make_idesc_f16(int m, int n, uint32_t a_fmt, uint32_t b_fmt,
+                                                      bool a_mn_major, bool b_mn_major) {
+  return (1u << 4) | (a_fmt << 7) | (b_fmt << 10) | ((a_mn_major ? 1u : 0u) << 15) |
          ((b_mn_major ? 1u : 0u) << 16) | (static_cast<uint32_t>(n >> 3) << 17) |
          (static_cast<uint32_t>(m >> 4) << 24);
 }
 
 // ---------------------------------------------------------------- host: tensor maps
-// Row-major 2-D tensor [rows, cols] of 16-bit elements with row pitch `pitch_elems`; the box is
-// [box_rows, box_cols] with box_cols * 2 == swizzle_bytes (128 or 64), written to shared memory
-// with that swizzle, as the descriptors above expect. Out-of-range elements read as zero.
-int encode_map_2d_f16(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
-                      uint64_t pitch_elems, uint32_t box_rows, uint32_t box_cols,
-                      int swizzle_bytes = 128);
+// Row-major 2-D tensor [rows, cols] of 16-bit elements (fp16 or bf16) with row pitch `pitch_elems`;
+// the box is [box_rows, box_cols] with box_cols * 2 == 128 bytes, moved to / from shared memory
+// with the 128-byte swizzle the descriptors above expect. Out-of-range elements read as zero and
+// are not written.
+int encode_map_2d_16bit(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
+                        uint64_t pitch_elems, uint32_t box_rows, uint32_t box_cols, bool bf16);
 
 }  // namespace umma
 }  // namespace soup

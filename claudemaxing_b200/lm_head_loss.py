@@ -56,9 +56,12 @@ def _chunk_tiles(chunk_cols):
 
 
 class HeadState:
-    """Per-row running state of one pass over a vocabulary range (fp32 / int32, all [n])."""
+    """Per-row state of one pass over a vocabulary range (fp32 / int32, all [n]). (run_max,
+    run_sum, run_dot) mean mass = run_sum * e^run_max and dot mass = run_dot * e^run_max; best /
+    best_val are the index and value of the largest logit; grad_ref is the log-sum-exp the
+    range's raw gradient is relative to."""
 
-    __slots__ = ("run_max", "run_sum", "run_dot", "best", "label_logit", "label_lse")
+    __slots__ = ("run_max", "run_sum", "run_dot", "best", "best_val", "label_logit", "grad_ref")
 
     def __init__(self, n, device):
         f32 = torch.float32
@@ -66,22 +69,47 @@ class HeadState:
         self.run_sum = torch.empty(n, dtype=f32, device=device)
         self.run_dot = torch.empty(n, dtype=f32, device=device)
         self.best = torch.empty(n, dtype=torch.int32, device=device)
+        self.best_val = torch.empty(n, dtype=f32, device=device)
         self.label_logit = torch.empty(n, dtype=f32, device=device)
-        self.label_lse = torch.empty(n, dtype=f32, device=device)
+        self.grad_ref = torch.empty(n, dtype=f32, device=device)
 
     def tensors(self):
-        return (self.run_max, self.run_sum, self.run_dot, self.best, self.label_logit,
-                self.label_lse)
+        return (self.run_max, self.run_sum, self.run_dot, self.best, self.best_val,
+                self.label_logit, self.grad_ref)
 
     def lse(self):
         return self.run_max + torch.log(self.run_sum)
 
 
-def head_partial(h16, w16, target, col_offset=0, chunk_cols=None, want_grad=True):
+_BF16_COPIES = {}  # id(weight) -> (weakref, data_ptr, version, bf16 copy)
+
+
+def bf16_copy_of_weight(w16):
+    """The head weight rounded to bf16, made once per (frozen) weight and kept until the weight
+    changes or dies. The gradient GEMM multiplies bf16 probabilities with it: the tensor core
+    takes one element format for both operands."""
+    import weakref
+
+    key = id(w16)
+    hit = _BF16_COPIES.get(key)
+    if (hit is not None and hit[0]() is w16 and hit[1] == w16.data_ptr()
+            and hit[2] == w16._version):
+        return hit[3]
+    copy = w16.detach().to(torch.bfloat16).contiguous()
+    try:
+        ref = weakref.ref(w16, lambda _r, k=key: _BF16_COPIES.pop(k, None))
+    except TypeError:
+        return copy
+    _BF16_COPIES[key] = (ref, w16.data_ptr(), w16._version, copy)
+    return copy
+
+
+def head_partial(h16, w16, target, col_offset=0, chunk_cols=None, want_grad=True, w_bf16=None):
     """One pass of the fused head over the columns of `w16` (a shard of the head weight whose
     first row is vocabulary index `col_offset`). Returns (state, grad_raw): the per-row state of
-    this range and, with `want_grad`, the fp32 [n, hidden] gradient at GRAD_SCALE against this
-    range's own log-sum-exp (the label's -1 included where the label falls in the range)."""
+    this range and, with `want_grad`, the raw fp32 [n, hidden] gradient sum_v exp(z_v -
+    state.grad_ref) W[v] over the range's columns except the label's; `head_finish` completes
+    it."""
     _lib.require_cuda(h16, w16, target)
     if h16.dtype != torch.float16 or w16.dtype != torch.float16:
         raise TypeError("the fused head computes in float16")
@@ -97,27 +125,32 @@ def head_partial(h16, w16, target, col_offset=0, chunk_cols=None, want_grad=True
     state = HeadState(n, dev)
     grad_raw = torch.empty((n, hidden), dtype=torch.float32, device=dev) if want_grad else None
     if n == 0 or vocab == 0:  # an empty shard contributes nothing: max -inf, sums 0, gradient 0
-        state.run_max.fill_(float("-inf"))
-        for t in state.tensors()[1:]:
+        for t in state.tensors():
             t.zero_()
+        state.run_max.fill_(float("-inf"))
+        state.best_val.fill_(float("-inf"))
         if grad_raw is not None:
             grad_raw.zero_()
         return state, grad_raw
     tiles = _chunk_tiles(chunk_cols)
     nbytes = _lib.lib().soup_lmhead_workspace_bytes(n, hidden, vocab, tiles)
     workspace = torch.empty(nbytes, dtype=torch.uint8, device=dev)
-    _lib.call("soup_lmhead_ce", _lib.ptr(h16), _lib.ptr(w16), _lib.ptr(target),
+    if want_grad and w_bf16 is None:
+        w_bf16 = bf16_copy_of_weight(w16)
+    _lib.call("soup_lmhead_ce", _lib.ptr(h16), _lib.ptr(w16),
+              _lib.ptr(w_bf16) if want_grad else None, _lib.ptr(target),
               *(_lib.ptr(t) for t in state.tensors()), _lib.ptr(grad_raw), _lib.ptr(workspace),
               nbytes, n, hidden, vocab, int(col_offset), tiles, int(bool(want_grad)),
               _lib.stream_of(h16))
     return state, grad_raw
 
 
-def head_finish(state, target, w16, grad_raw=None, col_offset=0, local_lse=None,
+def head_finish(state, target, w16, grad_raw=None, col_offset=0, grad_ref=None,
                 want_metrics=True):
     """Turns a (merged) state into token_loss / entropy / correct and completes `grad_raw` in
-    place: rescale from the shard's own lse to the state's (when `local_lse` is given) and put
-    back the part of the label's -W[label] that rescaling removed."""
+    place: GRAD_SCALE * (exp(grad_ref - lse) * grad_raw + (p_label - 1) * W[label]), the label
+    term where the label falls in `w16`'s range. `grad_ref` is the array of the state that
+    `head_partial` returned together with `grad_raw` (default: `state.grad_ref`)."""
     n = target.numel()
     dev = target.device
     token_loss = entropy = correct = None
@@ -125,9 +158,12 @@ def head_finish(state, target, w16, grad_raw=None, col_offset=0, local_lse=None,
         token_loss = torch.empty(n, dtype=torch.float32, device=dev)
         entropy = torch.empty(n, dtype=torch.float32, device=dev)
         correct = torch.empty(n, dtype=torch.int32, device=dev)
+    if grad_ref is None:
+        grad_ref = state.grad_ref
     if n:
-        _lib.call("soup_lmhead_finish", *(_lib.ptr(t) for t in state.tensors()),
-                  _lib.ptr(local_lse), _lib.ptr(target), _lib.ptr(w16), _lib.ptr(token_loss),
+        _lib.call("soup_lmhead_finish", _lib.ptr(state.run_max), _lib.ptr(state.run_sum),
+                  _lib.ptr(state.run_dot), _lib.ptr(state.best), _lib.ptr(state.label_logit),
+                  _lib.ptr(grad_ref), _lib.ptr(target), _lib.ptr(w16), _lib.ptr(token_loss),
                   _lib.ptr(entropy), _lib.ptr(correct), _lib.ptr(grad_raw), n, w16.shape[1],
                   w16.shape[0], int(col_offset), _lib.stream_of(target))
     return token_loss, entropy, correct
@@ -143,7 +179,9 @@ class _FusedHeadLoss(torch.autograd.Function):
         tgt = target.reshape(-1).contiguous().to(torch.int64)
         h_low = h2.to(compute_dtype)
         w_low = weight.detach().to(compute_dtype)
-        state, grad_raw = head_partial(h_low, w_low, tgt, 0, chunk_cols, want_grad)
+        # cached on the weight object itself (detach() makes a new tensor object every call)
+        w_bf16 = bf16_copy_of_weight(weight) if want_grad else None
+        state, grad_raw = head_partial(h_low, w_low, tgt, 0, chunk_cols, want_grad, w_bf16)
         token_loss, entropy, correct = head_finish(state, tgt, w_low, grad_raw)
         loss = token_loss.sum() / denominator
         ctx.shape, ctx.hidden_dtype, ctx.denominator = shape, hidden.dtype, denominator

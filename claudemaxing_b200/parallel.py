@@ -5,8 +5,8 @@ so nothing here replaces reference code; it extends the same arithmetic across r
 
 Vocabulary-parallel head: the weight is split into contiguous ranges of whole 256-column tiles,
 rank r owning columns [bounds[r], bounds[r+1]); hidden states and targets are replicated. Each rank
-runs `head_partial` on its shard and gets the per-row state (max, sum exp, sum exp*z, argmax,
-label logit, lse at the label's chunk) and a gradient against its *own* log-sum-exp. One
+runs `head_partial` on its shard and gets the per-row state (log-sum-exp bookkeeping, sum exp*z,
+argmax index and value, label logit) and a raw gradient against its *own* reference lse. One
 all-gather of the [6, n] states (24 bytes per row and rank) feeds the merge kernel; the finish
 kernel rescales the rank's gradient by exp(lse_rank - lse_global) and restores the label term on
 the rank that owns the label; one all-reduce sums the gradients. There is no other exchange.
@@ -34,10 +34,14 @@ def shard_bounds(vocab, world, tile=TILE_COLS):
     return bounds
 
 
+N_FIELDS = 6  # run_max, run_sum, run_dot, best (bits), best_val, label_logit
+
+
 def pack_state(state):
-    """[6, n] fp32 view of a HeadState for one collective (the int32 argmax travels as bits)."""
+    """[6, n] fp32 view of a HeadState for one collective (the int32 argmax travels as bits;
+    grad_ref stays local: only the rank itself needs it)."""
     return torch.stack([state.run_max, state.run_sum, state.run_dot,
-                        state.best.view(torch.float32), state.label_logit, state.label_lse])
+                        state.best.view(torch.float32), state.best_val, state.label_logit])
 
 
 def merge_states(gathered, target, bounds):
@@ -49,21 +53,24 @@ def merge_states(gathered, target, bounds):
     lse = torch.empty(n, dtype=torch.float32, device=dev)
     begin = torch.tensor(bounds, dtype=torch.int64, device=dev)
     if n:
-        _lib.call("soup_lmhead_merge", *(_lib.ptr(fields[i]) for i in range(6)), _lib.ptr(target),
-                  _lib.ptr(begin), *(_lib.ptr(t) for t in merged.tensors()), _lib.ptr(lse), n,
+        _lib.call("soup_lmhead_merge", *(_lib.ptr(fields[i]) for i in range(N_FIELDS)),
+                  _lib.ptr(target), _lib.ptr(begin), _lib.ptr(merged.run_max),
+                  _lib.ptr(merged.run_sum), _lib.ptr(merged.run_dot), _lib.ptr(merged.best),
+                  _lib.ptr(merged.best_val), _lib.ptr(merged.label_logit), _lib.ptr(lse), n,
                   world, _lib.stream_of(target))
     return merged, lse
 
 
 def vocab_parallel_head(h16, w_shard, target, bounds, group=None, want_grad=True,
-                        reduce_grad=True, chunk_cols=None):
+                        reduce_grad=True, chunk_cols=None, w_bf16=None):
     """The fused head with the vocabulary split across the ranks of `group`. `w_shard` is this
     rank's rows [bounds[rank], bounds[rank+1]) of the head weight. Returns dict(token_loss,
     entropy, correct, grad_raw): per-row terms identical on every rank, grad_raw the fp32
     [n, hidden] gradient at GRAD_SCALE, summed over ranks when `reduce_grad`."""
     rank, world = dist.get_rank(group), dist.get_world_size(group)
     target = target.contiguous().to(torch.int64)
-    state, grad_raw = head_partial(h16, w_shard, target, bounds[rank], chunk_cols, want_grad)
+    state, grad_raw = head_partial(h16, w_shard, target, bounds[rank], chunk_cols, want_grad,
+                                   w_bf16)
     mine = pack_state(state)
     # concatenated along dim 0: the output layout every backend accepts
     gathered = torch.empty((world * mine.shape[0], mine.shape[1]), dtype=mine.dtype,
@@ -71,7 +78,7 @@ def vocab_parallel_head(h16, w_shard, target, bounds, group=None, want_grad=True
     dist.all_gather_into_tensor(gathered, mine, group=group)
     merged, _ = merge_states(gathered.view(world, *mine.shape), target, bounds)
     token_loss, entropy, correct = head_finish(merged, target, w_shard, grad_raw, bounds[rank],
-                                               local_lse=state.lse())
+                                               grad_ref=state.grad_ref)
     if want_grad and reduce_grad:
         dist.all_reduce(grad_raw, group=group)
     return dict(token_loss=token_loss, entropy=entropy, correct=correct, grad_raw=grad_raw)
@@ -92,7 +99,7 @@ def emulate_vocab_parallel(h16, w, target, n_shards, chunk_cols=None):
     out = None
     for r in range(n_shards):
         res = head_finish(merged, target, w[bounds[r]:bounds[r + 1]], grads[r], bounds[r],
-                          local_lse=states[r].lse(), want_metrics=(r == 0))
+                          grad_ref=states[r].grad_ref, want_metrics=(r == 0))
         if r == 0:
             out = res
     return dict(token_loss=out[0], entropy=out[1], correct=out[2], grad_raw=torch.stack(grads).sum(0))

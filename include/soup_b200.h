@@ -139,23 +139,30 @@ int soup_dropout_unpack(const void* x16, const uint8_t* bits, const void* g16, v
 /* ---- fused LM head + cross-entropy (tcgen05 / TMEM / TMA) -------------------------------------
  * Replaces the chunk loop of _FusedHeadLoss.forward, solution/lm_head_loss.py:213-224 (torch.mm,
  * lm_head_vocab_chunk_kernel :108-160, torch.mm, mul_/add_), over the columns of one weight shard.
- * State arrays are fp32/int32 [n] and are initialised by the call:
- *   run_max, run_sum  running max and sum of exp(z - run_max) over the shard's columns
- *   run_dot           running sum of exp(z - run_max) * z                      (entropy)
- *   best              global vocabulary index of the first maximum             (accuracy)
- *   label_logit       the label's logit, where the label falls in this shard   (loss)
- *   label_lse         the running lse when the label's chunk was processed     (label fix-up)
- *   dh                fp32 [n,h]: 1024 * sum_v softmax_shard(z)_v * W[v] with the label's -1 in
- *                     place, against this shard's own log-sum-exp; NULL when want_grad == 0
+ * State arrays are fp32/int32 [n] and are initialised by the call; (run_max, run_sum, run_dot)
+ * mean: mass = run_sum * e^run_max, dot mass = run_dot * e^run_max (the call leaves them
+ * normalised, run_max = log-sum-exp of the shard, run_sum = 1):
+ *   run_max, run_sum  log-sum-exp bookkeeping over the shard's columns
+ *   run_dot           sum of softmax_shard(z) * z                               (entropy)
+ *   best, best_val    global vocabulary index and value of the first maximum    (accuracy)
+ *   label_logit       the label's logit, where the label falls in this shard    (loss)
+ *   grad_ref          the log-sum-exp dh is relative to
+ *   dh                fp32 [n,h]: sum over the shard's columns except the label's of
+ *                     exp(z_v - grad_ref) * W[v], zero for unlabelled rows; soup_lmhead_finish
+ *                     completes it. NULL when want_grad == 0
  * hidden fp16 [n,h] and weight fp16 [v_shard,h] row-major, 16-byte aligned, h % 8 == 0.
+ * weight_bf16: the same weight rounded to bf16 (needed when want_grad != 0; the gradient GEMM
+ * multiplies bf16 probabilities with it, and the tensor core takes one format for both operands).
  * col_offset = global index of the shard's first column. chunk_tiles = 256-column tiles per
- * chunk (0 = library default). workspace: soup_lmhead_workspace_bytes() bytes, 16-byte aligned. */
+ * chunk (0 = library default). workspace: soup_lmhead_workspace_bytes() bytes, 16-byte aligned.
+ * With SOUP_LMHEAD_DETERMINISTIC=1 in the environment the gradient GEMM does not split its
+ * reduction dimension and dh is bit-reproducible (at a lower SM occupancy). */
 int64_t soup_lmhead_workspace_bytes(int64_t n, int64_t h, int64_t v_shard, int64_t chunk_tiles);
-int soup_lmhead_ce(const void* hidden, const void* weight, const int64_t* target, float* run_max,
-                   float* run_sum, float* run_dot, int* best, float* label_logit,
-                   float* label_lse, float* dh, void* workspace, int64_t workspace_bytes,
-                   int64_t n, int64_t h, int64_t v_shard, int64_t col_offset,
-                   int64_t chunk_tiles, int want_grad, void* stream);
+int soup_lmhead_ce(const void* hidden, const void* weight, const void* weight_bf16,
+                   const int64_t* target, float* run_max, float* run_sum, float* run_dot, int* best,
+                   float* best_val, float* label_logit, float* grad_ref, float* dh, void* workspace,
+                   int64_t workspace_bytes, int64_t n, int64_t h, int64_t v_shard,
+                   int64_t col_offset, int64_t chunk_tiles, int want_grad, void* stream);
 
 /* Benchmark aid: while a host array of 6 floats is set, every soup_lmhead_ce call brackets its
  * launches with events, synchronises its stream before returning, and adds the milliseconds of the
@@ -178,20 +185,21 @@ int soup_lmhead_status(const void* workspace, int64_t n, int64_t v_shard, int64_
  * log-sum-exp. No counterpart in the reference, which is single-GPU (solution/lm_head_loss.py:
  * 426-428 refuses n_gpu > 1); the merge rule is the chunk-to-chunk carry of :119-145. */
 int soup_lmhead_merge(const float* g_max, const float* g_sum, const float* g_dot,
-                      const int* g_best, const float* g_label_logit, const float* g_label_lse,
+                      const int* g_best, const float* g_best_val, const float* g_label_logit,
                       const int64_t* target, const int64_t* shard_begin, float* o_max,
-                      float* o_sum, float* o_dot, int* o_best, float* o_label_logit,
-                      float* o_label_lse, float* o_lse, int64_t n, int n_ranks, void* stream);
+                      float* o_sum, float* o_dot, int* o_best, float* o_best_val,
+                      float* o_label_logit, float* o_lse, int64_t n, int n_ranks, void* stream);
 
 /* Finalisation, solution/lm_head_loss.py:225-237: token_loss = lse - label_logit (0 if ignored),
  * entropy = lse - run_dot/run_sum, correct = labelled && best == target (all nullable together);
- * dh (nullable, in place): scaled by exp(local_lse - lse) when local_lse is given, and, where the
- * label falls in this shard, dh -= W[label] * (1 - exp(label_lse - lse)) * 1024. */
+ * dh (nullable, in place): dh = 1024 * (exp(grad_ref - lse) * dh + (p_label - 1) * W[label]) with
+ * the label term only where the label falls in this shard; grad_ref is the array the same
+ * rank's soup_lmhead_ce returned (not a merged one). */
 int soup_lmhead_finish(const float* run_max, const float* run_sum, const float* run_dot,
-                       const int* best, const float* label_logit, const float* label_lse,
-                       const float* local_lse, const int64_t* target, const void* weight,
-                       float* token_loss, float* entropy, int* correct, float* dh, int64_t n,
-                       int64_t h, int64_t v_shard, int64_t col_offset, void* stream);
+                       const int* best, const float* label_logit, const float* grad_ref,
+                       const int64_t* target, const void* weight, float* token_loss,
+                       float* entropy, int* correct, float* dh, int64_t n, int64_t h,
+                       int64_t v_shard, int64_t col_offset, void* stream);
 
 /* out = out_dtype(dh * scale[0]) — _FusedHeadLoss.backward, solution/lm_head_loss.py:248-254. */
 int soup_lmhead_grad_scale(const float* dh, void* out, const float* scale, int64_t n,
