@@ -157,23 +157,29 @@ def run_reference(args, rank):
 # ------------------------------------------------------------------------------------------
 # memory-bound kernels of the path, cold L2 (rotating buffer sets larger than the 126 MB L2)
 # ------------------------------------------------------------------------------------------
-def time_rotating(make_call, n_sets, reps=20):
-    """Median milliseconds of `call(i)` over reps, cycling through n_sets independent buffer sets."""
-    for i in range(min(3, n_sets)):
-        make_call(i % n_sets)
+def time_rotating(make_call, n_sets, reps=10):
+    """Milliseconds per call of `make_call(i)`: the calls over all n_sets buffer sets are captured
+    into one CUDA graph (so the host's launch cost is out of the picture and consecutive launches
+    touch different, L2-cold buffers) and the graph is replayed `reps` times between two events."""
+    for i in range(n_sets):
+        make_call(i)
     torch.cuda.synchronize()
-    times = []
-    for r in range(reps):
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        make_call(r % n_sets)
-        b.record()
-        b.synchronize()
-        times.append(a.elapsed_time(b))
-    return statistics.median(times)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for i in range(n_sets):
+            make_call(i)
+    graph.replay()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(reps):
+        graph.replay()
+    b.record()
+    b.synchronize()
+    return a.elapsed_time(b) / (reps * n_sets)
 
 
-def kernel_suite(dev, hbm_peak, n_rows=2048):
+def kernel_suite(dev, hbm_peak, n_rows=2048, tag="", with_nf4=True):
     from claudemaxing_b200 import _lib, lora, qlora
     from claudemaxing_b200.nf4 import dequantize_nf4
     from claudemaxing_b200.swiglu_recompute import _silu_mul_bwd, _silu_mul_fwd
@@ -186,48 +192,50 @@ def kernel_suite(dev, hbm_peak, n_rows=2048):
 
     def record(name, ms, nbytes, launches=1):
         gbs = nbytes / (ms * 1e-3) / 1e9
-        out[name] = {"ms": round(ms, 5), "gb_s": round(gbs, 1), "frac_of_measured_hbm": round(gbs / hbm_peak, 3),
+        out[name + tag] = {"ms": round(ms, 5), "gb_s": round(gbs, 1), "frac_of_measured_hbm": round(gbs / hbm_peak, 3),
                      "algorithmic_bytes": int(nbytes), "launches": launches}
 
-    # NF4 dequant: the seven projection shapes of one Qwen2.5-1.5B layer, 28 distinct layers
-    shapes = [(1536, 1536), (256, 1536), (256, 1536), (1536, 1536), (8960, 1536), (8960, 1536),
-              (1536, 8960)]
-    code, code2 = qlora.normal_float4_levels().to(dev), qlora.absmax_levels().to(dev)
-    layers = []
-    gen = torch.Generator(device=dev).manual_seed(1)
-    for _ in range(28):
-        layer = []
-        for (o, i) in shapes:
-            n = o * i
-            packed = torch.randint(0, 256, (n // 2, 1), dtype=torch.uint8, device=dev, generator=gen)
-            absmax8 = torch.randint(0, 256, (n // 64,), dtype=torch.uint8, device=dev, generator=gen)
-            inner = qlora.QuantState(torch.rand(-(-n // 64 // 256), device=dev, generator=gen) * 0.01,
-                                     (n // 64,), code2, 256, f32)
-            st = qlora.QuantState(absmax8, (o, i), code, 64, f16,
-                                  offset=torch.tensor([0.02], device=dev), state2=inner)
-            layer.append((packed, st))
-        layers.append(layer)
-    outs = [torch.empty(o * i, dtype=f16, device=dev).view(o, i) for (o, i) in shapes]
-    elems = sum(o * i for o, i in shapes)
+    if with_nf4:
+        # NF4 dequant: the seven projection shapes of one Qwen2.5-1.5B layer, 28 distinct layers
+        shapes = [(1536, 1536), (256, 1536), (256, 1536), (1536, 1536), (8960, 1536), (8960, 1536),
+                  (1536, 8960)]
+        code, code2 = qlora.normal_float4_levels().to(dev), qlora.absmax_levels().to(dev)
+        layers = []
+        gen = torch.Generator(device=dev).manual_seed(1)
+        for _ in range(28):
+            layer = []
+            for (o, i) in shapes:
+                n = o * i
+                packed = torch.randint(0, 256, (n // 2, 1), dtype=torch.uint8, device=dev, generator=gen)
+                absmax8 = torch.randint(0, 256, (n // 64,), dtype=torch.uint8, device=dev, generator=gen)
+                inner = qlora.QuantState(torch.rand(-(-n // 64 // 256), device=dev, generator=gen) * 0.01,
+                                         (n // 64,), code2, 256, f32)
+                st = qlora.QuantState(absmax8, (o, i), code, 64, f16,
+                                      offset=torch.tensor([0.02], device=dev), state2=inner)
+                layer.append((packed, st))
+            layers.append(layer)
+        outs = [torch.empty(o * i, dtype=f16, device=dev).view(o, i) for (o, i) in shapes]
+        elems = sum(o * i for o, i in shapes)
 
-    def nf4_all():
-        for layer in layers:
-            for (packed, st), buf in zip(layer, outs):
-                dequantize_nf4(packed, st, f16, out=buf)
+        def nf4_all():
+            for layer in layers:
+                for (packed, st), buf in zip(layer, outs):
+                    dequantize_nf4(packed, st, f16, out=buf)
 
-    for _ in range(2):
-        nf4_all()
-    torch.cuda.synchronize()
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record()
-    nf4_all()
-    b.record()
-    b.synchronize()
-    record("nf4_dequant_28_layers", a.elapsed_time(b), 2.51587 * elems * 28, launches=28 * 7)
-    big = [(l[4][0], l[4][1]) for l in layers]  # the 8960 x 1536 gate projections, one per layer
-    ms = time_rotating(lambda i: dequantize_nf4(big[i][0], big[i][1], f16, out=outs[4]), len(big))
-    record("nf4_dequant_8960x1536", ms, 2.51587 * 8960 * 1536)
-    del layers, big
+        ms_all = time_rotating(lambda i: nf4_all(), 1, reps=5)
+        record("nf4_dequant_28_layers", ms_all, 2.51587 * elems * 28, launches=28 * 7)
+        from claudemaxing_b200.nf4 import dequantize_nf4_batch
+
+        def nf4_all_batched():  # the seven projections of a layer in one launch
+            for layer in layers:
+                dequantize_nf4_batch(layer, f16, outs=outs)
+
+        ms_b = time_rotating(lambda i: nf4_all_batched(), 1, reps=5)
+        record("nf4_dequant_28_layers_batched_per_layer", ms_b, 2.51587 * elems * 28, launches=28)
+        big = [(l[4][0], l[4][1]) for l in layers]  # the 8960 x 1536 gate projections, one per layer
+        ms = time_rotating(lambda i: dequantize_nf4(big[i][0], big[i][1], f16, out=outs[4]), len(big))
+        record("nf4_dequant_8960x1536", ms, 2.51587 * 8960 * 1536)
+        del layers, big
 
     H, I = 1536, 8960
     # RMSNorm, variant A (fp16 x, fp16 w) and variant B (fp32 x, fp32 w, fp16 copy + side buffer)
@@ -272,8 +280,6 @@ def kernel_suite(dev, hbm_peak, n_rows=2048):
     del xb, ob, lb
 
     # RoPE: packed row [1, n_rows], 12 q heads / 2 kv heads, head_dim 128
-    from claudemaxing_b200.rope import _rotate_pair
-
     nR = sets_for(2 * 14 * n_rows * 128 * 2)
     lens = [n_rows // 4, n_rows * 3 // 16, n_rows * 5 // 16, n_rows // 4]
     pos = torch.cat([torch.arange(x) for x in lens] + [torch.arange(n_rows - sum(lens))])
@@ -285,10 +291,19 @@ def kernel_suite(dev, hbm_peak, n_rows=2048):
     ks = [torch.randn(1, n_rows, 2 * 128, device=dev, dtype=f16).view(1, n_rows, 2, 128).transpose(1, 2)
           for _ in range(nR)]
     rope_bytes = 2 * 14 * n_rows * 128 * 2 + 2 * n_rows * 128 * 2
-    record("rope_fwd_q_and_k", time_rotating(lambda i: _rotate_pair(qs[i], ks[i], cos, sin, f16, f16, False), nR),
-           rope_bytes)
-    record("rope_bwd_q_and_k", time_rotating(lambda i: _rotate_pair(qs[i], ks[i], cos, sin, f16, f16, True), nR),
-           rope_bytes)
+    qo = [torch.empty(1, 12, n_rows, 128, device=dev, dtype=f16) for _ in range(nR)]
+    ko = [torch.empty(1, 2, n_rows, 128, device=dev, dtype=f16) for _ in range(nR)]
+
+    def rope_call(i, backward):
+        q, k = qs[i], ks[i]
+        _lib.call("soup_rope", q.data_ptr(), k.data_ptr(), cos.data_ptr(), sin.data_ptr(),
+                  qo[i].data_ptr(), ko[i].data_ptr(), 1, 12, 2, n_rows, 128, *q.stride()[:3],
+                  *k.stride()[:3], 0, cos.stride(1), _lib.F16, _lib.F16, _lib.F16, _lib.F16, _lib.F16,
+                  int(backward), torch.cuda.current_stream().cuda_stream)
+
+    record("rope_fwd_q_and_k", time_rotating(lambda i: rope_call(i, False), nR), rope_bytes)
+    record("rope_bwd_q_and_k", time_rotating(lambda i: rope_call(i, True), nR), rope_bytes)
+    del qo, ko
     del qs, ks
 
     # SwiGLU forward and recompute-backward writing over its inputs
@@ -308,11 +323,21 @@ def kernel_suite(dev, hbm_peak, n_rows=2048):
     ms_ = [torch.rand(n_rows, H, device=dev) > 0.05 for _ in range(nD)]
     packed_out = [lora._pack(xs[i], ms_[i], 1 / 0.95) for i in range(nD)]
     x16 = [x.half() for x in xs]
-    record("dropout_pack", time_rotating(lambda i: lora._pack(xs[i], ms_[i], 1 / 0.95), nD),
-           n_rows * H * (4 + 1 + 2) + n_rows * H // 8)
-    record("dropout_unpack", time_rotating(
-        lambda i: lora._unpack(x16[i], packed_out[i][1], packed_out[i][0], 1 / 0.95, f32), nD),
-        n_rows * H * (2 + 2 + 2 + 4) + n_rows * H // 8)
+    dxs = [torch.empty(n_rows, H, device=dev) for _ in range(nD)]
+    xd2 = [torch.empty(n_rows, H, device=dev, dtype=f16) for _ in range(nD)]
+    cur = lambda: torch.cuda.current_stream().cuda_stream  # noqa: E731
+
+    def pack(i):
+        _lib.call("soup_dropout_pack", xs[i].data_ptr(), ms_[i].data_ptr(), packed_out[i][0].data_ptr(),
+                  packed_out[i][1].data_ptr(), n_rows * H, 1 / 0.95, _lib.F32, cur())
+
+    def unpack(i):
+        _lib.call("soup_dropout_unpack", x16[i].data_ptr(), packed_out[i][1].data_ptr(),
+                  packed_out[i][0].data_ptr(), xd2[i].data_ptr(), dxs[i].data_ptr(), n_rows * H,
+                  1 / 0.95, _lib.F32, cur())
+
+    record("dropout_pack", time_rotating(pack, nD), n_rows * H * (4 + 1 + 2) + n_rows * H // 8)
+    record("dropout_unpack", time_rotating(unpack, nD), n_rows * H * (2 + 2 + 2 + 4) + n_rows * H // 8)
     return out
 
 
@@ -452,6 +477,9 @@ def main():
         if not args.no_suite:
             del hidden_dev
             kernels = kernel_suite(dev, peak["hbm_gbs"])
+            # the same kernels on 16x the rows: launch ramps amortised, data far larger than L2
+            kernels.update(kernel_suite(dev, peak["hbm_gbs"], n_rows=32768, tag="@32768rows",
+                                        with_nf4=False))
         if not args.no_cpu:
             cores = os.cpu_count() or 1
             w32 = weight_h.float()

@@ -25,6 +25,7 @@ _F = ctypes.c_float
 # name -> argument ctypes, in the order of include/soup_b200.h
 SIGNATURES = {
     "soup_nf4_dequant": [_P, _P, _P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _P],
+    "soup_nf4_dequant_batch": [_P, _I, _P, _I, _I, _I, _I, _P],
     "soup_rmsnorm_fwd": [_P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _F, _I, _I, _I, _P],
     "soup_rmsnorm_bwd": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _I, _I, _I, _I, _I, _P],
     "soup_rmsnorm_bwd_noalloc": [_P, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _I, _I, _I, _I, _I, _P],
@@ -45,6 +46,13 @@ SIGNATURES = {
 }
 _RESTYPE = {"soup_lmhead_workspace_bytes": _L, "soup_rmsnorm_bwd_partials": _L}
 SIGNATURES["soup_rmsnorm_bwd_partials"] = [_L, _L]
+
+class Nf4Item(ctypes.Structure):
+    """soup_nf4_item of include/soup_b200.h."""
+
+    _fields_ = [("packed", _P), ("absmax", _P), ("code2", _P), ("absmax2", _P), ("offset", _P),
+                ("out", _P), ("n_elems", _L)]
+
 
 _lock = threading.Lock()
 _handle = None

@@ -3,7 +3,9 @@
 // Layout of the work: a thread owns VPT column vectors of 8 elements and keeps them in registers;
 // a CTA of TPR threads covers one row (TPR * VPT * 8 >= n_cols) and processes R rows per step so
 // that two rows' worth of 128-bit loads are in flight before the first reduction. The row sums are
-// reduced with warp shuffles and one shared-memory exchange. Backward is persistent when dw is
+// reduced with warp shuffles and one shared-memory exchange. Backward reads each row twice (the
+// second time from L1/L2) instead of holding it in registers, which keeps ten CTAs per SM in
+// flight; it is persistent when dw is
 // wanted: a thread accumulates dw of its own columns in registers across the rows of its CTA and
 // writes one partial row per CTA; a second tiny kernel adds the partial rows in a fixed order, so
 // dw is deterministic.
@@ -179,22 +181,24 @@ rmsnorm_bwd_kernel(const void* __restrict__ dy, const void* __restrict__ xin,
       }
     }
   }
+  // Two passes per row with few live registers, so that many CTAs fit on an SM and their loads
+  // overlap: pass 1 reads dy and x for the row's dot product, pass 2 reads them again (they are
+  // still in L1/L2, the row is 6 KB) and writes dx.
   for (int64_t row = blockIdx.x; row < n_rows; row += gridDim.x) {
-    float gn[VPT][8], nrm[VPT][8];
     const float rstd = rstd_in[row];
     float dot[1] = {0.f};
 #pragma unroll
     for (int j = 0; j < VPT; ++j) {
       const int vi = threadIdx.x + j * blockDim.x;
       if (vi < n_vec) {
-        float yv[8], xv[8];
+        float yv[8], xv[8], gn[8], nrm[8];
         load8(dy, row * n_cols + (vi << 3), ydt, yv);
         load8(xin, row * n_cols + (vi << 3), xdt, xv);
         dot[0] += bwd_prepare(yv, xv, wv[j], sl[j], small, row * n_small, rstd, xdt,
-                              saved_output != 0, gn[j], nrm[j]);
+                              saved_output != 0, gn, nrm);
         if (DW) {
 #pragma unroll
-          for (int k = 0; k < 8; ++k) dw_acc[j][k] += yv[k] * round_through(nrm[j][k], xdt);
+          for (int k = 0; k < 8; ++k) dw_acc[j][k] += yv[k] * round_through(nrm[k], xdt);
         }
       }
     }
@@ -204,9 +208,12 @@ rmsnorm_bwd_kernel(const void* __restrict__ dy, const void* __restrict__ xin,
     for (int j = 0; j < VPT; ++j) {
       const int vi = threadIdx.x + j * blockDim.x;
       if (vi < n_vec) {
-        float o[8];
+        float yv[8], xv[8], gn[8], nrm[8], o[8];
+        load8(dy, row * n_cols + (vi << 3), ydt, yv);
+        load8(xin, row * n_cols + (vi << 3), xdt, xv);
+        bwd_prepare(yv, xv, wv[j], sl[j], small, row * n_small, rstd, xdt, saved_output != 0, gn, nrm);
 #pragma unroll
-        for (int k = 0; k < 8; ++k) o[k] = (gn[j][k] - nrm[j][k] * mean_dot) * rstd;
+        for (int k = 0; k < 8; ++k) o[k] = (gn[k] - nrm[k] * mean_dot) * rstd;
         store8(dx, row * n_cols + (vi << 3), dxdt, o);
       }
     }
@@ -323,7 +330,7 @@ extern "C" int soup_rmsnorm_fwd(const void* x, const void* w, void* out, float* 
                                                                w_dtype, out_dtype);
   } else {
     const Shape sh = pick_shape((int)n_cols);
-    constexpr int R = 2;
+    constexpr int R = 2;  // rows per CTA step (4 measured slower: fewer CTAs fit on an SM)
     const unsigned grid = (unsigned)((n_rows + R - 1) / R);
 #define SOUP_RMS_FWD(V_)                                                                       \
   rmsnorm_fwd_kernel<V_, R><<<grid, sh.tpr, 0, s>>>(x, w, out, rstd, low, slot, small, n_small, \
@@ -369,6 +376,7 @@ extern "C" int soup_rmsnorm_bwd(const void* dy, const void* xin, const void* w, 
   if (!dy || !xin || !w || !rstd || !dx) SOUP_FAIL(SOUP_ERR_ARG, "rmsnorm_bwd: null pointer");
   if (saved_output && (!slot || !small || n_small < 1))
     SOUP_FAIL(SOUP_ERR_ARG, "rmsnorm_bwd: saved-output path needs slot map and side buffer");
+  // one row per CTA, or a persistent grid (more CTAs than fit at once) when dw is accumulated
   const unsigned grid = (unsigned)(want_dw ? bwd_ctas(n_rows) : n_rows);
   const bool vec = (n_cols % 8 == 0) && aligned16(dy) && aligned16(xin) && aligned16(w) &&
                    aligned16(dx) && (!saved_output || aligned16(slot)) &&

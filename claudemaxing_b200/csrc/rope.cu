@@ -2,8 +2,8 @@
 //
 // A thread owns 8 elements of the first half of a head row and the matching 8 of the second half
 // (two 128-bit loads and two 128-bit stores per head). It loads its cos/sin vectors once and walks
-// kHeadsPerThread heads with them, q heads first, then k heads, so cos/sin traffic is amortised
-// over the heads and q and k need a single launch. Inputs are read through their strides (q and k
+// its share of the heads with them, kHeadsPerThread at a time, q heads first, then k heads, so
+// cos/sin traffic is amortised over the heads and q and k need a single launch. Inputs are read through their strides (q and k
 // arrive as transposed views of the projection outputs); outputs are contiguous [b, h, t, d].
 // Arithmetic is fp32, as in qwen_rope_kernel of the reference (solution/rope.py:17-43).
 #include "common.cuh"
@@ -12,7 +12,7 @@ namespace soup {
 namespace {
 
 constexpr int kThreads = 256;
-constexpr int kHeadsPerThread = 2;
+constexpr int kHeadsPerThread = 4;   // heads whose loads are in flight together
 
 struct RopeArgs {
   const void* x[2];   // q, k
@@ -53,32 +53,40 @@ __global__ void __launch_bounds__(kThreads) rope_vec_kernel(RopeArgs a) {
   load8(a.cos, cs_row + half, a.csdt, c2);
   load8(a.sin, cs_row, a.csdt, s1);
   load8(a.sin, cs_row + half, a.csdt, s2);
+  // This thread's share of the heads (q heads first, then k heads); a position's heads are
+  // adjacent in memory, so the threads of a position read whole contiguous rows.
   const int total_heads = a.heads[0] + a.heads[1];
-  const int h0 = blockIdx.y * kHeadsPerThread;
-  float x1[kHeadsPerThread][8], x2[kHeadsPerThread][8];
+  const int per = (total_heads + gridDim.y - 1) / gridDim.y;
+  const int h_begin = blockIdx.y * per;
+  const int h_end = min(total_heads, h_begin + per);
+  for (int h0 = h_begin; h0 < h_end; h0 += kHeadsPerThread) {
+    float x1[kHeadsPerThread][8], x2[kHeadsPerThread][8];
 #pragma unroll
-  for (int u = 0; u < kHeadsPerThread; ++u) {
-    const int h = h0 + u;
-    if (h >= total_heads) break;
-    const int which = h < a.heads[0] ? 0 : 1;
-    const int hh = which ? h - a.heads[0] : h;
-    const int64_t off = bi * a.sb[which] + hh * a.sh[which] + ti * a.st[which] + (gi << 3);
-    load8(a.x[which], off, a.xdt[which], x1[u]);
-    load8(a.x[which], off + half, a.xdt[which], x2[u]);
-  }
+    for (int u = 0; u < kHeadsPerThread; ++u) {
+      const int h = h0 + u;
+      if (h < h_end) {
+        const int which = h < a.heads[0] ? 0 : 1;
+        const int hh = which ? h - a.heads[0] : h;
+        const int64_t off = bi * a.sb[which] + hh * a.sh[which] + ti * a.st[which] + (gi << 3);
+        load8(a.x[which], off, a.xdt[which], x1[u]);
+        load8(a.x[which], off + half, a.xdt[which], x2[u]);
+      }
+    }
 #pragma unroll
-  for (int u = 0; u < kHeadsPerThread; ++u) {
-    const int h = h0 + u;
-    if (h >= total_heads) break;
-    const int which = h < a.heads[0] ? 0 : 1;
-    const int hh = which ? h - a.heads[0] : h;
-    float o1[8], o2[8];
+    for (int u = 0; u < kHeadsPerThread; ++u) {
+      const int h = h0 + u;
+      if (h < h_end) {
+        const int which = h < a.heads[0] ? 0 : 1;
+        const int hh = which ? h - a.heads[0] : h;
+        float o1[8], o2[8];
 #pragma unroll
-    for (int k = 0; k < 8; ++k)
-      rotate(x1[u][k], x2[u][k], c1[k], c2[k], s1[k], s2[k], a.backward, o1[k], o2[k]);
-    const int64_t orow = ((bi * a.heads[which] + hh) * a.t + ti) * a.d + (gi << 3);
-    store8(a.out[which], orow, a.odt[which], o1);
-    store8(a.out[which], orow + half, a.odt[which], o2);
+        for (int k = 0; k < 8; ++k)
+          rotate(x1[u][k], x2[u][k], c1[k], c2[k], s1[k], s2[k], a.backward, o1[k], o2[k]);
+        const int64_t orow = ((bi * a.heads[which] + hh) * a.t + ti) * a.d + (gi << 3);
+        store8(a.out[which], orow, a.odt[which], o1);
+        store8(a.out[which], orow + half, a.odt[which], o2);
+      }
+    }
   }
 }
 
@@ -143,8 +151,13 @@ extern "C" int soup_rope(const void* q, const void* k, const void* cos, const vo
   if (hk) vec = vec && aligned16(k) && aligned16(k_out) && mult8(k_sb) && mult8(k_sh) && mult8(k_st);
   if (vec) {
     const int64_t threads = b * t * (d >> 4);
-    dim3 grid((unsigned)((threads + kThreads - 1) / kThreads),
-              (unsigned)((hq + hk + kHeadsPerThread - 1) / kHeadsPerThread));
+    // One thread walks all heads of its position when there are enough positions to fill the
+    // GPU; otherwise the heads are split over grid.y so that about 2^17 threads exist.
+    int64_t hsplit = (131072 + threads - 1) / threads;
+    const int64_t max_split = (hq + hk + kHeadsPerThread - 1) / kHeadsPerThread;
+    if (hsplit > max_split) hsplit = max_split;
+    if (hsplit < 1) hsplit = 1;
+    dim3 grid((unsigned)((threads + kThreads - 1) / kThreads), (unsigned)hsplit);
     rope_vec_kernel<<<grid, kThreads, 0, s>>>(a);
   } else {
     const int64_t n = b * (hq + hk) * t * (d >> 1);

@@ -68,6 +68,45 @@ def dequantize_nf4(packed, state, dtype=None, out=None):
     return out
 
 
+def dequantize_nf4_batch(weights, dtype=None, outs=None):
+    """Dequantises several NF4 weights with one launch per eight tensors. `weights` is a list of
+    (packed, state) with a common blocksize / nesting; returns the list of [N, K] tensors
+    (`outs`, when given, are filled instead of allocating)."""
+    import ctypes
+
+    if not weights:
+        return []
+    first = weights[0][1]
+    dtype = dtype or first.dtype
+    nested = bool(first.nested)
+    items = (_lib.Nf4Item * len(weights))()
+    results = []
+    keep = []  # tensors whose pointers are in `items` must outlive the launch call
+    for i, (packed, st) in enumerate(weights):
+        _lib.require_cuda(packed)
+        if (bool(st.nested) != nested or st.blocksize != first.blocksize
+                or (nested and st.state2.blocksize != first.state2.blocksize)):
+            raise ValueError("a batch shares blocksize and nesting")
+        out = outs[i] if outs is not None else torch.empty(tuple(st.shape), dtype=dtype,
+                                                           device=packed.device)
+        results.append(out)
+        absmax = st.absmax.contiguous()
+        keep.append(absmax)
+        items[i].packed, items[i].absmax, items[i].out = packed.data_ptr(), absmax.data_ptr(), out.data_ptr()
+        items[i].n_elems = st.shape[0] * st.shape[1]
+        if nested:
+            code2, absmax2 = st.state2.code.contiguous(), st.state2.absmax.contiguous()
+            offset = _offset_tensor(st.offset, packed.device)
+            keep += [code2, absmax2, offset]
+            items[i].code2, items[i].absmax2, items[i].offset = (code2.data_ptr(), absmax2.data_ptr(),
+                                                                 offset.data_ptr())
+    _lib.call("soup_nf4_dequant_batch", ctypes.cast(items, ctypes.c_void_p), len(weights),
+              _lib.ptr(first.code), int(first.blocksize),
+              int(first.state2.blocksize) if nested else 1, int(nested),
+              _lib.dtype_code(results[0].dtype), _lib.stream_of(weights[0][0]))
+    return results
+
+
 ORIGINALS = {}
 _CODE = {}
 

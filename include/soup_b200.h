@@ -54,6 +54,23 @@ int soup_nf4_dequant(const void* packed, const void* absmax, const float* code, 
                      const float* absmax2, const float* offset, void* out, int64_t n_elems,
                      int blocksize, int blocksize2, int nested, int out_dtype, void* stream);
 
+/* The same for several weights in one launch per 8 tensors (e.g. the seven projections of a
+ * decoder layer): one element of `items` (a host array) per tensor, fields as the arguments of
+ * soup_nf4_dequant; blocksize, blocksize2, nested and out_dtype are common to the batch. The
+ * reference dequantises one weight per launch (solution/nf4.py:78-81); on B200 the launch latency
+ * is longer than the data movement of the small projections. */
+typedef struct {
+  const void* packed;
+  const void* absmax;
+  const float* code2;
+  const float* absmax2;
+  const float* offset;
+  void* out;
+  int64_t n_elems;
+} soup_nf4_item;
+int soup_nf4_dequant_batch(const soup_nf4_item* items, int count, const float* code, int blocksize,
+                           int blocksize2, int nested, int out_dtype, void* stream);
+
 /* RMSNorm forward: rstd = 1/sqrt(mean(x^2)+eps); normed = round_x_dtype(x*rstd);
  * out = round_out_dtype(normed*w). Replaces qwen_rmsnorm_fwd_kernel at solution/rmsnorm.py:180-184
  * (kernel :28-47).

@@ -81,6 +81,22 @@ def test_nf4_quantiser_matches_oracle_and_roundtrip_is_idempotent():
     assert (p_again != p_first).float().mean().item() < 0.02
 
 
+def test_nf4_batched_launch_is_bit_identical_to_single_launches():
+    from claudemaxing_b200.nf4 import dequantize_nf4, dequantize_nf4_batch
+    from oracle import nf4 as onf4
+
+    shapes = [(1536, 1536), (256, 1536), (256, 1536), (1536, 1536), (8960, 1536), (8960, 1536),
+              (1536, 8960), (3, 64), (7, 34)]  # one decoder layer + two odd ones: two launches
+    weights = []
+    for i, shape in enumerate(shapes):
+        w = (torch.randn(*shape, generator=torch.Generator().manual_seed(i)) * 0.02).half()
+        packed, state = onf4.quantize_nf4(w, blocksize=64)
+        weights.append((packed.to(DEV), state.to(DEV)))
+    batched = dequantize_nf4_batch(weights)
+    for (packed, state), got in zip(weights, batched):
+        assert torch.equal(_bits(got), _bits(dequantize_nf4(packed, state)))
+
+
 def test_nf4_rejects_bad_arguments():
     from claudemaxing_b200 import _lib
 
