@@ -341,6 +341,72 @@ def kernel_suite(dev, hbm_peak, n_rows=2048, tag="", with_nf4=True):
     return out
 
 
+
+# ------------------------------------------------------------------------------------------
+def qlora_step_leg(dev, rank, world, steps, warmup, timed):
+    """BASELINE config 4 (and 5b at N>1): the full Qwen2.5-1.5B-architecture QLoRA step, batch 4 per
+    GPU with lengths uniform in [64, 512], packed; forward, backward, LoRA-gradient all-reduce at
+    N>1, fused AdamW. Timed as CUDA-graph replays (CapturedStep) and, for comparison, eagerly."""
+    import torch.distributed as dist
+
+    import claudemaxing_b200 as solution
+    from claudemaxing_b200 import qlora
+
+    solution.apply()
+    model, lora = qlora.build_qlora_model(dev, seed=0)          # same weights on every rank
+    batch = qlora.synthetic_batch(seed=3 + rank)                 # each rank its own 4 rows (host)
+    for k in ("input_ids", "attention_mask", "labels"):
+        batch[k] = batch[k].pin_memory()
+    n_real = torch.tensor([batch["n_tokens"]], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(n_real)
+    n_real = int(n_real.item())
+    optimizer = torch.optim.AdamW(lora, lr=1e-4, fused=True, capturable=True)
+    scaler = torch.amp.GradScaler("cuda", init_scale=65536.0)
+    bucket = -(-batch["n_tokens"] // 128) * 128   # real tokens rounded up to the kernels' 128-row tile
+    captured = qlora.CapturedStep(model, lora, optimizer, bucket_tokens=bucket, scaler=scaler)
+    captured.load(batch)
+    first = float(captured.run())
+    for _ in range(max(warmup, 3)):
+        captured.run()
+    ms = timed(captured.run, steps) / steps
+
+    def e2e():
+        captured.load(batch)
+        return captured.run().item()
+
+    for _ in range(3):
+        last = e2e()
+    e2e_ms = timed(e2e, steps) / steps
+    dev_batch = {k: (v.to(dev) if torch.is_tensor(v) else v) for k, v in batch.items()}
+    eager_opt = torch.optim.AdamW(lora, lr=1e-4, fused=True)
+
+    def eager():
+        qlora.qlora_step(model, dev_batch, None, None)
+        if world > 1:
+            from claudemaxing_b200.parallel import allreduce_lora_grads
+            allreduce_lora_grads(lora)
+        eager_opt.step()
+        eager_opt.zero_grad(set_to_none=True)
+
+    for _ in range(2):
+        eager()
+    eager_ms = timed(eager, 5) / 5
+    return {
+        "metric": "QLoRA step tokens/s/GPU", "value": round(n_real / world / (ms * 1e-3), 1),
+        "aggregate_tokens_per_s": round(n_real / (ms * 1e-3), 1), "ms_per_step": round(ms, 4),
+        "real_tokens_per_step": n_real, "bucket_tokens_per_gpu": captured.bucket,
+        "e2e": {"value": round(n_real / world / (e2e_ms * 1e-3), 1), "ms_per_step": round(e2e_ms, 4),
+                "h2d_bytes_per_step": 4 * captured.bucket * 8, "d2h_bytes_per_step": 4},
+        "eager_ms_per_step": round(eager_ms, 4),
+        "loss_first": round(first, 5), "loss_last": round(float(last), 5),
+        "config": "configs[3]: 28 layers, hidden 1536, GQA 12/2, vocab 151936 tied, NF4 + LoRA r=16 "
+                  "on q_proj/v_proj, batch 4 x U[64,512] packed, fp16 autocast, dynamic loss scale, "
+                  "fused AdamW" + ("" if world == 1 else f"; data-parallel x{world}, flat LoRA-gradient all-reduce"),
+        "timing": "two CUDA graphs per step (forward+backward, optimizer), all-reduce between them",
+    }
+
+
 # ------------------------------------------------------------------------------------------
 def main():
     ap = argparse.ArgumentParser()
@@ -351,6 +417,7 @@ def main():
     ap.add_argument("--workload", default="c1", choices=["c1", "c5a"])
     ap.add_argument("--no-suite", action="store_true", help="skip the memory-bound kernel suite")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-step", action="store_true", help="skip the full QLoRA training step leg")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank = int(os.environ.get("RANK", "0"))
@@ -490,6 +557,12 @@ def main():
                    "sample": f"{rows} of the 2048 rows x full vocabulary, one pass, torch fp32 "
                              "matmul + log_softmax + autograd (oracle/head_ce.py)"}
 
+    step_leg = None
+    if not args.no_step and args.workload == "c1":
+        del w_dev
+        torch.cuda.empty_cache()
+        step_leg = qlora_step_leg(dev, rank, world, max(5, min(args.steps, 20)), args.warmup, timed)
+
     if rank == 0:
         line = {
             "metric": "fused LM-head+CE fwd+bwd tokens/s", "value": round(value, 1),
@@ -521,6 +594,8 @@ def main():
             line["kernels"] = kernels
         if cpu is not None:
             line["cpu_baseline"] = cpu
+        if step_leg is not None:
+            line["qlora_step"] = step_leg
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

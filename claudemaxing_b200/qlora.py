@@ -14,6 +14,7 @@ ops on whatever device the weight is on; it is set-up code, not part of the step
 """
 
 import math
+from types import SimpleNamespace
 
 import torch
 import torch.nn.functional as F
@@ -114,18 +115,21 @@ class NF4Linear(torch.nn.Module):
 
     _soup_nf4_linear = True
 
-    def __init__(self, in_features, out_features, packed, quant_state, compute_dtype=torch.float16):
+    def __init__(self, in_features, out_features, packed, quant_state, compute_dtype=torch.float16,
+                 bias=None):
         super().__init__()
         self.in_features, self.out_features = in_features, out_features
         self.register_buffer("packed", packed, persistent=False)
         self.quant_state = quant_state
         self.compute_dtype = compute_dtype
         self.bias = None
+        if bias is not None:
+            self.bias = torch.nn.Parameter(bias.detach().clone(), requires_grad=False)
 
     @classmethod
-    def from_weight(cls, weight, compute_dtype=torch.float16, blocksize=64):
+    def from_weight(cls, weight, compute_dtype=torch.float16, blocksize=64, bias=None):
         packed, state = quantize_nf4(weight.to(torch.float16), blocksize=blocksize, nested=True)
-        return cls(weight.shape[1], weight.shape[0], packed, state, compute_dtype)
+        return cls(weight.shape[1], weight.shape[0], packed, state, compute_dtype, bias)
 
     def _apply(self, fn, *args, **kwargs):
         super()._apply(fn, *args, **kwargs)
@@ -136,7 +140,10 @@ class NF4Linear(torch.nn.Module):
         return _MatMul4Bit.apply(x_low, self)
 
     def forward(self, x):
-        return self.matmul_4bit(x.to(self.compute_dtype)).to(x.dtype)
+        out = self.matmul_4bit(x.to(self.compute_dtype))
+        if self.bias is not None:
+            out = out + self.bias.to(out.dtype)
+        return out.to(x.dtype)
 
 
 class LoRALinear(torch.nn.Module):
@@ -161,3 +168,211 @@ class LoRALinear(torch.nn.Module):
             return result + lora
         xa = F.dropout(x.to(self.lora_A.weight.dtype), self.p, self.training)
         return result + self.lora_B(self.lora_A(xa)) * self.scaling
+
+
+QWEN25_1P5B = dict(hidden_size=1536, intermediate_size=8960, num_hidden_layers=28,
+                   num_attention_heads=12, num_key_value_heads=2, vocab_size=151936,
+                   max_position_embeddings=32768, rms_norm_eps=1e-6, rope_theta=1e6,
+                   tie_word_embeddings=True)
+
+
+def build_qlora_model(device, config=None, lora_targets=("q_proj", "v_proj"), r=16, alpha=32,
+                      dropout=0.05, seed=0):
+    """A Qwen2 causal LM prepared the way the reference's run prepares it, without its packages:
+    random fp16 weights of the given architecture (default Qwen2.5-1.5B), every decoder
+    projection NF4-quantised (blocksize 64, double-quantised absmax), norms and the tied
+    embedding/head in fp32 and frozen, LoRA (fp32 A Kaiming-uniform, B zero) on q_proj and v_proj.
+    Returns (model, list of trainable LoRA parameters)."""
+    from transformers import Qwen2Config, Qwen2ForCausalLM
+
+    cfg = dict(QWEN25_1P5B)
+    cfg.update(config or {})
+    hf_cfg = Qwen2Config(**cfg)
+    hf_cfg._attn_implementation = "sdpa"
+    torch.manual_seed(seed)
+    with torch.device(device):
+        model = Qwen2ForCausalLM(hf_cfg).to(torch.float16)
+    for p in model.parameters():
+        p.requires_grad_(False)
+    for layer in model.model.layers:
+        for parent, names in ((layer.self_attn, ("q_proj", "k_proj", "v_proj", "o_proj")),
+                              (layer.mlp, ("gate_proj", "up_proj", "down_proj"))):
+            for name in names:
+                lin = getattr(parent, name)
+                q = NF4Linear.from_weight(lin.weight.data, bias=lin.bias)
+                if name in lora_targets:
+                    q = LoRALinear(q, r=r, alpha=alpha, dropout=dropout).to(device)
+                setattr(parent, name, q)
+                del lin
+    # what prepare_model_for_kbit_training leaves: fp32 norms and fp32 (tied) embedding
+    for module in model.modules():
+        if type(module).__name__ == "Qwen2RMSNorm":
+            module.weight.data = module.weight.data.float()
+    model.model.embed_tokens.weight.data = model.model.embed_tokens.weight.data.float()
+    if hf_cfg.tie_word_embeddings:
+        model.lm_head.weight = model.model.embed_tokens.weight
+    lora_params = [p for n, p in model.named_parameters() if "lora_" in n]
+    for p in lora_params:
+        p.requires_grad_(True)
+    torch.cuda.empty_cache() if torch.cuda.is_available() else None
+    return model, lora_params
+
+
+def synthetic_batch(batch=4, min_len=64, max_len=512, vocab=151936, seed=3, device="cpu"):
+    """Right-padded batch of random token ids with lengths uniform in [min_len, max_len];
+    labels = inputs, -100 on the padding (the loss shifts them)."""
+    gen = torch.Generator().manual_seed(seed)
+    lengths = torch.randint(min_len, max_len + 1, (batch,), generator=gen)
+    width = int(lengths.max())
+    ids = torch.randint(0, vocab, (batch, width), generator=gen)
+    mask = (torch.arange(width)[None, :] < lengths[:, None]).long()
+    labels = torch.where(mask.bool(), ids, torch.full_like(ids, -100))
+    ids = ids * mask
+    return dict(input_ids=ids.to(device), attention_mask=mask.to(device), labels=labels.to(device),
+                n_tokens=int(lengths.sum()))
+
+
+def qlora_step(model, batch, optimizer=None, scaler=None, num_items=None):
+    """One training step under fp16 autocast through the patched forward (packed real tokens,
+    fused head): loss, backward, optional optimizer step. Returns the detached loss."""
+    from .lm_head_loss import _REQUEST_ATTR
+
+    model.train()
+    model.__dict__[_REQUEST_ATTR] = True  # what the patched SFTTrainer.compute_loss sets
+    with torch.autocast("cuda", dtype=torch.float16):
+        out = model(input_ids=batch["input_ids"], attention_mask=batch["attention_mask"],
+                    labels=batch["labels"], use_cache=False,
+                    **({"num_items_in_batch": num_items} if num_items is not None else {}))
+    loss = out.loss
+    (scaler.scale(loss) if scaler is not None else loss).backward()
+    if optimizer is not None:
+        if scaler is not None:
+            scaler.step(optimizer)
+            scaler.update()
+        else:
+            optimizer.step()
+        optimizer.zero_grad(set_to_none=True)
+    return loss.detach()
+
+
+class CapturedStep:
+    """One QLoRA training step replayed from CUDA graphs instead of ~3000 eager launches.
+
+    The packed real tokens of a batch are padded up to `bucket_tokens` (padding tokens attend to
+    nothing but themselves and carry ignore labels, so loss and gradients are those of the real
+    tokens) and copied into fixed device buffers. Forward, backward and the loss-scaled gradient
+    clean-up are one graph; the optimizer step is a second one, so a data-parallel job can
+    all-reduce the LoRA gradients (one flat fp32 buffer that every `.grad` is a view of) between
+    the two. The eager launch sequence it replaces is the trainer's compute_loss → backward →
+    optimizer.step of the reference (solution/lm_head_loss.py:375-430 wraps the first).
+
+    `load()` takes a host or device batch and moves 4 × bucket_tokens int64 values; `run()` replays
+    and returns the (device) loss of the step.
+    """
+
+    def __init__(self, model, params, optimizer, bucket_tokens, scaler=None, loss_scale=1024.0,
+                 group=None, warmup=3):
+        from . import lm_head_loss as L
+
+        self._L = L
+        self.model, self.params, self.optimizer, self.scaler = model, list(params), optimizer, scaler
+        self.loss_scale = float(loss_scale)
+        self.group = group
+        self.world = 1
+        if group is not None or (torch.distributed.is_available() and torch.distributed.is_initialized()):
+            self.world = torch.distributed.get_world_size(group)
+        dev = self.params[0].device
+        n = int(bucket_tokens)
+        self.bucket = n
+        self.ids = torch.zeros(1, n, dtype=torch.int64, device=dev)
+        self.col = torch.zeros(1, n, dtype=torch.int64, device=dev)
+        self.row = torch.arange(n, dtype=torch.int64, device=dev)[None].clone()
+        self.target = torch.full((1, n), -100, dtype=torch.int64, device=dev)
+        self.index = torch.arange(n, dtype=torch.int64, device=dev)
+        # every LoRA gradient is a view of one flat buffer: one all-reduce, no gather/scatter
+        total = sum(p.numel() for p in self.params)
+        self.flat_grad = torch.zeros(total, dtype=self.params[0].dtype, device=dev)
+        offset = 0
+        for p in self.params:
+            p.grad = self.flat_grad[offset:offset + p.numel()].view_as(p)
+            offset += p.numel()
+        self.loss = None
+        self._capture(warmup)
+
+    # ------------------------------------------------------------------ host side of a step
+    def load(self, batch):
+        """Packs `batch` (input_ids, attention_mask, labels of shape [B, T], host or device) and
+        copies ids / positions / row ids / shifted labels into the graph's buffers."""
+        L = self._L
+        ids, mask, labels = batch["input_ids"], batch["attention_mask"], batch["labels"]
+        B, T = ids.shape
+        keep = (mask.reshape(-1) != 0).nonzero().squeeze(1)
+        n = keep.numel()
+        if n > self.bucket:
+            raise ValueError(f"batch has {n} real tokens, the captured step holds {self.bucket}")
+        target = L.shift_labels_left(labels).reshape(-1)[keep]
+        stage = torch.empty(4, self.bucket, dtype=torch.int64, device=ids.device,
+                            pin_memory=not ids.is_cuda)
+        stage[0, :n] = ids.reshape(-1)[keep]
+        stage[1, :n] = keep % T
+        stage[2, :n] = keep // T
+        stage[3, :n] = target
+        if n < self.bucket:
+            pad = torch.arange(self.bucket - n, dtype=torch.int64, device=ids.device)
+            stage[0, n:] = 0
+            stage[1, n:] = 0
+            stage[2, n:] = B + pad      # a row of its own per padding token
+            stage[3, n:] = -100
+        self.ids.copy_(stage[0:1], non_blocking=True)
+        self.col.copy_(stage[1:2], non_blocking=True)
+        self.row.copy_(stage[2:3], non_blocking=True)
+        self.target.copy_(stage[3:4], non_blocking=True)
+        return n
+
+    def run(self):
+        self.graph_fb.replay()
+        if self.world > 1:
+            torch.distributed.all_reduce(self.flat_grad, group=self.group)
+            self.flat_grad.div_(self.world)
+        self.graph_opt.replay()
+        return self.loss
+
+    # ------------------------------------------------------------------ captured bodies
+    def _forward_backward(self):
+        L = self._L
+        row, col = self.row[0], self.col[0]
+        allowed = (row[:, None] == row[None, :]) & (col[None, :] <= col[:, None])
+        packed = SimpleNamespace(B=1, T=self.bucket, index=self.index, ids=self.ids, pos=self.col,
+                                 mask=allowed[None, None], target=self.target)
+        self.flat_grad.zero_()
+        with torch.autocast("cuda", dtype=torch.float16):
+            out = L._packed_forward(self.model, {"use_cache": False}, packed)
+        scaled = self.scaler.scale(out.loss) if self.scaler is not None else out.loss * self.loss_scale
+        scaled.backward()
+        return out.loss.detach()
+
+    def _optimizer_step(self):
+        if self.scaler is not None:
+            self.scaler.step(self.optimizer)
+            self.scaler.update()
+        else:
+            self.flat_grad.div_(self.loss_scale)
+            self.optimizer.step()
+
+    def _capture(self, warmup):
+        self.model.train()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(max(1, warmup)):
+                self._forward_backward()
+                self._optimizer_step()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        self.graph_fb = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph_fb):
+            self.loss = self._forward_backward()
+        self.graph_opt = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph_opt, pool=self.graph_fb.pool()):
+            self._optimizer_step()
+        torch.cuda.synchronize()

@@ -1,0 +1,129 @@
+"""The whole QLoRA training step through the patched model (packed tokens, NF4 linears, LoRA
+branch, RoPE, RMSNorm, SwiGLU recompute, fused head) against the installed transformers code run
+on the CPU in fp32 on the same weights. Criterion of the reference's end-to-end test
+(tests_local/test_lm_head_trainer.py:186-188): loss within 1 %; here also the LoRA gradients."""
+
+import pytest
+import torch
+
+from conftest import rel_norm
+
+pytestmark = pytest.mark.gpu
+
+TINY = dict(hidden_size=256, intermediate_size=512, num_hidden_layers=2, num_attention_heads=4,
+            num_key_value_heads=2, vocab_size=3000, max_position_embeddings=512)
+
+
+class _RefLoRA(torch.nn.Module):
+    def __init__(self, weight, bias, a, b, scaling):
+        super().__init__()
+        self.weight, self.bias, self.scaling = weight, bias, scaling
+        self.a = torch.nn.Parameter(a.clone())
+        self.b = torch.nn.Parameter(b.clone())
+
+    def forward(self, x):
+        base = torch.nn.functional.linear(x, self.weight, self.bias)
+        return base + torch.nn.functional.linear(torch.nn.functional.linear(x, self.a), self.b) * self.scaling
+
+
+def _cpu_reference(model_gpu, cfg):
+    """fp32 CPU copy with plain nn.Linear layers holding the dequantised weights."""
+    from transformers import Qwen2Config, Qwen2ForCausalLM
+
+    from claudemaxing_b200.nf4 import dequantize_nf4
+    from claudemaxing_b200.qlora import LoRALinear
+
+    hf_cfg = Qwen2Config(**model_gpu.config.to_dict())  # the builder's defaults (rope_theta, eps) included
+    hf_cfg._attn_implementation = "sdpa"
+    ref = Qwen2ForCausalLM(hf_cfg).float()
+    ref.model.embed_tokens.weight.data = model_gpu.model.embed_tokens.weight.detach().float().cpu()
+    ref.lm_head.weight = ref.model.embed_tokens.weight
+    ref.model.norm.weight.data = model_gpu.model.norm.weight.detach().float().cpu()
+    refs = {}
+    for lg, lr in zip(model_gpu.model.layers, ref.model.layers):
+        lr.input_layernorm.weight.data = lg.input_layernorm.weight.detach().float().cpu()
+        lr.post_attention_layernorm.weight.data = lg.post_attention_layernorm.weight.detach().float().cpu()
+        for pg, pr, names in ((lg.self_attn, lr.self_attn, ("q_proj", "k_proj", "v_proj", "o_proj")),
+                              (lg.mlp, lr.mlp, ("gate_proj", "up_proj", "down_proj"))):
+            for name in names:
+                mod = getattr(pg, name)
+                base = mod.base_layer if isinstance(mod, LoRALinear) else mod
+                w = dequantize_nf4(base.packed, base.quant_state, torch.float16).float().cpu()
+                bias = None if base.bias is None else base.bias.detach().float().cpu()
+                if isinstance(mod, LoRALinear):
+                    r = _RefLoRA(w, bias, mod.lora_A.weight.detach().cpu(), mod.lora_B.weight.detach().cpu(),
+                                 mod.scaling)
+                    setattr(pr, name, r)
+                    refs[id(mod)] = r
+                else:
+                    lin = getattr(pr, name)
+                    lin.weight.data = w
+                    if bias is not None:
+                        lin.bias.data = bias
+                    else:
+                        lin.bias = None
+    for p in ref.parameters():
+        p.requires_grad_(False)
+    for r in refs.values():
+        r.a.requires_grad_(True)
+        r.b.requires_grad_(True)
+    return ref, refs
+
+
+def test_step_matches_installed_transformers_on_cpu():
+    import claudemaxing_b200 as solution
+    from claudemaxing_b200 import qlora
+    from claudemaxing_b200.qlora import LoRALinear
+
+    solution.apply()
+    model, lora = qlora.build_qlora_model("cuda", TINY, dropout=1e-6, seed=1)
+    # B = 0 would make the adapter output and dA vanish: give B small values
+    torch.manual_seed(2)
+    for m in model.modules():
+        if isinstance(m, LoRALinear):
+            m.lora_B.weight.data.normal_(0, 0.02)
+    ref, refs = _cpu_reference(model, TINY)
+    batch = qlora.synthetic_batch(batch=4, min_len=16, max_len=96, vocab=TINY["vocab_size"], seed=5)
+    ref_out = ref(input_ids=batch["input_ids"], attention_mask=batch["attention_mask"],
+                  labels=batch["labels"])
+    ref_out.loss.backward()
+    dev_batch = {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in batch.items()}
+    calls = []
+    from claudemaxing_b200 import lm_head_loss
+
+    original = lm_head_loss.fused_head_loss
+
+    def spy(*args, **kwargs):  # the fused head must be what produced the loss
+        calls.append(1)
+        return original(*args, **kwargs)
+
+    lm_head_loss.fused_head_loss = spy
+    try:
+        loss = qlora.qlora_step(model, dev_batch)
+    finally:
+        lm_head_loss.fused_head_loss = original
+    assert calls, "the fused head did not run"
+    assert abs(loss.item() - ref_out.loss.item()) <= 1e-2 * abs(ref_out.loss.item())
+    checked = 0
+    for m in model.modules():
+        if isinstance(m, LoRALinear):
+            r = refs[id(m)]
+            assert rel_norm(m.lora_B.weight.grad.cpu(), r.b.grad) < 5e-2
+            assert rel_norm(m.lora_A.weight.grad.cpu(), r.a.grad) < 5e-2
+            checked += 1
+    assert checked == 2 * TINY["num_hidden_layers"]
+
+
+def test_step_trains():
+    import claudemaxing_b200 as solution
+    from claudemaxing_b200 import qlora
+
+    solution.apply()
+    model, lora = qlora.build_qlora_model("cuda", TINY, seed=3)
+    batch = qlora.synthetic_batch(batch=4, min_len=16, max_len=96, vocab=TINY["vocab_size"],
+                                  seed=6, device="cuda")
+    opt = torch.optim.AdamW(lora, lr=2e-3)
+    scaler = torch.amp.GradScaler("cuda")
+    losses = [qlora.qlora_step(model, batch, opt, scaler).item() for _ in range(8)]
+    assert all(torch.isfinite(torch.tensor(losses)))
+    assert losses[-1] < losses[0]
