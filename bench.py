@@ -71,12 +71,13 @@ class ClockSampler:
 
     def __init__(self, index):
         self.samples, self.proc, self.index = [], None, index
+        self.windows = []   # (start, end) wall-clock spans of the timed regions
 
     def __enter__(self):
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
-                 "--format=csv,noheader,nounits", "-lms", "100"],
+                 "--format=csv,noheader,nounits", "-lms", "50"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -84,11 +85,16 @@ class ClockSampler:
             self.proc = None
         return self
 
+    def wait_first_sample(self, limit_s=8.0):
+        t0 = time.time()
+        while self.proc is not None and not self.samples and time.time() - t0 < limit_s:
+            time.sleep(0.05)
+
     def _read(self):
         for line in self.proc.stdout:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) == 6:
-                self.samples.append(parts)
+                self.samples.append(parts + [time.time()])
 
     def __exit__(self, *exc):
         if self.proc is not None:
@@ -102,12 +108,18 @@ class ClockSampler:
     def summary(self):
         if not self.samples:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        sm = [float(s[0]) for s in self.samples if s[0].replace(".", "").isdigit()]
+        # samples taken inside a timed region (the sampler's period is 50 ms, so a sample stamped
+        # up to one period after a region's end still describes it); all samples if none fell inside
+        inside = [s for s in self.samples
+                  if any(a <= s[6] <= b + 0.05 for a, b in self.windows)]
+        used = inside or self.samples
+        sm = [float(s[0]) for s in used if s[0].replace(".", "").isdigit()]
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        reasons = [n for i, n in enumerate(names) if any(s[2 + i] == "Active" for s in self.samples)]
+        reasons = [n for i, n in enumerate(names) if any(s[2 + i] == "Active" for s in used)]
         return {"sm_mhz": statistics.median(sm) if sm else None,
-                "sm_max_mhz": float(self.samples[0][1]) if self.samples[0][1].isdigit() else None,
-                "reasons": reasons, "samples": len(self.samples)}
+                "sm_max_mhz": float(used[0][1]) if used[0][1].isdigit() else None,
+                "reasons": reasons, "samples": len(used),
+                "scope": "inside the timed regions" if inside else "whole run (regions shorter than the sampling period)"}
 
 
 def cpu_head_tokens_per_s(hidden, weight, target, rows, threads):
@@ -363,9 +375,7 @@ def qlora_step_leg(dev, rank, world, steps, warmup, timed):
     n_real = int(n_real.item())
     optimizer = torch.optim.AdamW(lora, lr=1e-4, fused=True, capturable=True)
     scaler = torch.amp.GradScaler("cuda", init_scale=65536.0)
-    bucket = -(-batch["n_tokens"] // 128) * 128   # real tokens rounded up to the kernels' 128-row tile
-    captured = qlora.CapturedStep(model, lora, optimizer, bucket_tokens=bucket, scaler=scaler)
-    captured.load(batch)
+    captured = qlora.CapturedStep(model, lora, optimizer, batch, scaler=scaler)
     first = float(captured.run())
     for _ in range(max(warmup, 3)):
         captured.run()
@@ -468,21 +478,28 @@ def main():
     def timed(fn, steps):
         barrier()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.time()
         a.record()
         for _ in range(steps):
             fn()
         b.record()
         barrier()
+        clocks.windows.append((t0, time.time()))
         ms = torch.tensor([a.elapsed_time(b)], device=dev)
         if world > 1:
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return ms.item()
 
     # ---- device-resident region (value)
+    # The clock sampler starts before the warm-up and is polled until its first sample arrives:
+    # nvidia-smi's start-up takes driver locks that stall launches, so it must be over before the
+    # timed regions begin. It keeps sampling through the value, e2e and per-kernel regions.
+    clocks = ClockSampler(local_rank)
+    clocks.__enter__()
+    clocks.wait_first_sample()
     for _ in range(args.warmup):
         loss, _ = step(hidden_dev, target_dev)
-    with ClockSampler(local_rank) as clocks:
-        total_ms = timed(lambda: step(hidden_dev, target_dev), args.steps)
+    total_ms = timed(lambda: step(hidden_dev, target_dev), args.steps)
     ms_per_step = total_ms / args.steps
     value = n_tokens / (ms_per_step * 1e-3)
 
@@ -508,6 +525,7 @@ def main():
         step(hidden_dev, target_dev)
     barrier()
     _lib.lib().soup_lmhead_set_timing(None)
+    clocks.__exit__(None, None, None)
     k_ms = [sink[i] / args.steps for i in range(3)]
     k_launch = [int(round(sink[3 + i] / args.steps)) for i in range(3)]
     v_local = bounds[rank + 1] - bounds[rank]

@@ -14,6 +14,7 @@ ops on whatever device the weight is on; it is set-up code, not part of the step
 """
 
 import math
+import weakref
 from types import SimpleNamespace
 
 import torch
@@ -21,6 +22,7 @@ import torch.nn.functional as F
 
 from .lora import LoRABranch, _shared_fp16, branch_covers
 from .nf4 import dequantize_nf4
+from .rmsnorm import fp16_copy_of
 
 
 class QuantState:
@@ -100,14 +102,64 @@ class _MatMul4Bit(torch.autograd.Function):
     """x @ dequant(W)^T; the weight is dequantised again in backward instead of being kept."""
 
     @staticmethod
-    def forward(ctx, x, layer):
-        ctx.layer = layer
-        return F.linear(x, dequantize_nf4(layer.packed, layer.quant_state, x.dtype))
+    def forward(ctx, x, layer, x_low=None):
+        """`x_low`, when given, is x already cast to the compute dtype (no autograd history of its
+        own): the product is formed from it and the gradient goes to x in x's dtype."""
+        ctx.layer, ctx.x_dtype = layer, x.dtype
+        src = x if x_low is None else x_low
+        return F.linear(src, layer.dequantized(src.dtype))
 
     @staticmethod
     def backward(ctx, grad):
-        w = dequantize_nf4(ctx.layer.packed, ctx.layer.quant_state, grad.dtype)
-        return torch.matmul(grad, w), None
+        if not ctx.needs_input_grad[0]:
+            return None, None, None
+        dx = torch.matmul(grad, ctx.layer.dequantized(grad.dtype))
+        return dx.to(ctx.x_dtype), None, None
+
+
+class NF4Group:
+    """The 4-bit projections of one decoder block, dequantised together.
+
+    A block's seven weights are used right after one another (q, k, v, o, gate, up, down forward;
+    the reverse in backward), each too small to fill the GPU with its own launch. The first member
+    that asks for its weight makes one batched launch write all of them into a workspace that every
+    group of the model shares (the largest block's fp16 weights, 94 MB for Qwen2.5-1.5B); the other
+    members then find theirs there. The workspace belongs to the group that filled it last, so the
+    usual layer-by-layer order costs one launch per block and direction, and any other order is
+    still correct (it only dequantises more often). The returned weight is a view that the next
+    group overwrites: use it on the current stream at once and do not keep it.
+    """
+
+    _workspaces = {}  # (device, dtype) -> [flat tensor, weakref to the owning group, its key]
+
+    def __init__(self, layers):
+        self.layers = list(layers)
+        self.sizes = [l.in_features * l.out_features for l in self.layers]
+        self.offsets = [0]
+        for n in self.sizes:
+            self.offsets.append(self.offsets[-1] + (n + 127) // 128 * 128)  # 256-byte aligned slices
+        for l in self.layers:
+            l.group = self
+
+    def _key(self):
+        return tuple(l.packed._version for l in self.layers) + tuple(l.packed.data_ptr() for l in self.layers)
+
+    def weight(self, layer, dtype):
+        from .nf4 import dequantize_nf4_batch
+
+        device = layer.packed.device
+        slot = NF4Group._workspaces.get((device, dtype))
+        if slot is None or slot[0].numel() < self.offsets[-1]:
+            slot = [torch.empty(self.offsets[-1], dtype=dtype, device=device), None, None]
+            NF4Group._workspaces[(device, dtype)] = slot
+        flat = slot[0]
+        views = [flat[o:o + n].view(l.out_features, l.in_features)
+                 for l, o, n in zip(self.layers, self.offsets, self.sizes)]
+        key = self._key()
+        if slot[1] is None or slot[1]() is not self or slot[2] != key:
+            dequantize_nf4_batch([(l.packed, l.quant_state) for l in self.layers], dtype, outs=views)
+            slot[1], slot[2] = weakref.ref(self), key
+        return views[self.layers.index(layer)]
 
 
 class NF4Linear(torch.nn.Module):
@@ -122,6 +174,7 @@ class NF4Linear(torch.nn.Module):
         self.register_buffer("packed", packed, persistent=False)
         self.quant_state = quant_state
         self.compute_dtype = compute_dtype
+        self.group = None   # an NF4Group when the block's weights are dequantised together
         self.bias = None
         if bias is not None:
             self.bias = torch.nn.Parameter(bias.detach().clone(), requires_grad=False)
@@ -136,11 +189,24 @@ class NF4Linear(torch.nn.Module):
         self.quant_state = self.quant_state.to(self.packed.device)
         return self
 
+    def dequantized(self, dtype):
+        """The [out, in] weight in `dtype`: a fresh tensor, or a short-lived view of the group's
+        workspace."""
+        if self.group is not None:
+            return self.group.weight(self, dtype)
+        return dequantize_nf4(self.packed, self.quant_state, dtype)
+
     def matmul_4bit(self, x_low):
         return _MatMul4Bit.apply(x_low, self)
 
     def forward(self, x):
-        out = self.matmul_4bit(x.to(self.compute_dtype))
+        x_low = None
+        if self.compute_dtype == torch.float16 and x.dtype == torch.float32:
+            x_low = fp16_copy_of(x)   # the copy the RMSNorm before this layer wrote, if any
+        if x_low is not None:
+            out = _MatMul4Bit.apply(x, self, x_low)
+        else:
+            out = self.matmul_4bit(x.to(self.compute_dtype))
         if self.bias is not None:
             out = out + self.bias.to(out.dtype)
         return out.to(x.dtype)
@@ -177,11 +243,12 @@ QWEN25_1P5B = dict(hidden_size=1536, intermediate_size=8960, num_hidden_layers=2
 
 
 def build_qlora_model(device, config=None, lora_targets=("q_proj", "v_proj"), r=16, alpha=32,
-                      dropout=0.05, seed=0):
+                      dropout=0.05, seed=0, group_dequant=True):
     """A Qwen2 causal LM prepared the way the reference's run prepares it, without its packages:
     random fp16 weights of the given architecture (default Qwen2.5-1.5B), every decoder
     projection NF4-quantised (blocksize 64, double-quantised absmax), norms and the tied
     embedding/head in fp32 and frozen, LoRA (fp32 A Kaiming-uniform, B zero) on q_proj and v_proj.
+    With `group_dequant` each block's seven weights are dequantised by one launch (NF4Group).
     Returns (model, list of trainable LoRA parameters)."""
     from transformers import Qwen2Config, Qwen2ForCausalLM
 
@@ -204,6 +271,12 @@ def build_qlora_model(device, config=None, lora_targets=("q_proj", "v_proj"), r=
                     q = LoRALinear(q, r=r, alpha=alpha, dropout=dropout).to(device)
                 setattr(parent, name, q)
                 del lin
+        if group_dequant:
+            NF4Group([getattr(parent, name).base_layer if isinstance(getattr(parent, name), LoRALinear)
+                      else getattr(parent, name)
+                      for parent, names in ((layer.self_attn, ("q_proj", "k_proj", "v_proj", "o_proj")),
+                                            (layer.mlp, ("gate_proj", "up_proj", "down_proj")))
+                      for name in names])
     # what prepare_model_for_kbit_training leaves: fp32 norms and fp32 (tied) embedding
     for module in model.modules():
         if type(module).__name__ == "Qwen2RMSNorm":
@@ -267,11 +340,15 @@ class CapturedStep:
     optimizer.step of the reference (solution/lm_head_loss.py:375-430 wraps the first).
 
     `load()` takes a host or device batch and moves 4 × bucket_tokens int64 values; `run()` replays
-    and returns the (device) loss of the step.
+    and returns the (device) loss of the step. Construction runs `warmup` eager steps and the
+    capture on `batch`, then puts the parameters, the optimizer state and the loss scale back to
+    what they were, so the first `run()` is the first training step. The optimizer must be built
+    with `capturable=True`; `bucket_tokens` defaults to the real tokens of `batch` rounded up to a
+    multiple of 128.
     """
 
-    def __init__(self, model, params, optimizer, bucket_tokens, scaler=None, loss_scale=1024.0,
-                 group=None, warmup=3):
+    def __init__(self, model, params, optimizer, batch, bucket_tokens=None, scaler=None,
+                 loss_scale=1024.0, group=None, warmup=3):
         from . import lm_head_loss as L
 
         self._L = L
@@ -282,7 +359,8 @@ class CapturedStep:
         if group is not None or (torch.distributed.is_available() and torch.distributed.is_initialized()):
             self.world = torch.distributed.get_world_size(group)
         dev = self.params[0].device
-        n = int(bucket_tokens)
+        real = int((batch["attention_mask"] != 0).sum())
+        n = int(bucket_tokens) if bucket_tokens else -(-real // 128) * 128
         self.bucket = n
         self.ids = torch.zeros(1, n, dtype=torch.int64, device=dev)
         self.col = torch.zeros(1, n, dtype=torch.int64, device=dev)
@@ -297,6 +375,7 @@ class CapturedStep:
             p.grad = self.flat_grad[offset:offset + p.numel()].view_as(p)
             offset += p.numel()
         self.loss = None
+        self.load(batch)
         self._capture(warmup)
 
     # ------------------------------------------------------------------ host side of a step
@@ -359,8 +438,32 @@ class CapturedStep:
             self.flat_grad.div_(self.loss_scale)
             self.optimizer.step()
 
+    def _snapshot(self):
+        state = {}
+        for p in self.params:
+            for key, value in self.optimizer.state.get(p, {}).items():
+                if torch.is_tensor(value):
+                    state[(p, key)] = value.clone()
+        scaler = self.scaler.state_dict() if self.scaler is not None else None
+        return [p.detach().clone() for p in self.params], state, scaler
+
+    def _restore(self, snapshot):
+        values, state, scaler = snapshot
+        with torch.no_grad():
+            for p, v in zip(self.params, values):
+                p.copy_(v)
+            for p in self.params:
+                for key, value in self.optimizer.state.get(p, {}).items():
+                    if torch.is_tensor(value):  # in place: the graphs hold these addresses
+                        old = state.get((p, key))
+                        value.copy_(old) if old is not None else value.zero_()
+            self.flat_grad.zero_()
+        if scaler is not None and scaler:
+            self.scaler.load_state_dict(scaler)
+
     def _capture(self, warmup):
         self.model.train()
+        snapshot = self._snapshot()
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
@@ -375,4 +478,5 @@ class CapturedStep:
         self.graph_opt = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph_opt, pool=self.graph_fb.pool()):
             self._optimizer_step()
+        self._restore(snapshot)
         torch.cuda.synchronize()

@@ -127,3 +127,34 @@ def test_step_trains():
     losses = [qlora.qlora_step(model, batch, opt, scaler).item() for _ in range(8)]
     assert all(torch.isfinite(torch.tensor(losses)))
     assert losses[-1] < losses[0]
+
+
+def test_single_call_grouped_attention_matches_repeat_kv():
+    from claudemaxing_b200.attention import _grouped_sdpa
+
+    torch.manual_seed(0)
+    n, hq, hk, d = 300, 12, 2, 128
+    q = torch.randn(1, n, hq, d, device="cuda", dtype=torch.float16).transpose(1, 2)
+    k = torch.randn(1, n, hk, d, device="cuda", dtype=torch.float16).transpose(1, 2)
+    v = torch.randn(1, n, hk, d, device="cuda", dtype=torch.float16).transpose(1, 2)
+    row = torch.arange(n, device="cuda") // 77
+    col = torch.arange(n, device="cuda") % 77
+    mask = ((row[:, None] == row[None, :]) & (col[None, :] <= col[:, None]))[None, None]
+    out = _grouped_sdpa(q, k, v, mask, d ** -0.5)
+    kk, vv = k.repeat_interleave(hq // hk, 1).float(), v.repeat_interleave(hq // hk, 1).float()
+    s = (q.float() @ kk.transpose(-1, -2)) * d ** -0.5
+    ref = (s.masked_fill(~mask, float("-inf")).softmax(-1) @ vv).transpose(1, 2)
+    assert rel_norm(out.cpu(), ref.cpu()) < 2e-3
+
+
+def test_group_dequant_equals_per_weight_dequant():
+    from claudemaxing_b200 import qlora
+    from claudemaxing_b200.nf4 import dequantize_nf4
+
+    model, _ = qlora.build_qlora_model("cuda", TINY, seed=4)
+    layers = model.model.layers
+    for layer in (layers[0], layers[1], layers[0]):      # ownership moves between blocks and back
+        for mod in (layer.self_attn.o_proj, layer.mlp.down_proj, layer.self_attn.k_proj):
+            got = mod.dequantized(torch.float16).clone()
+            want = dequantize_nf4(mod.packed, mod.quant_state, torch.float16)
+            assert torch.equal(got, want)
