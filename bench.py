@@ -169,10 +169,23 @@ def run_reference(args, rank):
 # ------------------------------------------------------------------------------------------
 # memory-bound kernels of the path, cold L2 (rotating buffer sets larger than the 126 MB L2)
 # ------------------------------------------------------------------------------------------
+PLAIN_LAUNCHES = False   # --plain-launches: no graphs, a few direct launches per case (for ncu)
+
+
 def time_rotating(make_call, n_sets, reps=10):
     """Milliseconds per call of `make_call(i)`: the calls over all n_sets buffer sets are captured
     into one CUDA graph (so the host's launch cost is out of the picture and consecutive launches
     touch different, L2-cold buffers) and the graph is replayed `reps` times between two events."""
+    if PLAIN_LAUNCHES:
+        n = min(n_sets, 3)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for i in range(n):
+            make_call(i)
+        b.record()
+        b.synchronize()
+        return a.elapsed_time(b) / n
     for i in range(n_sets):
         make_call(i)
     torch.cuda.synchronize()
@@ -289,6 +302,13 @@ def kernel_suite(dev, hbm_peak, n_rows=2048, tag="", with_nf4=True):
                   _lib.F32, _lib.F32, torch.cuda.current_stream().cuda_stream)
 
     record("rmsnorm_fwd_f32_with_f16_copy", time_rotating(rms_fwd_b, nB), 10 * n_rows * H + 4 * n_rows)
+
+    def rms_bwd_b(i):  # the 4-bit model's backward: fp32 dy, the fp16 copy of the output, fp32 dx
+        _lib.call("soup_rmsnorm_bwd", xb[i].data_ptr(), lb[i].data_ptr(), wb.data_ptr(), rstd.data_ptr(),
+                  ob[i].data_ptr(), None, None, slots.data_ptr(), small.data_ptr(), 15, n_rows, H,
+                  _lib.F32, code_f16, _lib.F32, _lib.F32, 1, torch.cuda.current_stream().cuda_stream)
+
+    record("rmsnorm_bwd_from_f16_copy", time_rotating(rms_bwd_b, nB), 10 * n_rows * H + 4 * n_rows)
     del xb, ob, lb
 
     # RoPE: packed row [1, n_rows], 12 q heads / 2 kv heads, head_dim 128
@@ -428,6 +448,11 @@ def main():
     ap.add_argument("--no-suite", action="store_true", help="skip the memory-bound kernel suite")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-step", action="store_true", help="skip the full QLoRA training step leg")
+    ap.add_argument("--suite-only", action="store_true",
+                    help="run only the memory-bound kernel suite and print its JSON")
+    ap.add_argument("--suite-rows", type=int, default=32768)
+    ap.add_argument("--plain-launches", action="store_true",
+                    help="with --suite-only: up to three direct launches per case instead of graph replays")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank = int(os.environ.get("RANK", "0"))
@@ -445,6 +470,14 @@ def main():
     assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
+    if args.suite_only:
+        global PLAIN_LAUNCHES
+        PLAIN_LAUNCHES = args.plain_launches
+        hbm = peaks()[0]["hbm_gbs"]
+        print(json.dumps({"kernels": kernel_suite(dev, hbm, n_rows=args.suite_rows,
+                                                  tag=f"@{args.suite_rows}rows",
+                                                  with_nf4=True)}), flush=True)
+        return
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     peak, peak_source = peaks()

@@ -94,6 +94,79 @@ __device__ __forceinline__ void store8(void* base, int64_t i, int dt, const floa
   }
 }
 
+// ---- 16-byte (or 8-byte) raw vectors: EPV elements of B bytes kept as bits until they are used ----
+template <int NB> struct Raw;
+template <> struct Raw<16> { uint4 v; };
+template <> struct Raw<8> { uint2 v; };
+
+template <int NB>
+__device__ __forceinline__ Raw<NB> ld_raw(const void* base, int64_t byte_off) {
+  Raw<NB> r;
+  const char* p = reinterpret_cast<const char*>(base) + byte_off;
+  if constexpr (NB == 16) r.v = *reinterpret_cast<const uint4*>(p);
+  else r.v = *reinterpret_cast<const uint2*>(p);
+  return r;
+}
+
+__device__ __forceinline__ float2 unpack2(uint32_t w, int dt) {
+  if (dt == SOUP_F16) return __half22float2(*reinterpret_cast<const __half2*>(&w));
+  return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w));
+}
+
+// EPV elements of B bytes each from their raw bits.
+template <int EPV, int B>
+__device__ __forceinline__ void unpack(const Raw<EPV * B>& r, int dt, float (&v)[EPV]) {
+  if constexpr (B == 4) {
+    static_assert(EPV == 4, "fp32 vectors hold four elements");
+    v[0] = __uint_as_float(r.v.x); v[1] = __uint_as_float(r.v.y);
+    v[2] = __uint_as_float(r.v.z); v[3] = __uint_as_float(r.v.w);
+  } else if constexpr (EPV == 8) {
+    const uint32_t w[4] = {r.v.x, r.v.y, r.v.z, r.v.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) { const float2 f = unpack2(w[k], dt); v[2 * k] = f.x; v[2 * k + 1] = f.y; }
+  } else {
+    const float2 a = unpack2(r.v.x, dt), b = unpack2(r.v.y, dt);
+    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+  }
+}
+
+// EPV (4 or 8) consecutive elements of a runtime dtype; element index a multiple of EPV.
+template <int EPV>
+__device__ __forceinline__ void loadv(const void* base, int64_t i, int dt, float (&v)[EPV]) {
+  if constexpr (EPV == 8) {
+    load8(base, i, dt, v);
+  } else {
+    if (dt == SOUP_F32) {
+      const float4 a = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(base) + i);
+      v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+    } else {
+      const uint2 r = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint16_t*>(base) + i);
+      const float2 a = unpack2(r.x, dt), b = unpack2(r.y, dt);
+      v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+    }
+  }
+}
+
+__device__ __forceinline__ uint32_t pack2(float a, float b, int dt) {
+  if (dt == SOUP_F16) { __half2 h = __floats2half2_rn(a, b); return *reinterpret_cast<uint32_t*>(&h); }
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+template <int EPV>
+__device__ __forceinline__ void storev(void* base, int64_t i, int dt, const float (&v)[EPV]) {
+  if constexpr (EPV == 8) {
+    store8(base, i, dt, v);
+  } else {
+    if (dt == SOUP_F32) {
+      *reinterpret_cast<float4*>(reinterpret_cast<float*>(base) + i) = make_float4(v[0], v[1], v[2], v[3]);
+    } else {
+      *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(base) + i) =
+          make_uint2(pack2(v[0], v[1], dt), pack2(v[2], v[3], dt));
+    }
+  }
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -14,6 +14,7 @@
 // dtype of x before it meets the weight; in backward dy*w is rounded to that dtype too, except on
 // the saved-output path, where x is fp32 and nothing is rounded.
 #include "common.cuh"
+#include "rowpipe.cuh"
 
 namespace soup {
 namespace {
@@ -288,6 +289,424 @@ rmsnorm_dw_reduce_kernel(const float* __restrict__ partial, void* __restrict__ d
   store1(dw, c, wdt, acc);
 }
 
+// ------------------------------------------------------------------------------------------
+// Warp-per-row kernels (rows of at most 16 vectors per lane: 2048 fp32 or 4096 16-bit columns).
+//
+// A warp owns a row: every lane issues all of its 16-byte loads of the row at once, keeps the raw
+// bits in registers (4 registers per vector whatever the dtype), reduces with shuffles only (no
+// shared memory, no CTA barrier) and streams the results out; then it takes its next row. A lane's
+// vector is 16 bytes of the widest streamed input, so every load instruction of the warp covers
+// 512 contiguous bytes. With ~50-80 registers per thread 24-36 warps are resident per SM, each
+// with a whole row (3-6 KB) in flight, which is what HBM latency x bandwidth asks for.
+// ------------------------------------------------------------------------------------------
+constexpr int kWarpsPerCta = 8;
+
+template <int EPV>
+__device__ __forceinline__ void load_slots(const int32_t* slot, int i, int (&sl)[EPV]) {
+#pragma unroll
+  for (int q = 0; q < EPV / 4; ++q) {
+    const int4 a = *reinterpret_cast<const int4*>(slot + i + 4 * q);
+    sl[4 * q] = a.x; sl[4 * q + 1] = a.y; sl[4 * q + 2] = a.z; sl[4 * q + 3] = a.w;
+  }
+}
+
+// Bit j of the result: vector j of this lane contains a column with a side-buffer slot.
+template <int NV, int EPV>
+__device__ __forceinline__ uint32_t lane_slot_mask(const int32_t* slot, int n_vec, int lane) {
+  uint32_t mask = 0;
+  if (!slot) return 0;
+#pragma unroll
+  for (int j = 0; j < NV; ++j) {
+    const int vi = j * 32 + lane;
+    if (vi < n_vec) {
+      int sl[EPV];
+      load_slots<EPV>(slot, vi * EPV, sl);
+#pragma unroll
+      for (int k = 0; k < EPV; ++k) if (sl[k] >= 0) mask |= 1u << j;
+    }
+  }
+  return mask;
+}
+
+// ------------------------------------------------------------------------------------------
+// Pipelined warp-per-row kernels: rows arrive in the warp's shared-memory ring (rowpipe.cuh), both
+// passes over a row read it from there, results go straight to global memory. Any n_cols whose
+// row slot fits the ring; vectors are 16 bytes of the widest streamed input.
+// ------------------------------------------------------------------------------------------
+template <int EPV, int B>
+__device__ __forceinline__ void unpack_smem(const char* row, int vi, int dt, float (&v)[EPV]) {
+  unpack<EPV, B>(ld_raw<EPV * B>(row, (int64_t)vi * EPV * B), dt, v);
+}
+
+// A dtype that is a template constant (>= 0) is folded by the compiler; -1 takes the run-time code.
+template <int C> __device__ __forceinline__ int dt_sel(int rt) { return C >= 0 ? C : rt; }
+
+// XDT / WDT / ODT: compile-time dtype codes of the hot combinations, or -1 for "read the argument".
+template <int XB, int XDT, int WDT, int ODT>
+__global__ void __launch_bounds__(rowpipe::kMaxWarps * 32, 2)
+rmsnorm_fwd_pipe_kernel(const void* __restrict__ x, const void* __restrict__ w,
+                        void* __restrict__ out, float* __restrict__ rstd_out,
+                        void* __restrict__ low, const int32_t* __restrict__ slot,
+                        void* __restrict__ small, int64_t n_small, int64_t n_rows, int n_cols,
+                        float eps, int xdt_rt, int wdt_rt, int odt_rt, int stages, int team, int* status) {
+  constexpr int EPV = 16 / XB;
+  const int xdt = dt_sel<XDT>(xdt_rt), wdt = dt_sel<WDT>(wdt_rt), odt = dt_sel<ODT>(odt_rt);
+  extern __shared__ __align__(128) char smem[];
+  __shared__ int s_abort;
+  __shared__ float s_part[2 * rowpipe::kMaxWarps];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  // a team of `team` (1 or 2) warps shares a row: member m owns vectors [v0, v0 + n_vec)
+  const int member = team == 2 ? (warp & 1) : 0;
+  const int n_vec = n_cols / EPV / team, v0 = member * n_vec;
+  const uint32_t row_bytes = (uint32_t)n_cols * XB / team;   // this member's share of a row
+  if (threadIdx.x == 0) s_abort = 0;
+  rowpipe::Ring ring;
+  ring.init(smem, row_bytes, stages, warp, lane);
+  __syncthreads();
+  const int64_t row0 = (int64_t)blockIdx.x * (warps / team) + warp / team;
+  const int64_t stride = (int64_t)gridDim.x * (warps / team);
+  const char* xb = reinterpret_cast<const char*>(x) + (size_t)member * row_bytes;
+  const int64_t row_pitch = (int64_t)n_cols * XB;
+  int64_t next = row0;   // next row to request
+  if (lane == 0) {
+    for (int s = 0; s < stages && next < n_rows; ++s, next += stride) {
+      umma::mbar_expect_tx(&ring.bars[s], row_bytes);
+      rowpipe::bulk_load(ring.slot_ptr(s), xb + next * row_pitch, row_bytes, &ring.bars[s]);
+    }
+  }
+  next = __shfl_sync(0xffffffffu, next, 0);
+  // bit v of slot_mask: this lane's v-th vector holds a column with a side-buffer slot
+  uint64_t slot_mask = 0;
+  if (low) {
+    for (int vi = lane, v = 0; vi < n_vec; vi += 32, ++v) {
+      int sl[EPV];
+      load_slots<EPV>(slot, (v0 + vi) * EPV, sl);
+#pragma unroll
+      for (int k = 0; k < EPV; ++k) if (sl[k] >= 0) slot_mask |= 1ull << v;
+    }
+  }
+  const float inv_cols = 1.0f / (float)n_cols;
+  int iter = 0;
+  for (int64_t row = row0; row < n_rows; row += stride, ++iter) {
+    if (!ring.wait(&s_abort, status, 11)) {
+      ring.drain((int)((next - row) / stride));   // the copies still travelling to this warp's slots
+      // a partner already waiting at this row's team barrier is released (it gives up at its next wait)
+      if (team == 2) asm volatile("bar.arrive %0, 64;" ::"r"((warp >> 1) + 1) : "memory");
+      return;
+    }
+    const char* src = ring.slot_ptr(ring.slot);
+    float ss = 0.f;
+#pragma unroll 4
+    for (int vi = lane; vi < n_vec; vi += 32) {
+      float xv[EPV];
+      unpack_smem<EPV, XB>(src, vi, xdt, xv);
+#pragma unroll
+      for (int k = 0; k < EPV; ++k) ss += xv[k] * xv[k];
+    }
+    ss = warp_sum(ss);
+    if (team == 2) ss = rowpipe::team_sum2(ss, s_part, warp, lane, iter);
+    const float rstd = 1.0f / sqrtf(ss * inv_cols + eps);
+    if (lane == 0 && member == 0) rstd_out[row] = rstd;
+    int v = 0;
+#pragma unroll 2
+    for (int vi = lane; vi < n_vec; vi += 32, ++v) {
+      float xv[EPV], wv[EPV], o[EPV], nrm[EPV];
+      unpack_smem<EPV, XB>(src, vi, xdt, xv);
+      const int col = (v0 + vi) * EPV;
+      loadv<EPV>(w, col, wdt, wv);   // a few KB of weights: L1-resident after the first row
+#pragma unroll
+      for (int k = 0; k < EPV; ++k) {
+        nrm[k] = round_through(xv[k] * rstd, xdt);
+        o[k] = nrm[k] * wv[k];
+      }
+      storev<EPV>(out, row * n_cols + col, odt, o);
+      if (low) {
+        storev<EPV>(low, row * n_cols + col, SOUP_F16, o);
+        if (slot_mask >> v & 1ull) {
+          int sl[EPV];
+          load_slots<EPV>(slot, col, sl);
+#pragma unroll
+          for (int k = 0; k < EPV; ++k)
+            if (sl[k] >= 0) store1(small, row * n_small + sl[k], SOUP_F16, nrm[k]);
+        }
+      }
+    }
+    __syncwarp();
+    if (next < n_rows) {
+      if (lane == 0) {
+        umma::fence_proxy_async_smem();   // the slot's reads are done before the copy overwrites it
+        umma::mbar_expect_tx(&ring.bars[ring.slot], row_bytes);
+        rowpipe::bulk_load(ring.slot_ptr(ring.slot), xb + next * row_pitch, row_bytes,
+                           &ring.bars[ring.slot]);
+      }
+      next += stride;
+    }
+    ring.advance();
+  }
+}
+
+// Backward without dw: a slot holds the dy row followed by the saved row (x, or the fp16 copy of
+// the output). YDT .. SAVED: compile-time values of the hot combinations, or -1 for the argument.
+template <int YB, int XB, int YDT, int XDT, int WDT, int DXDT, int SAVED>
+__global__ void __launch_bounds__(rowpipe::kMaxWarps * 32, 2)
+rmsnorm_bwd_pipe_kernel(const void* __restrict__ dy, const void* __restrict__ xin,
+                        const void* __restrict__ w, const float* __restrict__ rstd_in,
+                        void* __restrict__ dx, const int32_t* __restrict__ slot,
+                        const void* __restrict__ small, int64_t n_small, int64_t n_rows, int n_cols,
+                        int ydt_rt, int xdt_rt, int wdt_rt, int dxdt_rt, int saved_rt, int stages,
+                        int team, int* status) {
+  constexpr int EPV = 16 / (YB > XB ? YB : XB);
+  const int ydt = dt_sel<YDT>(ydt_rt), xdt = dt_sel<XDT>(xdt_rt), wdt = dt_sel<WDT>(wdt_rt);
+  const int dxdt = dt_sel<DXDT>(dxdt_rt), saved_output = dt_sel<SAVED>(saved_rt);
+  extern __shared__ __align__(128) char smem[];
+  __shared__ int s_abort;
+  __shared__ float s_part[2 * rowpipe::kMaxWarps];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  const int member = team == 2 ? (warp & 1) : 0;
+  const int n_vec = n_cols / EPV / team, v0 = member * n_vec;
+  // this member's share of a dy row and of a saved row
+  const uint32_t y_bytes = (uint32_t)n_cols * YB / team, x_bytes = (uint32_t)n_cols * XB / team;
+  const int64_t y_pitch = (int64_t)n_cols * YB, x_pitch = (int64_t)n_cols * XB;
+  if (threadIdx.x == 0) s_abort = 0;
+  rowpipe::Ring ring;
+  ring.init(smem, y_bytes + x_bytes, stages, warp, lane);
+  __syncthreads();
+  const int64_t row0 = (int64_t)blockIdx.x * (warps / team) + warp / team;
+  const int64_t stride = (int64_t)gridDim.x * (warps / team);
+  const char* yb = reinterpret_cast<const char*>(dy) + (size_t)member * y_bytes;
+  const char* xb = reinterpret_cast<const char*>(xin) + (size_t)member * x_bytes;
+  int64_t next = row0;
+  if (lane == 0) {
+    for (int s = 0; s < stages && next < n_rows; ++s, next += stride) {
+      umma::mbar_expect_tx(&ring.bars[s], y_bytes + x_bytes);
+      rowpipe::bulk_load(ring.slot_ptr(s), yb + next * y_pitch, y_bytes, &ring.bars[s]);
+      rowpipe::bulk_load(ring.slot_ptr(s) + y_bytes, xb + next * x_pitch, x_bytes, &ring.bars[s]);
+    }
+  }
+  next = __shfl_sync(0xffffffffu, next, 0);
+  uint64_t slot_mask = 0;
+  if (saved_output) {
+    for (int vi = lane, v = 0; vi < n_vec; vi += 32, ++v) {
+      int sl[EPV];
+      load_slots<EPV>(slot, (v0 + vi) * EPV, sl);
+#pragma unroll
+      for (int k = 0; k < EPV; ++k) if (sl[k] >= 0) slot_mask |= 1ull << v;
+    }
+  }
+  const float inv_cols = 1.0f / (float)n_cols;
+  int iter = 0;
+  for (int64_t row = row0; row < n_rows; row += stride, ++iter) {
+    if (!ring.wait(&s_abort, status, 12)) {
+      ring.drain((int)((next - row) / stride));
+      if (team == 2) asm volatile("bar.arrive %0, 64;" ::"r"((warp >> 1) + 1) : "memory");
+      return;
+    }
+    const char* ysrc = ring.slot_ptr(ring.slot);
+    const char* xsrc = ysrc + y_bytes;
+    const float rstd = rstd_in[row];
+    float dot = 0.f;
+    int v = 0;
+#pragma unroll 2
+    for (int vi = lane; vi < n_vec; vi += 32, ++v) {
+      float yv[EPV], xv[EPV], wv[EPV];
+      unpack_smem<EPV, YB>(ysrc, vi, ydt, yv);
+      unpack_smem<EPV, XB>(xsrc, vi, xdt, xv);
+      const int col = (v0 + vi) * EPV;
+      loadv<EPV>(w, col, wdt, wv);
+      int sl[EPV];
+#pragma unroll
+      for (int k = 0; k < EPV; ++k) sl[k] = -1;
+      if (slot_mask >> v & 1ull) load_slots<EPV>(slot, col, sl);
+#pragma unroll
+      for (int k = 0; k < EPV; ++k) {
+        float nrm, gn;
+        if (saved_output) {
+          nrm = sl[k] >= 0 ? load1(small, row * n_small + sl[k], SOUP_F16) : xv[k] / wv[k];
+          gn = yv[k] * wv[k];
+        } else {
+          nrm = xv[k] * rstd;
+          gn = round_through(yv[k] * wv[k], xdt);
+        }
+        dot += gn * nrm;
+      }
+    }
+    dot = warp_sum(dot);
+    if (team == 2) dot = rowpipe::team_sum2(dot, s_part, warp, lane, iter);
+    const float mean_dot = dot * inv_cols;
+    v = 0;
+#pragma unroll 2
+    for (int vi = lane; vi < n_vec; vi += 32, ++v) {
+      float yv[EPV], xv[EPV], wv[EPV], o[EPV];
+      unpack_smem<EPV, YB>(ysrc, vi, ydt, yv);
+      unpack_smem<EPV, XB>(xsrc, vi, xdt, xv);
+      const int col = (v0 + vi) * EPV;
+      loadv<EPV>(w, col, wdt, wv);
+      int sl[EPV];
+#pragma unroll
+      for (int k = 0; k < EPV; ++k) sl[k] = -1;
+      if (slot_mask >> v & 1ull) load_slots<EPV>(slot, col, sl);
+#pragma unroll
+      for (int k = 0; k < EPV; ++k) {
+        float nrm, gn;
+        if (saved_output) {
+          nrm = sl[k] >= 0 ? load1(small, row * n_small + sl[k], SOUP_F16) : xv[k] / wv[k];
+          gn = yv[k] * wv[k];
+        } else {
+          nrm = xv[k] * rstd;
+          gn = round_through(yv[k] * wv[k], xdt);
+        }
+        o[k] = (gn - nrm * mean_dot) * rstd;
+      }
+      storev<EPV>(dx, row * n_cols + col, dxdt, o);
+    }
+    __syncwarp();
+    if (next < n_rows) {
+      if (lane == 0) {
+        umma::fence_proxy_async_smem();
+        umma::mbar_expect_tx(&ring.bars[ring.slot], y_bytes + x_bytes);
+        rowpipe::bulk_load(ring.slot_ptr(ring.slot), yb + next * y_pitch, y_bytes,
+                           &ring.bars[ring.slot]);
+        rowpipe::bulk_load(ring.slot_ptr(ring.slot) + y_bytes, xb + next * x_pitch, x_bytes,
+                           &ring.bars[ring.slot]);
+      }
+      next += stride;
+    }
+    ring.advance();
+  }
+}
+
+// YB / XB: bytes per element of dy and of the saved tensor (x, or the fp16 copy of the output).
+template <int NV, int YB, int XB, bool DW>
+__global__ void __launch_bounds__(kWarpsPerCta * 32)
+rmsnorm_bwd_warp_kernel(const void* __restrict__ dy, const void* __restrict__ xin,
+                        const void* __restrict__ w, const float* __restrict__ rstd_in,
+                        void* __restrict__ dx, float* __restrict__ dw_partial,
+                        const int32_t* __restrict__ slot, const void* __restrict__ small,
+                        int64_t n_small, int64_t n_rows, int n_cols, int ydt, int xdt, int wdt,
+                        int dxdt, int saved_output) {
+  constexpr int EPV = 16 / (YB > XB ? YB : XB);
+  extern __shared__ float s_dw[];   // DW only: n_cols floats
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int n_vec = n_cols / EPV;
+  const int64_t warp0 = (int64_t)blockIdx.x * kWarpsPerCta + warp;
+  const int64_t stride = (int64_t)gridDim.x * kWarpsPerCta;
+  const uint32_t slot_mask = saved_output ? lane_slot_mask<NV, EPV>(slot, n_vec, lane) : 0u;
+  const float inv_cols = 1.0f / (float)n_cols;
+  float dw_acc[DW ? NV : 1][EPV];
+  if (DW) {
+#pragma unroll
+    for (int j = 0; j < NV; ++j)
+#pragma unroll
+      for (int k = 0; k < EPV; ++k) dw_acc[j][k] = 0.f;
+  }
+  for (int64_t row = warp0; row < n_rows; row += stride) {
+    Raw<EPV * YB> yraw[NV];
+    Raw<EPV * XB> xraw[NV];
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int vi = j * 32 + lane;
+      if (vi < n_vec) {
+        const int64_t e = row * n_cols + (int64_t)vi * EPV;
+        yraw[j] = ld_raw<EPV * YB>(dy, e * YB);
+        xraw[j] = ld_raw<EPV * XB>(xin, e * XB);
+      }
+    }
+    const float rstd = rstd_in[row];
+    float dot = 0.f;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int vi = j * 32 + lane;
+      if (vi < n_vec) {
+        float yv[EPV], xv[EPV], wv[EPV];
+        unpack<EPV, YB>(yraw[j], ydt, yv);
+        unpack<EPV, XB>(xraw[j], xdt, xv);
+        loadv<EPV>(w, vi * EPV, wdt, wv);
+        int sl[EPV];
+#pragma unroll
+        for (int k = 0; k < EPV; ++k) sl[k] = -1;
+        if (slot_mask >> j & 1u) load_slots<EPV>(slot, vi * EPV, sl);
+#pragma unroll
+        for (int k = 0; k < EPV; ++k) {
+          float nrm, gn;
+          if (saved_output) {
+            nrm = sl[k] >= 0 ? load1(small, row * n_small + sl[k], SOUP_F16) : xv[k] / wv[k];
+            gn = yv[k] * wv[k];
+          } else {
+            nrm = xv[k] * rstd;
+            gn = round_through(yv[k] * wv[k], xdt);
+          }
+          dot += gn * nrm;
+          if (DW) dw_acc[j][k] += yv[k] * round_through(nrm, xdt);
+        }
+      }
+    }
+    dot = warp_sum(dot);
+    const float mean_dot = dot * inv_cols;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int vi = j * 32 + lane;
+      if (vi < n_vec) {
+        float yv[EPV], xv[EPV], wv[EPV], o[EPV];
+        unpack<EPV, YB>(yraw[j], ydt, yv);
+        unpack<EPV, XB>(xraw[j], xdt, xv);
+        loadv<EPV>(w, vi * EPV, wdt, wv);
+        int sl[EPV];
+#pragma unroll
+        for (int k = 0; k < EPV; ++k) sl[k] = -1;
+        if (slot_mask >> j & 1u) load_slots<EPV>(slot, vi * EPV, sl);
+#pragma unroll
+        for (int k = 0; k < EPV; ++k) {
+          float nrm, gn;
+          if (saved_output) {
+            nrm = sl[k] >= 0 ? load1(small, row * n_small + sl[k], SOUP_F16) : xv[k] / wv[k];
+            gn = yv[k] * wv[k];
+          } else {
+            nrm = xv[k] * rstd;
+            gn = round_through(yv[k] * wv[k], xdt);
+          }
+          o[k] = (gn - nrm * mean_dot) * rstd;
+        }
+        storev<EPV>(dx, row * n_cols + (int64_t)vi * EPV, dxdt, o);
+      }
+    }
+  }
+  if (DW) {
+    // The CTA's warps add their column sums in warp order (deterministic), one partial row per CTA.
+    for (int turn = 0; turn < kWarpsPerCta; ++turn) {
+      if (warp == turn) {
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+          const int vi = j * 32 + lane;
+          if (vi < n_vec) {
+#pragma unroll
+            for (int k = 0; k < EPV; ++k) {
+              const int c = vi * EPV + k;
+              s_dw[c] = turn == 0 ? dw_acc[j][k] : s_dw[c] + dw_acc[j][k];
+            }
+          }
+        }
+      }
+      __syncthreads();
+    }
+    for (int c = threadIdx.x; c < n_cols; c += blockDim.x)
+      dw_partial[(int64_t)blockIdx.x * n_cols + c] = s_dw[c];
+  }
+}
+
+// Vectors per lane the warp kernels are built for; 0: the row is too wide for them.
+inline int pick_nv(int n_cols, int epv) {
+  const int need = (n_cols / epv + 31) / 32;
+  const int options[] = {2, 4, 6, 8, 12, 16};
+  for (int o : options) if (need <= o) return o;
+  return 0;
+}
+
+inline unsigned warp_grid(int64_t n_rows, int ctas_per_sm) {
+  const int64_t need = (n_rows + kWarpsPerCta - 1) / kWarpsPerCta;
+  const int64_t cap = (int64_t)sm_count() * ctas_per_sm;
+  return (unsigned)(need < cap ? (need < 1 ? 1 : need) : cap);
+}
+
 struct Shape { int vpt, tpr; };
 
 // Smallest VPT in {1,2,4,8} whose CTA (<= 256 threads) covers the row.
@@ -324,10 +743,32 @@ extern "C" int soup_rmsnorm_fwd(const void* x, const void* w, void* out, float* 
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   const bool vec = (n_cols % 8 == 0) && aligned16(x) && aligned16(w) && aligned16(out) &&
                    (!low || (aligned16(low) && aligned16(slot)));
+  const int xb = dtype_size(x_dtype);
+  // a team of two can split a row whose halves are whole 16-byte vectors
+  const rowpipe::Plan plan = vec ? rowpipe::make_plan((size_t)n_cols * xb, 0, (n_cols * xb) % 32 == 0, n_rows)
+                                 : rowpipe::Plan{8, 0, 1, 1, 0, 0};
+  int* status = plan.stages ? rowpipe::status_word() : nullptr;
   if (!vec) {
     rmsnorm_fwd_scalar_kernel<<<(unsigned)n_rows, 256, 0, s>>>(x, w, out, rstd, low, slot, small,
                                                                n_small, (int)n_cols, eps, x_dtype,
                                                                w_dtype, out_dtype);
+  } else if (plan.stages && status) {
+#define SOUP_RMS_FWD_P(XB_, X_, W_, O_)                                                          \
+  do {                                                                                            \
+    auto kernel = rmsnorm_fwd_pipe_kernel<XB_, X_, W_, O_>;                                       \
+    cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plan.smem);    \
+    kernel<<<plan.grid, plan.warps * 32, plan.smem, s>>>(x, w, out, rstd, low, slot, small,       \
+                                                         n_small, n_rows, (int)n_cols, eps,       \
+                                                         x_dtype, w_dtype, out_dtype, plan.stages, \
+                                                         plan.team, status);                      \
+  } while (0)
+    const bool same = x_dtype == w_dtype && x_dtype == out_dtype;
+    if (same && x_dtype == SOUP_F32) SOUP_RMS_FWD_P(4, SOUP_F32, SOUP_F32, SOUP_F32);
+    else if (same && x_dtype == SOUP_F16) SOUP_RMS_FWD_P(2, SOUP_F16, SOUP_F16, SOUP_F16);
+    else if (same && x_dtype == SOUP_BF16) SOUP_RMS_FWD_P(2, SOUP_BF16, SOUP_BF16, SOUP_BF16);
+    else if (xb == 4) SOUP_RMS_FWD_P(4, SOUP_F32, -1, -1);
+    else SOUP_RMS_FWD_P(2, -1, -1, -1);
+#undef SOUP_RMS_FWD_P
   } else {
     const Shape sh = pick_shape((int)n_cols);
     constexpr int R = 2;  // rows per CTA step (4 measured slower: fewer CTAs fit on an SM)
@@ -376,11 +817,20 @@ extern "C" int soup_rmsnorm_bwd(const void* dy, const void* xin, const void* w, 
   if (!dy || !xin || !w || !rstd || !dx) SOUP_FAIL(SOUP_ERR_ARG, "rmsnorm_bwd: null pointer");
   if (saved_output && (!slot || !small || n_small < 1))
     SOUP_FAIL(SOUP_ERR_ARG, "rmsnorm_bwd: saved-output path needs slot map and side buffer");
-  // one row per CTA, or a persistent grid (more CTAs than fit at once) when dw is accumulated
-  const unsigned grid = (unsigned)(want_dw ? bwd_ctas(n_rows) : n_rows);
+  // Rows of moderate width go to the warp-per-row kernel; wider ones to one CTA per row (a
+  // persistent grid when dw is accumulated). A 16-bit dy with a 32-bit saved tensor does not occur
+  // on the training path and takes the CTA kernel.
   const bool vec = (n_cols % 8 == 0) && aligned16(dy) && aligned16(xin) && aligned16(w) &&
                    aligned16(dx) && (!saved_output || aligned16(slot)) &&
                    (!want_dw || aligned16(dw_partial));
+  const int yb = dtype_size(dy_dtype), xb = dtype_size(xin_dtype);
+  const int nv = (vec && want_dw && yb >= xb) ? pick_nv((int)n_cols, 16 / yb) : 0;
+  const rowpipe::Plan plan = (vec && !want_dw && yb >= xb)
+                                 ? rowpipe::make_plan((size_t)n_cols * (yb + xb), 0,
+                                                      (n_cols * xb) % 32 == 0, n_rows)
+                                 : rowpipe::Plan{8, 0, 1, 1, 0, 0};
+  int* status = plan.stages ? rowpipe::status_word() : nullptr;
+  unsigned grid = (unsigned)(want_dw ? bwd_ctas(n_rows) : n_rows);
   if (!vec) {
     if (want_dw)
       rmsnorm_bwd_scalar_kernel<true><<<grid, 256, 0, s>>>(dy, xin, w, rstd, dx, dw_partial, slot,
@@ -392,6 +842,53 @@ extern "C" int soup_rmsnorm_bwd(const void* dy, const void* xin, const void* w, 
                                                             small, n_small, n_rows, (int)n_cols,
                                                             dy_dtype, xin_dtype, w_dtype, dx_dtype,
                                                             saved_output);
+  } else if (plan.stages && status) {
+    grid = plan.grid;
+#define SOUP_RMS_BWD_P(YB_, XB_, Y_, X_, W_, DX_, SV_)                                           \
+  do {                                                                                            \
+    auto kernel = rmsnorm_bwd_pipe_kernel<YB_, XB_, Y_, X_, W_, DX_, SV_>;                        \
+    cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plan.smem);    \
+    kernel<<<plan.grid, plan.warps * 32, plan.smem, s>>>(dy, xin, w, rstd, dx, slot, small,       \
+                                                         n_small, n_rows, (int)n_cols, dy_dtype,  \
+                                                         xin_dtype, w_dtype, dx_dtype,            \
+                                                         saved_output, plan.stages, plan.team,    \
+                                                         status);                                 \
+  } while (0)
+    const bool same = dy_dtype == xin_dtype && dy_dtype == w_dtype && dy_dtype == dx_dtype;
+    if (saved_output && dy_dtype == SOUP_F32 && xin_dtype == SOUP_F16 && w_dtype == SOUP_F32 &&
+        dx_dtype == SOUP_F32)
+      SOUP_RMS_BWD_P(4, 2, SOUP_F32, SOUP_F16, SOUP_F32, SOUP_F32, 1);   // the 4-bit model's path
+    else if (!saved_output && same && dy_dtype == SOUP_F16)
+      SOUP_RMS_BWD_P(2, 2, SOUP_F16, SOUP_F16, SOUP_F16, SOUP_F16, 0);
+    else if (!saved_output && same && dy_dtype == SOUP_BF16)
+      SOUP_RMS_BWD_P(2, 2, SOUP_BF16, SOUP_BF16, SOUP_BF16, SOUP_BF16, 0);
+    else if (!saved_output && same && dy_dtype == SOUP_F32)
+      SOUP_RMS_BWD_P(4, 4, SOUP_F32, SOUP_F32, SOUP_F32, SOUP_F32, 0);
+    else if (yb == 4 && xb == 4) SOUP_RMS_BWD_P(4, 4, SOUP_F32, SOUP_F32, -1, -1, -1);
+    else if (yb == 4) SOUP_RMS_BWD_P(4, 2, SOUP_F32, -1, -1, -1, -1);
+    else SOUP_RMS_BWD_P(2, 2, -1, -1, -1, -1, -1);
+#undef SOUP_RMS_BWD_P
+  } else if (nv) {
+    grid = warp_grid(n_rows, 2);
+    const size_t smem = (size_t)n_cols * sizeof(float);
+#define SOUP_RMS_BWD_W(NV_, YB_, XB_)                                                            \
+  rmsnorm_bwd_warp_kernel<NV_, YB_, XB_, true><<<grid, kWarpsPerCta * 32, smem, s>>>(             \
+      dy, xin, w, rstd, dx, dw_partial, slot, small, n_small, n_rows, (int)n_cols, dy_dtype,      \
+      xin_dtype, w_dtype, dx_dtype, saved_output)
+#define SOUP_RMS_BWD_NV(YB_, XB_)                                                                \
+  switch (nv) {                                                                                   \
+    case 2: SOUP_RMS_BWD_W(2, YB_, XB_); break;                                                   \
+    case 4: SOUP_RMS_BWD_W(4, YB_, XB_); break;                                                   \
+    case 6: SOUP_RMS_BWD_W(6, YB_, XB_); break;                                                   \
+    case 8: SOUP_RMS_BWD_W(8, YB_, XB_); break;                                                   \
+    case 12: SOUP_RMS_BWD_W(12, YB_, XB_); break;                                                 \
+    default: SOUP_RMS_BWD_W(16, YB_, XB_); break;                                                 \
+  }
+    if (yb == 4 && xb == 4) { SOUP_RMS_BWD_NV(4, 4) }
+    else if (yb == 4) { SOUP_RMS_BWD_NV(4, 2) }
+    else { SOUP_RMS_BWD_NV(2, 2) }
+#undef SOUP_RMS_BWD_NV
+#undef SOUP_RMS_BWD_W
   } else {
     const Shape sh = pick_shape((int)n_cols);
 #define SOUP_RMS_BWD(V_, D_)                                                                     \

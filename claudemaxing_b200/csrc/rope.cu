@@ -7,6 +7,7 @@
 // arrive as transposed views of the projection outputs); outputs are contiguous [b, h, t, d].
 // Arithmetic is fp32, as in qwen_rope_kernel of the reference (solution/rope.py:17-43).
 #include "common.cuh"
+#include "rowpipe.cuh"
 
 namespace soup {
 namespace {
@@ -90,6 +91,102 @@ __global__ void __launch_bounds__(kThreads) rope_vec_kernel(RopeArgs a) {
   }
 }
 
+// Pipelined variant for the model's layout (the heads of a position adjacent in memory, as in a
+// transposed view of the projection output): a warp owns a position; its q row, k row, cos row and
+// sin row arrive in the warp's shared-memory ring by bulk async copies (rowpipe.cuh) while it
+// rotates the previous position, so the bytes in flight are bounded by shared memory, not by
+// registers. Lanes walk the (head, 16-byte chunk) pairs of the position; stores go straight to
+// the [b, h, t, d] outputs, 128 contiguous bytes per quarter warp.
+// DT: the one dtype code of q, k, cos, sin and both outputs when they all agree (the hot cases:
+// all fp16, all bf16, all fp32), or -1 to read the codes from the arguments.
+template <int XB, int DT>
+__global__ void __launch_bounds__(rowpipe::kMaxWarps * 32, 2)
+rope_pipe_kernel(RopeArgs a, int stages, int* status) {
+  constexpr int EPV = 4;   // elements per lane and half: 8- or 16-byte vectors, 16 cos/sin registers
+  const int xdt_q = DT >= 0 ? DT : a.xdt[0], xdt_k = DT >= 0 ? DT : a.xdt[1];
+  const int odt_q = DT >= 0 ? DT : a.odt[0], odt_k = DT >= 0 ? DT : a.odt[1];
+  const int csdt = DT >= 0 ? DT : a.csdt;
+  extern __shared__ __align__(128) char smem[];
+  __shared__ int s_abort;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  const int half = a.d >> 1, chunks = half / EPV;   // chunks divides 32 (checked by the host)
+  const uint32_t q_bytes = (uint32_t)(a.heads[0] * a.d) * XB, k_bytes = (uint32_t)(a.heads[1] * a.d) * XB;
+  if (threadIdx.x == 0) s_abort = 0;
+  rowpipe::Ring ring;
+  ring.init(smem, q_bytes + k_bytes, stages, warp, lane);
+  __syncthreads();
+  const int64_t n_rows = a.b * a.t;
+  const int64_t row0 = (int64_t)blockIdx.x * warps + warp;
+  const int64_t stride = (int64_t)gridDim.x * warps;
+  // Two bulk copies per position (its q heads, its k heads). The copy engine has a cost per copy,
+  // so the 256-byte cos and sin rows do not go through it: every lane keeps the cos/sin values of
+  // its own chunk in registers (its chunk is the same for all heads, as chunks divides 32) and
+  // fetches the next position's with plain loads while it rotates the current one.
+  auto request = [&](int s, int64_t row) {   // lane 0 only
+    const int64_t bi = row / a.t, ti = row % a.t;
+    char* dst = ring.slot_ptr(s);
+    umma::mbar_expect_tx(&ring.bars[s], q_bytes + k_bytes);
+    if (q_bytes)
+      rowpipe::bulk_load(dst, reinterpret_cast<const char*>(a.x[0]) + (bi * a.sb[0] + ti * a.st[0]) * XB,
+                         q_bytes, &ring.bars[s]);
+    if (k_bytes)
+      rowpipe::bulk_load(dst + q_bytes,
+                         reinterpret_cast<const char*>(a.x[1]) + (bi * a.sb[1] + ti * a.st[1]) * XB,
+                         k_bytes, &ring.bars[s]);
+  };
+  int64_t next = row0;
+  if (lane == 0)
+    for (int s = 0; s < stages && next < n_rows; ++s, next += stride) request(s, next);
+  next = __shfl_sync(0xffffffffu, next, 0);
+  const int total_pairs = (a.heads[0] + a.heads[1]) * chunks;
+  const int dh = 32 / chunks;
+  const int h_first = lane / chunks, c = lane - h_first * chunks;
+  float c1[EPV], c2[EPV], s1[EPV], s2[EPV];
+  auto fetch_cs = [&](int64_t row) {
+    const int64_t cs_row = (row / a.t) * a.cs_b + (row % a.t) * a.cs_t + c * EPV;
+    loadv<EPV>(a.cos, cs_row, csdt, c1);
+    loadv<EPV>(a.cos, cs_row + half, csdt, c2);
+    loadv<EPV>(a.sin, cs_row, csdt, s1);
+    loadv<EPV>(a.sin, cs_row + half, csdt, s2);
+  };
+  if (row0 < n_rows) fetch_cs(row0);
+  for (int64_t row = row0; row < n_rows; row += stride) {
+    if (!ring.wait(&s_abort, status, 13)) {
+      ring.drain((int)((next - row) / stride));
+      return;
+    }
+    const int64_t bi = row / a.t, ti = row % a.t;
+    const char* src = ring.slot_ptr(ring.slot);
+    int h = h_first;
+#pragma unroll 2
+    for (int p = lane; p < total_pairs; p += 32, h += dh) {
+      const int which = h < a.heads[0] ? 0 : 1;
+      const int hh = which ? h - a.heads[0] : h;
+      float x1[EPV], x2[EPV], o1[EPV], o2[EPV];
+      const int e = h * a.d + c * EPV;   // q heads and then k heads are adjacent in the slot as well
+      unpack<EPV, XB>(ld_raw<EPV * XB>(src, (int64_t)e * XB), which ? xdt_k : xdt_q, x1);
+      unpack<EPV, XB>(ld_raw<EPV * XB>(src, (int64_t)(e + half) * XB), which ? xdt_k : xdt_q, x2);
+#pragma unroll
+      for (int k = 0; k < EPV; ++k)
+        rotate(x1[k], x2[k], c1[k], c2[k], s1[k], s2[k], a.backward, o1[k], o2[k]);
+      const int64_t orow = ((bi * (which ? a.heads[1] : a.heads[0]) + hh) * a.t + ti) * a.d + c * EPV;
+      void* dst = which ? a.out[1] : a.out[0];
+      storev<EPV>(dst, orow, which ? odt_k : odt_q, o1);
+      storev<EPV>(dst, orow + half, which ? odt_k : odt_q, o2);
+    }
+    if (row + stride < n_rows) fetch_cs(row + stride);   // in flight during the next wait
+    __syncwarp();
+    if (next < n_rows) {
+      if (lane == 0) {
+        umma::fence_proxy_async_smem();
+        request(ring.slot, next);
+      }
+      next += stride;
+    }
+    ring.advance();
+  }
+}
+
 // Any head_dim / strides / alignment: one thread per (b, head, t, i < half).
 __global__ void __launch_bounds__(kThreads) rope_scalar_kernel(RopeArgs a) {
   const int half = a.d >> 1;
@@ -149,7 +246,33 @@ extern "C" int soup_rope(const void* q, const void* k, const void* cos, const vo
   bool vec = (d % 16 == 0) && aligned16(cos) && aligned16(sin) && mult8(cs_b) && mult8(cs_t);
   if (hq) vec = vec && aligned16(q) && aligned16(q_out) && mult8(q_sb) && mult8(q_sh) && mult8(q_st);
   if (hk) vec = vec && aligned16(k) && aligned16(k_out) && mult8(k_sb) && mult8(k_sh) && mult8(k_st);
-  if (vec) {
+  // The pipelined kernel: both tensors with a position's heads adjacent (stride d between heads),
+  // one element size for q and k, a slot that fits the ring.
+  const int xb = dtype_size(hq ? q_dtype : k_dtype);
+  const bool adjacent = vec && (!hq || q_sh == d) && (!hk || k_sh == d) &&
+                        (!hq || !hk || dtype_size(q_dtype) == dtype_size(k_dtype));
+  rowpipe::Plan plan = {8, 0, 1, 1, 0, 0};
+  const int chunks = (int)(d / 2) / 4;
+  if (adjacent && chunks > 0 && 32 % chunks == 0)
+    plan = rowpipe::make_plan((size_t)(hq + hk) * d * xb, 0, false, b * t);
+  int* status = plan.stages ? rowpipe::status_word() : nullptr;
+  if (plan.stages && status) {
+    const int dt0 = hq ? q_dtype : k_dtype;
+    const bool same = (!hq || (q_dtype == dt0 && q_out_dtype == dt0)) &&
+                      (!hk || (k_dtype == dt0 && k_out_dtype == dt0)) && cs_dtype == dt0;
+#define SOUP_ROPE_P(XB_, DT_)                                                                    \
+  do {                                                                                            \
+    auto kernel = rope_pipe_kernel<XB_, DT_>;                                                     \
+    cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plan.smem);    \
+    kernel<<<plan.grid, plan.warps * 32, plan.smem, s>>>(a, plan.stages, status);                 \
+  } while (0)
+    if (same && dt0 == SOUP_F16) SOUP_ROPE_P(2, SOUP_F16);
+    else if (same && dt0 == SOUP_BF16) SOUP_ROPE_P(2, SOUP_BF16);
+    else if (same && dt0 == SOUP_F32) SOUP_ROPE_P(4, SOUP_F32);
+    else if (xb == 4) SOUP_ROPE_P(4, -1);
+    else SOUP_ROPE_P(2, -1);
+#undef SOUP_ROPE_P
+  } else if (vec) {
     const int64_t threads = b * t * (d >> 4);
     // One thread walks all heads of its position when there are enough positions to fill the
     // GPU; otherwise the heads are split over grid.y so that about 2^17 threads exist.

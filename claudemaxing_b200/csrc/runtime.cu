@@ -3,6 +3,7 @@
 #include <stdio.h>
 
 #include "common.cuh"
+#include "rowpipe.cuh"
 
 namespace soup {
 
@@ -29,7 +30,37 @@ int sm_count() {
   return cached[dev];
 }
 
+namespace rowpipe {
+namespace {
+__device__ int g_row_status = 0;
+}
+int sm_count_for_plan() { return sm_count(); }
+int* status_word() {
+  static int* cached[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (!cached[dev]) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_row_status) != cudaSuccess) return nullptr;
+    cached[dev] = reinterpret_cast<int*>(p);
+  }
+  return cached[dev];
+}
+}  // namespace rowpipe
+
 }  // namespace soup
+
+extern "C" int soup_row_status(int* host_status, void* stream) {
+  using namespace soup;
+  if (!host_status) SOUP_FAIL(SOUP_ERR_ARG, "row_status: null pointer");
+  int* word = rowpipe::status_word();
+  if (!word) SOUP_FAIL(SOUP_ERR_DEVICE, "row_status: no status word on this device");
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (cudaMemcpyAsync(host_status, word, sizeof(int), cudaMemcpyDeviceToHost, s) != cudaSuccess ||
+      cudaStreamSynchronize(s) != cudaSuccess)
+    SOUP_FAIL(SOUP_ERR_LAUNCH, "row_status: %s", cudaGetErrorString(cudaGetLastError()));
+  return SOUP_OK;
+}
 
 extern "C" int soup_version(void) { return 1; }
 

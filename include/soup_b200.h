@@ -37,6 +37,11 @@ extern "C" {
 int soup_version(void);
 /* Message of the last failing call on this thread ("" if none). */
 const char* soup_last_error_string(void);
+/* Status word of the pipelined row kernels (RMSNorm, RoPE) on the current device: 0, or the code
+ * of the first bounded wait that ran out (11 RMSNorm forward, 12 RMSNorm backward, 13 RoPE). The
+ * word is sticky. Synchronises `stream`. No counterpart in the reference (its Triton kernels have
+ * no waits). */
+int soup_row_status(int* host_status, void* stream);
 
 /* NF4 -> fp16/fp32 weight, nested (double-quantised) absmax fused, bit-exact unfused fp32 math.
  * Replaces nf4_dequant_kernel[grid](...) at solution/nf4.py:78-81 (kernel :26-46).

@@ -123,7 +123,8 @@ def test_rmsnorm_golden(tag):
     assert_close_rel_max(w.grad.cpu(), g["dw"], 5e-3, "dw")
 
 
-@pytest.mark.parametrize("shape", [(4, 512, 1536), (3, 77, 1001), (2, 1, 4096), (1, 3, 16384)])
+@pytest.mark.parametrize("shape", [(4, 512, 1536), (3, 77, 1001), (2, 1, 4096), (1, 3, 16384),
+                                   (2, 33, 1288), (5, 7, 2048), (1, 19, 64), (3, 11, 3072)])
 @pytest.mark.parametrize("dtypes", [(F16, F32), (F16, F16), (F32, F32), (BF16, BF16)])
 @pytest.mark.parametrize("train_w", [False, True])
 def test_rmsnorm_vs_oracle(shape, dtypes, train_w):
