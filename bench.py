@@ -221,6 +221,14 @@ def kernel_suite(dev, hbm_peak, n_rows=2048, tag="", with_nf4=True):
                      "algorithmic_bytes": int(nbytes), "launches": launches}
 
     if with_nf4:
+        # Context for the write-heavy kernels: what torch's own copy and fill reach on this GPU,
+        # timed the same way (NF4 dequant writes four bytes for every byte it reads).
+        big_a = [torch.empty(256 << 20, dtype=torch.uint8, device=dev) for _ in range(3)]
+        ms = time_rotating(lambda i: big_a[(i + 1) % 3].copy_(big_a[i]), 3)
+        record("reference_torch_copy_256MiB", ms, 2 * (256 << 20))
+        ms = time_rotating(lambda i: big_a[i].zero_(), 3)
+        record("reference_torch_fill_256MiB", ms, 256 << 20)
+        del big_a
         # NF4 dequant: the seven projection shapes of one Qwen2.5-1.5B layer, 28 distinct layers
         shapes = [(1536, 1536), (256, 1536), (256, 1536), (1536, 1536), (8960, 1536), (8960, 1536),
                   (1536, 8960)]
