@@ -38,7 +38,7 @@ SIGNATURES = {
     "soup_lmhead_workspace_bytes": [_L, _L, _L, _L],
     "soup_lmhead_ce": [_P] * 13 + [_L] * 6 + [_I, _P],
     "soup_lmhead_set_timing": [_P],
-    "soup_lmhead_plan": [_L, _L, _L, _P, _P],
+    "soup_lmhead_plan": [_L, _L, _L, _P, _P, _P],
     "soup_lmhead_status": [_P, _L, _L, _L, _P, _P],
     "soup_lmhead_merge": [_P] * 15 + [_L, _I, _P],
     "soup_lmhead_finish": [_P] * 12 + [_L] * 4 + [_P],

@@ -883,29 +883,37 @@ inline int pick_ksplit(int tiles, int pairs, int n_kb, bool deterministic) {
 
 struct Plan {
   int row_block;   // rows per row block
-  int ct;          // column tiles per chunk
+  int ct_first;    // column tiles of the first chunk
+  int ct;          // column tiles of every later chunk (>= ct_first)
 };
 
-// Rows per block and column tiles per chunk: the P buffer of one chunk must stay L2 resident
-// (about 40 MB) and row_tiles * ct should fill whole waves of CTA pairs.
+// Rows per block and column tiles per chunk. The first chunk is the one whose logits are computed
+// twice (once for its row statistics, once for its probabilities against them), so it is one wave
+// of CTA pairs wide and no wider. Every later chunk is written against the running statistics in
+// a single pass and can be large: eight waves (SOUP_LMHEAD_WAVES overrides), which cuts the
+// launches of a step, and the ramp and drain each one pays, from 55 to 13 at 2048 x 151936 (1.80 ->
+// 1.50 ms measured; four waves 1.56, sixteen 1.52). Its probabilities (bf16, 310 MB at 2048 rows)
+// then go through HBM instead of staying in L2, which these compute-bound kernels have bandwidth
+// to spare for. row_tiles * ct fills whole waves of CTA pairs. An override applies to all chunks.
 inline Plan make_plan(int64_t n, int64_t v_shard, int sms, int ct_override) {
   Plan p;
   p.row_block = (int)(n < 2048 ? (n < 1 ? 1 : n) : 2048);
   const int rt = (p.row_block + 2 * kBM - 1) / (2 * kBM);
   const int pairs = sms / 2 > 0 ? sms / 2 : 1;
   const int total_ct = (int)((v_shard + kBN - 1) / kBN);
-  int ct = 37;
-  if (ct_override > 0) {
-    ct = ct_override;
-  } else {
-    int best = -1;
-    for (int c = 40; c >= 8; --c)
-      if ((rt * c) % pairs == 0) { best = c; break; }
-    if (best > 0) ct = best;
-  }
-  if (ct > total_ct) ct = total_ct;
-  if (ct < 1) ct = 1;
-  p.ct = ct;
+  int wave = 37;
+  int best = -1;
+  for (int c = 40; c >= 8; --c)
+    if ((rt * c) % pairs == 0) { best = c; break; }
+  if (best > 0) wave = best;
+  p.ct_first = ct_override > 0 ? ct_override : wave;
+  int waves = 8;
+  if (const char* e = getenv("SOUP_LMHEAD_WAVES")) { const int v = atoi(e); if (v >= 1 && v <= 64) waves = v; }
+  p.ct = ct_override > 0 ? ct_override : waves * wave;
+  if (p.ct_first > total_ct) p.ct_first = total_ct;
+  if (p.ct_first < 1) p.ct_first = 1;
+  if (p.ct > total_ct) p.ct = total_ct;
+  if (p.ct < p.ct_first) p.ct = p.ct_first;
   return p;
 }
 
@@ -1088,9 +1096,10 @@ extern "C" int soup_lmhead_ce(const void* hidden, const void* weight, const void
   for (int64_t r0 = 0; r0 < n; r0 += plan.row_block) {
     const int rows = (int)((n - r0) < plan.row_block ? (n - r0) : plan.row_block);
     const int rt = (rows + 2 * kBM - 1) / (2 * kBM);
-    for (int t0 = 0; t0 < total_ct; t0 += plan.ct) {
-      const int ct = (total_ct - t0) < plan.ct ? (total_ct - t0) : plan.ct;
+    for (int t0 = 0; t0 < total_ct;) {
       const bool first = t0 == 0;
+      const int want_ct = first ? plan.ct_first : plan.ct;
+      const int ct = (total_ct - t0) < want_ct ? (total_ct - t0) : want_ct;
       LogitsArgs la;
       la.target = target + r0;
       la.ref = run_max + r0;
@@ -1162,6 +1171,7 @@ extern "C" int soup_lmhead_ce(const void* hidden, const void* weight, const void
         timer.mark(2);
         SOUP_CHECK_LAUNCH("lmhead_grad");
       }
+      t0 += ct;
     }
   }
   timer.finish();
@@ -1174,10 +1184,11 @@ extern "C" int soup_lmhead_set_timing(float* host_sink6) {
 }
 
 extern "C" int soup_lmhead_plan(int64_t n, int64_t v_shard, int64_t chunk_tiles, int64_t* row_block,
-                                int64_t* tiles_per_chunk) {
+                                int64_t* first_chunk_tiles, int64_t* tiles_per_chunk) {
   using namespace soup;
   const Plan p = make_plan(n, v_shard, sm_count(), (int)chunk_tiles);
   if (row_block) *row_block = p.row_block;
+  if (first_chunk_tiles) *first_chunk_tiles = p.ct_first;
   if (tiles_per_chunk) *tiles_per_chunk = p.ct;
   return SOUP_OK;
 }

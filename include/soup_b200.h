@@ -193,9 +193,10 @@ int soup_lmhead_ce(const void* hidden, const void* weight, const void* weight_bf
  * harness times kernels from Python, harness/_train.py:44-83). */
 int soup_lmhead_set_timing(float* host_sink6);
 
-/* The tiling soup_lmhead_ce uses for a shape: rows per row block and 256-column tiles per chunk. */
+/* The tiling soup_lmhead_ce uses for a shape: rows per row block, 256-column tiles of the first
+ * chunk (whose logits are computed twice) and of every later chunk. */
 int soup_lmhead_plan(int64_t n, int64_t v_shard, int64_t chunk_tiles, int64_t* row_block,
-                     int64_t* tiles_per_chunk);
+                     int64_t* first_chunk_tiles, int64_t* tiles_per_chunk);
 
 /* Reads back the device status word of the last soup_lmhead_ce on this workspace (synchronises
  * `stream`): 0 = every bounded wait completed; otherwise the code of the wait that gave up. */
