@@ -1,7 +1,9 @@
 // Fused LM head + cross-entropy, forward and hidden-state gradient, without the logits in HBM.
 //
-// The vocabulary is walked in chunks of `ct` column tiles (256 columns each). Per chunk three
-// kernels run back to back on the caller's stream; what they exchange stays in the 126 MB L2:
+// The vocabulary is walked in chunks of column tiles (256 columns each): a first chunk of one
+// wave of CTA pairs, then chunks of eight waves. Per chunk three kernels run back to back on the
+// caller's stream; a chunk's probabilities pass from the first to the third through a bf16 buffer
+// in HBM (the GEMMs leave more than 80 % of the memory bandwidth unused):
 //
 //   logits kernel  tcgen05 GEMM  S = H[rows,K] * W[cols,K]^T on CTA pairs (cta_group::2): a pair
 //                  owns a 256 x 256 tile, each CTA 128 rows of it and half of the W columns, fp32
