@@ -31,6 +31,7 @@ SIGNATURES = {
     "soup_rmsnorm_bwd_noalloc": [_P, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _I, _I, _I, _I, _I, _P],
     "soup_rope": [_P, _P, _P, _P, _P, _P] + [_L] * 13 + [_I] * 6 + [_P],
     "soup_row_status": [_P, _P],
+    "soup_wait_selftest": [_L, _P, _P, _P],
     "soup_silu_mul_fwd": [_P, _P, _P, _L, _I, _I, _I, _I, _P],
     "soup_silu_mul_bwd": [_P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _P],
     "soup_dropout_pack": [_P, _P, _P, _P, _L, _F, _I, _P],

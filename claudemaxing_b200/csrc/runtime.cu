@@ -50,6 +50,49 @@ int* status_word() {
 
 }  // namespace soup
 
+namespace soup {
+namespace {
+__device__ int g_selftest[2] = {0, 0};   // [0] status code, [1] 1 when the wait returned "gave up"
+
+// A barrier that nothing ever completes: every thread's bounded wait has to run out, record its
+// code and return, leaving the context healthy.
+__global__ void wait_selftest_kernel(int* words, uint64_t limit_ns) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    umma::mbar_init(&bar, 1);
+    abort_flag = 0;
+  }
+  umma::fence_barrier_init();
+  __syncthreads();
+  const bool ok = umma::mbar_wait_for(&bar, 0, &abort_flag, &words[0], 99, limit_ns);
+  if (!ok && threadIdx.x == 0) words[1] = 1;
+}
+}  // namespace
+}  // namespace soup
+
+extern "C" int soup_wait_selftest(int64_t limit_ns, int* host_gave_up, int* host_status,
+                                  void* stream) {
+  using namespace soup;
+  if (limit_ns <= 0 || limit_ns > 100000000 || !host_gave_up || !host_status)
+    SOUP_FAIL(SOUP_ERR_ARG, "wait_selftest: limit must be in (0, 100 ms] and the outputs non-null");
+  void* words = nullptr;
+  if (cudaGetSymbolAddress(&words, g_selftest) != cudaSuccess || !words)
+    SOUP_FAIL(SOUP_ERR_DEVICE, "wait_selftest: no scratch on this device");
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  int out[2] = {0, 0};
+  if (cudaMemsetAsync(words, 0, sizeof(out), s) != cudaSuccess)
+    SOUP_FAIL(SOUP_ERR_LAUNCH, "wait_selftest: %s", cudaGetErrorString(cudaGetLastError()));
+  wait_selftest_kernel<<<1, 64, 0, s>>>(reinterpret_cast<int*>(words), (uint64_t)limit_ns);
+  SOUP_CHECK_LAUNCH("wait_selftest");
+  if (cudaMemcpyAsync(out, words, sizeof(out), cudaMemcpyDeviceToHost, s) != cudaSuccess ||
+      cudaStreamSynchronize(s) != cudaSuccess)
+    SOUP_FAIL(SOUP_ERR_LAUNCH, "wait_selftest: %s", cudaGetErrorString(cudaGetLastError()));
+  *host_status = out[0];
+  *host_gave_up = out[1];
+  return SOUP_OK;
+}
+
 extern "C" int soup_row_status(int* host_status, void* stream) {
   using namespace soup;
   if (!host_status) SOUP_FAIL(SOUP_ERR_ARG, "row_status: null pointer");

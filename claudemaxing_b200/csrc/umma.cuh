@@ -62,20 +62,25 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 // Bounded wait: gives up after kWaitLimitNs of wall time. `abort_flag` is a shared-memory word
 // every role of the CTA polls, so that one role giving up releases the others too. Returns false
 // when the wait was abandoned; the first abandoning waiter records `code` in `status`.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                          int* status, int code) {
+__device__ __forceinline__ bool mbar_wait_for(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                              int* status, int code, uint64_t limit_ns) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = global_timer_ns();
   for (uint32_t i = 1;; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((i & 63u) == 0u) {
       if (*abort_flag) return false;
-      if (global_timer_ns() - t0 > kWaitLimitNs) break;
+      if (global_timer_ns() - t0 > limit_ns) break;
     }
   }
   *abort_flag = 1;
   if (status) atomicCAS(status, 0, code);
   return false;
+}
+
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                          int* status, int code) {
+  return mbar_wait_for(bar, parity, abort_flag, status, code, kWaitLimitNs);
 }
 
 // ---------------------------------------------------------------- TMA

@@ -12,13 +12,11 @@ reference's: fp16 operands, fp32 statistics, the gradient accumulated at GRAD_SC
 the running log-sum-exp, the label's -1 restored at the end.
 """
 
-import functools
-from types import SimpleNamespace
+import dataclasses
 
 import torch
 
 from . import _lib
-from .embedding import shrink_tied_embedding
 
 IGNORE_INDEX = -100
 GRAD_SCALE = 1024.0
@@ -205,274 +203,70 @@ class _FusedHeadLoss(torch.autograd.Function):
         return grad.view(ctx.shape), None, None, None, None, None, None
 
 
+@dataclasses.dataclass
+class StepTerms:
+    """What the trainer's metrics need from a step: per-token loss and entropy `[batch, seq]`
+    (fp32, zero at ignored positions), the number of correct argmax predictions and of labelled
+    positions (0-d tensors)."""
+
+    token_loss: torch.Tensor
+    token_entropy: torch.Tensor
+    correct: torch.Tensor
+    labelled: torch.Tensor
+
+
 def fused_head_loss(hidden, weight, labels, num_items_in_batch=None, chunk_cols=None,
                     target=None):
-    """ForCausalLMLoss(linear(hidden, weight), labels) and the per-token terms the trainer's
-    metrics need, without materialising the logits. `weight` must be frozen: the gradient goes to
-    `hidden` only. Returns (loss, step) with step.token_loss and step.token_entropy of shape
-    [batch, seq] (fp32), step.correct and step.labelled (counts). `target` (the labels already
-    shifted, same leading shape as `hidden`) replaces `labels` when given."""
-    if target is None:
-        target = shift_labels_left(labels)
-    target = target.to(hidden.device)
-    labelled = (target != IGNORE_INDEX).sum()
-    if num_items_in_batch is None:
-        denominator = labelled
-    elif torch.is_tensor(num_items_in_batch):
-        denominator = num_items_in_batch.to(hidden.device)
-    else:
-        denominator = num_items_in_batch
-    compute_dtype = head_compute_dtype(hidden, weight)
-    if compute_dtype is None:
+    """ForCausalLMLoss(linear(hidden, weight), labels) plus the per-token terms the trainer's
+    metrics need, without the logits. `weight` must be frozen: only `hidden` gets a gradient.
+    Returns (loss, StepTerms). `target` (labels already shifted, same leading shape as `hidden`)
+    replaces `labels` when given; `num_items_in_batch` (number or tensor) replaces the count of
+    labelled positions as the divisor of the loss."""
+    dtype = head_compute_dtype(hidden, weight)
+    if dtype is None:
         raise TypeError(f"hidden {hidden.dtype} and head {weight.dtype} differ outside autocast")
-    want_grad = torch.is_grad_enabled() and hidden.requires_grad
-    loss, token_loss, entropy, correct = _FusedHeadLoss.apply(
-        hidden, weight, target, denominator, compute_dtype, chunk_cols, want_grad)
-    step = SimpleNamespace(token_loss=token_loss, token_entropy=entropy,
-                           correct=correct.sum(), labelled=labelled)
-    return loss, step
+    scored = (shift_labels_left(labels) if target is None else target).to(hidden.device)
+    n_scored = scored.ne(IGNORE_INDEX).sum()
+    divisor = n_scored
+    if num_items_in_batch is not None:
+        divisor = (num_items_in_batch.to(hidden.device) if torch.is_tensor(num_items_in_batch)
+                   else num_items_in_batch)
+    needs_grad = hidden.requires_grad and torch.is_grad_enabled()
+    loss, per_token, entropy, hits = _FusedHeadLoss.apply(hidden, weight, scored, divisor, dtype,
+                                                          chunk_cols, needs_grad)
+    return loss, StepTerms(per_token, entropy, hits.sum(), n_scored)
 
 
 @torch.no_grad()
 def head_metrics_from_logits(logits, labels):
-    """The same per-token terms from logits that were built anyway (fallback path of the
-    reference, solution/lm_head_loss.py:285-297): one warp per row over the full logits."""
-    target = shift_labels_left(labels).to(logits.device).reshape(-1).contiguous().to(torch.int64)
-    flat = logits.reshape(-1, logits.shape[-1]).contiguous()
-    _lib.require_cuda(flat)
-    n = flat.shape[0]
-    token_loss = torch.empty(n, dtype=torch.float32, device=logits.device)
-    entropy = torch.empty_like(token_loss)
-    correct = torch.empty(n, dtype=torch.int32, device=logits.device)
+    """StepTerms from logits that exist anyway (the route the reference keeps for steps that end
+    up building them, solution/lm_head_loss.py:285-297): one warp per row over the full logits."""
+    rows = logits.reshape(-1, logits.shape[-1]).contiguous()
+    _lib.require_cuda(rows)
+    scored = shift_labels_left(labels).to(rows.device).reshape(-1).to(torch.int64).contiguous()
+    n = rows.shape[0]
+    per_token = torch.empty(n, dtype=torch.float32, device=rows.device)
+    entropy = torch.empty(n, dtype=torch.float32, device=rows.device)
+    hits = torch.empty(n, dtype=torch.int32, device=rows.device)
     if n:
-        _lib.call("soup_xent_rows", _lib.ptr(flat), _lib.ptr(target), _lib.ptr(token_loss),
-                  _lib.ptr(entropy), _lib.ptr(correct), n, flat.shape[1], flat.stride(0),
-                  _lib.dtype_code(flat.dtype), _lib.stream_of(flat))
-    shape = logits.shape[:-1]
-    return SimpleNamespace(token_loss=token_loss.view(shape), token_entropy=entropy.view(shape),
-                           correct=correct.sum(), labelled=(target != IGNORE_INDEX).sum())
+        _lib.call("soup_xent_rows", _lib.ptr(rows), _lib.ptr(scored), _lib.ptr(per_token),
+                  _lib.ptr(entropy), _lib.ptr(hits), n, rows.shape[1], rows.stride(0),
+                  _lib.dtype_code(rows.dtype), _lib.stream_of(rows))
+    lead = logits.shape[:-1]
+    return StepTerms(per_token.view(lead), entropy.view(lead), hits.sum(),
+                     scored.ne(IGNORE_INDEX).sum())
 
 
-def _pack_batch(lm, kwargs, labels):
-    """The real (non-pad) tokens of a padded batch as one row [1, N] with per-token position ids,
-    a [1, 1, N, N] mask (same batch row, key column not after the query's) and the shifted
-    targets; None to run the batch as it is (solution/lm_head_loss.py:300-336)."""
-    ids, mask = kwargs.get("input_ids"), kwargs.get("attention_mask")
-    head = lm.lm_head
-    if (not isinstance(ids, torch.Tensor) or ids.dim() != 2 or not ids.is_cuda
-            or not isinstance(mask, torch.Tensor) or mask.shape != ids.shape
-            or kwargs.get("inputs_embeds") is not None or kwargs.get("past_key_values") is not None
-            or labels.shape != ids.shape
-            or type(head) is not torch.nn.Linear or head.bias is not None
-            or head.weight.requires_grad
-            or getattr(lm.config, "_attn_implementation", None) != "sdpa"
-            or getattr(lm.config, "use_sliding_window", False)):
-        return None
-    return pack_tokens(ids, mask, labels, kwargs.get("position_ids"))
-
-
-def pack_tokens(ids, mask, labels, position_ids=None):
-    """The device-independent part of `_pack_batch` (also used to build synthetic packed rows)."""
-    B, T = ids.shape
-    keep = mask.reshape(-1) != 0
-    index = keep.nonzero().squeeze(1)
-    n = index.numel()
-    if n == 0 or n == B * T:
-        return None
-    pos = position_ids
-    if isinstance(pos, torch.Tensor) and pos.shape == ids.shape:
-        pos = pos.reshape(-1)[index]
-    elif pos is None:
-        pos = index % T
-    else:
-        return None
-    row, col = index // T, index % T
-    allowed = (row[:, None] == row[None, :]) & (col[None, :] <= col[:, None])
-    target = shift_labels_left(labels.to(ids.device)).reshape(-1)[index]
-    return SimpleNamespace(B=B, T=T, index=index, ids=ids.reshape(-1)[index][None],
-                           pos=pos[None], mask=allowed[None, None], target=target[None])
-
-
-def _packed_forward(lm, kwargs, packed):
-    """The fused training forward on the packed real tokens; the per-token terms go back to their
-    [batch, seq] places (zeros at pads, which every consumer masks out)."""
-    from transformers.modeling_outputs import CausalLMOutputWithPast
-
-    rest = {k: v for k, v in kwargs.items()
-            if k not in ("input_ids", "attention_mask", "position_ids")}
-    outputs = lm.model(input_ids=packed.ids, attention_mask=packed.mask,
-                       position_ids=packed.pos, **rest)
-    hidden = outputs.last_hidden_state
-    loss, step = fused_head_loss(hidden, lm.lm_head.weight, None,
-                                 num_items_in_batch=kwargs.get("num_items_in_batch"),
-                                 target=packed.target)
-    full = packed.B * packed.T
-
-    def spread(values):
-        out = torch.zeros(full, dtype=values.dtype, device=values.device)
-        out[packed.index] = values.reshape(-1)
-        return out.view(packed.B, packed.T)
-
-    step = SimpleNamespace(token_loss=spread(step.token_loss),
-                           token_entropy=spread(step.token_entropy),
-                           correct=step.correct, labelled=step.labelled)
-    lm.__dict__[_STEP_ATTR] = step
-    return CausalLMOutputWithPast(loss=loss, logits=None)
-
-
-def _head_is_fusable(head):
-    return (type(head) is torch.nn.Linear and head.bias is None
-            and not head.weight.requires_grad)
-
-
-def patch_qwen2_causal_lm_head():
-    """Qwen2ForCausalLM.forward: when the trainer has asked for it (and only then), build the loss
-    from the hidden states with the fused head and return no logits."""
-    from transformers.modeling_outputs import CausalLMOutputWithPast
-    from transformers.models.qwen2 import modeling_qwen2
-
-    cls = getattr(modeling_qwen2, "Qwen2ForCausalLM", None)
-    if cls is None or getattr(cls.forward, "_fused_head", False):
-        return
-    original = cls.forward
-
-    @functools.wraps(original)  # the trainer reads the forward's signature
-    def forward(self, *args, **kwargs):
-        asked = self.__dict__.pop(_REQUEST_ATTR, False)
-        labels = kwargs.get("labels")
-        keep = kwargs.get("logits_to_keep", 0)
-        if (not asked or args or labels is None or not isinstance(keep, int) or keep != 0
-                or "shift_labels" in kwargs or kwargs.get("return_dict") is False):
-            return original(self, *args, **kwargs)
-        kwargs.pop("labels")
-        kwargs.pop("logits_to_keep", None)
-        shrink_tied_embedding(self)
-        packed = _pack_batch(self, kwargs, labels)
-        if packed is not None:
-            return _packed_forward(self, kwargs, packed)
-        outputs = self.model(**kwargs)
-        hidden = outputs.last_hidden_state
-        head = self.lm_head
-        if (not _head_is_fusable(head) or not hidden.is_cuda
-                or head_compute_dtype(hidden, head.weight) != torch.float16):
-            logits = head(hidden)  # what the original forward does from here on
-            loss = self.loss_function(logits=logits, labels=labels,
-                                      vocab_size=self.config.vocab_size, **kwargs)
-            return CausalLMOutputWithPast(loss=loss, logits=logits,
-                                          past_key_values=outputs.past_key_values,
-                                          hidden_states=outputs.hidden_states,
-                                          attentions=outputs.attentions)
-        loss, step = fused_head_loss(hidden, head.weight, labels,
-                                     num_items_in_batch=kwargs.get("num_items_in_batch"))
-        self.__dict__[_STEP_ATTR] = step
-        return CausalLMOutputWithPast(loss=loss, logits=None,
-                                      past_key_values=outputs.past_key_values,
-                                      hidden_states=outputs.hidden_states,
-                                      attentions=outputs.attentions)
-
-    forward._fused_head = True
-    cls.forward = forward
-
-
-def _causal_lm(model):
-    while isinstance(getattr(model, "module", None), torch.nn.Module):
-        model = model.module
-    get_base = getattr(model, "get_base_model", None)
-    return get_base() if callable(get_base) else model
-
-
-def _fused_target(trainer, model, inputs):
-    """The causal LM to run with the fused head, or None to keep TRL's own path."""
-    if (not isinstance(model, torch.nn.Module) or not getattr(trainer.model, "training", False)
-            or isinstance(model, torch.nn.DataParallel)
-            or getattr(trainer.args, "n_gpu", 1) > 1
-            or not isinstance(inputs, dict) or "labels" not in inputs
-            or "shift_labels" in inputs
-            or getattr(trainer.args, "use_liger_kernel", False)
-            or getattr(trainer, "num_virtual_tokens", 0)
-            or getattr(trainer, "aux_loss_enabled", False)
-            or getattr(trainer, "compute_loss_func", None) is not None
-            or getattr(trainer, "label_smoother", None) is not None
-            or not hasattr(trainer, "_metrics")):
-        return None
-    lm = _causal_lm(model)
-    if not getattr(type(lm).forward, "_fused_head", False):
-        return None
-    head = lm.get_output_embeddings()
-    if (not _head_is_fusable(head) or not head.weight.is_cuda
-            or getattr(lm.config, "final_logit_softcapping", None) is not None):
-        return None
-    return lm
-
-
-def _log_trl_metrics(trainer, mode, inputs, step):
-    """entropy, num_tokens and mean_token_accuracy as SFTTrainer.compute_loss logs them from the
-    logits: same masks, same gathers, same order of reductions
-    (solution/lm_head_loss.py:449-472)."""
-    gather = trainer.accelerator.gather_for_metrics
-    if "attention_mask" in inputs:
-        mask = inputs["attention_mask"]
-        entropy = torch.sum(step.token_entropy * mask) / mask.sum()
-    elif "position_ids" in inputs:
-        entropy = torch.mean(step.token_entropy)
-    else:
-        raise ValueError("Expected 'attention_mask' or 'position_ids' in inputs.")
-    trainer._metrics[mode]["entropy"].append(gather(entropy).mean().item())
-    if mode == "train":
-        if "attention_mask" in inputs:
-            num_tokens = gather(inputs["attention_mask"].sum()).sum().item()
-        else:
-            local = torch.tensor(inputs["position_ids"].size(1),
-                                 device=inputs["position_ids"].device)
-            num_tokens = gather(local).sum().item()
-        trainer._total_train_tokens += num_tokens
-    trainer._metrics[mode]["num_tokens"] = [trainer._total_train_tokens]
-    correct, total = gather(step.correct), gather(step.labelled)
-    total_sum = total.sum()
-    accuracy = (correct.sum() / total_sum).item() if total_sum > 0 else 0.0
-    trainer._metrics[mode]["mean_token_accuracy"].append(accuracy)
-
-
-def patch_sft_compute_loss():
-    """TRL's SFTTrainer.compute_loss, for a training step of a patched causal LM: ask the model for
-    the fused head, log TRL's metrics from the per-token terms and leave the per-token losses where
-    Soup's rewind recorder looks for them. Without TRL there is nothing to patch."""
-    try:
-        from trl.trainer import sft_trainer as trl_sft
-    except Exception:  # noqa: BLE001
-        return
-    cls = trl_sft.SFTTrainer
-    if getattr(cls.compute_loss, "_fused_head", False):
-        return
-    original = cls.compute_loss
-
-    def compute_loss(self, model, inputs, return_outputs=False, num_items_in_batch=None):
-        lm = _fused_target(self, model, inputs)
-        if lm is None:
-            setattr(self, SOUP_STEP_ATTR, None)
-            return original(self, model, inputs, return_outputs=return_outputs,
-                            num_items_in_batch=num_items_in_batch)
-        inputs.pop("_prediction_loss_only", None)
-        labels = inputs["labels"]
-        inputs["use_cache"] = False
-        setattr(self, SOUP_STEP_ATTR, None)
-        lm.__dict__[_REQUEST_ATTR] = True
-        try:
-            loss, outputs = super(cls, self).compute_loss(
-                model, inputs, return_outputs=True, num_items_in_batch=num_items_in_batch)
-        finally:
-            lm.__dict__.pop(_REQUEST_ATTR, None)
-        step = lm.__dict__.pop(_STEP_ATTR, None)
-        if step is None:  # the forward built the logits after all
-            step = head_metrics_from_logits(outputs.logits, labels)
-        _log_trl_metrics(self, "train", inputs, step)
-        setattr(self, SOUP_STEP_ATTR, SimpleNamespace(token_loss=step.token_loss))
-        return (loss, outputs) if return_outputs else loss
-
-    compute_loss._fused_head = True
-    cls.compute_loss = compute_loss
-
-
-def patch_fused_head_loss():
-    patch_qwen2_causal_lm_head()
-    patch_sft_compute_loss()
+# The transformers / TRL side lives in trainer_glue.py; its names stay importable from here, where
+# the reference keeps them.
+from .trainer_glue import (  # noqa: E402,F401
+    PackedRow,
+    _pack_batch,
+    _packed_forward,
+    explain_batch_route,
+    explain_trainer_route,
+    pack_tokens,
+    patch_fused_head_loss,
+    patch_qwen2_causal_lm_head,
+    patch_sft_compute_loss,
+)

@@ -59,14 +59,14 @@ class LoRABranch(torch.autograd.Function):
         a16, b16 = weight_a.to(torch.float16), weight_b.to(torch.float16)
         a = torch.nn.functional.linear(xd, a16)
         out = torch.nn.functional.linear(a, b16) * scaling
-        ctx.save_for_backward(x16, bits, a, weight_a, weight_b)
+        ctx.save_for_backward(x16, bits, a, a16, b16)   # the fp16 adapter copies are 50 KB each
         ctx.scale, ctx.scaling, ctx.x_dtype = scale, scaling, x.dtype
+        ctx.weight_dtypes = (weight_a.dtype, weight_b.dtype)
         return out
 
     @staticmethod
     def backward(ctx, grad):
-        x16, bits, a, weight_a, weight_b = ctx.saved_tensors
-        a16, b16 = weight_a.to(torch.float16), weight_b.to(torch.float16)
+        x16, bits, a, a16, b16 = ctx.saved_tensors
         g = grad.to(torch.float16) * ctx.scaling
         g2 = g.reshape(-1, g.shape[-1])
         grad_b = g2.t().mm(a.reshape(-1, a.shape[-1]))
@@ -75,73 +75,101 @@ class LoRABranch(torch.autograd.Function):
         grad_xd = grad_a_in.matmul(a16)
         xd, dx = _unpack(x16, bits, grad_xd.contiguous(), ctx.scale, ctx.x_dtype)
         grad_a = ga2.t().mm(xd.reshape(-1, xd.shape[-1]))
-        return dx, None, grad_a.to(weight_a.dtype), grad_b.to(weight_b.dtype), None, None
+        return dx, None, grad_a.to(ctx.weight_dtypes[0]), grad_b.to(ctx.weight_dtypes[1]), None, None
 
 
-# (weakref to x, (version, data_ptr, shape), weakref to its fp16 copy)
-_X16 = [None, None, None]
+class _SharedCopy:
+    """The fp16 copy of the tensor the adapter layers of a block all see (q_proj and v_proj get the
+    same hidden states): made once, found again by identity, version and storage of the source."""
+
+    def __init__(self):
+        self.source = self.copy = None
+        self.stamp = None
+
+    @staticmethod
+    def _stamp(x):
+        return x._version, x.data_ptr(), tuple(x.shape)
+
+    def lookup(self, x):
+        if self.source is None or self.copy is None:
+            return None
+        src, low = self.source(), self.copy()
+        if src is x and low is not None and self.stamp == self._stamp(x):
+            return low
+        return None
+
+    def remember(self, x, low):
+        self.source, self.copy, self.stamp = weakref.ref(x), weakref.ref(low), self._stamp(x)
+
+
+_COPY = _SharedCopy()
 
 
 def _shared_fp16(x):
-    """One fp16 copy of `x` for all the adapter layers that see the same tensor (q and v of a
-    block): the copy the preceding RMSNorm wrote if there is one, else a fresh cast."""
-    ref, key, x16_ref = _X16
-    now = (x._version, x.data_ptr(), tuple(x.shape))
-    x16 = x16_ref() if x16_ref is not None else None
-    if x16 is not None and ref is not None and ref() is x and key == now:
-        return x16
+    """The fp16 copy of `x`: the one a previous adapter layer used, else the one the preceding
+    RMSNorm wrote, else a fresh cast."""
     from .rmsnorm import fp16_copy_of
 
-    x16 = fp16_copy_of(x)
-    if x16 is None:
-        x16 = x.detach().to(torch.float16).contiguous()
-    _X16[0], _X16[1], _X16[2] = weakref.ref(x), now, weakref.ref(x16)
-    return x16
+    low = _COPY.lookup(x)
+    if low is None:
+        low = fp16_copy_of(x)
+        if low is None:
+            low = x.detach().to(torch.float16).contiguous()
+        _COPY.remember(x, low)
+    return low
 
 
 def _autocast_fp16():
     try:
-        return (torch.is_autocast_enabled("cuda")
-                and torch.get_autocast_dtype("cuda") == torch.float16)
+        on, dtype = torch.is_autocast_enabled("cuda"), torch.get_autocast_dtype("cuda")
     except (TypeError, AttributeError):
-        return torch.is_autocast_enabled() and torch.get_autocast_gpu_dtype() == torch.float16
+        on, dtype = torch.is_autocast_enabled(), torch.get_autocast_gpu_dtype()
+    return bool(on) and dtype == torch.float16
 
 
 def branch_covers(x, p, training):
-    """Whether LoRABranch reproduces the adapter for this input: fp32 contiguous CUDA x under fp16
-    autocast, training with gradients on, 0 < p < 1, last dim a multiple of 8."""
-    return (training and torch.is_grad_enabled() and _autocast_fp16()
-            and isinstance(x, torch.Tensor) and x.is_cuda and x.dtype == torch.float32
-            and x.shape[-1] % 8 == 0 and x.is_contiguous() and 0.0 < p < 1.0)
+    """Whether LoRABranch reproduces the adapter for this input: training with gradients on under
+    fp16 autocast, a contiguous fp32 CUDA tensor whose last dimension is a multiple of 8, and a
+    dropout probability strictly between 0 and 1."""
+    if not (training and torch.is_grad_enabled() and _autocast_fp16()):
+        return False
+    if not (isinstance(x, torch.Tensor) and x.is_cuda and x.dtype == torch.float32):
+        return False
+    return x.is_contiguous() and x.shape[-1] % 8 == 0 and 0.0 < p < 1.0
 
 
-def _make_forward(original):
+def _single_vanilla_adapter(layer):
+    """Name of the layer's only active adapter when it is plain LoRA (bias-free fp32 nn.Linear A
+    and B behind an nn.Dropout, no DoRA or other variant, not merged, not disabled), else None."""
+    names = layer.active_adapters
+    if len(names) != 1 or layer.disable_adapters or layer.merged:
+        return None
+    name = names[0]
+    if name not in layer.lora_A or name not in getattr(layer, "lora_dropout", {}):
+        return None
+    if name in getattr(layer, "lora_variant", {}) or getattr(layer, "use_dora", {}).get(name, False):
+        return None
+    if getattr(layer, "fan_in_fan_out", False) or type(layer.lora_dropout[name]) is not torch.nn.Dropout:
+        return None
+    for part in (layer.lora_A[name], layer.lora_B[name]):
+        if type(part) is not torch.nn.Linear or part.bias is not None or part.weight.dtype != torch.float32:
+            return None
+    return name
+
+
+def _wrap_peft_forward(installed):
     def forward(self, x, *args, **kwargs):
-        active = self.active_adapters
-        name = active[0] if len(active) == 1 else None
-        drop = self.lora_dropout[name] if name in getattr(self, "lora_dropout", {}) else None
-        plain = (not args and not kwargs and not self.disable_adapters and not self.merged
-                 and name is not None and name in self.lora_A
-                 and name not in getattr(self, "lora_variant", {})
-                 and type(drop) is torch.nn.Dropout
-                 and type(self.lora_A[name]) is torch.nn.Linear
-                 and type(self.lora_B[name]) is torch.nn.Linear
-                 and self.lora_A[name].bias is None and self.lora_B[name].bias is None
-                 and self.lora_A[name].weight.dtype == torch.float32
-                 and self.lora_B[name].weight.dtype == torch.float32
-                 and not getattr(self, "use_dora", {}).get(name, False)
-                 and not getattr(self, "fan_in_fan_out", False))
-        if not plain or not branch_covers(x, drop.p, self.training):
-            return original(self, x, *args, **kwargs)
+        name = None if (args or kwargs) else _single_vanilla_adapter(self)
+        if name is None or not branch_covers(x, self.lora_dropout[name].p, self.training):
+            return installed(self, x, *args, **kwargs)
         self._check_forward_args(x)
-        result = self.base_layer(x)
-        lora = LoRABranch.apply(x, _shared_fp16(x), self.lora_A[name].weight,
-                                self.lora_B[name].weight, float(drop.p),
-                                float(self.scaling[name]))
-        return result + lora
+        frozen_part = self.base_layer(x)
+        adapter = LoRABranch.apply(x, _shared_fp16(x), self.lora_A[name].weight, self.lora_B[name].weight,
+                                   float(self.lora_dropout[name].p), float(self.scaling[name]))
+        return frozen_part + adapter
 
     forward._lora_branch = True
-    forward._original = original
+    forward._original = installed
     return forward
 
 
@@ -149,19 +177,13 @@ def patch_peft_lora_4bit():
     """peft's LoRA Linear layers (the bitsandbytes 4-bit one and the plain one): vanilla LoRA with
     dropout on an fp32 input under fp16 autocast in training goes through LoRABranch; everything
     else keeps peft's forward. Without peft there is nothing to patch."""
-    classes = []
-    try:
-        from peft.tuners.lora import bnb as lora_bnb
+    import importlib
 
-        classes.append(getattr(lora_bnb, "Linear4bit", None))
-    except Exception:  # noqa: BLE001
-        pass
-    try:
-        from peft.tuners.lora import layer as lora_layer
-
-        classes.append(getattr(lora_layer, "Linear", None))
-    except Exception:  # noqa: BLE001
-        pass
-    for cls in classes:
+    for module_name, class_name in (("peft.tuners.lora.bnb", "Linear4bit"),
+                                    ("peft.tuners.lora.layer", "Linear")):
+        try:
+            cls = getattr(importlib.import_module(module_name), class_name, None)
+        except Exception:  # noqa: BLE001 - peft (or its bitsandbytes half) is not installed
+            continue
         if cls is not None and not getattr(cls.forward, "_lora_branch", False):
-            cls.forward = _make_forward(cls.forward)
+            cls.forward = _wrap_peft_forward(cls.forward)

@@ -104,10 +104,14 @@ class _MatMul4Bit(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, layer, x_low=None):
         """`x_low`, when given, is x already cast to the compute dtype (no autograd history of its
-        own): the product is formed from it and the gradient goes to x in x's dtype."""
+        own): the product is formed from it and the gradient goes to x in x's dtype. The layer's
+        bias (frozen) is added by the GEMM's epilogue."""
         ctx.layer, ctx.x_dtype = layer, x.dtype
         src = x if x_low is None else x_low
-        return F.linear(src, layer.dequantized(src.dtype))
+        bias = layer.bias
+        if bias is not None and bias.dtype != src.dtype:
+            bias = bias.to(src.dtype)
+        return F.linear(src, layer.dequantized(src.dtype), bias)
 
     @staticmethod
     def backward(ctx, grad):
@@ -207,8 +211,6 @@ class NF4Linear(torch.nn.Module):
             out = _MatMul4Bit.apply(x, self, x_low)
         else:
             out = self.matmul_4bit(x.to(self.compute_dtype))
-        if self.bias is not None:
-            out = out + self.bias.to(out.dtype)
         return out.to(x.dtype)
 
 

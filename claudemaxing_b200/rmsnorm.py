@@ -21,8 +21,6 @@ _SUPPORTED = (torch.float16, torch.bfloat16, torch.float32)
 MIN_ABS_WEIGHT = 2.0 ** -10
 MAX_SMALL = 64
 
-# (weakref to the last output, its version, weakref to its fp16 copy)
-_LAST_LOW = [None, -1, None]
 _SMALL = {}
 
 
@@ -46,78 +44,102 @@ def _small_columns(weight):
     return result
 
 
+class _LastCopy:
+    """The fp16 copy written by the most recent fused forward, findable from its fp32 output
+    (weak references: neither tensor is kept alive by the cache)."""
+
+    output = copy = None
+    version = -1
+
+    @classmethod
+    def record(cls, output, copy):
+        cls.output, cls.copy, cls.version = weakref.ref(output), weakref.ref(copy), output._version
+
+    @classmethod
+    def find(cls, tensor):
+        if cls.output is None or cls.output() is not tensor or tensor._version != cls.version:
+            return None
+        return cls.copy()
+
+
 def fp16_copy_of(t):
-    """The fp16 copy of `t` if `t` is the last output of the fused RMSNorm (bit-identical to
-    t.to(torch.float16)), else None."""
-    ref, version, low_ref = _LAST_LOW
-    if ref is None or ref() is not t or t._version != version:
-        return None
-    low = low_ref()
+    """The fp16 copy of `t` if `t` is the last output of the fused RMSNorm and has not been
+    written since (bit-identical to t.to(torch.float16)), else None."""
+    low = _LastCopy.find(t)
     return None if low is None else low.view(t.shape)
 
 
+def _forward_launch(rows, weight, eps, out_dtype, keep_copy):
+    """Runs the forward kernel on `rows` [n, cols]; returns (out, rstd, low, slots, small) where
+    the last three are None unless `keep_copy` found a usable slot map for the weight."""
+    n, cols = rows.shape
+    dev = rows.device
+    out = torch.empty((n, cols), dtype=out_dtype, device=dev)
+    rstd = torch.empty(n, dtype=torch.float32, device=dev)
+    low = slots = small = None
+    side = 1
+    mapping = _small_columns(weight) if keep_copy else None
+    if mapping is not None:
+        slots, tiny_count = mapping
+        side = max(tiny_count, 1)
+        low = torch.empty((n, cols), dtype=torch.float16, device=dev)
+        small = torch.empty((n, side), dtype=torch.float16, device=dev)
+    if n:
+        _lib.call("soup_rmsnorm_fwd", _lib.ptr(rows), _lib.ptr(weight), _lib.ptr(out), _lib.ptr(rstd),
+                  _lib.ptr(low), _lib.ptr(slots), _lib.ptr(small), side, n, cols, float(eps),
+                  _lib.dtype_code(rows.dtype), _lib.dtype_code(weight.dtype),
+                  _lib.dtype_code(out_dtype), _lib.stream_of(rows))
+    return out, rstd, low, slots, small
+
+
 class RMSNorm(torch.autograd.Function):
+    """`RMSNorm.apply(x, weight, eps)`. Saves x (any dtype) for backward, or, for an fp32 x with a
+    frozen fp32 weight, only the fp16 copy of the output plus the normalised values of the
+    tiny-|w| columns."""
+
     @staticmethod
     def forward(ctx, x, weight, eps):
         _lib.require_cuda(x, weight)
-        shape = x.shape
-        n_cols = shape[-1]
-        x2 = x.contiguous().view(-1, n_cols)
+        rows = x.contiguous().view(-1, x.shape[-1])
         weight = weight.contiguous()
-        n_rows = x2.shape[0]
-        out_dtype = torch.promote_types(x.dtype, weight.dtype)
-        out = torch.empty((n_rows, n_cols), dtype=out_dtype, device=x.device)
-        rstd = torch.empty(n_rows, dtype=torch.float32, device=x.device)
-        compress = (x.dtype == torch.float32 and weight.dtype == torch.float32
-                    and not weight.requires_grad and ctx.needs_input_grad[0])
-        small_cols = _small_columns(weight) if compress else None
-        low = slots = small = None
-        n_small = 1
-        if small_cols is not None:
-            slots, count = small_cols
-            n_small = max(count, 1)
-            low = torch.empty((n_rows, n_cols), dtype=torch.float16, device=x.device)
-            small = torch.empty((n_rows, n_small), dtype=torch.float16, device=x.device)
-        if n_rows:
-            _lib.call("soup_rmsnorm_fwd", _lib.ptr(x2), _lib.ptr(weight), _lib.ptr(out),
-                      _lib.ptr(rstd), _lib.ptr(low), _lib.ptr(slots), _lib.ptr(small), n_small,
-                      n_rows, n_cols, float(eps), _lib.dtype_code(x2.dtype),
-                      _lib.dtype_code(weight.dtype), _lib.dtype_code(out_dtype),
-                      _lib.stream_of(x2))
-        if low is not None:
+        fp32_frozen = (x.dtype == torch.float32 and weight.dtype == torch.float32
+                       and not weight.requires_grad and ctx.needs_input_grad[0])
+        out, rstd, low, slots, small = _forward_launch(
+            rows, weight, eps, torch.promote_types(x.dtype, weight.dtype), fp32_frozen)
+        ctx.from_copy = low is not None
+        if ctx.from_copy:
             ctx.save_for_backward(low, weight, rstd, slots, small)
         else:
-            ctx.save_for_backward(x2, weight, rstd, rstd, rstd)
-        ctx.x_dtype = x.dtype
-        ctx.shape = shape
-        result = out.view(shape)
-        if low is not None:
-            _LAST_LOW[0], _LAST_LOW[1], _LAST_LOW[2] = (weakref.ref(result), result._version,
-                                                         weakref.ref(low))
+            ctx.save_for_backward(rows, weight, rstd)
+        ctx.x_dtype, ctx.x_shape = x.dtype, x.shape
+        result = out.view(x.shape)
+        if ctx.from_copy:
+            _LastCopy.record(result, low)
         return result
 
     @staticmethod
     def backward(ctx, grad):
-        x2, weight, rstd, slots, small = ctx.saved_tensors
-        n_rows, n_cols = x2.shape
-        grad2 = grad.contiguous().view(n_rows, n_cols)
-        dx = torch.empty(x2.shape, dtype=ctx.x_dtype, device=x2.device)
-        need_dw = ctx.needs_input_grad[1]
-        saved_output = x2.dtype != ctx.x_dtype
+        if ctx.from_copy:
+            saved, weight, rstd, slots, small = ctx.saved_tensors
+            side = small.shape[-1]
+        else:
+            saved, weight, rstd = ctx.saved_tensors
+            slots = small = None
+            side = 1
+        n, cols = saved.shape
+        dy = grad.contiguous().view(n, cols)
+        dx = torch.empty((n, cols), dtype=ctx.x_dtype, device=saved.device)
         dw = partial = None
-        if need_dw:
-            dw = torch.empty(n_cols, dtype=weight.dtype, device=x2.device)
-            parts = _lib.lib().soup_rmsnorm_bwd_partials(n_rows, n_cols)
-            partial = torch.empty((max(parts, 1), n_cols), dtype=torch.float32, device=x2.device)
-        _lib.call("soup_rmsnorm_bwd", _lib.ptr(grad2), _lib.ptr(x2), _lib.ptr(weight),
-                  _lib.ptr(rstd), _lib.ptr(dx), _lib.ptr(partial), _lib.ptr(dw),
-                  _lib.ptr(slots) if saved_output else None,
-                  _lib.ptr(small) if saved_output else None,
-                  small.shape[-1] if saved_output else 1, n_rows, n_cols,
-                  _lib.dtype_code(grad2.dtype), _lib.dtype_code(x2.dtype),
-                  _lib.dtype_code(weight.dtype), _lib.dtype_code(ctx.x_dtype),
-                  int(saved_output), _lib.stream_of(x2))
-        return dx.view(ctx.shape), dw, None
+        if ctx.needs_input_grad[1]:   # trainable weight: per-CTA partial rows, reduced in fixed order
+            dw = torch.empty(cols, dtype=weight.dtype, device=saved.device)
+            n_partial = max(_lib.lib().soup_rmsnorm_bwd_partials(n, cols), 1)
+            partial = torch.empty((n_partial, cols), dtype=torch.float32, device=saved.device)
+        _lib.call("soup_rmsnorm_bwd", _lib.ptr(dy), _lib.ptr(saved), _lib.ptr(weight), _lib.ptr(rstd),
+                  _lib.ptr(dx), _lib.ptr(partial), _lib.ptr(dw), _lib.ptr(slots), _lib.ptr(small),
+                  side, n, cols, _lib.dtype_code(dy.dtype), _lib.dtype_code(saved.dtype),
+                  _lib.dtype_code(weight.dtype), _lib.dtype_code(ctx.x_dtype), int(ctx.from_copy),
+                  _lib.stream_of(saved))
+        return dx.view(ctx.x_shape), dw, None
 
 
 def rmsnorm(x, weight, eps):

@@ -5,8 +5,9 @@ inplace)`, `swiglu_recompute(gate, up, inplace=False)`, `MLPInputRecompute.apply
 up_proj, down_compute=None)` and `patch_qwen2_mlp_recompute()`. Backward keeps nothing but the two
 inputs (silu is recomputed) and, with `inplace`, writes dgate over gate and dup over up.
 `MLPInputRecompute` keeps only the MLP input and re-runs the two frozen projections in backward;
-for 4-bit projections (bitsandbytes' Linear4bit or this package's NF4Linear) gate and up stay fp16
-and the fp16 copy of the input written by the preceding RMSNorm is reused.
+for 4-bit projections (bitsandbytes' Linear4bit or this package's NF4Linear, wrapped by
+`_FourBitWeight`) gate and up stay fp16 and the fp16 copy of the input written by the preceding
+RMSNorm is reused.
 """
 
 import torch
@@ -78,127 +79,135 @@ def _autocast_state():
         return torch.is_autocast_enabled(), torch.get_autocast_gpu_dtype()
 
 
-def _matmul_4bit(x_low, handle):
-    """x_low @ dequant(W)^T for a 4-bit layer handle returned by `_nf4_layer`."""
-    kind, weight, state = handle
-    if kind == "bnb":
-        import bitsandbytes as bnb
+class _FourBitWeight:
+    """A bias-free 4-bit projection reduced to what the MLP needs: `matmul(x_low)` = x_low @
+    dequant(W)^T with the weight dequantised again in its own backward, and the fixed compute
+    dtype. Wraps bitsandbytes' Linear4bit or this package's NF4Linear."""
 
-        return bnb.matmul_4bit(x_low, weight, quant_state=state)
-    return weight.matmul_4bit(x_low)  # this package's NF4Linear
+    def __init__(self, compute_dtype, matmul):
+        self.compute_dtype, self.matmul = compute_dtype, matmul
+
+    @classmethod
+    def of(cls, linear):
+        """The wrapper for `linear`, or None when the module has to be called as a whole (bias,
+        hooks that a direct matmul would skip, no fixed compute dtype, not a 4-bit layer)."""
+        if getattr(linear, "bias", None) is not None or hasattr(linear, "_hf_hook"):
+            return None
+        if linear._forward_hooks or linear._forward_pre_hooks:
+            return None
+        if getattr(linear, "_soup_nf4_linear", False):
+            return cls(linear.compute_dtype, linear.matmul_4bit)
+        if type(linear).__name__ != "Linear4bit":
+            return None
+        try:
+            import bitsandbytes as bnb
+            from bitsandbytes.nn.modules import fix_4bit_weight_quant_state_from_module as restore_state
+        except Exception:  # noqa: BLE001 - a look-alike class without bitsandbytes behind it
+            return None
+        if not isinstance(linear, bnb.nn.Linear4bit):
+            return None
+        if not linear.compute_type_is_set or linear.compute_dtype is None:
+            return None
+        restore_state(linear)
+        weight = linear.weight
+        return cls(linear.compute_dtype,
+                   lambda x_low: bnb.matmul_4bit(x_low, weight, quant_state=weight.quant_state))
+
+
+def _four_bit_pair(gate_proj, up_proj, x):
+    """Both projections as _FourBitWeight when they share a compute dtype that x can be cast to."""
+    gate, up = _FourBitWeight.of(gate_proj), _FourBitWeight.of(up_proj)
+    if gate is None or up is None or gate.compute_dtype != up.compute_dtype:
+        return None
+    if x.dtype != torch.float32 and x.dtype != gate.compute_dtype:
+        return None
+    return gate, up
 
 
 class MLPInputRecompute(torch.autograd.Function):
-    """silu(gate_proj(x)) * up_proj(x) for frozen projections, keeping only `x` for backward
-    (solution/swiglu_recompute.py:138-215 of the reference)."""
+    """silu(gate_proj(x)) * up_proj(x) for frozen projections, keeping only the MLP input for
+    backward (the reference's solution/swiglu_recompute.py:138-215): backward runs the two
+    projections again, lets the kernel write dgate / dup over the recomputed gate / up, and sends
+    those back through the projections."""
 
     @staticmethod
     def forward(ctx, x, gate_proj, up_proj, down_compute=None):
-        nf4 = _nf4_pair(gate_proj, up_proj, x)
-        if nf4 is not None:
-            hg, hu, compute = nf4
-            x_low = fp16_copy_of(x) if compute == torch.float16 else None
-            if x_low is None:  # the norm before the MLP usually wrote this exact copy already
-                x_low = x.to(compute)
-            gate, up = _matmul_4bit(x_low, hg), _matmul_4bit(x_low, hu)
-            out_dtype, round_silu = x.dtype, x.dtype == compute
-            if down_compute == compute:
-                out_dtype = compute  # the 4-bit down_proj casts its input to `compute` anyway
-        else:
+        pair = _four_bit_pair(gate_proj, up_proj, x)
+        if pair is None:
+            kept = x
             gate, up = gate_proj(x), up_proj(x)
             out_dtype, round_silu = torch.promote_types(gate.dtype, up.dtype), True
+        else:
+            compute = pair[0].compute_dtype
+            kept = fp16_copy_of(x) if compute == torch.float16 else None
+            if kept is None:   # usually the norm before the MLP has written exactly this copy
+                kept = x.to(compute)
+            gate, up = pair[0].matmul(kept), pair[1].matmul(kept)
+            round_silu = x.dtype == compute
+            # a 4-bit down_proj casts its input to `compute` anyway: hand it that dtype directly
+            out_dtype = compute if down_compute == compute else x.dtype
         out = torch.empty(gate.shape, dtype=out_dtype, device=gate.device)
         _silu_mul_fwd(gate.contiguous(), up.contiguous(), out, round_silu)
-        ctx.save_for_backward(x_low if nf4 is not None else x)
-        ctx.x_dtype = x.dtype
-        ctx.projs, ctx.nf4, ctx.round_silu = (gate_proj, up_proj), nf4, round_silu
-        ctx.autocast = _autocast_state()
+        ctx.save_for_backward(kept)
+        ctx.modules, ctx.pair = (gate_proj, up_proj), pair
+        ctx.round_silu, ctx.x_dtype, ctx.autocast = round_silu, x.dtype, _autocast_state()
         return out
 
     @staticmethod
     def backward(ctx, grad):
-        (x,) = ctx.saved_tensors
-        enabled, dtype = ctx.autocast
-        with torch.enable_grad(), torch.autocast("cuda", dtype=dtype, enabled=enabled):
-            x_again = x.detach().requires_grad_(True)
-            if ctx.nf4 is not None:
-                hg, hu, _ = ctx.nf4
-                gate, up = _matmul_4bit(x_again, hg), _matmul_4bit(x_again, hu)
+        (kept,) = ctx.saved_tensors
+        on, dtype = ctx.autocast
+        leaf = kept.detach().requires_grad_(True)
+        with torch.enable_grad(), torch.autocast("cuda", dtype=dtype, enabled=on):
+            if ctx.pair is None:
+                gate, up = ctx.modules[0](leaf), ctx.modules[1](leaf)
             else:
-                gate_proj, up_proj = ctx.projs
-                gate, up = gate_proj(x_again), up_proj(x_again)
-        g, u = gate.detach(), up.detach()
-        if not (g.is_contiguous() and u.is_contiguous()):
-            g, u = g.contiguous(), u.contiguous()
-        # gradients written over the recomputed buffers, nothing else allocated
-        _silu_mul_bwd(grad.contiguous(), g, u, g, u, ctx.round_silu)
-        if ctx.nf4 is not None:
-            (dx_gate,) = torch.autograd.grad(gate, x_again, g)
-            (dx_up,) = torch.autograd.grad(up, x_again, u)
-            return dx_gate.to(ctx.x_dtype) + dx_up.to(ctx.x_dtype), None, None, None
-        torch.autograd.backward((gate, up), (g, u), inputs=[x_again])
-        return x_again.grad, None, None, None
+                gate, up = ctx.pair[0].matmul(leaf), ctx.pair[1].matmul(leaf)
+        d_gate, d_up = gate.detach().contiguous(), up.detach().contiguous()
+        # the two gradients overwrite the recomputed activations: nothing else is allocated
+        _silu_mul_bwd(grad.contiguous(), d_gate, d_up, d_gate, d_up, ctx.round_silu)
+        if ctx.pair is None:
+            torch.autograd.backward((gate, up), (d_gate, d_up), inputs=[leaf])
+            return leaf.grad, None, None, None
+        from_gate = torch.autograd.grad(gate, leaf, d_gate)[0]
+        from_up = torch.autograd.grad(up, leaf, d_up)[0]
+        return from_gate.to(ctx.x_dtype) + from_up.to(ctx.x_dtype), None, None, None
 
 
-def _nf4_layer(linear):
-    """(handle, compute dtype) of a bias-free 4-bit linear whose compute dtype is fixed, else None
-    (then the module itself is called). Handles bitsandbytes' Linear4bit and this package's
-    NF4Linear."""
-    if getattr(linear, "bias", None) is not None:
-        return None
-    if linear._forward_hooks or linear._forward_pre_hooks or hasattr(linear, "_hf_hook"):
-        return None  # calling the matmul directly would skip the hooks
-    if getattr(linear, "_soup_nf4_linear", False):
-        return ("soup", linear, None), linear.compute_dtype
-    if type(linear).__name__ != "Linear4bit":
-        return None
-    try:
-        import bitsandbytes as bnb
-        from bitsandbytes.nn.modules import fix_4bit_weight_quant_state_from_module
-    except Exception:  # noqa: BLE001
-        return None
-    if (not isinstance(linear, bnb.nn.Linear4bit) or not linear.compute_type_is_set
-            or linear.compute_dtype is None):
-        return None
-    fix_4bit_weight_quant_state_from_module(linear)
-    return ("bnb", linear.weight, linear.weight.quant_state), linear.compute_dtype
+def _all_frozen(*modules):
+    return not any(p.requires_grad for m in modules for p in m.parameters())
 
 
-def _nf4_pair(gate_proj, up_proj, x):
-    gate, up = _nf4_layer(gate_proj), _nf4_layer(up_proj)
-    if gate is None or up is None or gate[1] != up[1] or x.dtype not in (torch.float32, gate[1]):
-        return None
-    return gate[0], up[0], gate[1]
-
-
-def _frozen(module):
-    return not any(p.requires_grad for p in module.parameters())
+def _mlp_forward(mlp, x, installed):
+    """Qwen2MLP.forward with the activation (and, for frozen projections in training, the two
+    projections' outputs) not kept for backward."""
+    silu = getattr(getattr(mlp, "config", None), "hidden_act", "silu") == "silu"
+    if not (silu and isinstance(x, torch.Tensor) and x.is_cuda):
+        return installed(mlp, x)
+    training_input = torch.is_grad_enabled() and x.requires_grad
+    if training_input and x.dtype in _SUPPORTED and _all_frozen(mlp.gate_proj, mlp.up_proj):
+        down = _FourBitWeight.of(mlp.down_proj)
+        hidden = MLPInputRecompute.apply(x, mlp.gate_proj, mlp.up_proj,
+                                         down.compute_dtype if down is not None else None)
+        return mlp.down_proj(hidden)
+    gate, up = mlp.gate_proj(x), mlp.up_proj(x)
+    if gate.shape == up.shape and gate.dtype in _SUPPORTED and up.dtype in _SUPPORTED:
+        return mlp.down_proj(swiglu_recompute(gate, up, True))
+    return mlp.down_proj(mlp.act_fn(gate) * up)
 
 
 def patch_qwen2_mlp_recompute():
-    """Send the activation of Qwen2MLP.forward through the recomputing kernels. Class-level. CPU
-    tensors, another activation or unusual dtypes keep the installed behaviour."""
+    """Qwen2MLP.forward goes through `_mlp_forward` (class-level patch; CPU tensors, another
+    activation or unusual dtypes keep the installed behaviour)."""
     from transformers.models.qwen2 import modeling_qwen2
 
     cls = getattr(modeling_qwen2, "Qwen2MLP", None)
     if cls is None or getattr(cls.forward, "_swiglu_recompute", False):
         return
-    original = cls.forward
+    installed = cls.forward
 
     def forward(self, x):
-        act = getattr(getattr(self, "config", None), "hidden_act", "silu")
-        if act != "silu" or not isinstance(x, torch.Tensor) or not x.is_cuda:
-            return original(self, x)
-        if (x.dtype in _SUPPORTED and _frozen(self.gate_proj) and _frozen(self.up_proj)
-                and torch.is_grad_enabled() and x.requires_grad):
-            down = _nf4_layer(self.down_proj)
-            return self.down_proj(MLPInputRecompute.apply(x, self.gate_proj, self.up_proj,
-                                                          down[1] if down else None))
-        gate, up = self.gate_proj(x), self.up_proj(x)
-        if (gate.shape != up.shape or gate.dtype not in _SUPPORTED
-                or up.dtype not in _SUPPORTED):
-            return self.down_proj(self.act_fn(gate) * up)
-        return self.down_proj(swiglu_recompute(gate, up, True))
+        return _mlp_forward(self, x, installed)
 
     forward._swiglu_recompute = True
     cls.forward = forward

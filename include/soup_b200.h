@@ -42,6 +42,11 @@ const char* soup_last_error_string(void);
  * word is sticky. Synchronises `stream`. No counterpart in the reference (its Triton kernels have
  * no waits). */
 int soup_row_status(int* host_status, void* stream);
+/* Self-test of the bounded waits every kernel of the library uses: launches one small CTA that
+ * waits, with a limit of `limit_ns` (at most 100 ms), on a barrier nothing ever completes. The
+ * wait has to run out: *host_gave_up becomes 1 and *host_status the code 99, and the context stays
+ * usable. Synchronises `stream`. No counterpart in the reference. */
+int soup_wait_selftest(int64_t limit_ns, int* host_gave_up, int* host_status, void* stream);
 
 /* NF4 -> fp16/fp32 weight, nested (double-quantised) absmax fused, bit-exact unfused fp32 math.
  * Replaces nf4_dequant_kernel[grid](...) at solution/nf4.py:78-81 (kernel :26-46).

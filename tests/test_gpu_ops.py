@@ -364,3 +364,23 @@ def test_ops_refuse_cpu_tensors():
         rmsnorm(torch.randn(4, 64), torch.ones(64), 1e-6)
     with pytest.raises(RuntimeError, match="CUDA"):
         swiglu_recompute(torch.randn(4, 64), torch.randn(4, 64))
+
+
+# ------------------------------------------------------------------------- bounded waits
+def test_a_wait_that_nothing_completes_runs_out_and_reports():
+    """Failure detection on the device: the kernels' waits give up after their limit, record a
+    code and return; the context stays usable (no trap, no hang)."""
+    import ctypes
+
+    from claudemaxing_b200 import _lib
+
+    gave_up, status = ctypes.c_int(-1), ctypes.c_int(-1)
+    _lib.call("soup_wait_selftest", 2_000_000, ctypes.byref(gave_up), ctypes.byref(status),
+              torch.cuda.current_stream().cuda_stream)
+    assert gave_up.value == 1 and status.value == 99
+    # the device still works and the row kernels' own status word is untouched
+    x = torch.arange(8, device=DEV).sum().item()
+    assert x == 28
+    row = ctypes.c_int(-1)
+    _lib.call("soup_row_status", ctypes.byref(row), torch.cuda.current_stream().cuda_stream)
+    assert row.value == 0
