@@ -158,3 +158,34 @@ def test_group_dequant_equals_per_weight_dequant():
             got = mod.dequantized(torch.float16).clone()
             want = dequantize_nf4(mod.packed, mod.quant_state, torch.float16)
             assert torch.equal(got, want)
+
+
+def test_captured_step_equals_the_eager_step_and_trains():
+    """The CUDA-graph step on the padded packed bucket gives the eager step's loss (padding tokens
+    attend only to themselves and carry ignore labels), leaves the adapters untouched by its own
+    warm-up, and its replays train."""
+    import claudemaxing_b200 as solution
+    from claudemaxing_b200 import qlora
+
+    solution.apply()
+    model, lora = qlora.build_qlora_model("cuda", TINY, dropout=0.05, seed=3)
+    batch = qlora.synthetic_batch(batch=4, min_len=16, max_len=96, vocab=TINY["vocab_size"], seed=9)
+    dev_batch = {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in batch.items()}
+    eager_loss = float(qlora.qlora_step(model, dev_batch))      # B = 0: dropout cannot matter yet
+    for p in lora:
+        p.grad = None
+    before = [p.detach().clone() for p in lora]
+    opt = torch.optim.AdamW(lora, lr=2e-3, fused=True, capturable=True)
+    step = qlora.CapturedStep(model, lora, opt, batch, loss_scale=1024.0)
+    assert step.bucket % 128 == 0 and step.bucket >= batch["n_tokens"]
+    assert all(torch.equal(a, b) for a, b in zip(before, lora))
+    first = float(step.run())
+    assert abs(first - eager_loss) < 2e-3 * abs(eager_loss)
+    losses = [float(step.run()) for _ in range(12)]
+    assert losses[-1] < first - 0.02
+    assert any(not torch.equal(a, b) for a, b in zip(before, lora))
+    # a different batch of at most the bucket's size goes through the same graphs
+    other = qlora.synthetic_batch(batch=4, min_len=16, max_len=80, vocab=TINY["vocab_size"], seed=10)
+    if other["n_tokens"] <= step.bucket:
+        step.load(other)
+        assert torch.isfinite(step.run()).item()
