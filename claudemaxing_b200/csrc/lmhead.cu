@@ -25,8 +25,9 @@
 //                  fire-and-forget reductions; dH is kept relative to `base`, the lse after the
 //                  first chunk.
 //
-// The first chunk has no earlier lse: its statistics are taken against the tile maxima in a first
-// launch (two sweeps), merged, and a second launch writes P against the merged lse. A last kernel
+// The first chunk has no earlier lse: its statistics and its P are taken against each tile's own
+// maximum (two sweeps over the accumulator), the row kernel merges the tiles, and a small kernel
+// rescales the chunk's P in place to the merged lse. A last kernel
 // turns the state into loss / entropy / correct, rescales dH from `base` to the final lse and
 // adds (p_label - 1) * W[label] in fp32.
 //
@@ -75,8 +76,8 @@ constexpr int kSmemLogits = kStages * kStageBytes + kStageP + 1024 + 256;
 constexpr int kSmemGrad = kStages * kStageBytes + kStageT + 1024 + 256;
 
 enum LogitsMode {
-  kModeTileMax = 0,  // statistics against the tile maximum, no P (first chunk, first launch)
-  kModePOnly = 1,    // P against ref, no statistics (first chunk, second launch)
+  kModeTileMax = 0,  // statistics (and P, when wanted) against the tile maximum: the first chunk
+  kModePOnly = 1,    // P against ref, no statistics (kept for callers that recompute a chunk)
   kModeCombined = 2  // statistics and P against ref (all later chunks)
 };
 
@@ -273,6 +274,30 @@ __device__ __noinline__ void tile_stats_tilemax(uint32_t taddr, int n_valid, int
   dot_out = d0 + d1;
   lab_out = lab;
   arg_out = arg;
+}
+
+// The tile's maximum over its valid columns (one sweep over the accumulator).
+template <bool FULL>
+__device__ __noinline__ float tile_max_sweep(uint32_t taddr, int n_valid) {
+  constexpr int kLoads = kBN / kEW;
+  uint32_t ra[kEW], rb[kEW];
+  float m = -INFINITY;
+  auto sweep = [&](const uint32_t (&r)[kEW], int col0) {
+#pragma unroll
+    for (int j = 0; j < kEW; ++j)
+      if (FULL || col0 + j < n_valid) m = fmaxf(m, __uint_as_float(r[j]));
+  };
+  tmem_ld_32x16(taddr, ra);
+#pragma unroll 1
+  for (int i = 0; i < kLoads; i += 2) {
+    tmem_ld_wait_on(ra);
+    tmem_ld_32x16(taddr + (i + 1) * kEW, rb);
+    sweep(ra, i * kEW);
+    tmem_ld_wait_on(rb);
+    if (i + 2 < kLoads) tmem_ld_32x16(taddr + (i + 2) * kEW, ra);
+    sweep(rb, (i + 1) * kEW);
+  }
+  return m;
 }
 
 // All other launches: one sweep against `ref`, the row's log-sum-exp over the earlier chunks.
@@ -478,7 +503,19 @@ lmhead_logits_kernel(const __grid_constant__ CUtensorMap map_h,
       float m, sum, dot, lab;
       int arg;
       const bool full = n_valid == kBN;
-      if (a.mode == kModeTileMax) {
+      if (a.mode == kModeTileMax && a.store_p) {
+        // first chunk with a gradient wanted: P is written against the tile's own maximum (the
+        // row's lse is not known yet) and rescaled in place once the row kernel has merged the tiles
+        if (full) {
+          const float tm = tile_max_sweep<true>(taddr, n_valid);
+          tile_ref_pass<true, true>(taddr, n_valid, label_local, tm, keep_mask, true, &map_p,
+                                    stage_warp, tc * kBN, p_row0, m, sum, dot, lab, arg);
+        } else {
+          const float tm = tile_max_sweep<false>(taddr, n_valid);
+          tile_ref_pass<false, true>(taddr, n_valid, label_local, tm, keep_mask, true, &map_p,
+                                     stage_warp, tc * kBN, p_row0, m, sum, dot, lab, arg);
+        }
+      } else if (a.mode == kModeTileMax) {
         if (full) tile_stats_tilemax<true>(taddr, n_valid, label_local, m, sum, dot, lab, arg);
         else tile_stats_tilemax<false>(taddr, n_valid, label_local, m, sum, dot, lab, arg);
       } else if (a.mode == kModeCombined) {
@@ -614,6 +651,33 @@ __global__ void __launch_bounds__(256) lmhead_row_kernel(const RowArgs a) {
     a.best[row] = best;
     a.best_val[row] = best_val;
     if (a.want_grad) a.mult[row] = mult;
+  }
+}
+
+// First chunk only: P was written as exp(z - tile maximum); bring it to exp(z - lse) in place, one
+// warp per row, one 16-byte vector (8 bf16) per lane and tile. A memory-bound pass over a chunk
+// that is still in L2, instead of a second GEMM pass over the chunk's logits.
+__global__ void __launch_bounds__(256)
+lmhead_rescale_first_kernel(__nv_bfloat16* __restrict__ p, int ld_p,
+                            const float4* __restrict__ tile_stats, int ct_stride,
+                            const float* __restrict__ lse, int n_rows, int ct) {
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= n_rows) return;
+  const float row_lse = lse[row];
+  uint4* prow = reinterpret_cast<uint4*>(p + (size_t)row * ld_p);
+#pragma unroll 2
+  for (int t = 0; t < ct; ++t) {
+    const float f = exp2f((tile_stats[(size_t)row * ct_stride + t].x - row_lse) * kLog2e);
+    uint4 v = prow[t * (kBN / 8) + lane];
+    uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 e = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[k]));
+      __nv_bfloat162 h = __floats2bfloat162_rn(e.x * f, e.y * f);
+      w[k] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    prow[t * (kBN / 8) + lane] = make_uint4(w[0], w[1], w[2], w[3]);
   }
 }
 
@@ -1149,12 +1213,12 @@ extern "C" int soup_lmhead_ce(const void* hidden, const void* weight, const void
       SOUP_CHECK_LAUNCH("lmhead_row");
 
       if (want_grad) {
-        if (first) {  // the first chunk's P, against the lse the row kernel just produced
-          la.mode = kModePOnly;
-          timer.mark(0);
-          lmhead_logits_kernel<<<grid1, kThreadsGemm, kSmemLogits, s>>>(map_h, map_w_k, map_p_st, la);
-          timer.mark(0);
-          SOUP_CHECK_LAUNCH("lmhead_logits");
+        if (first) {  // the first chunk's P from "against its tile maximum" to "against the lse"
+          timer.mark(1);
+          lmhead_rescale_first_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, s>>>(
+              ws.p_buf, ld_p, ws.tile_stats, plan.ct, run_max + r0, rows, ct);
+          timer.mark(1);
+          SOUP_CHECK_LAUNCH("lmhead_rescale_first");
         }
         GradArgs ga;
         ga.dh = dh + r0 * h;
