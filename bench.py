@@ -231,6 +231,7 @@ def kernel_suite(dev, hbm_peak, n_rows=2048, tag="", with_nf4=True):
     def record(name, ms, nbytes, launches=1):
         gbs = nbytes / (ms * 1e-3) / 1e9
         out[name + tag] = {"ms": round(ms, 5), "gb_s": round(gbs, 1), "frac_of_measured_hbm": round(gbs / hbm_peak, 3),
+                     "frac_of_nominal_8000": round(gbs / 8000.0, 3),
                      "algorithmic_bytes": int(nbytes), "launches": launches}
 
     if with_nf4:
@@ -393,6 +394,64 @@ def kernel_suite(dev, hbm_peak, n_rows=2048, tag="", with_nf4=True):
     record("dropout_unpack", time_rotating(unpack, nD), n_rows * H * (2 + 2 + 2 + 4) + n_rows * H // 8)
     return out
 
+
+
+# ------------------------------------------------------------------------------------------
+def cpu_oracle_suite(cores):
+    """The oracle's CPU torch implementations of the memory-bound ops at config-3 size (2048 rows),
+    one timed call each after one warm-up call, all host cores: what the reference's patches fall
+    through to on CPU tensors. Returns {suite key: milliseconds}."""
+    from oracle import elementwise as ew
+    from oracle import nf4 as onf4
+
+    torch.set_num_threads(cores)
+    gen = torch.Generator().manual_seed(2)
+    n, H, inter = 2048, 1536, 8960
+    out = {}
+
+    def timed_ms(fn):
+        fn()
+        t0 = time.perf_counter()
+        fn()
+        return (time.perf_counter() - t0) * 1e3
+
+    x16 = torch.randn(n, H, generator=gen).half()
+    w16 = (torch.rand(H, generator=gen) + 0.5).half()
+    dy16 = torch.randn(n, H, generator=gen).half()
+    x32, w32, dy32 = x16.float(), w16.float(), dy16.float()
+    out["rmsnorm_fwd_f16"] = timed_ms(lambda: ew.rmsnorm(x16, w16))
+    out["rmsnorm_fwd_f32_with_f16_copy"] = timed_ms(lambda: ew.rmsnorm(x32, w32).half())
+    fwd16 = timed_ms(lambda: ew.rmsnorm(x16, w16))
+    out["rmsnorm_bwd_f16"] = max(timed_ms(lambda: ew.rmsnorm_fwd_bwd(x16, w16, dy16)) - fwd16, 0.0)
+    fwd32 = timed_ms(lambda: ew.rmsnorm(x32, w32))
+    out["rmsnorm_bwd_from_f16_copy"] = max(timed_ms(lambda: ew.rmsnorm_fwd_bwd(x32, w32, dy32)) - fwd32, 0.0)
+    pos = torch.cat([torch.arange(512), torch.arange(384), torch.arange(640), torch.arange(512)])
+    cos, sin = ew.rope_tables(pos, 128, dtype=torch.float16)
+    q = torch.randn(1, n, 12 * 128, generator=gen).half().view(1, n, 12, 128).transpose(1, 2)
+    k = torch.randn(1, n, 2 * 128, generator=gen).half().view(1, n, 2, 128).transpose(1, 2)
+    out["rope_fwd_q_and_k"] = timed_ms(lambda: ew.rope(q, k, cos, sin))
+    gq, gk = torch.randn(1, 12, n, 128, generator=gen).half(), torch.randn(1, 2, n, 128, generator=gen).half()
+    out["rope_bwd_q_and_k"] = max(timed_ms(lambda: ew.rope_fwd_bwd(q, k, cos, sin, gq, gk))
+                                  - out["rope_fwd_q_and_k"], 0.0)
+    g = torch.randn(n, inter, generator=gen).half()
+    u = torch.randn(n, inter, generator=gen).half()
+    dy = torch.randn(n, inter, generator=gen).half()
+    out["silu_mul_fwd"] = timed_ms(lambda: ew.swiglu(g, u))
+    out["silu_mul_bwd_inplace"] = max(timed_ms(lambda: ew.swiglu_fwd_bwd(g, u, dy)) - out["silu_mul_fwd"], 0.0)
+    xd = torch.randn(n, H, generator=gen)
+    mask = torch.rand(n, H, generator=gen) > 0.05
+    out["dropout_pack"] = timed_ms(lambda: ew.dropout_pack(xd, mask, 1 / 0.95))
+    _, bits = ew.dropout_pack(xd, mask, 1 / 0.95)
+    g16 = torch.randn(n, H, generator=gen).half()
+    out["dropout_unpack"] = timed_ms(lambda: ew.dropout_unpack(xd.half(), bits, g16, 1 / 0.95, torch.float32))
+    wq = (torch.randn(1536, 1536, generator=gen) * 0.02).half()
+    packed, state = onf4.quantize_nf4(wq)
+    one = timed_ms(lambda: onf4.dequantize_nf4(packed, state, torch.float16))
+    # 1536 x 1536 is 2.36 M of the 1310 M elements of the 28 layers: scaled by the element count
+    out["nf4_dequant_28_layers"] = one * (1310195712 / wq.numel())
+    out["nf4_dequant_28_layers_batched_per_layer"] = out["nf4_dequant_28_layers"]
+    out["nf4_dequant_8960x1536"] = one * (8960 * 1536 / wq.numel())
+    return {k: round(v, 3) for k, v in out.items()}
 
 
 # ------------------------------------------------------------------------------------------
@@ -670,6 +729,12 @@ def main():
             # the same kernels on 16x the rows: launch ramps amortised, data far larger than L2
             kernels.update(kernel_suite(dev, peak["hbm_gbs"], n_rows=32768, tag="@32768rows",
                                         with_nf4=False))
+        if not args.no_cpu and kernels is not None:
+            cpu_ms = cpu_oracle_suite(os.cpu_count() or 1)
+            for key, ms in cpu_ms.items():
+                if key in kernels:
+                    kernels[key]["cpu_oracle_ms"] = ms
+                    kernels[key]["cpu_oracle_cores"] = os.cpu_count() or 1
         if not args.no_cpu:
             cores = os.cpu_count() or 1
             w32 = weight_h.float()

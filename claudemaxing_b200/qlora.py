@@ -369,6 +369,10 @@ class CapturedStep:
         self.row = torch.arange(n, dtype=torch.int64, device=dev)[None].clone()
         self.target = torch.full((1, n), -100, dtype=torch.int64, device=dev)
         self.index = torch.arange(n, dtype=torch.int64, device=dev)
+        # divisor of the loss: the labelled tokens of the whole job divided by the ranks, so that
+        # the mean of the ranks' gradients is the gradient of the job's mean token loss (what the
+        # reference's trainer gets from a global num_items_in_batch)
+        self.denominator = torch.ones((), dtype=torch.float32, device=dev)
         # every LoRA gradient is a view of one flat buffer: one all-reduce, no gather/scatter
         total = sum(p.numel() for p in self.params)
         self.flat_grad = torch.zeros(total, dtype=self.params[0].dtype, device=dev)
@@ -408,6 +412,11 @@ class CapturedStep:
         self.col.copy_(stage[1:2], non_blocking=True)
         self.row.copy_(stage[2:3], non_blocking=True)
         self.target.copy_(stage[3:4], non_blocking=True)
+        labelled = (self.target != -100).sum().to(torch.float32)
+        if self.world > 1:
+            torch.distributed.all_reduce(labelled, group=self.group)
+            labelled = labelled / self.world
+        self.denominator.copy_(labelled.clamp(min=1.0))
         return n
 
     def run(self):
@@ -427,7 +436,8 @@ class CapturedStep:
                                  mask=allowed[None, None], target=self.target)
         self.flat_grad.zero_()
         with torch.autocast("cuda", dtype=torch.float16):
-            out = L._packed_forward(self.model, {"use_cache": False}, packed)
+            out = L._packed_forward(self.model, {"use_cache": False,
+                                                 "num_items_in_batch": self.denominator}, packed)
         scaled = self.scaler.scale(out.loss) if self.scaler is not None else out.loss * self.loss_scale
         scaled.backward()
         return out.loss.detach()
