@@ -697,11 +697,12 @@ def main():
         "frac_of_sustained": round(logits_tf / peak["bf16_tflops_sustained"], 4),
         "frac_of_nominal_2250": round(logits_tf / 2250.0, 4),
         "ms_per_launch": round(k_ms[0] / max(k_launch[0], 1), 5), "launches_per_step": k_launch[0],
-        # dram__bytes_read + dram__bytes_write of the four logits launches of a step from the ncu
-        # capture summarised in profiles/lmhead_c1_kernels_full.md (35.5 + 40.9 + 521.2 + 455.0 MB),
+        # dram__bytes_read + dram__bytes_write of the three logits launches of a step from the ncu
+        # capture summarised in profiles/lmhead_c1_kernels_full.md (40.5 + 520.8 + 454.5 MB),
         # averaged per launch like `ms_per_launch`; valid for the single-GPU config-1 shape only
-        "traffic": 263.2e6 if (world == 1 and args.workload == "c1") else None,
-        "traffic_algorithmic": round((2.0 * v_local * HIDDEN * (1 + 37 / 594) + 4 * 2.0 * n_tokens * HIDDEN
+        "traffic": 338.6e6 if (world == 1 and args.workload == "c1") else None,
+        # W once + hidden once per launch + P written once, per launch
+        "traffic_algorithmic": round((2.0 * v_local * HIDDEN + max(k_launch[0], 1) * 2.0 * n_tokens * HIDDEN
                                       + 2.0 * n_tokens * v_local) / max(k_launch[0], 1)),
         "grad_kernel": {"achieved": round(grad_tf, 1), "frac": round(grad_tf / tensor_peak, 4),
                         "ms_per_launch": round(k_ms[2] / max(k_launch[2], 1), 5),
