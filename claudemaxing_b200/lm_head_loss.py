@@ -102,12 +102,13 @@ def bf16_copy_of_weight(w16):
     return copy
 
 
-def head_partial(h16, w16, target, col_offset=0, chunk_cols=None, want_grad=True, w_bf16=None):
+def head_partial(h16, w16, target, col_offset=0, chunk_cols=None, want_grad=True, w_bf16=None,
+                 grad_out=None):
     """One pass of the fused head over the columns of `w16` (a shard of the head weight whose
     first row is vocabulary index `col_offset`). Returns (state, grad_raw): the per-row state of
     this range and, with `want_grad`, the raw fp32 [n, hidden] gradient sum_v exp(z_v -
     state.grad_ref) W[v] over the range's columns except the label's; `head_finish` completes
-    it."""
+    it. `grad_out` (contiguous fp32 [n, hidden]) is used for the gradient instead of a new tensor."""
     _lib.require_cuda(h16, w16, target)
     if h16.dtype != torch.float16 or w16.dtype != torch.float16:
         raise TypeError("the fused head computes in float16")
@@ -121,7 +122,14 @@ def head_partial(h16, w16, target, col_offset=0, chunk_cols=None, want_grad=True
         target = target.to(torch.int64)
     dev = h16.device
     state = HeadState(n, dev)
-    grad_raw = torch.empty((n, hidden), dtype=torch.float32, device=dev) if want_grad else None
+    grad_raw = None
+    if want_grad:
+        grad_raw = grad_out
+        if grad_raw is None:
+            grad_raw = torch.empty((n, hidden), dtype=torch.float32, device=dev)
+        elif (grad_raw.shape != (n, hidden) or grad_raw.dtype != torch.float32
+              or not grad_raw.is_contiguous()):
+            raise ValueError("grad_out must be a contiguous fp32 [n, hidden] tensor")
     if n == 0 or vocab == 0:  # an empty shard contributes nothing: max -inf, sums 0, gradient 0
         for t in state.tensors():
             t.zero_()

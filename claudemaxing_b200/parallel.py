@@ -61,26 +61,56 @@ def merge_states(gathered, target, bounds):
     return merged, lse
 
 
-def vocab_parallel_head(h16, w_shard, target, bounds, group=None, want_grad=True,
-                        reduce_grad=True, chunk_cols=None, w_bf16=None):
-    """The fused head with the vocabulary split across the ranks of `group`. `w_shard` is this
-    rank's rows [bounds[rank], bounds[rank+1]) of the head weight. Returns dict(token_loss,
-    entropy, correct, grad_raw): per-row terms identical on every rank, grad_raw the fp32
-    [n, hidden] gradient at GRAD_SCALE, summed over ranks when `reduce_grad`."""
-    rank, world = dist.get_rank(group), dist.get_world_size(group)
-    target = target.contiguous().to(torch.int64)
+ROW_BLOCK = 2048   # rows whose exchange is overlapped with the next rows' GEMMs
+
+
+def _one_block(h16, w_shard, target, bounds, rank, world, group, want_grad, chunk_cols, w_bf16,
+               grad_out):
+    """Partial pass, state exchange, merge and finish for one block of rows; the gradient (not yet
+    summed over ranks) lands in `grad_out`."""
     state, grad_raw = head_partial(h16, w_shard, target, bounds[rank], chunk_cols, want_grad,
-                                   w_bf16)
+                                   w_bf16, grad_out)
     mine = pack_state(state)
     # concatenated along dim 0: the output layout every backend accepts
     gathered = torch.empty((world * mine.shape[0], mine.shape[1]), dtype=mine.dtype,
                            device=mine.device)
     dist.all_gather_into_tensor(gathered, mine, group=group)
     merged, _ = merge_states(gathered.view(world, *mine.shape), target, bounds)
-    token_loss, entropy, correct = head_finish(merged, target, w_shard, grad_raw, bounds[rank],
-                                               grad_ref=state.grad_ref)
-    if want_grad and reduce_grad:
-        dist.all_reduce(grad_raw, group=group)
+    terms = head_finish(merged, target, w_shard, grad_raw, bounds[rank], grad_ref=state.grad_ref)
+    return terms, grad_raw
+
+
+def vocab_parallel_head(h16, w_shard, target, bounds, group=None, want_grad=True,
+                        reduce_grad=True, chunk_cols=None, w_bf16=None):
+    """The fused head with the vocabulary split across the ranks of `group`. `w_shard` is this
+    rank's rows [bounds[rank], bounds[rank+1]) of the head weight. Returns dict(token_loss,
+    entropy, correct, grad_raw): per-row terms identical on every rank, grad_raw the fp32
+    [n, hidden] gradient at GRAD_SCALE, summed over ranks when `reduce_grad`.
+
+    Inputs of more than ROW_BLOCK rows are walked in blocks of that many rows: a block's gradient
+    all-reduce is issued asynchronously and runs beside the GEMMs of the next block (the kernels
+    process 2048 rows at a time anyway), so only the last block's reduction is exposed."""
+    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    target = target.contiguous().to(torch.int64)
+    n = h16.shape[0]
+    if n <= ROW_BLOCK or not (want_grad and reduce_grad):
+        (token_loss, entropy, correct), grad_raw = _one_block(
+            h16, w_shard, target, bounds, rank, world, group, want_grad, chunk_cols, w_bf16, None)
+        if want_grad and reduce_grad:
+            dist.all_reduce(grad_raw, group=group)
+        return dict(token_loss=token_loss, entropy=entropy, correct=correct, grad_raw=grad_raw)
+    h16 = h16.contiguous()
+    grad_raw = torch.empty((n, h16.shape[1]), dtype=torch.float32, device=h16.device)
+    pieces, pending = [], []
+    for r0 in range(0, n, ROW_BLOCK):
+        rows = slice(r0, min(n, r0 + ROW_BLOCK))
+        terms, block_grad = _one_block(h16[rows], w_shard, target[rows], bounds, rank, world, group,
+                                       True, chunk_cols, w_bf16, grad_raw[rows])
+        pieces.append(terms)
+        pending.append(dist.all_reduce(block_grad, group=group, async_op=True))
+    for work in pending:
+        work.wait()
+    token_loss, entropy, correct = (torch.cat([p[i] for p in pieces]) for i in range(3))
     return dict(token_loss=token_loss, entropy=entropy, correct=correct, grad_raw=grad_raw)
 
 

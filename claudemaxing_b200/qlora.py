@@ -117,24 +117,62 @@ class _MatMul4Bit(torch.autograd.Function):
     def backward(ctx, grad):
         if not ctx.needs_input_grad[0]:
             return None, None, None
-        dx = torch.matmul(grad, ctx.layer.dequantized(grad.dtype))
+        dx = torch.matmul(grad, ctx.layer.dequantized(grad.dtype, backward=True))
         return dx.to(ctx.x_dtype), None, None
+
+
+class _DequantBuffers:
+    """Two fp16 weight buffers per (device, dtype) shared by all groups of a model: the block in
+    use and the block that is being dequantised ahead on a side stream."""
+
+    def __init__(self, numel, dtype, device):
+        self.flat = [torch.empty(numel, dtype=dtype, device=device) for _ in range(2)]
+        self.owner = [None, None]      # weakref to the group whose weights the buffer holds
+        self.key = [None, None]
+        self.ready = [None, None]      # event of a prefetch the main stream has not waited for yet
+        self.last = None               # weakref to the group served last
+        self.side = torch.cuda.Stream(device=device)
+
+    def holds(self, group, key):
+        for i in (0, 1):
+            if self.owner[i] is not None and self.owner[i]() is group and self.key[i] == key:
+                return i
+        return None
 
 
 class NF4Group:
     """The 4-bit projections of one decoder block, dequantised together.
 
     A block's seven weights are used right after one another (q, k, v, o, gate, up, down forward;
-    the reverse in backward), each too small to fill the GPU with its own launch. The first member
-    that asks for its weight makes one batched launch write all of them into a workspace that every
-    group of the model shares (the largest block's fp16 weights, 94 MB for Qwen2.5-1.5B); the other
-    members then find theirs there. The workspace belongs to the group that filled it last, so the
-    usual layer-by-layer order costs one launch per block and direction, and any other order is
-    still correct (it only dequantises more often). The returned weight is a view that the next
-    group overwrites: use it on the current stream at once and do not keep it.
+    the reverse in backward), each too small to fill the GPU with its own launch. One batched
+    launch writes all of them into one of two buffers that every group of the model shares (the
+    largest block's fp16 weights each, 94 MB for Qwen2.5-1.5B); a block stays resident until two
+    other blocks have been used, so backward finds the last two blocks of forward still there. Any
+    order of use stays correct: a block that is not in a buffer is dequantised on the spot. The
+    returned weight is a view that a later block overwrites: use it on the current stream at once
+    and do not keep it.
+
+    With `NF4Group.prefetch = True` the neighbour the computation will reach next (`next` going
+    forward, `prev` in backward) is dequantised on a side stream into the other buffer while the
+    current block's GEMMs run. Measured on the Qwen2.5-1.5B step this is slower (24.2 ms against
+    22.5 ms per captured step): the dequant CTAs take SM slots and HBM bandwidth from the GEMMs
+    for longer than the 26 us they would have cost in line. It is off by default.
     """
 
-    _workspaces = {}  # (device, dtype) -> [flat tensor, weakref to the owning group, its key]
+    _buffers = {}  # (device, dtype) -> _DequantBuffers
+    prefetch = False
+
+    @classmethod
+    def forget(cls):
+        """Declares every buffer's contents unknown (after waiting for prefetches still running).
+        A CUDA graph must not start from weights that happen to be resident at capture time, and
+        what a capture "ran" never ran."""
+        for bufs in cls._buffers.values():
+            for i in (0, 1):
+                if bufs.ready[i] is not None:
+                    torch.cuda.current_stream(bufs.flat[i].device).wait_event(bufs.ready[i])
+                bufs.owner[i] = bufs.key[i] = bufs.ready[i] = None
+            bufs.last = None
 
     def __init__(self, layers):
         self.layers = list(layers)
@@ -142,28 +180,67 @@ class NF4Group:
         self.offsets = [0]
         for n in self.sizes:
             self.offsets.append(self.offsets[-1] + (n + 127) // 128 * 128)  # 256-byte aligned slices
+        self.next = self.prev = None   # neighbours in forward order (set by `chain`)
         for l in self.layers:
             l.group = self
+
+    @staticmethod
+    def chain(groups):
+        """Tells every group its neighbours in forward order."""
+        for before, after in zip(groups, groups[1:]):
+            before.next, after.prev = after, before
 
     def _key(self):
         return tuple(l.packed._version for l in self.layers) + tuple(l.packed.data_ptr() for l in self.layers)
 
-    def weight(self, layer, dtype):
+    def _views(self, flat):
+        return [flat[o:o + n].view(l.out_features, l.in_features)
+                for l, o, n in zip(self.layers, self.offsets, self.sizes)]
+
+    def _fill(self, bufs, i, dtype):
         from .nf4 import dequantize_nf4_batch
 
+        dequantize_nf4_batch([(l.packed, l.quant_state) for l in self.layers], dtype,
+                             outs=self._views(bufs.flat[i]))
+        bufs.owner[i], bufs.key[i] = weakref.ref(self), self._key()
+
+    def weight(self, layer, dtype, backward=False):
         device = layer.packed.device
-        slot = NF4Group._workspaces.get((device, dtype))
-        if slot is None or slot[0].numel() < self.offsets[-1]:
-            slot = [torch.empty(self.offsets[-1], dtype=dtype, device=device), None, None]
-            NF4Group._workspaces[(device, dtype)] = slot
-        flat = slot[0]
-        views = [flat[o:o + n].view(l.out_features, l.in_features)
-                 for l, o, n in zip(self.layers, self.offsets, self.sizes)]
-        key = self._key()
-        if slot[1] is None or slot[1]() is not self or slot[2] != key:
-            dequantize_nf4_batch([(l.packed, l.quant_state) for l in self.layers], dtype, outs=views)
-            slot[1], slot[2] = weakref.ref(self), key
-        return views[self.layers.index(layer)]
+        bufs = NF4Group._buffers.get((device, dtype))
+        if bufs is None or bufs.flat[0].numel() < self.offsets[-1]:
+            bufs = _DequantBuffers(self.offsets[-1], dtype, device)
+            NF4Group._buffers[(device, dtype)] = bufs
+        main = torch.cuda.current_stream(device)
+        i = bufs.holds(self, self._key())
+        if i is None:
+            # not resident: take the buffer that does not hold the block served last
+            i = 0
+            if bufs.last is not None and bufs.owner[0] is not None and bufs.owner[0]() is bufs.last():
+                i = 1
+            if bufs.ready[i] is not None:       # an unused prefetch is still running into it
+                main.wait_event(bufs.ready[i])
+                bufs.ready[i] = None
+            self._fill(bufs, i, dtype)
+        elif bufs.ready[i] is not None:         # prefetched: the main stream joins the side stream
+            main.wait_event(bufs.ready[i])
+            bufs.ready[i] = None
+        moved_on = bufs.last is None or bufs.last() is not self
+        bufs.last = weakref.ref(self)
+        neighbour = self.prev if backward else self.next
+        if (moved_on and NF4Group.prefetch and neighbour is not None
+                and neighbour.offsets[-1] <= bufs.flat[0].numel()
+                and bufs.holds(neighbour, neighbour._key()) is None):
+            j = 1 - i
+            # everything enqueued so far (the last user of the other buffer included) comes first
+            fence = torch.cuda.Event()
+            fence.record(main)
+            with torch.cuda.stream(bufs.side):
+                bufs.side.wait_event(fence)
+                neighbour._fill(bufs, j, dtype)
+                done = torch.cuda.Event()
+                done.record(bufs.side)
+            bufs.ready[j] = done
+        return self._views(bufs.flat[i])[self.layers.index(layer)]
 
 
 class NF4Linear(torch.nn.Module):
@@ -193,11 +270,11 @@ class NF4Linear(torch.nn.Module):
         self.quant_state = self.quant_state.to(self.packed.device)
         return self
 
-    def dequantized(self, dtype):
+    def dequantized(self, dtype, backward=False):
         """The [out, in] weight in `dtype`: a fresh tensor, or a short-lived view of the group's
-        workspace."""
+        buffer (`backward` tells the group which neighbour to dequantise ahead)."""
         if self.group is not None:
-            return self.group.weight(self, dtype)
+            return self.group.weight(self, dtype, backward)
         return dequantize_nf4(self.packed, self.quant_state, dtype)
 
     def matmul_4bit(self, x_low):
@@ -263,6 +340,7 @@ def build_qlora_model(device, config=None, lora_targets=("q_proj", "v_proj"), r=
         model = Qwen2ForCausalLM(hf_cfg).to(torch.float16)
     for p in model.parameters():
         p.requires_grad_(False)
+    groups = []
     for layer in model.model.layers:
         for parent, names in ((layer.self_attn, ("q_proj", "k_proj", "v_proj", "o_proj")),
                               (layer.mlp, ("gate_proj", "up_proj", "down_proj"))):
@@ -274,11 +352,13 @@ def build_qlora_model(device, config=None, lora_targets=("q_proj", "v_proj"), r=
                 setattr(parent, name, q)
                 del lin
         if group_dequant:
-            NF4Group([getattr(parent, name).base_layer if isinstance(getattr(parent, name), LoRALinear)
-                      else getattr(parent, name)
-                      for parent, names in ((layer.self_attn, ("q_proj", "k_proj", "v_proj", "o_proj")),
-                                            (layer.mlp, ("gate_proj", "up_proj", "down_proj")))
-                      for name in names])
+            groups.append(NF4Group(
+                [getattr(parent, name).base_layer if isinstance(getattr(parent, name), LoRALinear)
+                 else getattr(parent, name)
+                 for parent, names in ((layer.self_attn, ("q_proj", "k_proj", "v_proj", "o_proj")),
+                                       (layer.mlp, ("gate_proj", "up_proj", "down_proj")))
+                 for name in names]))
+    NF4Group.chain(groups)
     # what prepare_model_for_kbit_training leaves: fp32 norms and fp32 (tied) embedding
     for module in model.modules():
         if type(module).__name__ == "Qwen2RMSNorm":
@@ -484,9 +564,11 @@ class CapturedStep:
                 self._optimizer_step()
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
+        NF4Group.forget()           # the graph dequantises its first block itself
         self.graph_fb = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph_fb):
             self.loss = self._forward_backward()
+        NF4Group.forget()           # nothing the capture recorded has run
         self.graph_opt = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph_opt, pool=self.graph_fb.pool()):
             self._optimizer_step()

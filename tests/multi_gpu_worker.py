@@ -25,12 +25,12 @@ def rel(a, b):
     return ((a.double() - b).norm() / b.norm().clamp(min=1e-30)).item()
 
 
-def check_head(rank, world, dev):
+def check_head(rank, world, dev, n=1024):
     from claudemaxing_b200 import parallel
     from claudemaxing_b200.lm_head_loss import GRAD_SCALE, fused_head_loss
     from oracle import head_ce
 
-    n, hdim, vocab = 1024, 512, 50021   # vocabulary not a multiple of anything
+    hdim, vocab = 512, 50021   # vocabulary not a multiple of anything
     gen = torch.Generator().manual_seed(7)
     h = torch.randn(n, hdim, generator=gen).half()
     w = (torch.randn(vocab, hdim, generator=gen) * 0.05).half()
@@ -113,10 +113,12 @@ def main():
     dist.init_process_group("nccl", device_id=dev)
     try:
         ok1, e1 = check_head(rank, world, dev)
+        # more rows than one block: blocks' exchanges overlap the next block's GEMMs, ragged tail
+        ok3, e3 = check_head(rank, world, dev, n=4500)
         ok2, e2 = check_step(rank, world, dev)
-        flag = torch.tensor([int(ok1 and ok2)], device=dev)
+        flag = torch.tensor([int(ok1 and ok2 and ok3)], device=dev)
         dist.all_reduce(flag, op=dist.ReduceOp.MIN)
-        print(f"rank {rank}: head {ok1} {e1} step {ok2} {e2}", flush=True)
+        print(f"rank {rank}: head {ok1} {e1} head-4500 {ok3} {e3} step {ok2} {e2}", flush=True)
         if rank == 0 and int(flag) == 1:
             print("MULTI_GPU_OK", flush=True)
     finally:
