@@ -44,6 +44,21 @@ def pack_state(state):
                         state.best.view(torch.float32), state.best_val, state.label_logit])
 
 
+_BOUNDS_ON_DEVICE = {}
+
+
+def _bounds_tensor(bounds, device):
+    """The shard bounds as an int64 device tensor, made once per (bounds, device): building it from
+    the Python list on every call is a pageable host-to-device copy, which makes the host wait for
+    everything enqueued before it and so ends the host's run-ahead twice per step."""
+    key = (tuple(int(b) for b in bounds), str(device))
+    hit = _BOUNDS_ON_DEVICE.get(key)
+    if hit is None:
+        hit = torch.tensor(key[0], dtype=torch.int64, device=device)
+        _BOUNDS_ON_DEVICE[key] = hit
+    return hit
+
+
 def merge_states(gathered, target, bounds):
     """gathered [world, 6, n] (rank order) -> (merged HeadState, merged lse [n])."""
     world, _, n = gathered.shape
@@ -51,7 +66,7 @@ def merge_states(gathered, target, bounds):
     fields = gathered.permute(1, 0, 2).contiguous()  # [6, world, n]
     merged = HeadState(n, dev)
     lse = torch.empty(n, dtype=torch.float32, device=dev)
-    begin = torch.tensor(bounds, dtype=torch.int64, device=dev)
+    begin = _bounds_tensor(bounds, dev)
     if n:
         _lib.call("soup_lmhead_merge", *(_lib.ptr(fields[i]) for i in range(N_FIELDS)),
                   _lib.ptr(target), _lib.ptr(begin), _lib.ptr(merged.run_max),
