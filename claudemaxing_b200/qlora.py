@@ -14,6 +14,7 @@ ops on whatever device the weight is on; it is set-up code, not part of the step
 """
 
 import math
+import os
 import weakref
 from types import SimpleNamespace
 
@@ -160,7 +161,7 @@ class NF4Group:
     """
 
     _buffers = {}  # (device, dtype) -> _DequantBuffers
-    prefetch = False
+    prefetch = os.environ.get("SOUP_NF4_PREFETCH", "0") == "1"
 
     @classmethod
     def forget(cls):
