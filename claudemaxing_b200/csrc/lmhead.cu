@@ -963,23 +963,30 @@ struct Plan {
 // to spare for. row_tiles * ct fills whole waves of CTA pairs. An override applies to all chunks.
 inline Plan make_plan(int64_t n, int64_t v_shard, int sms, int ct_override) {
   Plan p;
-  p.row_block = (int)(n < 2048 ? (n < 1 ? 1 : n) : 2048);
-  const int rt = (p.row_block + 2 * kBM - 1) / (2 * kBM);
   const int pairs = sms / 2 > 0 ? sms / 2 : 1;
   const int total_ct = (int)((v_shard + kBN - 1) / kBN);
-  int wave = 37;
-  int best = -1;
-  for (int c = 40; c >= 8; --c)
-    if ((rt * c) % pairs == 0) { best = c; break; }
-  if (best > 0) wave = best;
-  p.ct_first = ct_override > 0 ? ct_override : wave;
   int waves = 8;
   if (const char* e = getenv("SOUP_LMHEAD_WAVES")) { const int v = atoi(e); if (v >= 1 && v <= 64) waves = v; }
+  // A chunk is `wave` column tiles per wave of CTA pairs at eight row tiles (2048 rows).
+  int wave = 37;
+  for (int c = 40; c >= 8; --c)
+    if ((8 * c) % pairs == 0) { wave = c; break; }
+  p.ct_first = ct_override > 0 ? ct_override : wave;
   p.ct = ct_override > 0 ? ct_override : waves * wave;
   if (p.ct_first > total_ct) p.ct_first = total_ct;
   if (p.ct_first < 1) p.ct_first = 1;
   if (p.ct > total_ct) p.ct = total_ct;
   if (p.ct < p.ct_first) p.ct = p.ct_first;
+  // Rows per block: 2048 for a full-width chunk; more when the shard is narrow (a rank of a
+  // vocabulary-parallel group), so that a launch still has a dozen tiles per CTA pair and the
+  // probability buffer stays around 600 MB. Whole multiples of 2048, at most 8192.
+  int64_t rb = 2048;
+  if (ct_override <= 0) {
+    rb = 2048 * (int64_t)((2 * waves * wave) / p.ct);
+    if (rb < 2048) rb = 2048;
+    if (rb > 8192) rb = 8192;
+  }
+  p.row_block = (int)(n < rb ? (n < 1 ? 1 : n) : rb);
   return p;
 }
 

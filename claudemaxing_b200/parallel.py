@@ -76,7 +76,17 @@ def merge_states(gathered, target, bounds):
     return merged, lse
 
 
-ROW_BLOCK = 2048   # rows whose exchange is overlapped with the next rows' GEMMs
+def _row_block(n, hidden, v_shard, chunk_cols):
+    """Rows per exchange step: the row block the kernels use for this shard width (2048 for a wide
+    shard, up to 8192 for a narrow one), so that a step is one pass of the kernels."""
+    import ctypes
+
+    from .lm_head_loss import _chunk_tiles
+
+    rows = ctypes.c_int64(2048)
+    _lib.lib().soup_lmhead_plan(int(n), int(v_shard), _chunk_tiles(chunk_cols), ctypes.byref(rows),
+                                None, None)
+    return max(int(rows.value), 1)
 
 
 def _one_block(h16, w_shard, target, bounds, rank, world, group, want_grad, chunk_cols, w_bf16,
@@ -102,13 +112,14 @@ def vocab_parallel_head(h16, w_shard, target, bounds, group=None, want_grad=True
     entropy, correct, grad_raw): per-row terms identical on every rank, grad_raw the fp32
     [n, hidden] gradient at GRAD_SCALE, summed over ranks when `reduce_grad`.
 
-    Inputs of more than ROW_BLOCK rows are walked in blocks of that many rows: a block's gradient
+    Inputs of more rows than the kernels' row block are walked block by block: a block's gradient
     all-reduce is issued asynchronously and runs beside the GEMMs of the next block (the kernels
-    process 2048 rows at a time anyway), so only the last block's reduction is exposed."""
+    process a row block at a time anyway), so only the last block's reduction is exposed."""
     rank, world = dist.get_rank(group), dist.get_world_size(group)
     target = target.contiguous().to(torch.int64)
     n = h16.shape[0]
-    if n <= ROW_BLOCK or not (want_grad and reduce_grad):
+    block = _row_block(n, h16.shape[1], w_shard.shape[0], chunk_cols)
+    if n <= block or not (want_grad and reduce_grad):
         (token_loss, entropy, correct), grad_raw = _one_block(
             h16, w_shard, target, bounds, rank, world, group, want_grad, chunk_cols, w_bf16, None)
         if want_grad and reduce_grad:
@@ -117,8 +128,8 @@ def vocab_parallel_head(h16, w_shard, target, bounds, group=None, want_grad=True
     h16 = h16.contiguous()
     grad_raw = torch.empty((n, h16.shape[1]), dtype=torch.float32, device=h16.device)
     pieces, pending = [], []
-    for r0 in range(0, n, ROW_BLOCK):
-        rows = slice(r0, min(n, r0 + ROW_BLOCK))
+    for r0 in range(0, n, block):
+        rows = slice(r0, min(n, r0 + block))
         terms, block_grad = _one_block(h16[rows], w_shard, target[rows], bounds, rank, world, group,
                                        True, chunk_cols, w_bf16, grad_raw[rows])
         pieces.append(terms)

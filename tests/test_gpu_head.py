@@ -182,3 +182,26 @@ def test_full_size_linearity_property():
     ref_row = (p3 @ w.double()) / n_lab
     assert (dh[3].double() - ref_row).abs().max().item() <= 1e-2 * ref_row.abs().max().item()
     assert abs(loss.item() - tl.sum().item() / n_lab) <= 1e-4
+
+
+@pytest.mark.parametrize("dims", [(9000, 64, 700), (5000, 128, 2100), (4200, 64, 80000)])
+def test_more_rows_than_a_row_block(dims):
+    # narrow vocabularies use row blocks of up to 8192 rows, wide ones 4096: several blocks with a
+    # ragged last one, and the statistics and gradients of rows next to a block boundary. The
+    # oracle runs on a sample of rows (rows are independent given the common divisor).
+    from oracle.head_ce import head_ce
+
+    n, hidden, vocab = dims
+    h, w, t = make(n, hidden, vocab, seed=11)
+    n_lab = int((t != -100).sum())
+    loss, step, dh = run_ours(h, w, t)
+    picks = sorted(set(list(range(0, 48)) + list(range(4080, min(n, 4112))) +
+                       list(range(max(0, min(n, 8192) - 16), min(n, 8208))) + list(range(n - 48, n))))
+    idx = torch.tensor(picks)
+    ref = head_ce(h[idx], w, t[idx], denominator=n_lab)
+    tl, en = step.token_loss[0].cpu()[idx], step.token_entropy[0].cpu()[idx]
+    assert (tl - ref["token_loss"]).abs().max().item() <= 1e-3
+    assert (en - ref["entropy"]).abs().max().item() <= 1e-3
+    assert_close_rel_max(dh[idx], ref["dhidden"], 1e-2, "dhidden")
+    assert step.labelled.item() == n_lab
+    assert abs(loss.item() - step.token_loss.sum().item() / n_lab) <= 1e-4 * max(1.0, abs(loss.item()))
