@@ -184,11 +184,14 @@ def test_full_size_linearity_property():
     assert abs(loss.item() - tl.sum().item() / n_lab) <= 1e-4
 
 
-@pytest.mark.parametrize("dims", [(9000, 64, 700), (5000, 128, 2100), (4200, 64, 80000)])
+@pytest.mark.parametrize("dims", [(9000, 64, 700), (5000, 128, 2100), (4200, 64, 80000),
+                                  (8192, 1536, 37984), (16384, 1536, 18992)])
 def test_more_rows_than_a_row_block(dims):
     # narrow vocabularies use row blocks of up to 8192 rows, wide ones 4096: several blocks with a
-    # ragged last one, and the statistics and gradients of rows next to a block boundary. The
-    # oracle runs on a sample of rows (rows are independent given the common divisor).
+    # ragged last one, and the statistics and gradients of rows next to a block boundary. The last
+    # two shapes are what one rank of a 4- and of an 8-way vocabulary-parallel group computes in
+    # the scaling benchmark. The oracle runs on a sample of rows (rows are independent given the
+    # common divisor).
     from oracle.head_ce import head_ce
 
     n, hidden, vocab = dims
@@ -196,6 +199,7 @@ def test_more_rows_than_a_row_block(dims):
     n_lab = int((t != -100).sum())
     loss, step, dh = run_ours(h, w, t)
     picks = sorted(set(list(range(0, 48)) + list(range(4080, min(n, 4112))) +
+                       list(range(max(0, min(n, 6144) - 16), min(n, 6160))) +
                        list(range(max(0, min(n, 8192) - 16), min(n, 8208))) + list(range(n - 48, n))))
     idx = torch.tensor(picks)
     ref = head_ce(h[idx], w, t[idx], denominator=n_lab)
