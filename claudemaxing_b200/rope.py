@@ -48,24 +48,24 @@ def _rotate_pair(q, k, cos, sin, q_dtype, k_dtype, backward):
 
 
 class RoPE(torch.autograd.Function):
+    """`RoPE.apply(q, k, cos, sin) -> (q', k')`; the gradient of a rotation is the rotation by the
+    opposite angle, so backward is the same kernel with its `backward` flag set."""
+
     @staticmethod
     def forward(ctx, q, k, cos, sin):
-        cos, sin = cos.contiguous(), sin.contiguous()
-        q_dtype = torch.promote_types(q.dtype, cos.dtype)
-        k_dtype = torch.promote_types(k.dtype, cos.dtype)
-        ctx.save_for_backward(cos, sin)
-        ctx.dtypes = (q.dtype, k.dtype)
-        return _rotate_pair(q, k, cos, sin, q_dtype, k_dtype, False)
+        tables = (cos.contiguous(), sin.contiguous())
+        ctx.save_for_backward(*tables)
+        ctx.in_dtypes = (q.dtype, k.dtype)           # what the gradients have to come back in
+        out_dtypes = tuple(torch.promote_types(t.dtype, cos.dtype) for t in (q, k))
+        return _rotate_pair(q, k, *tables, *out_dtypes, False)
 
     @staticmethod
     def backward(ctx, grad_q, grad_k):
-        cos, sin = ctx.saved_tensors
-        q_dtype, k_dtype = ctx.dtypes
-        gq = grad_q if ctx.needs_input_grad[0] and grad_q is not None else None
-        gk = grad_k if ctx.needs_input_grad[1] and grad_k is not None else None
-        if gq is None and gk is None:
+        wanted = [g if (g is not None and ctx.needs_input_grad[i]) else None
+                  for i, g in enumerate((grad_q, grad_k))]
+        if wanted[0] is None and wanted[1] is None:
             return None, None, None, None
-        dq, dk = _rotate_pair(gq, gk, cos, sin, q_dtype, k_dtype, True)
+        dq, dk = _rotate_pair(*wanted, *ctx.saved_tensors, *ctx.in_dtypes, True)
         return dq, dk, None, None
 
 
@@ -75,42 +75,48 @@ def rope(q, k, cos, sin):
     return RoPE.apply(q, k, cos, sin)
 
 
-ORIGINAL = None
+ORIGINAL = None   # the installed apply_rotary_pos_emb, once patched
 
 
-def _covered(q, k, cos, sin, unsqueeze_dim):
+def _why_not(q, k, cos, sin, unsqueeze_dim):
+    """Why a call keeps the installed implementation ("" when the kernel covers it)."""
+    tensors = (q, k, cos, sin)
     if unsqueeze_dim != 1:
-        return False
-    if not all(isinstance(x, torch.Tensor) and x.is_cuda for x in (q, k, cos, sin)):
-        return False
+        return "heads are not on dim 1"
+    if not all(isinstance(t, torch.Tensor) and t.is_cuda for t in tensors):
+        return "not CUDA tensors"
+    if len({t.device for t in tensors}) != 1 or not all(t.dtype in _SUPPORTED for t in tensors):
+        return "mixed devices or an unsupported dtype"
+    if q.dim() != 4 or k.dim() != 4 or cos.dim() != 3 or sin.shape != cos.shape or sin.dtype != cos.dtype:
+        return "unexpected ranks"
     d = q.shape[-1]
-    half = d // 2
-    return (q.dim() == 4 and k.dim() == 4 and cos.dim() == 3 and sin.shape == cos.shape
-            and k.shape[-1] == d and cos.shape[-1] == d and d % 2 == 0 and d <= 256
-            and half & (half - 1) == 0
-            and cos.shape[0] in (1, q.shape[0]) and q.shape[2] == cos.shape[1]
-            and k.shape[0] == q.shape[0] and k.shape[2] == q.shape[2]
-            and not cos.requires_grad and not sin.requires_grad and sin.dtype == cos.dtype
-            and len({x.device for x in (q, k, cos, sin)}) == 1
-            and all(x.dtype in _SUPPORTED for x in (q, k, cos, sin)))
+    if d != k.shape[-1] or d != cos.shape[-1] or d % 2 or d > 256 or (d // 2) & (d // 2 - 1):
+        return "head_dim must be an even power of two up to 256, the same for q, k and the tables"
+    if k.shape[0] != q.shape[0] or k.shape[2] != q.shape[2] or cos.shape[1] != q.shape[2]:
+        return "batch or sequence sizes differ"
+    if cos.shape[0] not in (1, q.shape[0]):
+        return "tables neither shared nor per batch row"
+    if cos.requires_grad or sin.requires_grad:
+        return "the tables want a gradient"
+    return ""
 
 
 def patch_qwen2_rope():
     """Replace transformers.models.qwen2.modeling_qwen2.apply_rotary_pos_emb, which
-    Qwen2Attention.forward looks up by name on every call. Layouts the kernel does not cover
-    (CPU, another unsqueeze_dim, odd head_dim, gradients for cos/sin) keep the installed one."""
+    Qwen2Attention.forward looks up by name on every call. Calls the kernel does not cover (see
+    `_why_not`) keep the installed function."""
     global ORIGINAL
-    from transformers.models.qwen2 import modeling_qwen2
+    from transformers.models.qwen2 import modeling_qwen2 as qwen2
 
-    current = getattr(modeling_qwen2, "apply_rotary_pos_emb", None)
-    if current is None or getattr(current, "_fused_rope", False):
+    installed = getattr(qwen2, "apply_rotary_pos_emb", None)
+    if installed is None or getattr(installed, "_fused_rope", False):
         return
-    ORIGINAL = original = current
 
     def apply_rotary_pos_emb(q, k, cos, sin, unsqueeze_dim=1):
-        if not _covered(q, k, cos, sin, unsqueeze_dim):
-            return original(q, k, cos, sin, unsqueeze_dim)
+        if _why_not(q, k, cos, sin, unsqueeze_dim):
+            return installed(q, k, cos, sin, unsqueeze_dim)
         return rope(q, k, cos, sin)
 
     apply_rotary_pos_emb._fused_rope = True
-    modeling_qwen2.apply_rotary_pos_emb = apply_rotary_pos_emb
+    ORIGINAL = installed
+    qwen2.apply_rotary_pos_emb = apply_rotary_pos_emb
