@@ -77,8 +77,8 @@ def merge_states(gathered, target, bounds):
 
 
 def _row_block(n, hidden, v_shard, chunk_cols):
-    """Rows per exchange step: the row block the kernels use for this shard width (2048 for a wide
-    shard, up to 8192 for a narrow one), so that a step is one pass of the kernels."""
+    """The row block the kernels use for a shard `v_shard` columns wide (2048 for a wide shard, up
+    to 8192 for a narrow one). Host arithmetic only."""
     import ctypes
 
     from .lm_head_loss import _chunk_tiles
@@ -87,6 +87,18 @@ def _row_block(n, hidden, v_shard, chunk_cols):
     _lib.lib().soup_lmhead_plan(int(n), int(v_shard), _chunk_tiles(chunk_cols), ctypes.byref(rows),
                                 None, None)
     return max(int(rows.value), 1)
+
+
+def exchange_rows(n, hidden, bounds, chunk_cols=None):
+    """Rows per exchange step, the same number on every rank. It is derived from the shard bounds
+    (which all ranks hold), never from the local shard: shards differ by one column tile when the
+    tiles do not divide evenly, the kernels' row block depends on the tile count (151936 columns
+    over 4 ranks: 149 tiles -> 6144 rows, 148 tiles -> 8192), and ranks that walked the rows in
+    different block sizes would issue different numbers of collectives and wait for each other
+    forever. The widest shard has the smallest row block, so one exchange step is at most one
+    pass of the kernels on every rank."""
+    widest = max(int(bounds[r + 1]) - int(bounds[r]) for r in range(len(bounds) - 1))
+    return _row_block(n, hidden, max(widest, 1), chunk_cols)
 
 
 def _one_block(h16, w_shard, target, bounds, rank, world, group, want_grad, chunk_cols, w_bf16,
@@ -116,9 +128,12 @@ def vocab_parallel_head(h16, w_shard, target, bounds, group=None, want_grad=True
     all-reduce is issued asynchronously and runs beside the GEMMs of the next block (the kernels
     process a row block at a time anyway), so only the last block's reduction is exposed."""
     rank, world = dist.get_rank(group), dist.get_world_size(group)
+    if len(bounds) != world + 1 or w_shard.shape[0] != bounds[rank + 1] - bounds[rank]:
+        raise ValueError(f"rank {rank}: w_shard has {w_shard.shape[0]} rows, the bounds {list(bounds)} "
+                         f"give this rank {bounds[rank + 1] - bounds[rank] if len(bounds) == world + 1 else '?'}")
     target = target.contiguous().to(torch.int64)
     n = h16.shape[0]
-    block = _row_block(n, h16.shape[1], w_shard.shape[0], chunk_cols)
+    block = exchange_rows(n, h16.shape[1], bounds, chunk_cols)
     if n <= block or not (want_grad and reduce_grad):
         (token_loss, entropy, correct), grad_raw = _one_block(
             h16, w_shard, target, bounds, rank, world, group, want_grad, chunk_cols, w_bf16, None)

@@ -67,3 +67,128 @@ def test_two_cpu_ranks_vocab_parallel_and_grad_allreduce():
         results = manager.dict()
         mp.spawn(_worker, args=(world, _free_port(), results), nprocs=world, join=True)
         assert dict(results) == {0: True, 1: True}
+
+
+# --- the block-wise exchange of vocab_parallel_head itself, kernels replaced by torch on CPU -------
+
+def _cpu_partial(h16, w, target, col_offset=0, chunk_cols=None, want_grad=True, w_bf16=None,
+                 grad_out=None):
+    from claudemaxing_b200.lm_head_loss import HeadState
+
+    n = h16.shape[0]
+    z = h16.float() @ w.float().t()
+    st = HeadState(n, h16.device)
+    st.best_val, idx = z.max(dim=1)
+    st.best = (idx + col_offset).to(torch.int32)
+    st.run_max = st.best_val.clone()
+    e = torch.exp(z - st.run_max[:, None])
+    st.run_sum, st.run_dot = e.sum(1), (e * z).sum(1)
+    local = target - col_offset
+    inside = (target >= 0) & (local >= 0) & (local < w.shape[0])
+    rows = torch.arange(n)
+    st.label_logit = torch.where(inside, z[rows, local.clamp(0, w.shape[0] - 1)], torch.zeros(n))
+    st.grad_ref = st.run_max + torch.log(st.run_sum)
+    p = torch.exp(z - st.grad_ref[:, None])
+    p[rows[inside], local[inside]] = 0.0
+    p[target < 0] = 0.0
+    grad = p @ w.float()
+    if grad_out is not None:
+        grad_out.copy_(grad)
+        grad = grad_out
+    return st, grad
+
+
+def _cpu_merge(gathered, target, bounds):
+    from claudemaxing_b200.lm_head_loss import HeadState
+
+    world, _, n = gathered.shape
+    run_max, run_sum, run_dot, best, best_val, label_logit = (gathered[:, i] for i in range(6))
+    top = run_max.max(dim=0).values
+    scale = torch.exp(run_max - top)
+    out = HeadState(n, gathered.device)
+    out.run_max, out.run_sum, out.run_dot = top, (run_sum * scale).sum(0), (run_dot * scale).sum(0)
+    first = best_val.argmax(dim=0)          # ties: the lowest rank, i.e. the lowest column
+    cols = torch.arange(n)
+    out.best = best.contiguous().view(torch.int32)[first, cols]
+    out.best_val = best_val[first, cols]
+    owner = torch.bucketize(target.clamp(min=0), torch.tensor(bounds[1:-1]), right=True)
+    out.label_logit = label_logit[owner, cols]
+    out.grad_ref = out.run_max + torch.log(out.run_sum)
+    return out, out.grad_ref.clone()
+
+
+def _cpu_finish(state, target, w, grad_raw=None, col_offset=0, grad_ref=None, want_metrics=True):
+    lse = state.run_max + torch.log(state.run_sum)
+    labelled = target >= 0
+    loss = torch.where(labelled, lse - state.label_logit, torch.zeros_like(lse))
+    entropy = lse - state.run_dot / state.run_sum
+    correct = (labelled & (state.best.long() == target)).to(torch.int32)
+    if grad_raw is not None:
+        grad_raw.mul_(torch.exp(grad_ref - lse)[:, None])
+        local = target - col_offset
+        inside = labelled & (local >= 0) & (local < w.shape[0])
+        p_label = torch.exp(state.label_logit - lse)
+        grad_raw[inside] += (p_label[inside] - 1.0)[:, None] * w.float()[local[inside]]
+        grad_raw.mul_(1024.0)
+    return loss, entropy, correct
+
+
+def _block_worker(rank, world, port, results):
+    import datetime
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world,
+                            timeout=datetime.timedelta(seconds=60))
+    try:
+        from claudemaxing_b200 import parallel
+        from oracle import head_ce
+
+        parallel.head_partial, parallel.merge_states = _cpu_partial, _cpu_merge
+        parallel.head_finish = _cpu_finish
+        # as in the kernels' plan, the row block shrinks with the shard's tile count: the ranks'
+        # own shards (3, 3, 2, 2 tiles of 8 columns) would give 16, 16, 32, 32 rows
+        parallel._row_block = lambda n, hidden, v_shard, chunk_cols: 16 if v_shard > 16 else 32
+        gen = torch.Generator().manual_seed(1)
+        h = (torch.randn(40, 32, generator=gen)).half()
+        w = (torch.randn(77, 32, generator=gen) * 0.3).half()
+        t = torch.randint(0, 77, (40,), generator=gen)
+        t[::7] = -100
+        bounds = parallel.shard_bounds(77, world, tile=8)
+        widths = [bounds[r + 1] - bounds[r] for r in range(world)]
+        assert len({16 if v > 16 else 32 for v in widths}) == 2, widths
+        assert parallel.exchange_rows(40, 32, bounds) == 16
+        out = parallel.vocab_parallel_head(h, w[bounds[rank]:bounds[rank + 1]], t, bounds)
+        ref = head_ce.head_ce(h.float(), w.float(), t)
+        n_lab = (t != -100).sum()
+        results[rank] = bool(
+            torch.allclose(out["token_loss"], ref["token_loss"], atol=1e-4)
+            and torch.allclose(out["entropy"], ref["entropy"], atol=1e-4)
+            and torch.equal(out["correct"], ref["correct"])
+            and torch.allclose(out["grad_raw"] / (1024.0 * n_lab), ref["dhidden"], atol=1e-5))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_four_cpu_ranks_with_uneven_shards_walk_the_same_row_blocks():
+    """Shards that differ by a column tile have different kernel row blocks; the exchange has to
+    use one block size on all ranks or the ranks issue different numbers of collectives."""
+    world = 4
+    with mp.Manager() as manager:
+        results = manager.dict()
+        mp.spawn(_block_worker, args=(world, _free_port(), results), nprocs=world, join=True)
+        assert dict(results) == {r: True for r in range(world)}
+
+
+def test_exchange_rows_is_common_to_all_ranks_for_the_real_plan():
+    """With the library's own plan: for every world size the exchange block computed from the
+    bounds is one number, although the ranks' own shards can plan different row blocks."""
+    from claudemaxing_b200 import parallel
+
+    differing = 0
+    for world in (2, 3, 4, 5, 6, 7, 8):
+        bounds = parallel.shard_bounds(151936, world)
+        for n in (2048 * world, 65536):
+            own = {parallel._row_block(n, 1536, bounds[r + 1] - bounds[r], None) for r in range(world)}
+            differing += len(own) > 1
+            assert parallel.exchange_rows(n, 1536, bounds) == min(own)
+    assert differing, "expected at least one world size (4) whose shards plan different row blocks"
