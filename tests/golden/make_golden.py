@@ -19,7 +19,9 @@ import numpy as np
 import torch
 
 assert os.environ.get("TRITON_INTERPRET") == "1", "run with TRITON_INTERPRET=1"
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) < 2:
+    sys.exit("usage: TRITON_INTERPRET=1 python tests/golden/make_golden.py /path/to/reference")
+REF = sys.argv[1]
 sys.path.insert(0, REF)
 sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", ".."))
 OUT = os.path.dirname(os.path.abspath(__file__))
