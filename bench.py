@@ -21,6 +21,7 @@ on the host cores over a bounded sample of the same workload).
 import argparse
 import ctypes
 import json
+import math
 import os
 import statistics
 import sys
@@ -47,18 +48,40 @@ def peaks():
         return dict(FALLBACK_PEAKS), "fallback"
 
 
-def make_inputs(n_tokens, seed=0):
-    """BASELINE config 1 recipe: hidden ~N(0,1) fp16, W ~N(0,0.02) fp16, targets uniform with 10 %
-    set to ignore_index. Generated on the CPU so that oracle and kernels see identical bits."""
-    gen = torch.Generator().manual_seed(seed)
-    hidden = torch.randn(n_tokens, HIDDEN, generator=gen).half()
+SLAB = 2048   # rows of hidden states generated from one seed
+
+
+def make_weight():
+    """The tied head weight of BASELINE config 1: [151936, 1536] ~N(0, 0.02) fp16, generated on the
+    CPU slab by slab (no 900 MB fp32 temporary) so that oracle and kernels see identical bits."""
+    gen = torch.Generator().manual_seed(1000)
     weight = torch.empty(VOCAB, HIDDEN, dtype=torch.float16)
-    for r0 in range(0, VOCAB, 16384):  # slab by slab: no 900 MB fp32 temporary
+    for r0 in range(0, VOCAB, 16384):
         rows = min(16384, VOCAB - r0)
         weight[r0:r0 + rows] = (torch.randn(rows, HIDDEN, generator=gen) * 0.02).half()
-    target = torch.randint(0, VOCAB, (n_tokens,), generator=gen)
-    target[torch.rand(n_tokens, generator=gen) < 0.1] = -100
-    return hidden, weight, target
+    return weight
+
+
+def make_rows(slab):
+    """Slab `slab` of the token rows: hidden [2048, 1536] ~N(0,1) fp16 and targets uniform over the
+    vocabulary with 10 % set to ignore_index (BASELINE config 1 recipe). Every slab has its own
+    seed, so a rank generates only the rows it feeds and any rank can regenerate any row."""
+    gen = torch.Generator().manual_seed(2000 + slab)
+    hidden = torch.randn(SLAB, HIDDEN, generator=gen).half()
+    target = torch.randint(0, VOCAB, (SLAB,), generator=gen)
+    target[torch.rand(SLAB, generator=gen) < 0.1] = -100
+    return hidden, target
+
+
+def make_local_rows(rank, slabs_per_rank):
+    parts = [make_rows(rank * slabs_per_rank + i) for i in range(slabs_per_rank)]
+    return torch.cat([p[0] for p in parts]), torch.cat([p[1] for p in parts])
+
+
+def make_inputs(n_tokens):
+    """Config 1 inputs for a single process: (hidden, weight, target) of n_tokens rows."""
+    hidden, target = make_local_rows(0, -(-n_tokens // SLAB))
+    return hidden[:n_tokens].contiguous(), make_weight(), target[:n_tokens].contiguous()
 
 
 class ClockSampler:
@@ -117,6 +140,14 @@ class ClockSampler:
         self.stop.set()
         if self.thread is not None:
             self.thread.join(timeout=2)
+
+    def window_mhz(self, index):
+        """Median SM clock of the samples that fell inside timed region `index` (None if none)."""
+        if index >= len(self.windows):
+            return None
+        a, b = self.windows[index]
+        inside = [s[0] for s in self.samples if a <= s[2] <= b]
+        return statistics.median(inside) if inside else None
 
     def summary(self):
         if not self.samples:
@@ -502,7 +533,25 @@ def qlora_step_leg(dev, rank, world, steps, warmup, timed):
     for _ in range(2):
         eager()
     eager_ms = timed(eager, 5) / 5
+    dp_check = None
+    if world > 1:
+        # outside the timed regions: the all-reduced flat LoRA gradient is the mean of the ranks'
+        captured.load(batch)
+        captured.graph_fb.replay()
+        mine = captured.flat_grad.clone()
+        gathered = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(gathered, mine)
+        want = torch.stack(gathered).double().mean(0)
+        dist.all_reduce(captured.flat_grad)
+        captured.flat_grad.div_(world)
+        err = ((captured.flat_grad.double() - want).norm() / want.norm().clamp(min=1e-30)).item()
+        dp_check = {"allreduce_vs_mean_of_ranks_rel": err, "grad_norm": float(want.norm()),
+                    "ok": bool(err < 1e-6 and float(want.norm()) > 0)}
+    from claudemaxing_b200 import _lib as _soup_lib
+
+    _soup_lib.check_device_status()
     return {
+        "dp_gradient_check": dp_check,
         "metric": "QLoRA step tokens/s/GPU", "value": round(n_real / world / (ms * 1e-3), 1),
         "aggregate_tokens_per_s": round(n_real / (ms * 1e-3), 1), "ms_per_step": round(ms, 4),
         "real_tokens_per_step": n_real, "bucket_tokens_per_gpu": captured.bucket,
@@ -518,6 +567,127 @@ def qlora_step_leg(dev, rank, world, steps, warmup, timed):
 
 
 # ------------------------------------------------------------------------------------------
+LOSS_SCALE = 4096.0   # the loss is scaled as a trainer's GradScaler does: fp16 dHidden stays normal
+C5A_TOKENS = 65536
+
+
+def recorded_traffic():
+    """DRAM bytes per step of the two GEMM kernels at config 1 on one GPU, as recorded from an ncu
+    capture in the line `traffic_bytes_per_step logits=<bytes> grad=<bytes>` of
+    profiles/lmhead_c1_kernels_full.md (None when the file or the line is missing)."""
+    try:
+        with open(os.path.join(ROOT, "profiles", "lmhead_c1_kernels_full.md")) as f:
+            for line in f:
+                if line.startswith("traffic_bytes_per_step"):
+                    return {k: float(v) for k, v in (kv.split("=") for kv in line.split()[1:])}
+    except Exception:  # noqa: BLE001
+        pass
+    return None
+
+
+def head_launches(n_rows, v_local, world):
+    """Kernels of this library one head pass over n_rows x v_local launches: state init, per row
+    block and chunk (logits, row merge, gradient) plus the first chunk's rescale, status publish,
+    finish, backward scale (or rounding before the reduce-scatter); at N>1 also the merge."""
+    from claudemaxing_b200 import _lib
+
+    rb, ct1, ct = ctypes.c_int64(), ctypes.c_int64(), ctypes.c_int64()
+    _lib.lib().soup_lmhead_plan(n_rows, v_local, 0, ctypes.byref(rb), ctypes.byref(ct1), ctypes.byref(ct))
+    row_blocks = -(-n_rows // rb.value)
+    col_tiles = -(-v_local // 256)
+    chunks = 1 + -(-max(col_tiles - ct1.value, 0) // ct.value)
+    return 1 + row_blocks * (chunks * 3 + 1) + 1 + 1 + 1 + (1 if world > 1 else 0)
+
+
+class HeadJob:
+    """One workload of the fused head on this rank: `slabs` slabs of rows fed by this rank (pinned
+    host copies and device copies), the weight shard, and the step through the public API."""
+
+    def __init__(self, dev, rank, world, slabs, w_dev, bounds):
+        import torch.distributed as dist
+
+        self.dev, self.rank, self.world, self.slabs = dev, rank, world, slabs
+        self.w_dev, self.bounds = w_dev, bounds
+        hidden, target = make_local_rows(rank, slabs)
+        self.n_local = hidden.shape[0]
+        self.n_tokens = self.n_local * world
+        self.hidden_pin, self.target_pin = hidden.pin_memory(), target.pin_memory()
+        self.hidden_dev, self.target_dev = self.hidden_pin.to(dev), self.target_pin.to(dev)
+        self.dh_pin = torch.empty(self.n_local, HIDDEN, dtype=torch.float16).pin_memory()
+        labelled = (self.target_dev != -100).sum()
+        if world > 1:
+            dist.all_reduce(labelled)
+        self.n_labelled = int(labelled)
+        self.scale = torch.tensor(LOSS_SCALE, device=dev)
+
+    def step(self, h_dev, t_dev):
+        """fwd+bwd; returns (loss of the whole job, fp16 dHidden of this rank's rows at LOSS_SCALE,
+        per-row loss, per-row entropy of this rank's rows)."""
+        from claudemaxing_b200 import parallel
+        from claudemaxing_b200.lm_head_loss import GRAD_SCALE, fused_head_loss
+
+        if self.world == 1:
+            h = h_dev.detach().requires_grad_(True)
+            loss, terms = fused_head_loss(h[None], self.w_dev, None, target=t_dev[None])
+            loss.backward(self.scale)
+            return loss.detach(), h.grad, terms.token_loss[0], terms.token_entropy[0]
+        res = parallel.vocab_parallel_head_rows(h_dev, t_dev, self.w_dev, self.bounds)
+        loss = res["loss_sum"] / res["labelled"]
+        grad = res["grad"] * (LOSS_SCALE / (GRAD_SCALE * res["labelled"]))
+        return loss, grad, res["token_loss"], res["entropy"]
+
+    def parity(self, weight_h, sample_per_rank, cpu_rows=None):
+        """Per-row loss / entropy / dHidden of a sample of rows from every rank against the CPU
+        oracle (fp32 matmul + log_softmax + autograd). At N=1 `cpu_rows` makes the sample the first
+        `cpu_rows` rows (the pass the CPU baseline times anyway) and its duration is returned too."""
+        import torch.distributed as dist
+
+        from oracle.head_ce import head_ce
+
+        loss, grad, tl, en = self.step(self.hidden_dev, self.target_dev)
+        if cpu_rows:
+            idx = torch.arange(min(cpu_rows, self.n_local))
+        else:
+            k = min(sample_per_rank, self.n_local)
+            idx = torch.linspace(0, self.n_local - 1, k).round().long().unique()
+        idx_dev = idx.to(self.dev)
+        mine = torch.cat([tl[idx_dev, None].float(), en[idx_dev, None].float(),
+                          grad[idx_dev].float()], 1).contiguous()
+        everyone = mine
+        if self.world > 1:
+            everyone = torch.empty((self.world * mine.shape[0], mine.shape[1]), device=self.dev)
+            dist.all_gather_into_tensor(everyone, mine)
+        if self.rank != 0:
+            return None, None
+        got = everyone.cpu().view(self.world, idx.numel(), -1)
+        h_rows, t_rows = [], []
+        for r in range(self.world):   # regenerate the sampled rows of every rank from their seeds
+            if r == 0:
+                h_r, t_r = self.hidden_pin, self.target_pin
+            else:
+                h_r, t_r = make_local_rows(r, self.slabs)
+            h_rows.append(h_r[idx])
+            t_rows.append(t_r[idx])
+        h_s, t_s = torch.cat(h_rows), torch.cat(t_rows)
+        torch.set_num_threads(os.cpu_count() or 1)
+        t0 = time.perf_counter()
+        ref = head_ce(h_s, weight_h, t_s, denominator=self.n_labelled, grad_scale=LOSS_SCALE)
+        seconds = time.perf_counter() - t0
+        got = got.view(-1, got.shape[-1])
+        dh_scale = ref["dhidden"].abs().max().item()
+        rec = {
+            "rows": int(got.shape[0]), "ranks_sampled": self.world,
+            "max_abs_loss": float((got[:, 0] - ref["token_loss"]).abs().max()),
+            "max_abs_entropy": float((got[:, 1] - ref["entropy"]).abs().max()),
+            "dh_rel_max": float((got[:, 2:] - ref["dhidden"]).abs().max() / max(dh_scale, 1e-30)),
+            "oracle": "oracle/head_ce.py, fp32 CPU, same rows regenerated from their seeds",
+            "tolerances": {"loss": 1e-3, "entropy": 1e-3, "dh_rel_max": 1e-2},
+        }
+        rec["ok"] = bool(rec["max_abs_loss"] <= 1e-3 and rec["max_abs_entropy"] <= 1e-3
+                         and rec["dh_rel_max"] <= 1e-2 and math.isfinite(float(loss)))
+        return rec, (int(got.shape[0]), seconds)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -525,9 +695,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c1", choices=["c1", "c5a"])
+    ap.add_argument("--regions", type=int, default=5, help="timed regions of --steps steps each")
     ap.add_argument("--no-suite", action="store_true", help="skip the memory-bound kernel suite")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-step", action="store_true", help="skip the full QLoRA training step leg")
+    ap.add_argument("--no-c5a", action="store_true", help="skip the 65536-token sub-record")
     ap.add_argument("--suite-only", action="store_true",
                     help="run only the memory-bound kernel suite and print its JSON")
     ap.add_argument("--suite-rows", type=int, default=32768)
@@ -535,6 +707,7 @@ def main():
                     help="with --suite-only: up to three direct launches per case instead of graph replays")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    args.regions = max(args.regions, 1)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -545,7 +718,6 @@ def main():
     import torch.distributed as dist
 
     from claudemaxing_b200 import _lib, parallel
-    from claudemaxing_b200.lm_head_loss import GRAD_SCALE, fused_head_loss
 
     assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
     dev = torch.device("cuda", local_rank)
@@ -562,26 +734,18 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
     peak, peak_source = peaks()
 
-    n_tokens = 65536 if args.workload == "c5a" else TOKENS_PER_GPU * world
-    hidden_h, weight_h, target_h = make_inputs(n_tokens)
+    c5a_slabs = C5A_TOKENS // SLAB // world if (C5A_TOKENS // SLAB) % world == 0 else 0
+    slabs = c5a_slabs if args.workload == "c5a" else TOKENS_PER_GPU // SLAB
+    if slabs == 0:
+        raise SystemExit(f"--workload c5a needs a GPU count that divides {C5A_TOKENS // SLAB}")
+    weight_h = make_weight()
     bounds = parallel.shard_bounds(VOCAB, world)
     w_dev = weight_h[bounds[rank]:bounds[rank + 1]].to(dev)
-    hidden_pin, target_pin = hidden_h.pin_memory(), target_h.pin_memory()
-    hidden_dev, target_dev = hidden_pin.to(dev), target_pin.to(dev)
-    dh_pin = torch.empty(n_tokens, HIDDEN, dtype=torch.float16).pin_memory()
-    n_labelled = int((target_h != -100).sum())
-
-    def step(h_dev, t_dev):
-        """fwd+bwd through the public API; returns (loss, dHidden fp16)."""
-        if world == 1:
-            h = h_dev.detach().requires_grad_(True)
-            loss, _ = fused_head_loss(h[None], w_dev, None, target=t_dev[None])
-            loss.backward()
-            return loss.detach(), h.grad
-        res = parallel.vocab_parallel_head(h_dev, w_dev, t_dev, bounds)
-        loss = res["token_loss"].sum() / n_labelled
-        grad = (res["grad_raw"] * (1.0 / (GRAD_SCALE * n_labelled))).half()
-        return loss, grad
+    if rank != 0:
+        del weight_h
+        weight_h = None
+    job = HeadJob(dev, rank, world, slabs, w_dev, bounds)
+    n_tokens, n_local = job.n_tokens, job.n_local
 
     def barrier():
         if world > 1:
@@ -603,34 +767,48 @@ def main():
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return ms.item()
 
-    # ---- device-resident region (value)
-    # The clock sampler starts before the warm-up and is polled until its first sample arrives:
-    # nvidia-smi's start-up takes driver locks that stall launches, so it must be over before the
-    # timed regions begin. It keeps sampling through the value, e2e and per-kernel regions.
+    def regions_of(fn, steps, count):
+        """`count` timed regions of exactly `steps` steps: [(ms per step, median SM MHz inside)]."""
+        out = []
+        for _ in range(count):
+            ms = timed(fn, steps) / steps
+            out.append((ms, clocks.window_mhz(len(clocks.windows) - 1)))
+        return out
+
+    def summarise(regs):
+        ms = sorted(r[0] for r in regs)
+        return {"median_ms": round(statistics.median(ms), 5), "min_ms": round(ms[0], 5),
+                "regions": [{"ms_per_step": round(m, 5), "sm_mhz": c,
+                             "ms_x_ghz": None if c is None else round(m * c / 1e3, 5)} for m, c in regs]}
+
+    # ---- device-resident regions (value). The clock sampler (an NVML thread of this process)
+    # starts before the warm-up and keeps sampling through every timed region.
     clocks = ClockSampler(local_rank)
     clocks.__enter__()
     clocks.wait_first_sample()
     for _ in range(args.warmup):
-        loss, _ = step(hidden_dev, target_dev)
-    # The region of exactly K steps is measured three times and the median region is reported: on
-    # these shared hosts a region now and then contains a one-off stall of tens of milliseconds
-    # (seen with and without the clock sampler), which says nothing about the kernels.
-    regions = sorted(timed(lambda: step(hidden_dev, target_dev), args.steps) / args.steps
-                     for _ in range(3))
-    ms_per_step = regions[1]
+        loss = job.step(job.hidden_dev, job.target_dev)[0]
+    # Several regions of exactly K steps: a K-step region is tens of milliseconds, on a part whose
+    # clock moves with the power cap, and on these shared hosts a region now and then contains a
+    # one-off stall. The median region is the reported value; the minimum and each region's
+    # sampled SM clock (time x clock separates clock effects from kernel effects) are beside it.
+    value_regions = regions_of(lambda: job.step(job.hidden_dev, job.target_dev), args.steps, args.regions)
+    value_sum = summarise(value_regions)
+    ms_per_step = value_sum["median_ms"]
     value = n_tokens / (ms_per_step * 1e-3)
 
-    # ---- end-to-end region: host buffers in, loss and dHidden out, every step
+    # ---- end-to-end regions: this rank's rows from pinned host memory in, loss (host read) and
+    # this rank's dHidden rows out, every step
     def e2e_serial_step():
-        h = hidden_pin.to(dev, non_blocking=True)
-        t = target_pin.to(dev, non_blocking=True)
-        loss, grad = step(h, t)
-        dh_pin.copy_(grad.reshape(n_tokens, HIDDEN), non_blocking=True)
+        h = job.hidden_pin.to(dev, non_blocking=True)
+        t = job.target_pin.to(dev, non_blocking=True)
+        loss, grad = job.step(h, t)[:2]
+        job.dh_pin.copy_(grad.reshape(n_local, HIDDEN), non_blocking=True)
         return loss.item()
 
     for _ in range(3):
         e2e_serial_step()
-    e2e_serial_ms = sorted(timed(e2e_serial_step, args.steps) / args.steps for _ in range(3))[1]
+    e2e_serial = summarise(regions_of(e2e_serial_step, args.steps, 3))
 
     # The same with the feed a trainer's data loader gives: while a step computes, a copy stream
     # brings the next step's inputs from pinned host memory into the other of two device buffer
@@ -638,30 +816,30 @@ def main():
     # GEMMs. Every step still copies its inputs in, copies dHidden out and reads its loss on the
     # host; the one prefetch issued before a region starts is matched by one left over at its end.
     copy_stream = torch.cuda.Stream()
-    h_bufs = [torch.empty_like(hidden_dev) for _ in range(2)]
-    t_bufs = [torch.empty_like(target_dev) for _ in range(2)]
+    h_bufs = [torch.empty_like(job.hidden_dev) for _ in range(2)]
+    t_bufs = [torch.empty_like(job.target_dev) for _ in range(2)]
     ready = [torch.cuda.Event() for _ in range(2)]
     state = {"cur": 0, "grad": None}
 
     def prefetch(slot):
         with torch.cuda.stream(copy_stream):
-            h_bufs[slot].copy_(hidden_pin, non_blocking=True)
-            t_bufs[slot].copy_(target_pin, non_blocking=True)
+            h_bufs[slot].copy_(job.hidden_pin, non_blocking=True)
+            t_bufs[slot].copy_(job.target_pin, non_blocking=True)
             ready[slot].record(copy_stream)
 
     def e2e_step():
         cur = state["cur"]
-        main = torch.cuda.current_stream()
-        main.wait_event(ready[cur])
-        copy_stream.wait_stream(main)        # the other pair is free: the previous step has been enqueued
+        main_stream = torch.cuda.current_stream()
+        main_stream.wait_event(ready[cur])
+        copy_stream.wait_stream(main_stream)   # the other pair is free: the previous step has been enqueued
         prefetch(cur ^ 1)
-        loss, grad = step(h_bufs[cur], t_bufs[cur])
+        loss, grad = job.step(h_bufs[cur], t_bufs[cur])[:2]
         done = torch.cuda.Event()
-        done.record(main)
+        done.record(main_stream)
         with torch.cuda.stream(copy_stream):
             copy_stream.wait_event(done)
-            dh_pin.copy_(grad.reshape(n_tokens, HIDDEN), non_blocking=True)
-        grad.record_stream(copy_stream)      # its memory is not reused before the copy has run
+            job.dh_pin.copy_(grad.reshape(n_local, HIDDEN), non_blocking=True)
+        grad.record_stream(copy_stream)        # its memory is not reused before the copy has run
         state["grad"] = grad
         state["cur"] = cur ^ 1
         return loss.item()
@@ -669,20 +847,23 @@ def main():
     prefetch(0)
     for _ in range(3):
         e2e_step()
-    e2e_ms = sorted(timed(e2e_step, args.steps) / args.steps for _ in range(3))[1]
+    e2e = summarise(regions_of(e2e_step, args.steps, args.regions))
+    e2e_ms = e2e["median_ms"]
     copy_stream.synchronize()
-    h2d = hidden_pin.numel() * 2 + target_pin.numel() * 8
-    d2h = dh_pin.numel() * 2 + 4
+    h2d = (job.hidden_pin.numel() * 2 + job.target_pin.numel() * 8) * world
+    d2h = (job.dh_pin.numel() * 2 + 4) * world
+    del h_bufs, t_bufs
 
     # ---- per-kernel region: event-bracketed launches inside the library
     sink = (ctypes.c_float * 6)()
     _lib.lib().soup_lmhead_set_timing(ctypes.cast(sink, ctypes.c_void_p))
     barrier()
     for _ in range(args.steps):
-        step(hidden_dev, target_dev)
+        job.step(job.hidden_dev, job.target_dev)
     barrier()
     _lib.lib().soup_lmhead_set_timing(None)
     clocks.__exit__(None, None, None)
+    _lib.check_device_status()
     k_ms = [sink[i] / args.steps for i in range(3)]
     k_launch = [int(round(sink[3 + i] / args.steps)) for i in range(3)]
     v_local = bounds[rank + 1] - bounds[rank]
@@ -690,6 +871,8 @@ def main():
     tf = lambda ms: flops_gemm / (ms * 1e-3) / 1e12 if ms > 0 else 0.0  # noqa: E731
     tensor_peak = peak["bf16_tflops"]
     logits_tf, grad_tf = tf(k_ms[0]), tf(k_ms[2])
+    traffic = recorded_traffic() if (world == 1 and args.workload == "c1") else None
+    minimum_bytes = 2.0 * v_local * HIDDEN + 2.0 * n_tokens * HIDDEN + 4.0 * n_tokens * HIDDEN
     roofline = {
         "kernel": "lmhead_logits_kernel (tcgen05 GEMM + softmax-statistics epilogue)",
         "bound": "tensor", "achieved": round(logits_tf, 1), "peak": tensor_peak, "unit": "TFLOP/s",
@@ -697,54 +880,89 @@ def main():
         "frac_of_sustained": round(logits_tf / peak["bf16_tflops_sustained"], 4),
         "frac_of_nominal_2250": round(logits_tf / 2250.0, 4),
         "ms_per_launch": round(k_ms[0] / max(k_launch[0], 1), 5), "launches_per_step": k_launch[0],
-        # dram__bytes_read + dram__bytes_write of the three logits launches of a step from the ncu
-        # capture summarised in profiles/lmhead_c1_kernels_full.md (40.5 + 520.8 + 454.5 MB),
-        # averaged per launch like `ms_per_launch`; valid for the single-GPU config-1 shape only
-        "traffic": 338.6e6 if (world == 1 and args.workload == "c1") else None,
-        # W once + hidden once per launch + P written once, per launch
-        "traffic_algorithmic": round((2.0 * v_local * HIDDEN + max(k_launch[0], 1) * 2.0 * n_tokens * HIDDEN
-                                      + 2.0 * n_tokens * v_local) / max(k_launch[0], 1)),
+        # DRAM bytes (read + write) of the logits launches of one step divided by their number,
+        # from the ncu capture recorded in profiles/; config 1 on one GPU only
+        "traffic": None if not traffic else round(traffic["logits"] / max(k_launch[0], 1)),
+        "traffic_per_step": None if not traffic else {
+            "logits_kernel": traffic["logits"], "grad_kernel": traffic["grad"],
+            "both": traffic["logits"] + traffic["grad"],
+            "minimum_w_once_hidden_dh": minimum_bytes,
+            "ratio_to_minimum": round((traffic["logits"] + traffic["grad"]) / minimum_bytes, 2),
+            "note": "the probabilities of a chunk pass from the logits to the gradient kernel "
+                    "through a bf16 buffer and the gradient GEMM reads a bf16 copy of W: that "
+                    "traffic is measured here and is not part of the minimum"},
         "grad_kernel": {"achieved": round(grad_tf, 1), "frac": round(grad_tf / tensor_peak, 4),
                         "ms_per_launch": round(k_ms[2] / max(k_launch[2], 1), 5),
                         "launches_per_step": k_launch[2]},
         "row_kernel_ms_per_step": round(k_ms[1], 5),
         "fused_op": {"achieved": round(2 * flops_gemm / (ms_per_step * 1e-3) / 1e12, 1),
                      "frac": round(2 * flops_gemm / (ms_per_step * 1e-3) / 1e12 / tensor_peak, 4),
-                     "note": "4*N*H*V_local / whole step time (all kernels, launch gaps included)"},
+                     "min_region_frac": round(2 * flops_gemm / (value_sum["min_ms"] * 1e-3) / 1e12 / tensor_peak, 4),
+                     "note": "4*N*H*V_local / whole step time (all kernels, launch gaps, collectives)"},
     }
+    if world == 1:
+        launches = head_launches(n_tokens, v_local, 1)
+    else:
+        steps_plan = parallel.plan_exchange_steps(n_local, world,
+                                                  parallel.exchange_rows(n_tokens, HIDDEN, bounds))
+        launches = sum(head_launches((z - a) * world, v_local, world) for a, z in steps_plan)
 
-    rb, ct1, ct = ctypes.c_int64(), ctypes.c_int64(), ctypes.c_int64()
-    _lib.lib().soup_lmhead_plan(n_tokens, v_local, 0, ctypes.byref(rb), ctypes.byref(ct1), ctypes.byref(ct))
-    row_blocks = -(-n_tokens // rb.value)
-    col_tiles = -(-v_local // 256)
-    chunks = 1 + -(-max(col_tiles - ct1.value, 0) // ct.value)
-    # init + per row block (logits, row, grad per chunk + the first chunk's second logits launch)
-    # + finish + backward scale
-    launches = 1 + row_blocks * (chunks * 3 + 1) + 1 + 1
+    # ---- parity against the CPU oracle, outside every timed region, at every N
+    cpu = None
+    cores = os.cpu_count() or 1
+    cpu_rows = None
+    if rank == 0:
+        weight_h = weight_h.float()   # once: the oracle multiplies in fp32
+    if rank == 0 and world == 1 and not args.no_cpu and args.workload == "c1":
+        probe_rec, probe = job.parity(weight_h, 32, cpu_rows=32)
+        cpu_rows = int(max(32, min(n_local, probe[0] / probe[1] * 12.0)) // 32 * 32)
+    parity, timing = job.parity(weight_h, max(16, 128 // world), cpu_rows=cpu_rows)
+    if cpu_rows and timing:
+        cpu = {"value": round(timing[0] / timing[1], 2), "unit": "tokens/s", "cores": cores,
+               "kind": "port",
+               "sample": f"{timing[0]} of the {n_local} rows x full vocabulary, one pass, torch fp32 "
+                         "matmul + log_softmax + autograd (oracle/head_ce.py); its output is the "
+                         "reference of `parity`"}
 
-    kernels, cpu = None, None
+    # ---- BASELINE configs[4](a): the fixed 65536-token job, vocabulary-parallel over N
+    c5a = None
+    if args.workload == "c1" and not args.no_c5a and c5a_slabs:
+        del job
+        torch.cuda.empty_cache()
+        big = HeadJob(dev, rank, world, c5a_slabs, w_dev, bounds)
+        for _ in range(2):
+            big.step(big.hidden_dev, big.target_dev)
+        c5a_regions = regions_of(lambda: big.step(big.hidden_dev, big.target_dev), 5, 2)
+        c5a_sum = summarise(c5a_regions)
+        c5a_parity, _ = big.parity(weight_h, max(16, 128 // world))
+        _lib.check_device_status()
+        c5a = {"workload": f"configs[4a]: {C5A_TOKENS} tokens, vocabulary-parallel x{world}, "
+                           f"{big.n_local} rows fed by each rank", "tokens": C5A_TOKENS,
+               "steps": 5, "warmup": 2, "scaling": "strong",
+               "ms_per_step": c5a_sum["median_ms"], "min_ms_per_step": c5a_sum["min_ms"],
+               "value": round(C5A_TOKENS / (c5a_sum["median_ms"] * 1e-3), 1), "unit": "tokens/s",
+               "tflops": round(4.0 * C5A_TOKENS * HIDDEN * VOCAB / (c5a_sum["median_ms"] * 1e-3) / 1e12, 1),
+               "frac_of_measured_burst_per_gpu": round(
+                   4.0 * C5A_TOKENS * HIDDEN * VOCAB / (c5a_sum["median_ms"] * 1e-3) / 1e12 / world / tensor_peak, 4),
+               "regions": c5a_sum["regions"], "parity": c5a_parity}
+        del big
+        torch.cuda.empty_cache()
+
+    kernels = None
     if rank == 0 and world == 1:
         if not args.no_suite:
-            del hidden_dev
             kernels = kernel_suite(dev, peak["hbm_gbs"])
-            # the same kernels on 16x the rows: launch ramps amortised, data far larger than L2
+            # the same kernels on 16x and 32x the rows: launch ramps amortised, data far larger than L2
             kernels.update(kernel_suite(dev, peak["hbm_gbs"], n_rows=32768, tag="@32768rows",
                                         with_nf4=False))
+            kernels.update(kernel_suite(dev, peak["hbm_gbs"], n_rows=65536, tag="@65536rows",
+                                        with_nf4=False))
         if not args.no_cpu and kernels is not None:
-            cpu_ms = cpu_oracle_suite(os.cpu_count() or 1)
+            cpu_ms = cpu_oracle_suite(cores)
             for key, ms in cpu_ms.items():
                 if key in kernels:
                     kernels[key]["cpu_oracle_ms"] = ms
-                    kernels[key]["cpu_oracle_cores"] = os.cpu_count() or 1
-        if not args.no_cpu:
-            cores = os.cpu_count() or 1
-            w32 = weight_h.float()
-            probe = cpu_head_tokens_per_s(hidden_h, w32, target_h, 32, cores)
-            rows = int(max(32, min(TOKENS_PER_GPU, probe * 12.0)) // 32 * 32)
-            cpu_v = cpu_head_tokens_per_s(hidden_h, w32, target_h, rows, cores)
-            cpu = {"value": round(cpu_v, 2), "unit": "tokens/s", "cores": cores, "kind": "port",
-                   "sample": f"{rows} of the 2048 rows x full vocabulary, one pass, torch fp32 "
-                             "matmul + log_softmax + autograd (oracle/head_ce.py)"}
+                    kernels[key]["cpu_oracle_cores"] = cores
 
     step_leg = None
     if not args.no_step and args.workload == "c1":
@@ -756,33 +974,42 @@ def main():
         line = {
             "metric": "fused LM-head+CE fwd+bwd tokens/s", "value": round(value, 1),
             "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": round(ms_per_step, 5),
-            "regions_ms_per_step": [round(r, 5) for r in regions], "higher_is_better": True,
+            "ms_per_step": round(ms_per_step, 5), "min_ms_per_step": value_sum["min_ms"],
+            "regions": value_sum["regions"], "higher_is_better": True,
             "scaling": "strong" if args.workload == "c5a" else "weak", "vs_baseline": None,
-            "dtype": "f16", "data": "synthetic",
+            "dtype": "f16 (logits GEMM fp16 x fp16; gradient GEMM bf16 probabilities x bf16 copy of "
+                     "the weight; fp32 accumulation and statistics)",
+            "data": "synthetic",
             "config": {
                 "workload": ("configs[4a]: 65536 tokens" if args.workload == "c5a" else
                              "configs[0]: fused LM-head+CE fwd+bwd, 2048 packed tokens per GPU") +
                             f", hidden {HIDDEN}, tied fp16 head {VOCAB} x {HIDDEN}, 10% ignored",
                 "tokens": n_tokens,
                 "parallelism": "single GPU" if world == 1 else
-                               f"vocabulary-parallel x{world}: all-gather of per-row states + all-reduce of dHidden",
+                               f"vocabulary-parallel x{world}, rows fed data-parallel: per exchange "
+                               "step an all-gather of hidden rows and targets, an all-gather of "
+                               "per-row states, a reduce-scatter of fp16 dHidden",
+                "loss_scale": LOSS_SCALE,
                 "l2": "inputs larger than L2: the 467 MB head weight streams from HBM every step",
                 "tflops_per_step_algorithmic": round(4.0 * n_tokens * HIDDEN * VOCAB / 1e12, 4),
             },
             "tflops": round(4.0 * n_tokens * HIDDEN * VOCAB / (ms_per_step * 1e-3) / 1e12, 1),
             "e2e": {"value": round(n_tokens / (e2e_ms * 1e-3), 1), "unit": "tokens/s",
-                    "ms_per_step": round(e2e_ms, 5), "h2d_bytes_per_step": h2d,
-                    "d2h_bytes_per_step": d2h,
-                    "feed": "double-buffered: the next step's host->device copies and the previous "
-                            "step's dHidden device->host copy run on a copy stream beside the step",
-                    "serial_ms_per_step": round(e2e_serial_ms, 5)},
+                    "ms_per_step": round(e2e_ms, 5), "min_ms_per_step": e2e["min_ms"],
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "feed": "every rank copies only the rows it owns; double-buffered: the next "
+                            "step's host->device copies and the previous step's dHidden "
+                            "device->host copy run on a copy stream beside the step",
+                    "serial_ms_per_step": e2e_serial["median_ms"]},
             "gpu_launches": launches * args.steps,
             "gpu_launches_per_step": launches,
             "clocks": clocks.summary(),
             "roofline": roofline,
+            "parity": parity,
             "loss": round(float(loss), 6),
         }
+        if c5a is not None:
+            line["c5a"] = c5a
         if kernels is not None:
             line["kernels"] = kernels
         if cpu is not None:

@@ -7,6 +7,7 @@ kernel through the C ABI of libsoup_b200 (include/soup_b200.h); there is no Trit
 fallback and no backend dispatch. `import claudemaxing_b200 as solution` is the drop-in.
 """
 
+from ._lib import check_device_status, device_status
 from .attention import patch_qwen2_grouped_sdpa
 from .lm_head_loss import fused_head_loss, patch_fused_head_loss
 from .lora import patch_peft_lora_4bit
@@ -15,7 +16,8 @@ from .rmsnorm import patch_qwen2_rmsnorm, rmsnorm
 from .rope import patch_qwen2_rope, rope
 from .swiglu_recompute import patch_qwen2_mlp_recompute, swiglu_recompute
 
-__all__ = ["apply", "fused_head_loss", "dequantize_nf4", "rmsnorm", "rope", "swiglu_recompute"]
+__all__ = ["apply", "fused_head_loss", "dequantize_nf4", "rmsnorm", "rope", "swiglu_recompute",
+           "check_device_status", "device_status"]
 
 
 def apply():

@@ -31,6 +31,7 @@ SIGNATURES = {
     "soup_rmsnorm_bwd_noalloc": [_P, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _I, _I, _I, _I, _I, _P],
     "soup_rope": [_P, _P, _P, _P, _P, _P] + [_L] * 13 + [_I] * 6 + [_P],
     "soup_row_status": [_P, _P],
+    "soup_device_status": [_P, _I, _P],
     "soup_wait_selftest": [_L, _P, _P, _P],
     "soup_silu_mul_fwd": [_P, _P, _P, _L, _I, _I, _I, _I, _P],
     "soup_silu_mul_bwd": [_P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _P],
@@ -105,20 +106,86 @@ def ptr(t):
     return None if t is None else t.data_ptr()
 
 
+class _StreamOf(int):
+    """A cudaStream_t value that remembers which device it belongs to, so that `call` can make
+    that device current for the launch."""
+
+    device_index = None
+
+
 def stream_of(t):
-    return torch.cuda.current_stream(t.device).cuda_stream
+    """The current torch stream of `t`'s device, as the void* the C ABI takes."""
+    handle = _StreamOf(torch.cuda.current_stream(t.device).cuda_stream)
+    handle.device_index = t.device.index
+    return handle
 
 
 def require_cuda(*tensors):
+    """Every given tensor lives on one CUDA device (there is no CPU path and a launch reaches one
+    device only)."""
+    device = None
     for t in tensors:
-        if t is not None and not t.is_cuda:
+        if t is None:
+            continue
+        if not t.is_cuda:
             raise RuntimeError("libsoup_b200 ops run on CUDA tensors only (no CPU fallback)")
+        if device is None:
+            device = t.device
+        elif t.device != device:
+            raise RuntimeError(f"libsoup_b200: tensors on {device} and {t.device} in one call")
 
 
 def call(name, *args):
+    """Invokes an entry point. The launch, the library's per-device caches (SM count, status word,
+    built-in scratch) and the stream all belong to one device: the one of the tensor `stream_of`
+    was asked about, which is made current for the duration of the call when it is not already."""
     fn = getattr(lib(), name)
-    rc = fn(*args)
+    index = next((a.device_index for a in args if isinstance(a, _StreamOf)), None)
+    if index is not None and index != torch.cuda.current_device():
+        with torch.cuda.device(index):
+            rc = fn(*args)
+    else:
+        rc = fn(*args)
     if rc < 0:
         msg = lib().soup_last_error_string().decode("utf-8", "replace")
         raise RuntimeError(f"{name} failed ({rc}): {msg}")
     return rc
+
+
+_STATUS_MEANING = {
+    11: "RMSNorm forward or LM-head logits producer: a bounded wait ran out",
+    12: "RMSNorm backward or LM-head logits accumulator: a bounded wait ran out",
+    13: "RoPE or LM-head logits operand: a bounded wait ran out",
+    14: "LM-head logits epilogue: a bounded wait ran out",
+    21: "LM-head gradient producer: a bounded wait ran out",
+    22: "LM-head gradient accumulator: a bounded wait ran out",
+    23: "LM-head gradient operand: a bounded wait ran out",
+    24: "LM-head gradient epilogue: a bounded wait ran out",
+    90: "LM-head row merge: non-finite sum of exponentials",
+    99: "bounded-wait self-test",
+}
+
+
+def device_status(device=None, clear=True):
+    """The sticky status word of `device` (default: the current one): 0, or the code of the first
+    kernel since the last clear that gave up a bounded wait or met a non-finite sum. Synchronises
+    the device's current stream, so call it where the host waits for the step anyway."""
+    index = torch.cuda.current_device() if device is None else torch.device(device).index
+    word = ctypes.c_int(0)
+    with torch.cuda.device(index):
+        stream = torch.cuda.current_stream().cuda_stream
+        rc = lib().soup_device_status(ctypes.byref(word), int(bool(clear)), stream)
+    if rc < 0:
+        msg = lib().soup_last_error_string().decode("utf-8", "replace")
+        raise RuntimeError(f"soup_device_status failed ({rc}): {msg}")
+    return int(word.value)
+
+
+def check_device_status(device=None):
+    """Raises RuntimeError when a kernel on `device` reported a failure since the last check (and
+    clears the word): the outputs of the steps since then may be unwritten. Returns None."""
+    code = device_status(device, clear=True)
+    if code != 0:
+        what = _STATUS_MEANING.get(code, "unknown code")
+        raise RuntimeError(f"libsoup_b200 device status {code}: {what}; results since the last "
+                           "check are not valid")

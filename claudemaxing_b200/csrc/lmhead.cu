@@ -49,6 +49,7 @@
 #include <vector>
 
 #include "common.cuh"
+#include "rowpipe.cuh"
 #include "umma.cuh"
 
 namespace soup {
@@ -66,7 +67,9 @@ constexpr int kStages = 6;
 constexpr int kThreadsGemm = 192;  // warp 0 TMA, warp 1 MMA, warps 2-5 epilogue
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kGradScale = 1024.0f;  // as GRAD_SCALE of the reference
-constexpr float kRebase = 60.0f;       // rebase dH when the multiplier would exceed e^60
+constexpr float kRebase = 30.0f;       // rebase dH when the multiplier would exceed e^30
+constexpr float kHot = 30.0f;          // a tile whose maximum is this far above the running lse is
+                                       // written against its own maximum instead (see is_hot)
 constexpr int kIgnore = -100;
 constexpr int kEW = 16;                // accumulator columns per tcgen05.ld in the epilogues
 
@@ -75,11 +78,25 @@ constexpr int kStageT = 4 * 32 * 33 * 4;       // gradient: per epilogue warp a 
 constexpr int kSmemLogits = kStages * kStageBytes + kStageP + 1024 + 256;
 constexpr int kSmemGrad = kStages * kStageBytes + kStageT + 1024 + 256;
 
+// Waits until all of this thread's bulk stores have completed (written, not only read).
+__device__ __forceinline__ void tma_store_wait_done() {
+  asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+}
+
 enum LogitsMode {
   kModeTileMax = 0,  // statistics (and P, when wanted) against the tile maximum: the first chunk
   kModePOnly = 1,    // P against ref, no statistics (kept for callers that recompute a chunk)
   kModeCombined = 2  // statistics and P against ref (all later chunks)
 };
+
+// Later chunks exponentiate against `ref`, the row's log-sum-exp over the earlier chunks. A tile
+// whose maximum lies more than kHot above it ("hot": a logit far larger than anything the row has
+// seen, legal for fp16 inputs) would overflow exp(z - ref); such a (row, tile) is written against
+// the tile's own maximum instead. The logits epilogue and the row kernel both decide with this one
+// predicate on the same two stored fp32 values, so they always agree.
+__device__ __forceinline__ bool is_hot(float tile_max, float ref) {
+  return tile_max > __fadd_rn(ref, kHot);
+}
 
 struct PipeState {
   int stage = 0;
@@ -525,6 +542,25 @@ lmhead_logits_kernel(const __grid_constant__ CUtensorMap map_h,
         else
           tile_ref_pass<false, true>(taddr, n_valid, label_local, ref, keep_mask, a.store_p != 0,
                                      &map_p, stage_warp, tc * kBN, p_row0, m, sum, dot, lab, arg);
+        // Rare: some row of this warp met a logit far above its running lse. The pass is repeated
+        // (tcgen05.ld is warp-wide) with the hot rows exponentiated against their tile maximum;
+        // the other rows get the values they had. The first pass's stores must have landed
+        // before the same boxes are stored again. The row kernel sees the same predicate and
+        // brings the row's tiles to one reference.
+        const bool hot = row_ok && is_hot(m, ref);
+        if (__any_sync(0xffffffffu, hot)) {
+          if (a.store_p) {
+            if (lane == 0) tma_store_wait_done();
+            __syncwarp();
+          }
+          const float rho = hot ? m : ref;
+          if (full)
+            tile_ref_pass<true, true>(taddr, n_valid, label_local, rho, keep_mask, a.store_p != 0,
+                                      &map_p, stage_warp, tc * kBN, p_row0, m, sum, dot, lab, arg);
+          else
+            tile_ref_pass<false, true>(taddr, n_valid, label_local, rho, keep_mask, a.store_p != 0,
+                                       &map_p, stage_warp, tc * kBN, p_row0, m, sum, dot, lab, arg);
+        }
       } else {
         if (full)
           tile_ref_pass<true, false>(taddr, n_valid, label_local, ref, keep_mask, true, &map_p,
@@ -561,6 +597,8 @@ struct RowArgs {
   float* base;      // [n_rows] lse that dH is relative to (set by the first chunk)
   float* mult;      // [n_rows] out: exp(ref - base) for the gradient kernel of this chunk
   float* dh;        // nullable: [n_rows, k_dim], touched only when a row is rebased
+  __nv_bfloat16* p; // nullable: the chunk's probabilities [n_rows, ld_p], touched only for hot rows
+  int ld_p;
   int n_rows;
   int k_dim;
   int ct;
@@ -579,6 +617,7 @@ __global__ void __launch_bounds__(256) lmhead_row_kernel(const RowArgs a) {
   int best = a.best[row];
   float best_val = a.mode == kModeTileMax ? -INFINITY : a.best_val[row];
   float new_lse, new_dot;
+  bool hot_row = false;
   if (a.mode == kModeTileMax) {
     // statistics relative to each tile's own maximum: log-sum-exp merge
     float run_max = -INFINITY, run_sum = 0.f;
@@ -625,12 +664,60 @@ __global__ void __launch_bounds__(256) lmhead_row_kernel(const RowArgs a) {
     const float total = 1.0f + add_sum;
     new_lse = ref + logf(total);
     new_dot = (run_dot + add_dot) / total;
-    if (!(total < INFINITY) && lane == 0) atomicCAS(a.status, 0, 90);  // exp(z - ref) overflowed
+    // Hot tiles (is_hot: written against their own maximum, not against ref) make the sums above
+    // meaningless for this row; best_val is then the largest of them. Redo the merge with every
+    // tile's own reference, relative to rho = best_val.
+    hot_row = is_hot(best_val, ref);
+    if (hot_row) {
+      const float rho = best_val;
+      const float w_ref = exp2f((ref - rho) * kLog2e);   // < e^-30
+      float sum = 0.f, dot = 0.f;
+      for (int t0 = 0; t0 < a.ct; t0 += 32) {
+        const int t = t0 + lane;
+        float4 st = make_float4(-INFINITY, 0.f, 0.f, 0.f);
+        if (t < a.ct) st = a.tile_stats[(size_t)row * a.ct_stride + t];
+        const float w = t < a.ct ? (is_hot(st.x, ref) ? exp2f((st.x - rho) * kLog2e) : w_ref) : 0.f;
+        sum += warp_sum(st.y * w);
+        dot += warp_sum(st.z * w);
+      }
+      const float total_hot = w_ref + sum;
+      new_lse = rho + logf(total_hot);
+      new_dot = (run_dot * w_ref + dot) / total_hot;
+    } else if (!(total < INFINITY) && lane == 0) {
+      atomicCAS(a.status, 0, 90);  // cannot happen: every non-hot tile sum is below 256 e^30
+    }
   }
   float mult = 1.0f;
   if (a.want_grad) {
     if (a.mode == kModeTileMax) {
       if (lane == 0) a.base[row] = new_lse;   // the first chunk's P is written against this lse
+    } else if (hot_row) {
+      // The chunk's P of this row mixes references (ref for ordinary tiles, the tile maximum for
+      // hot ones). Bring all of it to rho = best_val, move dH of the row to the same reference and
+      // let the gradient kernel add the chunk with multiplier 1. Everything that was relative to
+      // ref shrinks by more than e^-30.
+      const float rho = best_val;
+      const float w_ref = exp2f((ref - rho) * kLog2e);
+      uint4* prow = reinterpret_cast<uint4*>(a.p + (size_t)row * a.ld_p);
+      for (int t = 0; t < a.ct; ++t) {
+        const float tm = a.tile_stats[(size_t)row * a.ct_stride + t].x;
+        const float f = is_hot(tm, ref) ? exp2f((tm - rho) * kLog2e) : w_ref;
+        if (f == 1.0f) continue;
+        uint4 v = prow[t * (kBN / 8) + lane];
+        uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float2 e = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[k]));
+          __nv_bfloat162 h = __floats2bfloat162_rn(e.x * f, e.y * f);
+          w[k] = *reinterpret_cast<uint32_t*>(&h);
+        }
+        prow[t * (kBN / 8) + lane] = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+      const float down = expf(a.base[row] - rho);
+      for (int i = lane; i < a.k_dim; i += 32) a.dh[(size_t)row * a.k_dim + i] *= down;
+      __syncwarp();
+      if (lane == 0) a.base[row] = rho;
+      mult = 1.0f;
     } else {
       float base = a.base[row];
       if (ref - base > kRebase) {
@@ -931,6 +1018,13 @@ __global__ void lmhead_scale_cast_kernel(const float* __restrict__ dh, void* __r
     for (int64_t i = n8 << 3; i < n; ++i) store1(out, i, odt, dh[i] * scale);
 }
 
+// Copies a non-zero status of the call into the device's sticky status word (read and cleared by
+// soup_device_status), so that a failure outlives the call's workspace.
+__global__ void lmhead_publish_status_kernel(const int* call_status, int* sticky) {
+  const int code = *call_status;
+  if (code != 0) atomicCAS(sticky, 0, code);
+}
+
 inline int64_t round_up(int64_t v, int64_t m) { return (v + m - 1) / m * m; }
 
 // K splits per gradient tile that minimise the makespan of `tiles` output tiles on `pairs` CTA
@@ -1207,6 +1301,8 @@ extern "C" int soup_lmhead_ce(const void* hidden, const void* weight, const void
       ra.base = grad_ref + r0;
       ra.mult = ws.mult;
       ra.dh = want_grad ? dh + r0 * h : nullptr;
+      ra.p = want_grad ? ws.p_buf : nullptr;
+      ra.ld_p = ld_p;
       ra.n_rows = rows;
       ra.k_dim = (int)h;
       ra.ct = ct;
@@ -1246,6 +1342,10 @@ extern "C" int soup_lmhead_ce(const void* hidden, const void* weight, const void
       }
       t0 += ct;
     }
+  }
+  if (int* sticky = rowpipe::status_word()) {
+    lmhead_publish_status_kernel<<<1, 1, 0, s>>>(ws.status, sticky);
+    SOUP_CHECK_LAUNCH("lmhead_publish_status");
   }
   timer.finish();
   return SOUP_OK;

@@ -56,7 +56,7 @@ __device__ int g_selftest[2] = {0, 0};   // [0] status code, [1] 1 when the wait
 
 // A barrier that nothing ever completes: every thread's bounded wait has to run out, record its
 // code and return, leaving the context healthy.
-__global__ void wait_selftest_kernel(int* words, uint64_t limit_ns) {
+__global__ void wait_selftest_kernel(int* words, uint64_t limit_ns, int* sticky) {
   __shared__ uint64_t bar;
   __shared__ int abort_flag;
   if (threadIdx.x == 0) {
@@ -66,7 +66,10 @@ __global__ void wait_selftest_kernel(int* words, uint64_t limit_ns) {
   umma::fence_barrier_init();
   __syncthreads();
   const bool ok = umma::mbar_wait_for(&bar, 0, &abort_flag, &words[0], 99, limit_ns);
-  if (!ok && threadIdx.x == 0) words[1] = 1;
+  if (!ok && threadIdx.x == 0) {
+    words[1] = 1;
+    if (sticky) atomicCAS(sticky, 0, words[0]);   // as the real kernels publish a wait that gave up
+  }
 }
 }  // namespace
 }  // namespace soup
@@ -83,7 +86,8 @@ extern "C" int soup_wait_selftest(int64_t limit_ns, int* host_gave_up, int* host
   int out[2] = {0, 0};
   if (cudaMemsetAsync(words, 0, sizeof(out), s) != cudaSuccess)
     SOUP_FAIL(SOUP_ERR_LAUNCH, "wait_selftest: %s", cudaGetErrorString(cudaGetLastError()));
-  wait_selftest_kernel<<<1, 64, 0, s>>>(reinterpret_cast<int*>(words), (uint64_t)limit_ns);
+  wait_selftest_kernel<<<1, 64, 0, s>>>(reinterpret_cast<int*>(words), (uint64_t)limit_ns,
+                                        rowpipe::status_word());
   SOUP_CHECK_LAUNCH("wait_selftest");
   if (cudaMemcpyAsync(out, words, sizeof(out), cudaMemcpyDeviceToHost, s) != cudaSuccess ||
       cudaStreamSynchronize(s) != cudaSuccess)
@@ -105,6 +109,19 @@ extern "C" int soup_row_status(int* host_status, void* stream) {
   return SOUP_OK;
 }
 
-extern "C" int soup_version(void) { return 1; }
+extern "C" int soup_device_status(int* host_status, int clear, void* stream) {
+  using namespace soup;
+  if (!host_status) SOUP_FAIL(SOUP_ERR_ARG, "device_status: null pointer");
+  int* word = rowpipe::status_word();
+  if (!word) SOUP_FAIL(SOUP_ERR_DEVICE, "device_status: no status word on this device");
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (cudaMemcpyAsync(host_status, word, sizeof(int), cudaMemcpyDeviceToHost, s) != cudaSuccess ||
+      (clear && cudaMemsetAsync(word, 0, sizeof(int), s) != cudaSuccess) ||
+      cudaStreamSynchronize(s) != cudaSuccess)
+    SOUP_FAIL(SOUP_ERR_LAUNCH, "device_status: %s", cudaGetErrorString(cudaGetLastError()));
+  return SOUP_OK;
+}
+
+extern "C" int soup_version(void) { return 2; }
 
 extern "C" const char* soup_last_error_string(void) { return soup::g_error; }

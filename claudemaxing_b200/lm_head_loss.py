@@ -246,12 +246,14 @@ def fused_head_loss(hidden, weight, labels, num_items_in_batch=None, chunk_cols=
 
 
 @torch.no_grad()
-def head_metrics_from_logits(logits, labels):
+def head_metrics_from_logits(logits, labels, target=None):
     """StepTerms from logits that exist anyway (the route the reference keeps for steps that end
-    up building them, solution/lm_head_loss.py:285-297): one warp per row over the full logits."""
+    up building them, solution/lm_head_loss.py:285-297): one warp per row over the full logits.
+    `target` (labels already shifted) replaces `labels` when given."""
     rows = logits.reshape(-1, logits.shape[-1]).contiguous()
     _lib.require_cuda(rows)
-    scored = shift_labels_left(labels).to(rows.device).reshape(-1).to(torch.int64).contiguous()
+    scored = shift_labels_left(labels) if target is None else target
+    scored = scored.to(rows.device).reshape(-1).to(torch.int64).contiguous()
     n = rows.shape[0]
     per_token = torch.empty(n, dtype=torch.float32, device=rows.device)
     entropy = torch.empty(n, dtype=torch.float32, device=rows.device)

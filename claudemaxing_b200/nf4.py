@@ -38,9 +38,9 @@ def _supported(packed, state, dtype):
 
 
 def _offset_tensor(offset, device):
-    if isinstance(offset, torch.Tensor):
-        return offset.to(device=device, dtype=torch.float32).reshape(1)
-    return torch.tensor([float(offset)], dtype=torch.float32, device=device)
+    """The offset of the nested statistics as a one-element fp32 tensor on `device` (bitsandbytes
+    keeps a 0-d tensor; a Python number is accepted too). No host round trip for a tensor."""
+    return torch.as_tensor(offset, dtype=torch.float32, device=device).reshape(1)
 
 
 def dequantize_nf4(packed, state, dtype=None, out=None):
@@ -107,7 +107,7 @@ def dequantize_nf4_batch(weights, dtype=None, outs=None):
     return results
 
 
-ORIGINALS = {}
+ORIGINALS = {}    # "fallback" / "dequant": bitsandbytes' own functions, kept for everything we leave alone
 _CODE = {}
 
 
@@ -120,53 +120,79 @@ def _nf4_code(device):
     return _CODE[device]
 
 
+# Why a gemm_4bit fallback call stays with bitsandbytes: (reason, predicate over the call's
+# arguments). The first that holds wins; `explain_fallback_route` returns its reason.
+_FALLBACK_RULES = (
+    ("not nf4", lambda a: a["quant_type"] != "nf4"),
+    ("activation dtype other than fp16/fp32", lambda a: a["A"].dtype not in (torch.float16, torch.float32)),
+    ("activation not on a CUDA device", lambda a: not a["A"].is_cuda),
+    ("nested statistics incomplete",
+     lambda a: a["absmax_8bit"] is not None and (a["absmax_code"] is None or a["absmax_offset"] is None)),
+)
+
+
+def explain_fallback_route(**call):
+    """"" when `_dequant_linear_fallback(**call)` can use this package's kernel, else the reason."""
+    for reason, holds in _FALLBACK_RULES:
+        if holds(call):
+            return reason
+    return ""
+
+
+def _state_of_call(state_cls, call, code):
+    """The QuantState a gemm_4bit fallback call describes. bitsandbytes hands the pieces over
+    separately; with double quantisation `absmax` is the inner (fp32, per 256 blocks) statistic and
+    `absmax_8bit` the per-block codes."""
+    common = dict(shape=torch.Size(call["shapeB"]), code=code, blocksize=call["blocksize"],
+                  quant_type="nf4", dtype=call["A"].dtype)
+    if call["absmax_8bit"] is None:
+        return state_cls(absmax=call["absmax"], **common)
+    inner = state_cls(absmax=call["absmax"], code=call["absmax_code"], blocksize=256,
+                      dtype=torch.float32)
+    return state_cls(absmax=call["absmax_8bit"], offset=call["absmax_offset"], state2=inner, **common)
+
+
 def patch_bnb_nf4_dequant():
-    """Route bitsandbytes' NF4 dequantisation (the dequant + F.linear path of gemm_4bit and
-    functional.dequantize_4bit) through `dequantize_nf4`. fp4, bf16, CPU tensors or an `out=`
-    buffer keep bitsandbytes' own code. Without bitsandbytes there is nothing to patch
-    (the reference's patch raises there, solution/nf4.py:94-96)."""
+    """Routes the two places where bitsandbytes dequantises an NF4 weight through
+    `dequantize_nf4`: the dequant + F.linear fallback of gemm_4bit (forward of Linear4bit for more
+    than one row) and functional.dequantize_4bit (the input gradient of MatMul4Bit.backward).
+    Everything the kernel does not cover (fp4, bf16, CPU tensors, an `out=` buffer, layouts
+    `_supported` refuses) is handed to bitsandbytes' own function unchanged. Idempotent; without
+    bitsandbytes there is nothing to patch and the call returns (the reference's patch raises
+    there, solution/nf4.py:94-96)."""
     if ORIGINALS:
         return
     try:
         import bitsandbytes.functional as bnbF
         from bitsandbytes.backends.cuda import ops as cuda_ops
-        from bitsandbytes.functional import QuantState
     except Exception:  # noqa: BLE001
         return
-    original_fallback = cuda_ops._dequant_linear_fallback
-    original_dequant = bnbF.dequantize_4bit
-    ORIGINALS.update(fallback=original_fallback, dequant=original_dequant)
+    state_cls = bnbF.QuantState
+    theirs_linear, theirs_dequant = cuda_ops._dequant_linear_fallback, bnbF.dequantize_4bit
+    ORIGINALS.update(fallback=theirs_linear, dequant=theirs_dequant)
 
     def _dequant_linear_fallback(A, B, shapeB, absmax, blocksize, quant_type, bias=None,
                                  absmax_8bit=None, absmax_code=None, absmax_offset=None):
-        def keep():
-            return original_fallback(A, B, shapeB, absmax, blocksize, quant_type, bias,
-                                     absmax_8bit=absmax_8bit, absmax_code=absmax_code,
-                                     absmax_offset=absmax_offset)
-
-        if (quant_type != "nf4" or A.dtype not in (torch.float16, torch.float32) or not A.is_cuda
-                or (absmax_8bit is not None and (absmax_code is None or absmax_offset is None))):
-            return keep()
-        code = _nf4_code(A.device)
-        if absmax_8bit is not None:  # `absmax` is then the nested state's absmax
-            inner = QuantState(absmax=absmax, code=absmax_code, blocksize=256, dtype=torch.float32)
-            state = QuantState(absmax=absmax_8bit, shape=torch.Size(shapeB), code=code,
-                               blocksize=blocksize, quant_type="nf4", dtype=A.dtype,
-                               offset=absmax_offset, state2=inner)
-        else:
-            state = QuantState(absmax=absmax, shape=torch.Size(shapeB), code=code,
-                               blocksize=blocksize, quant_type="nf4", dtype=A.dtype)
-        if not _supported(B, state, A.dtype):
-            return keep()
+        call = dict(A=A, B=B, shapeB=shapeB, absmax=absmax, blocksize=blocksize,
+                    quant_type=quant_type, absmax_8bit=absmax_8bit, absmax_code=absmax_code,
+                    absmax_offset=absmax_offset)
+        state = None
+        if not explain_fallback_route(**call):
+            state = _state_of_call(state_cls, call, _nf4_code(A.device))
+        if state is None or not _supported(B, state, A.dtype):
+            return theirs_linear(A, B, shapeB, absmax, blocksize, quant_type, bias,
+                                 absmax_8bit=absmax_8bit, absmax_code=absmax_code,
+                                 absmax_offset=absmax_offset)
         return torch.nn.functional.linear(A, dequantize_nf4(B, state, A.dtype), bias)
 
     def dequantize_4bit(A, quant_state=None, absmax=None, out=None, blocksize=None,
                         quant_type="fp4"):
-        if out is None and quant_state is not None and _supported(A, quant_state,
-                                                                    quant_state.dtype):
-            weight = dequantize_nf4(A, quant_state)
-            return weight.t() if A.shape[0] == 1 else weight  # bitsandbytes' [1, X] packed layout
-        return original_dequant(A, quant_state, absmax, out, blocksize, quant_type)
+        ours = out is None and quant_state is not None and _supported(A, quant_state, quant_state.dtype)
+        if not ours:
+            return theirs_dequant(A, quant_state, absmax, out, blocksize, quant_type)
+        weight = dequantize_nf4(A, quant_state)
+        # a weight packed as one row [1, X] is stored transposed by bitsandbytes
+        return weight.t() if A.shape[0] == 1 else weight
 
     cuda_ops._dequant_linear_fallback = _dequant_linear_fallback
     bnbF.dequantize_4bit = dequantize_4bit

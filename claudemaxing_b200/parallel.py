@@ -155,6 +155,116 @@ def vocab_parallel_head(h16, w_shard, target, bounds, group=None, want_grad=True
     return dict(token_loss=token_loss, entropy=entropy, correct=correct, grad_raw=grad_raw)
 
 
+def plan_exchange_steps(n_local, world, block_rows):
+    """[(begin, end)] ranges of a rank's local rows, one per exchange step. A step gathers the
+    same range from every rank (world * (end - begin) rows, at most `block_rows`, the kernels'
+    row block) and the steps are of equal size up to rounding to 8 rows, so that no step is a
+    sliver whose launches run the GPU half empty."""
+    if n_local <= 0:
+        return []
+    per_rank = max(8, block_rows // world)
+    steps = -(-n_local // per_rank)
+    size = -(-n_local // steps)
+    size = -(-size // 8) * 8
+    return [(a, min(n_local, a + size)) for a in range(0, n_local, size)]
+
+
+_ONE = {}
+
+
+def _one(device):
+    if device not in _ONE:
+        _ONE[device] = torch.ones(1, dtype=torch.float32, device=device)
+    return _ONE[device]
+
+
+def _rounded(grad_raw, dtype):
+    """`grad_raw` (fp32, at GRAD_SCALE) rounded to `dtype` in a new tensor, one pass."""
+    low = torch.empty(grad_raw.shape, dtype=dtype, device=grad_raw.device)
+    _lib.call("soup_lmhead_grad_scale", _lib.ptr(grad_raw), _lib.ptr(low),
+              _lib.ptr(_one(grad_raw.device)), grad_raw.numel(), _lib.dtype_code(dtype),
+              _lib.stream_of(grad_raw))
+    return low
+
+
+def vocab_parallel_head_rows(h_local, target_local, w_shard, bounds, group=None, want_grad=True,
+                             chunk_cols=None, w_bf16=None, grad_dtype=torch.float16):
+    """The vocabulary-parallel head for a data-parallel upstream: every rank brings its own rows
+    (the same number on every rank), and gets back the terms and the hidden-state gradient of
+    exactly those rows. Nothing of full size is replicated or all-reduced.
+
+    Per exchange step (`plan_exchange_steps`): the ranks' row ranges are all-gathered over NVLink
+    (hidden fp16 and targets), each rank runs `head_partial` over the gathered rows on its
+    vocabulary shard, the per-row states are all-gathered and merged, `head_finish` rescales the
+    rank's gradient to the global log-sum-exp, and the gradient, rounded to `grad_dtype` at
+    GRAD_SCALE (values of order 1: fp16 keeps 11 bits of each partial), is reduce-scattered so
+    that every rank receives the sum for its own rows. The gather of step s+1 and the
+    reduce-scatter of step s run beside the GEMMs of the neighbouring steps; what stays exposed is
+    the first gather and the last reduce-scatter (rows x hidden x 2 bytes each).
+
+    Returns dict(token_loss, entropy, correct: [n_local] for this rank's rows; grad: `grad_dtype`
+    [n_local, hidden] at GRAD_SCALE, summed over the ranks, or None; loss_sum, labelled, hits:
+    0-d tensors over the rows of ALL ranks, identical on every rank, no further collective)."""
+    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    if len(bounds) != world + 1 or w_shard.shape[0] != bounds[rank + 1] - bounds[rank]:
+        raise ValueError(f"rank {rank}: w_shard has {w_shard.shape[0]} rows, the bounds {list(bounds)} "
+                         "give this rank another range")
+    n_local, hidden = h_local.shape
+    dev = h_local.device
+    h_local = h_local.contiguous()
+    target_local = target_local.contiguous().to(torch.int64)
+    block = exchange_rows(n_local * world, hidden, bounds, chunk_cols)
+    steps = plan_exchange_steps(n_local, world, block)
+    f32 = torch.float32
+    token_loss = torch.empty(n_local, dtype=f32, device=dev)
+    entropy = torch.empty(n_local, dtype=f32, device=dev)
+    correct = torch.empty(n_local, dtype=torch.int32, device=dev)
+    grad = torch.empty((n_local, hidden), dtype=grad_dtype, device=dev) if want_grad else None
+    loss_sum = torch.zeros((), dtype=f32, device=dev)
+    labelled = torch.zeros((), dtype=torch.int64, device=dev)
+    hits = torch.zeros((), dtype=torch.int64, device=dev)
+
+    def gather(step):
+        a, z = steps[step]
+        hg = torch.empty((world * (z - a), hidden), dtype=h_local.dtype, device=dev)
+        tg = torch.empty(world * (z - a), dtype=torch.int64, device=dev)
+        works = (dist.all_gather_into_tensor(hg, h_local[a:z], group=group, async_op=True),
+                 dist.all_gather_into_tensor(tg, target_local[a:z], group=group, async_op=True))
+        return hg, tg, works
+
+    pending, keep = [], []
+    raw = None
+    nxt = gather(0) if steps else None
+    for step, (a, z) in enumerate(steps):
+        hg, tg, works = nxt
+        for work in works:
+            work.wait()
+        nxt = gather(step + 1) if step + 1 < len(steps) else None   # travels beside this step's GEMMs
+        rows = z - a
+        if want_grad and (raw is None or raw.shape[0] != world * rows):
+            raw = torch.empty((world * rows, hidden), dtype=f32, device=dev)
+        state, grad_raw = head_partial(hg, w_shard, tg, bounds[rank], chunk_cols, want_grad, w_bf16,
+                                       raw if want_grad else None)
+        mine = pack_state(state)
+        gathered = torch.empty((world * mine.shape[0], mine.shape[1]), dtype=mine.dtype, device=dev)
+        dist.all_gather_into_tensor(gathered, mine, group=group)
+        merged, _ = merge_states(gathered.view(world, *mine.shape), tg, bounds)
+        tl, en, co = head_finish(merged, tg, w_shard, grad_raw, bounds[rank], grad_ref=state.grad_ref)
+        own = slice(rank * rows, (rank + 1) * rows)
+        token_loss[a:z], entropy[a:z], correct[a:z] = tl[own], en[own], co[own]
+        loss_sum += tl.sum()
+        labelled += tg.ne(-100).sum()
+        hits += co.sum()
+        if want_grad:
+            low = _rounded(grad_raw, grad_dtype)
+            pending.append(dist.reduce_scatter_tensor(grad[a:z], low, group=group, async_op=True))
+            keep.append(low)
+    for work in pending:
+        work.wait()
+    return dict(token_loss=token_loss, entropy=entropy, correct=correct, grad=grad,
+                loss_sum=loss_sum, labelled=labelled, hits=hits)
+
+
 def emulate_vocab_parallel(h16, w, target, n_shards, chunk_cols=None):
     """The same data flow as `vocab_parallel_head` with every rank's shard processed on this GPU
     in turn (no collective): for tests on a single device."""

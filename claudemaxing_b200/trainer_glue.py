@@ -101,6 +101,24 @@ def _unpacked(values, packed):
     return full.view(packed.B, packed.T)
 
 
+def _packed_logits_loss(lm, hidden, target, num_items_in_batch=None):
+    """The packed row's loss and per-token terms through the logits, for a step whose head does
+    not compute in float16 (bf16 autocast, an fp32 model without autocast): the tensor-core head
+    kernel takes fp16 operands only, and the reference's packed route accepts every compute dtype
+    (solution/lm_head_loss.py:339-362), so such a step keeps the packing and builds the logits of
+    the real tokens only. Sum of the per-token cross-entropies over `num_items_in_batch` (default:
+    the labelled tokens), as ForCausalLMLoss divides."""
+    logits = lm.lm_head(hidden)
+    flat = target.reshape(-1).to(logits.device)
+    total = torch.nn.functional.cross_entropy(logits.reshape(-1, logits.shape[-1]).float(), flat,
+                                              ignore_index=head.IGNORE_INDEX, reduction="sum")
+    divisor = flat.ne(head.IGNORE_INDEX).sum() if num_items_in_batch is None else num_items_in_batch
+    if torch.is_tensor(divisor):
+        divisor = divisor.to(total.device)
+    terms = head.head_metrics_from_logits(logits.detach(), None, target=target)
+    return total / divisor, terms
+
+
 def _packed_forward(lm, kwargs, packed):
     """Decoder on the packed row, fused head on its hidden states; the per-token terms return to
     the padded layout (every consumer masks the padding out). `packed` needs the attributes of
@@ -112,9 +130,14 @@ def _packed_forward(lm, kwargs, packed):
         passthrough.pop(replaced, None)
     decoded = lm.model(input_ids=packed.ids, attention_mask=packed.mask, position_ids=packed.pos,
                        **passthrough)
-    loss, terms = head.fused_head_loss(decoded.last_hidden_state, lm.lm_head.weight, None,
-                                       num_items_in_batch=kwargs.get("num_items_in_batch"),
-                                       target=packed.target)
+    hidden, weight = decoded.last_hidden_state, lm.lm_head.weight
+    if head.head_compute_dtype(hidden, weight) == torch.float16:
+        loss, terms = head.fused_head_loss(hidden, weight, None,
+                                           num_items_in_batch=kwargs.get("num_items_in_batch"),
+                                           target=packed.target)
+    else:
+        loss, terms = _packed_logits_loss(lm, hidden, packed.target,
+                                          kwargs.get("num_items_in_batch"))
     lm.__dict__[head._STEP_ATTR] = StepTerms(_unpacked(terms.token_loss, packed),
                                              _unpacked(terms.token_entropy, packed),
                                              terms.correct, terms.labelled)
@@ -248,6 +271,12 @@ def _log_trl_metrics(trainer, mode, inputs, terms):
 
     hits, scored = across_ranks(terms.correct).sum(), across_ranks(terms.labelled).sum()
     store["mean_token_accuracy"].append((hits / scored).item() if scored > 0 else 0.0)
+    # the host has just waited for this step's numbers: the one place a kernel that gave up a
+    # bounded wait (its outputs are then unwritten) is turned into an exception, per step
+    if terms.token_entropy.is_cuda:
+        from . import _lib
+
+        _lib.check_device_status(terms.token_entropy.device)
 
 
 @dataclasses.dataclass

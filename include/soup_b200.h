@@ -11,9 +11,18 @@
  *  - Return value: 0 = enqueued; negative = SOUP_ERR_*; the message is in soup_last_error_string()
  *    (thread local). Nothing aborts or traps.
  *  - dtype codes: SOUP_F32, SOUP_F16, SOUP_BF16.
- *  - All entries are re-entrant: no global scratch, so autograd worker threads may call them
- *    concurrently on different streams. The one exception is soup_rmsnorm_bwd_noalloc, which
- *    says so in its own comment.
+ *  - The compute entries keep no state between calls and use no scratch of their own, so autograd
+ *    worker threads may call them concurrently on different streams. Exceptions, each said again
+ *    in its own comment: soup_rmsnorm_bwd_noalloc (built-in workspace, calls must not overlap);
+ *    soup_lmhead_set_timing (a benchmark aid, off by default, that installs a process-wide host
+ *    pointer which every soup_lmhead_ce then writes to and synchronises on: never set it while
+ *    other threads call the library); the sticky per-device status word behind
+ *    soup_device_status (written with atomics, safe from any number of calls). soup_lmhead_ce
+ *    reads the environment (SOUP_LMHEAD_WAVES, SOUP_LMHEAD_DETERMINISTIC) on every call.
+ *  - Accumulation order: soup_lmhead_ce splits the vocabulary dimension of the gradient GEMM
+ *    across CTA pairs that add into dH with atomics, so dH can differ in the last fp32 bits from
+ *    run to run; SOUP_LMHEAD_DETERMINISTIC=1 switches the split off (one adder per element, fixed
+ *    order). The RMSNorm dw reduction is always in a fixed order.
  */
 #ifndef SOUP_B200_H
 #define SOUP_B200_H
@@ -42,6 +51,15 @@ const char* soup_last_error_string(void);
  * word is sticky. Synchronises `stream`. No counterpart in the reference (its Triton kernels have
  * no waits). */
 int soup_row_status(int* host_status, void* stream);
+/* The same sticky word, for every kernel family: besides the row-kernel codes it receives the
+ * code of a soup_lmhead_ce call whose bounded waits gave up (11-14 logits kernel, 21-24 gradient
+ * kernel: producer, accumulator, operand and epilogue waits) or whose row merge met a non-finite
+ * sum (90), copied from the call's workspace by the call's last launch, and 99 from
+ * soup_wait_selftest. `clear` != 0 resets the word after reading it. Synchronises `stream`; meant
+ * to be called where the host waits for the step's loss anyway. A non-zero word means outputs
+ * since the last clear may be unwritten. No counterpart in the reference (its kernels cannot
+ * time out; its failures are Python exceptions). */
+int soup_device_status(int* host_status, int clear, void* stream);
 /* Self-test of the bounded waits every kernel of the library uses: launches one small CTA that
  * waits, with a limit of `limit_ns` (at most 100 ms), on a barrier nothing ever completes. The
  * wait has to run out: *host_gave_up becomes 1 and *host_status the code 99, and the context stays

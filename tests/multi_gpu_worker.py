@@ -2,7 +2,8 @@
 torch.distributed.run, one process per GPU, NCCL):
 
   * vocabulary-parallel fused head against the single-GPU fused head on the full weight and
-    against the oracle on a sample of rows;
+    against the oracle on a sample of rows, once within one exchange block and once over several;
+  * the row-sharded variant (every rank feeds its own rows; fp16 reduce-scatter) against the oracle;
   * data-parallel captured QLoRA step: the all-reduced LoRA gradients equal the mean of the
     per-rank gradients, and the adapters stay identical across ranks after the optimizer step.
 
@@ -25,7 +26,7 @@ def rel(a, b):
     return ((a.double() - b).norm() / b.norm().clamp(min=1e-30)).item()
 
 
-def check_head(rank, world, dev, n=1024):
+def check_head(rank, world, dev, n=1024, chunk_cols=None):
     from claudemaxing_b200 import parallel
     from claudemaxing_b200.lm_head_loss import GRAD_SCALE, fused_head_loss
     from oracle import head_ce
@@ -38,7 +39,10 @@ def check_head(rank, world, dev, n=1024):
     t[torch.rand(n, generator=gen) < 0.1] = -100
     bounds = parallel.shard_bounds(vocab, world)
     hd, td = h.to(dev), t.to(dev)
-    res = parallel.vocab_parallel_head(hd, w[bounds[rank]:bounds[rank + 1]].to(dev), td, bounds)
+    if chunk_cols is not None:   # the case is meant to walk several exchange blocks
+        assert n > parallel.exchange_rows(n, hdim, bounds, chunk_cols)
+    res = parallel.vocab_parallel_head(hd, w[bounds[rank]:bounds[rank + 1]].to(dev), td, bounds,
+                                       chunk_cols=chunk_cols)
     n_lab = int((t != -100).sum())
     grad = res["grad_raw"] / (GRAD_SCALE * n_lab)
     # single-GPU fused head on the whole weight
@@ -58,6 +62,46 @@ def check_head(rank, world, dev, n=1024):
     ok = (errs["loss_vs_single"] < 1e-3 and errs["entropy_vs_single"] < 1e-3
           and errs["grad_vs_single"] < 1e-2 and errs["correct_vs_single"] == 0
           and errs["loss_vs_oracle"] < 1e-3 and errs["entropy_vs_oracle"] < 1e-3)
+    return ok, errs
+
+
+def check_rows(rank, world, dev, n_local=1100, chunk_cols=4096):
+    """The row-sharded head: every rank feeds its own rows and gets their terms and their fp16
+    gradient back (hidden all-gather, state all-gather, fp16 reduce-scatter per exchange step,
+    several steps with a ragged last one), against the oracle on the whole job."""
+    from claudemaxing_b200 import parallel
+    from claudemaxing_b200.lm_head_loss import GRAD_SCALE
+    from oracle import head_ce
+
+    hdim, vocab = 256, 30011
+    n = n_local * world
+    gen = torch.Generator().manual_seed(9)
+    h = torch.randn(n, hdim, generator=gen).half()
+    w = (torch.randn(vocab, hdim, generator=gen) * 0.06).half()
+    t = torch.randint(0, vocab, (n,), generator=gen)
+    t[torch.rand(n, generator=gen) < 0.1] = -100
+    bounds = parallel.shard_bounds(vocab, world)
+    steps = parallel.plan_exchange_steps(n_local, world, parallel.exchange_rows(n, hdim, bounds, chunk_cols))
+    assert len(steps) >= 2, steps
+    mine = slice(rank * n_local, (rank + 1) * n_local)
+    res = parallel.vocab_parallel_head_rows(h[mine].to(dev), t[mine].to(dev),
+                                            w[bounds[rank]:bounds[rank + 1]].to(dev), bounds,
+                                            chunk_cols=chunk_cols)
+    ref = head_ce.head_ce(h.float(), w.float(), t)
+    n_lab = int((t != -100).sum())
+    grad = res["grad"].float().cpu() / (GRAD_SCALE * n_lab)
+    scale = ref["dhidden"].abs().max().item()
+    errs = {
+        "loss": (res["token_loss"].cpu() - ref["token_loss"][mine]).abs().max().item(),
+        "entropy": (res["entropy"].cpu() - ref["entropy"][mine]).abs().max().item(),
+        "grad_rel_max": (grad - ref["dhidden"][mine]).abs().max().item() / scale,
+        "job_loss": abs(float(res["loss_sum"]) / n_lab - float(ref["loss"])),
+        "labelled": int(res["labelled"]) - n_lab,
+        "hits": abs(int(res["hits"]) - int(ref["correct"].sum())),
+        "steps": len(steps),
+    }
+    ok = (errs["loss"] < 1e-3 and errs["entropy"] < 1e-3 and errs["grad_rel_max"] < 1e-2
+          and errs["job_loss"] < 1e-3 and errs["labelled"] == 0 and errs["hits"] <= 2)
     return ok, errs
 
 
@@ -114,11 +158,16 @@ def main():
     try:
         ok1, e1 = check_head(rank, world, dev)
         # more rows than one block: blocks' exchanges overlap the next block's GEMMs, ragged tail
-        ok3, e3 = check_head(rank, world, dev, n=4500)
+        ok3, e3 = check_head(rank, world, dev, n=4500, chunk_cols=4096)
+        ok4, e4 = check_rows(rank, world, dev)
         ok2, e2 = check_step(rank, world, dev)
-        flag = torch.tensor([int(ok1 and ok2 and ok3)], device=dev)
+        from claudemaxing_b200 import _lib
+
+        _lib.check_device_status()
+        flag = torch.tensor([int(ok1 and ok2 and ok3 and ok4)], device=dev)
         dist.all_reduce(flag, op=dist.ReduceOp.MIN)
-        print(f"rank {rank}: head {ok1} {e1} head-4500 {ok3} {e3} step {ok2} {e2}", flush=True)
+        print(f"rank {rank}: head {ok1} {e1} head-4500 {ok3} {e3} rows {ok4} {e4} step {ok2} {e2}",
+              flush=True)
         if rank == 0 and int(flag) == 1:
             print("MULTI_GPU_OK", flush=True)
     finally:

@@ -86,6 +86,59 @@ def test_confident_labels(sharp):
     check(*make(160, 128, 5000, seed=3, sharp=sharp))
 
 
+@pytest.mark.parametrize("chunk_cols", [512, None])
+def test_logits_far_above_everything_seen_in_earlier_chunks(chunk_cols):
+    """Later chunks are exponentiated against the log-sum-exp of the earlier ones. A logit 80 to
+    160 above it (legal for fp16 inputs; exp(z - lse) overflows fp32 beyond 88) must give the
+    oracle's numbers, not inf: as the label, as a wrong prediction, twice in one chunk with
+    different peaks, and again in a still later chunk (the max-subtracted carry of
+    solution/lm_head_loss.py:119-145 is exact for all of these)."""
+    from oracle.head_ce import head_ce
+
+    n, hidden, vocab = 192, 128, 24000 if chunk_cols is None else 6000
+    h, w, t = make(n, hidden, vocab, seed=21, drop=0.1)
+    late = vocab - 900                        # all planted columns sit in the last chunks
+    unit = h.float() / h.float().pow(2).sum(1, keepdim=True)     # h[r] . unit[r] = 1
+    w = w.clone()
+    for r in range(0, 48):                    # one peak of 150: label for even rows, not for odd
+        w[late + r] = (150.0 * unit[r]).half()
+        if r % 2 == 0 and t[r] != -100:
+            t[r] = late + r
+    for r in range(48, 80):                   # two peaks in neighbouring tiles: 100 and 140
+        w[late + 300 + r] = (100.0 * unit[r]).half()
+        w[late + 600 + r] = (140.0 * unit[r]).half()
+    for r in range(80, 112):                  # a peak of 80 early, one of 160 late
+        w[vocab // 2 + r] = (80.0 * unit[r]).half()
+        w[late + r] = (160.0 * unit[r]).half()
+    ref = head_ce(h, w, t)
+    loss, step, dh = run_ours(h, w, t, chunk_cols)
+    tl, en = step.token_loss[0].cpu(), step.token_entropy[0].cpu()
+    assert torch.isfinite(tl).all() and torch.isfinite(en).all() and torch.isfinite(dh.float()).all()
+    tol = 1e-3 + 2e-5 * ref["token_loss"].abs()
+    assert ((tl - ref["token_loss"]).abs() <= tol).all(), (tl - ref["token_loss"]).abs().max()
+    assert ((en - ref["entropy"]).abs() <= 1e-3 + 2e-5 * ref["lse"].abs()).all()
+    assert abs(step.correct.item() - int(ref["correct"].sum())) <= 2
+    assert_close_rel_max(dh, ref["dhidden"], 1e-2, "dhidden")
+    # row by row too: a planted row's gradient must not hide behind the largest row of the tensor
+    for r in (0, 1, 49, 81, 150):
+        assert_close_rel_max(dh[r], ref["dhidden"][r], 1e-2, f"dhidden row {r}")
+    from claudemaxing_b200 import _lib
+
+    _lib.check_device_status()
+
+
+def test_gradient_is_reproducible_with_the_k_split_off(monkeypatch):
+    """SOUP_LMHEAD_DETERMINISTIC=1: one adder per dH element and chunk, fixed order, so two runs
+    give identical bits (the default splits the vocabulary dimension over CTA pairs that add
+    with atomics in no fixed order)."""
+    monkeypatch.setenv("SOUP_LMHEAD_DETERMINISTIC", "1")
+    h, w, t = make(700, 256, 60000, seed=22)
+    _, s1, d1 = run_ours(h, w, t)
+    _, s2, d2 = run_ours(h, w, t)
+    assert torch.equal(d1, d2)
+    assert torch.equal(s1.token_loss, s2.token_loss) and torch.equal(s1.token_entropy, s2.token_entropy)
+
+
 def test_num_items_and_loss_scale():
     h, w, t = make(128, 128, 1000, seed=4)
     check(h, w, t, num_items=77)

@@ -378,9 +378,28 @@ def test_a_wait_that_nothing_completes_runs_out_and_reports():
     _lib.call("soup_wait_selftest", 2_000_000, ctypes.byref(gave_up), ctypes.byref(status),
               torch.cuda.current_stream().cuda_stream)
     assert gave_up.value == 1 and status.value == 99
-    # the device still works and the row kernels' own status word is untouched
+    # the device still works
     x = torch.arange(8, device=DEV).sum().item()
     assert x == 28
+    # the code reached the device's sticky status word, where the host-side check finds it: the
+    # package raises instead of handing out results of a step whose kernels gave up
     row = ctypes.c_int(-1)
     _lib.call("soup_row_status", ctypes.byref(row), torch.cuda.current_stream().cuda_stream)
-    assert row.value == 0
+    assert row.value == 99
+    with pytest.raises(RuntimeError, match="device status 99"):
+        _lib.check_device_status()
+    _lib.check_device_status()          # cleared by the failing check: healthy again
+    assert _lib.device_status() == 0
+
+
+def test_device_status_stays_clear_after_a_healthy_step():
+    from claudemaxing_b200 import _lib, fused_head_loss
+
+    _lib.device_status(clear=True)
+    gen = torch.Generator().manual_seed(3)
+    h = torch.randn(300, 256, generator=gen).half().to(DEV).requires_grad_(True)
+    w = (torch.randn(5000, 256, generator=gen) * 0.05).half().to(DEV)
+    t = torch.randint(0, 5000, (300,), generator=gen).to(DEV)
+    loss, _ = fused_head_loss(h[None], w, None, target=t[None])
+    loss.backward()
+    _lib.check_device_status()

@@ -189,3 +189,53 @@ def test_captured_step_equals_the_eager_step_and_trains():
     if other["n_tokens"] <= step.bucket:
         step.load(other)
         assert torch.isfinite(step.run()).item()
+
+
+@pytest.mark.parametrize("autocast_dtype", [torch.bfloat16, None])
+def test_padded_batch_outside_fp16_keeps_the_packing_and_goes_through_the_logits(autocast_dtype):
+    """A padded batch under bf16 autocast, or of an fp32 model without autocast, is still packed,
+    but its head cannot be the fp16 tensor-core kernel: the loss and the per-token terms come
+    from the logits of the packed row and match the installed forward on the padded batch."""
+    import contextlib
+
+    import claudemaxing_b200 as solution
+    from claudemaxing_b200 import lm_head_loss, qlora
+    from transformers import Qwen2Config, Qwen2ForCausalLM
+
+    solution.apply()
+    cfg = Qwen2Config(**dict(qlora.QWEN25_1P5B, **TINY))
+    cfg._attn_implementation = "sdpa"
+    torch.manual_seed(0)
+    model = Qwen2ForCausalLM(cfg).float().cuda()
+    for p in model.parameters():
+        p.requires_grad_(False)
+    model.model.layers[0].mlp.down_proj.weight.requires_grad_(True)   # something to train
+    batch = qlora.synthetic_batch(batch=3, min_len=8, max_len=40, vocab=TINY["vocab_size"],
+                                  seed=12, device="cuda")
+    ctx = (torch.autocast("cuda", dtype=autocast_dtype) if autocast_dtype is not None
+           else contextlib.nullcontext())
+    kwargs = dict(input_ids=batch["input_ids"], attention_mask=batch["attention_mask"],
+                  labels=batch["labels"], use_cache=False)
+    with ctx:
+        ref = model(**kwargs)                      # not flagged: the installed forward, padded
+    ref.loss.backward()
+    ref_grad = model.model.layers[0].mlp.down_proj.weight.grad.clone()
+    model.zero_grad(set_to_none=True)
+    fused_calls = []
+    original = lm_head_loss.fused_head_loss
+    lm_head_loss.fused_head_loss = lambda *a, **k: (fused_calls.append(1), original(*a, **k))[1]
+    try:
+        model.__dict__[lm_head_loss._REQUEST_ATTR] = True
+        with ctx:
+            out = model(**kwargs)
+    finally:
+        lm_head_loss.fused_head_loss = original
+    assert out.logits is None and not fused_calls
+    terms = model.__dict__.pop(lm_head_loss._STEP_ATTR)
+    assert terms.token_loss.shape == batch["input_ids"].shape
+    tol = 2e-2 if autocast_dtype is not None else 1e-4
+    assert abs(out.loss.item() - ref.loss.item()) <= tol * abs(ref.loss.item())
+    n_lab = int(terms.labelled)
+    assert abs(terms.token_loss.sum().item() / n_lab - ref.loss.item()) <= tol * abs(ref.loss.item())
+    out.loss.backward()
+    assert rel_norm(model.model.layers[0].mlp.down_proj.weight.grad, ref_grad) < (5e-2 if autocast_dtype else 1e-3)

@@ -192,3 +192,69 @@ def test_exchange_rows_is_common_to_all_ranks_for_the_real_plan():
             differing += len(own) > 1
             assert parallel.exchange_rows(n, 1536, bounds) == min(own)
     assert differing, "expected at least one world size (4) whose shards plan different row blocks"
+
+
+# --- the row-sharded variant: every rank brings its own rows, gathers, reduce-scatters ------------
+
+def _rows_worker(rank, world, port, results):
+    import datetime
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world,
+                            timeout=datetime.timedelta(seconds=60))
+    try:
+        from claudemaxing_b200 import parallel
+        from oracle import head_ce
+
+        parallel.head_partial, parallel.merge_states = _cpu_partial, _cpu_merge
+        parallel.head_finish = _cpu_finish
+        parallel._rounded = lambda g, dtype: g.to(dtype)
+        parallel._row_block = lambda n, hidden, v_shard, chunk_cols: 32
+        n_local, hidden, vocab = 27, 32, 77                 # 27 rows per rank: ragged last step
+        gen = torch.Generator().manual_seed(5)
+        h = torch.randn(world * n_local, hidden, generator=gen).half()
+        w = (torch.randn(vocab, hidden, generator=gen) * 0.3).half()
+        t = torch.randint(0, vocab, (world * n_local,), generator=gen)
+        t[::6] = -100
+        bounds = parallel.shard_bounds(vocab, world, tile=8)
+        steps = parallel.plan_exchange_steps(n_local, world, 32)
+        assert len(steps) > 2 and steps[0][0] == 0 and steps[-1][1] == n_local
+        mine = slice(rank * n_local, (rank + 1) * n_local)   # any split of the rows over ranks works
+        out = parallel.vocab_parallel_head_rows(h[mine], t[mine], w[bounds[rank]:bounds[rank + 1]],
+                                                bounds, grad_dtype=torch.float32)
+        ref = head_ce.head_ce(h.float(), w.float(), t)
+        n_lab = int((t != -100).sum())
+        results[rank] = bool(
+            torch.allclose(out["token_loss"], ref["token_loss"][mine], atol=1e-4)
+            and torch.allclose(out["entropy"], ref["entropy"][mine], atol=1e-4)
+            and torch.equal(out["correct"], ref["correct"][mine])
+            and torch.allclose(out["grad"] / (1024.0 * n_lab), ref["dhidden"][mine], atol=1e-5)
+            and abs(float(out["loss_sum"]) / n_lab - float(ref["loss"])) < 1e-4
+            and int(out["labelled"]) == n_lab
+            and int(out["hits"]) == int(ref["correct"].sum()))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_four_cpu_ranks_row_sharded_head_gathers_and_reduce_scatters():
+    """vocab_parallel_head_rows on 4 gloo ranks (kernels replaced by torch): each rank feeds its
+    own rows, several exchange steps with a ragged last one, and gets its own rows' terms and
+    gradient back; the job-wide sums are identical on every rank without another collective."""
+    world = 4
+    with mp.Manager() as manager:
+        results = manager.dict()
+        mp.spawn(_rows_worker, args=(world, _free_port(), results), nprocs=world, join=True)
+        assert dict(results) == {r: True for r in range(world)}
+
+
+def test_exchange_steps_cover_the_rows_in_near_equal_pieces():
+    from claudemaxing_b200 import parallel
+
+    for n_local, world, block in ((2048, 8, 8192), (8192, 8, 8192), (2048, 4, 6144), (2048, 2, 4096),
+                                  (8192, 4, 6144), (27, 4, 32), (1, 8, 8192)):
+        steps = parallel.plan_exchange_steps(n_local, world, block)
+        assert steps[0][0] == 0 and steps[-1][1] == n_local
+        assert all(a[1] == b[0] for a, b in zip(steps, steps[1:]))
+        sizes = [z - a for a, z in steps]
+        assert max(sizes) * world <= max(block, 8 * world) and max(sizes) - min(sizes[:-1] or sizes) <= 8
+    assert parallel.plan_exchange_steps(0, 4, 4096) == []

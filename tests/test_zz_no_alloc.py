@@ -48,6 +48,15 @@ def test_noalloc_matches_workspace_entry_on_two_calls_in_a_row(dtype):
         assert torch.equal(got_dw, ref_dw)
         scale = ref_dw.float().abs().max().item()
         assert (got_dw.float() - ref_dw.float()).abs().max().item() <= 2e-3 * scale
+        # and against the CPU oracle (autograd of Qwen2RMSNorm.forward), so that the check does not
+        # rest on the sibling entry alone; tolerances of the other RMSNorm tests
+        from conftest import assert_close_rel_max
+        from oracle import elementwise as ew
+
+        _, o_dx, o_dw = ew.rmsnorm_fwd_bwd(x.cpu(), w.cpu(), dy.cpu(), weight_grad=True)
+        tol = 2e-3 if dtype == torch.float16 else 1e-4
+        assert_close_rel_max(got_dx.cpu(), o_dx, tol, "dx against the oracle")
+        assert_close_rel_max(got_dw.cpu(), o_dw, 5 * tol, "dw against the oracle")
         results.append(got_dw)
     assert results[0].shape != results[1].shape
 
