@@ -46,8 +46,12 @@ SIGNATURES = {
     "soup_lmhead_finish": [_P] * 12 + [_L] * 4 + [_P],
     "soup_lmhead_grad_scale": [_P, _P, _P, _L, _I, _P],
     "soup_xent_rows": [_P] * 5 + [_L, _L, _L, _I, _P],
+    "soup_nf4_gemm_workspace_bytes": [_L, _L],
+    "soup_nf4_linear_fwd": [_P, _P, _I, _P, _L, _L, _I, _I, _I, _P, _L, _P],
+    "soup_nf4_linear_dx": [_P, _I, _P, _P, _I, _L, _L, _I, _I, _I, _P, _L, _P],
 }
-_RESTYPE = {"soup_lmhead_workspace_bytes": _L, "soup_rmsnorm_bwd_partials": _L}
+_RESTYPE = {"soup_lmhead_workspace_bytes": _L, "soup_rmsnorm_bwd_partials": _L,
+            "soup_nf4_gemm_workspace_bytes": _L}
 SIGNATURES["soup_rmsnorm_bwd_partials"] = [_L, _L]
 
 class Nf4Item(ctypes.Structure):
@@ -55,6 +59,13 @@ class Nf4Item(ctypes.Structure):
 
     _fields_ = [("packed", _P), ("absmax", _P), ("code2", _P), ("absmax2", _P), ("offset", _P),
                 ("out", _P), ("n_elems", _L)]
+
+
+class Nf4GemmItem(ctypes.Structure):
+    """soup_nf4_gemm_item of include/soup_b200.h."""
+
+    _fields_ = [("packed", _P), ("absmax", _P), ("code2", _P), ("absmax2", _P), ("offset", _P),
+                ("bias", _P), ("out", _P), ("dy", _P), ("n_out", _L)]
 
 
 _lock = threading.Lock()

@@ -181,6 +181,50 @@ int soup_dropout_pack(const void* x, const uint8_t* mask, void* xd, uint8_t* bit
 int soup_dropout_unpack(const void* x16, const uint8_t* bits, const void* g16, void* xd, void* dx,
                         int64_t n, float scale, int dx_dtype, void* stream);
 
+/* ---- linear layers on NF4 weights: tcgen05 GEMM with the dequantisation in its operand prologue --
+ * One weight of a launch. `packed`, `absmax`, `code2`, `absmax2`, `offset` as in soup_nf4_dequant
+ * (blocksize 64 only: one block is one 128-byte row of the operand tile). Forward reads `bias`
+ * (fp16 [n_out] or NULL) and writes `out` (fp16 [m, n_out] row-major); backward reads `dy`
+ * (fp16 [m, n_out] row-major). The dequantised operand is bit-identical to soup_nf4_dequant's
+ * fp16 output (same unfused fp32 operations in the same order). */
+typedef struct {
+  const void* packed;
+  const void* absmax;
+  const float* code2;
+  const float* absmax2;
+  const float* offset;
+  const void* bias;
+  void* out;
+  const void* dy;
+  int64_t n_out;
+} soup_nf4_gemm_item;
+
+/* Bytes of the optional fp32 buffer of the two entries below for an [m, cols] result. */
+int64_t soup_nf4_gemm_workspace_bytes(int64_t m, int64_t cols);
+
+/* out_i[m, n_i] = x[m, k] * dequant(W_i)[n_i, k]^T (+ bias_i) for up to four weights that share x
+ * (one launch: gate_proj and up_proj, or q/k/v). fp16 operands, fp32 accumulation, fp16 result.
+ * Replaces the dequantise + F.linear pair of solution/nf4.py:122 and bnb.matmul_4bit at
+ * solution/swiglu_recompute.py:165-166 (forward) and :198-199 (recompute in backward); the fp16
+ * weight never exists in HBM. x fp16 [m, k] row-major, k % 64 == 0, n_i % 8 == 0, blocksize 64.
+ * `workspace` (nullable, fp32 [m, n_0]): with a single weight and a long k the contraction is
+ * split over CTA pairs that add into it (the result is then not bit-reproducible from run to
+ * run); without it nothing is split. A failed bounded wait reports through soup_device_status
+ * (codes 31-35). */
+int soup_nf4_linear_fwd(const void* x, const soup_nf4_gemm_item* items, int n_items,
+                        const float* code, int64_t m, int64_t k, int nested, int blocksize,
+                        int blocksize2, void* workspace, int64_t workspace_bytes, void* stream);
+
+/* dx[m, k] = sum_i dy_i[m, n_i] * dequant(W_i)[n_i, k] for one or two weights (the input gradient
+ * of the projections above; two weights: gate_proj and up_proj of one MLP, summed in the
+ * accumulator). Replaces the dequantise + matmul of bitsandbytes' MatMul4Bit.backward, reached
+ * from solution/nf4.py:127-132 and solution/swiglu_recompute.py:210-213. dx fp16 or fp32
+ * (dx_dtype), n_i % 64 == 0. A long contraction is split over CTA pairs that add partial sums
+ * into dx itself when it is fp32, else into `workspace` (nullable, fp32 [m, k]). */
+int soup_nf4_linear_dx(const soup_nf4_gemm_item* items, int n_items, const float* code, void* dx,
+                       int dx_dtype, int64_t m, int64_t k, int nested, int blocksize,
+                       int blocksize2, void* workspace, int64_t workspace_bytes, void* stream);
+
 /* ---- fused LM head + cross-entropy (tcgen05 / TMEM / TMA) -------------------------------------
  * Replaces the chunk loop of _FusedHeadLoss.forward, solution/lm_head_loss.py:213-224 (torch.mm,
  * lm_head_vocab_chunk_kernel :108-160, torch.mm, mul_/add_), over the columns of one weight shard.

@@ -11,6 +11,7 @@ bitsandbytes is not installed, so the 4-bit projections are this package's NF4Li
 the same cast -> dequantise -> linear -> cast-back formula."""
 
 import copy
+import importlib
 
 import pytest
 import torch
@@ -39,7 +40,7 @@ def _saved_pointers(fn):
 
 @pytest.mark.parametrize("autocast", [False, True])
 def test_frozen_mlp_recompute_keeps_only_its_input(autocast):
-    from claudemaxing_b200 import swiglu_recompute as mod
+    mod = importlib.import_module("claudemaxing_b200.swiglu_recompute")
 
     modeling, mlp = _small_mlp()
     installed = modeling.Qwen2MLP.forward
@@ -83,7 +84,7 @@ def _nf4_mlp():
 
 @pytest.mark.parametrize("x_dtype", [F32, F16])
 def test_nf4_mlp_fast_path_matches_the_module_path_bitwise(x_dtype):
-    from claudemaxing_b200 import swiglu_recompute as mod
+    mod = importlib.import_module("claudemaxing_b200.swiglu_recompute")
     from claudemaxing_b200.nf4 import dequantize_nf4
 
     modeling, mlp = _nf4_mlp()
