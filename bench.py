@@ -427,6 +427,64 @@ def kernel_suite(dev, hbm_peak, n_rows=2048, tag="", with_nf4=True):
 
 
 
+def nf4_gemm_suite(dev, tensor_peak, rows=1280):
+    """The projections of one Qwen2.5-1.5B decoder block at the training step's row count, forward
+    and input gradient: the tcgen05 GEMM that dequantises NF4 in its operand prologue against the
+    two-step path it replaces (this library's dequant kernel into an fp16 buffer, then cuBLAS
+    through torch). Weights rotate over 28 layers' worth of packed bytes (655 MB: cold in L2, as
+    in a training step); values are random codes, which cost the same as real ones."""
+    from claudemaxing_b200 import qlora
+    from claudemaxing_b200.nf4 import dequantize_nf4, nf4_linear, nf4_linear_dx
+
+    f16, f32 = torch.float16, torch.float32
+    code, code2 = qlora.normal_float4_levels().to(dev), qlora.absmax_levels().to(dev)
+    gen = torch.Generator(device=dev).manual_seed(4)
+    layers = 28
+
+    def weight(o, i):
+        n = o * i
+        packed = torch.randint(0, 256, (n // 2, 1), dtype=torch.uint8, device=dev, generator=gen)
+        absmax8 = torch.randint(0, 256, (n // 64,), dtype=torch.uint8, device=dev, generator=gen)
+        inner = qlora.QuantState(torch.rand(-(-n // 64 // 256), device=dev, generator=gen) * 0.01,
+                                 (n // 64,), code2, 256, f32)
+        return packed, qlora.QuantState(absmax8, (o, i), code, 64, f16,
+                                        offset=torch.tensor([0.02], device=dev), state2=inner)
+
+    out = {}
+    cases = (("q_or_o_1536x1536", [(1536, 1536)]), ("k_or_v_256x1536", [(256, 1536)]),
+             ("gate_and_up_2x8960x1536", [(8960, 1536), (8960, 1536)]), ("down_1536x8960", [(1536, 8960)]))
+    for name, shapes in cases:
+        sets = [[weight(o, i) for (o, i) in shapes] for _ in range(layers)]
+        k = shapes[0][1]
+        x = torch.randn(rows, k, device=dev, dtype=f16)
+        grads = [torch.randn(rows, o, device=dev, dtype=f16) for (o, _) in shapes]
+        bufs = [torch.empty(o, i, device=dev, dtype=f16) for (o, i) in shapes]
+        flops = 2.0 * rows * sum(o * i for o, i in shapes)
+
+        def two_step_fwd(j):
+            for (packed, st), buf in zip(sets[j], bufs):
+                torch.nn.functional.linear(x, dequantize_nf4(packed, st, f16, out=buf))
+
+        def two_step_dx(j):
+            acc = None
+            for (packed, st), buf, g in zip(sets[j], bufs, grads):
+                part = torch.matmul(g, dequantize_nf4(packed, st, f16, out=buf))
+                acc = part if acc is None else acc + part
+
+        legs = (("fwd", lambda j: nf4_linear(x, sets[j]), two_step_fwd),
+                ("dx", lambda j: nf4_linear_dx(grads, sets[j], f16), two_step_dx))
+        for leg, fused, two_step in legs:
+            ms_f = time_rotating(fused, layers, reps=5)
+            ms_t = time_rotating(two_step, layers, reps=5)
+            out[f"nf4_linear_{leg}_{name}@{rows}rows"] = {
+                "ms": round(ms_f, 5), "tflops": round(flops / (ms_f * 1e-3) / 1e12, 1),
+                "frac_of_measured_bf16_burst": round(flops / (ms_f * 1e-3) / 1e12 / tensor_peak, 3),
+                "two_step_dequant_plus_cublas_ms": round(ms_t, 5),
+                "speedup_over_two_step": round(ms_t / ms_f, 3), "flops": flops}
+        del sets
+    return out
+
+
 # ------------------------------------------------------------------------------------------
 def cpu_oracle_suite(cores):
     """The oracle's CPU torch implementations of the memory-bound ops at config-3 size (2048 rows),
@@ -533,11 +591,31 @@ def qlora_step_leg(dev, rank, world, steps, warmup, timed):
     for _ in range(2):
         eager()
     eager_ms = timed(eager, 5) / 5
+    # the same captured step with the 4-bit projections on the tcgen05 GEMM that dequantises in its
+    # operand prologue (off by default: see NF4Linear.fused_gemm)
+    fused_ms = None
+    if world == 1:
+        qlora.NF4Linear.fused_gemm = True
+        try:
+            opt2 = torch.optim.AdamW(lora, lr=1e-4, fused=True, capturable=True)
+            fused_step = qlora.CapturedStep(model, lora, opt2, batch, scaler=torch.amp.GradScaler("cuda", init_scale=65536.0))
+            for _ in range(3):
+                fused_step.run()
+            fused_ms = sorted(timed(fused_step.run, steps) / steps for _ in range(3))[1]
+            del fused_step, opt2
+        finally:
+            qlora.NF4Linear.fused_gemm = False
     dp_check = None
     if world > 1:
         # outside the timed regions: the all-reduced flat LoRA gradient is the mean of the ranks'
         captured.load(batch)
-        captured.graph_fb.replay()
+        for _ in range(6):   # dynamic loss scaling: a step whose scaled gradient overflowed says nothing
+            captured.graph_fb.replay()
+            finite = torch.isfinite(captured.flat_grad).all().float()
+            dist.all_reduce(finite, op=dist.ReduceOp.MIN)
+            if bool(finite):
+                break
+            captured.graph_opt.replay()   # the scaler lowers the scale and skips the update
         mine = captured.flat_grad.clone()
         gathered = [torch.empty_like(mine) for _ in range(world)]
         dist.all_gather(gathered, mine)
@@ -558,6 +636,7 @@ def qlora_step_leg(dev, rank, world, steps, warmup, timed):
         "e2e": {"value": round(n_real / world / (e2e_ms * 1e-3), 1), "ms_per_step": round(e2e_ms, 4),
                 "h2d_bytes_per_step": 4 * captured.bucket * 8, "d2h_bytes_per_step": 4},
         "eager_ms_per_step": round(eager_ms, 4),
+        "nf4_gemm_in_prologue_ms_per_step": None if fused_ms is None else round(fused_ms, 4),
         "loss_first": round(first, 5), "loss_last": round(float(last), 5),
         "config": "configs[3]: 28 layers, hidden 1536, GQA 12/2, vocab 151936 tied, NF4 + LoRA r=16 "
                   "on q_proj/v_proj, batch 4 x U[64,512] packed, fp16 autocast, dynamic loss scale, "
@@ -703,6 +782,8 @@ def main():
     ap.add_argument("--suite-only", action="store_true",
                     help="run only the memory-bound kernel suite and print its JSON")
     ap.add_argument("--suite-rows", type=int, default=32768)
+    ap.add_argument("--gemm-only", action="store_true",
+                    help="run only the NF4 GEMM comparison and print its JSON")
     ap.add_argument("--plain-launches", action="store_true",
                     help="with --suite-only: up to three direct launches per case instead of graph replays")
     args = ap.parse_args()
@@ -722,13 +803,17 @@ def main():
     assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
+    global PLAIN_LAUNCHES
     if args.suite_only:
-        global PLAIN_LAUNCHES
         PLAIN_LAUNCHES = args.plain_launches
         hbm = peaks()[0]["hbm_gbs"]
         print(json.dumps({"kernels": kernel_suite(dev, hbm, n_rows=args.suite_rows,
                                                   tag=f"@{args.suite_rows}rows",
                                                   with_nf4=True)}), flush=True)
+        return
+    if args.gemm_only:
+        PLAIN_LAUNCHES = args.plain_launches
+        print(json.dumps({"kernels": nf4_gemm_suite(dev, peaks()[0]["bf16_tflops"])}), flush=True)
         return
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
@@ -957,6 +1042,7 @@ def main():
                                         with_nf4=False))
             kernels.update(kernel_suite(dev, peak["hbm_gbs"], n_rows=65536, tag="@65536rows",
                                         with_nf4=False))
+            kernels.update(nf4_gemm_suite(dev, tensor_peak))
         if not args.no_cpu and kernels is not None:
             cpu_ms = cpu_oracle_suite(cores)
             for key, ms in cpu_ms.items():

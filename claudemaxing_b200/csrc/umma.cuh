@@ -59,18 +59,24 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
   return t;
 }
 
-// Bounded wait: gives up after kWaitLimitNs of wall time. `abort_flag` is a shared-memory word
+// Bounded wait: gives up after about `limit_ns` of wall time. `abort_flag` is a shared-memory word
 // every role of the CTA polls, so that one role giving up releases the others too. Returns false
 // when the wait was abandoned; the first abandoning waiter records `code` in `status`.
+// The limit is counted on the SM's cycle counter (clock64, a register read) at two cycles per
+// nanosecond (the SM clock stays below 2 GHz, so the real limit is never shorter than asked for):
+// reading %globaltimer takes on the order of a microsecond, and a wait that read it whenever the
+// first try failed put that microsecond into every pipeline step whose data was not there yet.
 __device__ __forceinline__ bool mbar_wait_for(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                               int* status, int code, uint64_t limit_ns) {
   if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = global_timer_ns();
+  long long t0 = 0;
   for (uint32_t i = 1;; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 63u) == 0u) {
+    if ((i & 255u) == 0u) {
       if (*abort_flag) return false;
-      if (global_timer_ns() - t0 > limit_ns) break;
+      const long long now = clock64();
+      if (t0 == 0) t0 = now;
+      else if (static_cast<uint64_t>(now - t0) > 2ull * limit_ns) break;
     }
   }
   *abort_flag = 1;
@@ -256,6 +262,15 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
                : "memory");
 }
 
+// Arrival on a barrier of another CTA of the cluster with the default (CTA-scope) release. For a
+// hand-over of shared-memory tiles that the arriving thread has already made visible to the
+// tensor core's proxy (fence.proxy.async) this is what is needed; the cluster-scope release of
+// mbar_arrive_cluster costs the arriving thread on the order of a thousand cycles, which matters
+// when it happens every pipeline step.
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+
 // TMA load whose completion bytes are counted on a barrier given by its shared::cluster address
 // (the leader's barrier, also when the peer CTA issues the load into its own shared memory).
 __device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, int32_t c0,
@@ -343,6 +358,12 @@ __host__ __device__ constexpr uint32_t make_idesc_f16(int m, int n, uint32_t a_f
 // are not written.
 int encode_map_2d_16bit(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
                         uint64_t pitch_elems, uint32_t box_rows, uint32_t box_cols, bool bf16);
+
+// Row-major 2-D byte matrix [rows, cols] with row pitch `pitch_bytes` (a multiple of 16); the box
+// is [box_rows, box_cols] with box_cols a multiple of 16, copied to shared memory row after row
+// without swizzle. Out-of-range bytes read as zero.
+int encode_map_2d_bytes(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
+                        uint64_t pitch_bytes, uint32_t box_rows, uint32_t box_cols);
 
 }  // namespace umma
 }  // namespace soup

@@ -107,6 +107,120 @@ def dequantize_nf4_batch(weights, dtype=None, outs=None):
     return results
 
 
+# ------------------------------------------------------------------ GEMMs on the packed weight
+def gemm_supported(state, k=None):
+    """Whether the tcgen05 GEMM with the dequantisation in its prologue takes this weight: NF4 with
+    blocksize 64 (one block = one 128-byte row of the operand tile), rows a multiple of 64 long,
+    fp32 tables, plain or double-quantised absmax."""
+    if getattr(state, "quant_type", None) != "nf4" or state.blocksize != 64 or len(state.shape) != 2:
+        return False
+    if state.shape[1] % 64 or state.shape[0] % 8 or (k is not None and state.shape[1] != k):
+        return False
+    code = getattr(state, "code", None)
+    if code is None or code.numel() != 16 or code.dtype != torch.float32 or not code.is_cuda:
+        return False
+    if state.nested:
+        s2 = state.state2
+        return (s2.blocksize > 0 and (s2.blocksize & (s2.blocksize - 1)) == 0
+                and s2.code.dtype == torch.float32 and s2.code.numel() == 256
+                and s2.absmax.dtype == torch.float32 and state.absmax.dtype == torch.uint8)
+    return state.absmax.dtype == torch.float32
+
+
+def _gemm_items(weights, keep):
+    import ctypes
+
+    items = (_lib.Nf4GemmItem * len(weights))()
+    first = weights[0][1]
+    for i, (packed, st) in enumerate(weights):
+        _lib.require_cuda(packed)
+        if (bool(st.nested) != bool(first.nested)
+                or (st.nested and st.state2.blocksize != first.state2.blocksize)):
+            raise ValueError("the weights of one launch share their nesting")
+        absmax = st.absmax.contiguous()
+        keep.append(absmax)
+        items[i].packed, items[i].absmax = packed.data_ptr(), absmax.data_ptr()
+        items[i].n_out = st.shape[0]
+        if st.nested:
+            code2, absmax2 = st.state2.code.contiguous(), st.state2.absmax.contiguous()
+            offset = _offset_tensor(st.offset, packed.device)
+            keep += [code2, absmax2, offset]
+            items[i].code2, items[i].absmax2, items[i].offset = (code2.data_ptr(), absmax2.data_ptr(),
+                                                                 offset.data_ptr())
+    return items, ctypes.cast(items, ctypes.c_void_p)
+
+
+# contractions at least this long may be split over CTA pairs (needs an fp32 buffer; the result is
+# then summed with atomics and not bit-reproducible)
+SPLIT_MIN_K = 4096
+
+
+def nf4_linear(x, weights, biases=None):
+    """[x @ dequant(W_i)^T (+ bias_i)] for up to four NF4 weights that share the input, in one
+    launch, without the fp16 weights in memory. `x` fp16 [..., k]; `weights` a list of
+    (packed, state); returns a list of fp16 [..., n_i]."""
+    if x.dtype != torch.float16:
+        raise TypeError("the NF4 GEMM computes in float16")
+    k = x.shape[-1]
+    rows = x.reshape(-1, k).contiguous()
+    m = rows.shape[0]
+    keep = []
+    items, items_ptr = _gemm_items(weights, keep)
+    outs = []
+    for i, (packed, st) in enumerate(weights):
+        if not gemm_supported(st, k):
+            raise ValueError(f"weight {i} ({tuple(st.shape)}, blocksize {st.blocksize}) is not one "
+                             "the NF4 GEMM takes")
+        out = torch.empty((m, st.shape[0]), dtype=torch.float16, device=x.device)
+        outs.append(out)
+        items[i].out = out.data_ptr()
+        bias = None if biases is None else biases[i]
+        if bias is not None:
+            bias = bias.to(torch.float16).contiguous()
+            keep.append(bias)
+            items[i].bias = bias.data_ptr()
+    first = weights[0][1]
+    workspace, nbytes = None, 0
+    if len(weights) == 1 and k >= SPLIT_MIN_K and m:
+        nbytes = _lib.lib().soup_nf4_gemm_workspace_bytes(m, first.shape[0])
+        workspace = torch.empty(nbytes, dtype=torch.uint8, device=x.device)
+    _lib.call("soup_nf4_linear_fwd", _lib.ptr(rows), items_ptr, len(weights), _lib.ptr(first.code), m, k,
+              int(bool(first.nested)), int(first.blocksize),
+              int(first.state2.blocksize) if first.nested else 1, _lib.ptr(workspace), nbytes,
+              _lib.stream_of(rows))
+    return [o.view(*x.shape[:-1], o.shape[-1]) for o in outs]
+
+
+def nf4_linear_dx(grads, weights, dx_dtype=torch.float16):
+    """sum_i grads[i] @ dequant(W_i): the input gradient of `nf4_linear` for one or two weights,
+    the sum formed in the accumulator. `grads[i]` fp16 [..., n_i]; returns `dx_dtype` (fp16 or
+    fp32) [..., k]."""
+    first = weights[0][1]
+    k = first.shape[1]
+    keep = []
+    items, items_ptr = _gemm_items(weights, keep)
+    lead = grads[0].shape[:-1]
+    m = grads[0].reshape(-1, grads[0].shape[-1]).shape[0]
+    for i, ((packed, st), g) in enumerate(zip(weights, grads)):
+        if g.dtype != torch.float16:
+            raise TypeError("the NF4 GEMM computes in float16")
+        if not gemm_supported(st, k) or st.shape[0] % 64 or g.shape[-1] != st.shape[0]:
+            raise ValueError(f"weight {i} ({tuple(st.shape)}) is not one the NF4 GEMM takes")
+        g2 = g.reshape(-1, st.shape[0]).contiguous()
+        keep.append(g2)
+        items[i].dy = g2.data_ptr()
+    dx = torch.empty((m, k), dtype=dx_dtype, device=grads[0].device)
+    workspace, nbytes = None, 0
+    if dx_dtype != torch.float32 and sum(st.shape[0] for _, st in weights) >= SPLIT_MIN_K and m:
+        nbytes = _lib.lib().soup_nf4_gemm_workspace_bytes(m, k)
+        workspace = torch.empty(nbytes, dtype=torch.uint8, device=dx.device)
+    _lib.call("soup_nf4_linear_dx", items_ptr, len(weights), _lib.ptr(first.code), _lib.ptr(dx),
+              _lib.dtype_code(dx_dtype), m, k, int(bool(first.nested)), int(first.blocksize),
+              int(first.state2.blocksize) if first.nested else 1, _lib.ptr(workspace), nbytes,
+              _lib.stream_of(dx))
+    return dx.view(*lead, k)
+
+
 ORIGINALS = {}    # "fallback" / "dequant": bitsandbytes' own functions, kept for everything we leave alone
 _CODE = {}
 

@@ -22,7 +22,7 @@ import torch
 import torch.nn.functional as F
 
 from .lora import LoRABranch, _shared_fp16, branch_covers
-from .nf4 import dequantize_nf4
+from .nf4 import dequantize_nf4, gemm_supported, nf4_linear, nf4_linear_dx
 from .rmsnorm import fp16_copy_of
 
 
@@ -100,7 +100,11 @@ def quantize_nf4(w, blocksize=64, nested=True, blocksize2=256, code=None, code2=
 
 
 class _MatMul4Bit(torch.autograd.Function):
-    """x @ dequant(W)^T; the weight is dequantised again in backward instead of being kept."""
+    """x @ dequant(W)^T; the weight is dequantised again in backward instead of being kept. With
+    `NF4Linear.fused_gemm` both products run on the tcgen05 GEMM that dequantises inside its
+    operand prologue, so the fp16 weight is never written to memory; otherwise (the default) the
+    weight is dequantised into a buffer and cuBLAS multiplies (the reference's two steps,
+    solution/nf4.py:122)."""
 
     @staticmethod
     def forward(ctx, x, layer, x_low=None):
@@ -110,6 +114,8 @@ class _MatMul4Bit(torch.autograd.Function):
         ctx.layer, ctx.x_dtype = layer, x.dtype
         src = x if x_low is None else x_low
         bias = layer.bias
+        if layer.takes_fused_gemm(src):
+            return nf4_linear(src, [(layer.packed, layer.quant_state)], [bias])[0]
         if bias is not None and bias.dtype != src.dtype:
             bias = bias.to(src.dtype)
         return F.linear(src, layer.dequantized(src.dtype), bias)
@@ -118,7 +124,12 @@ class _MatMul4Bit(torch.autograd.Function):
     def backward(ctx, grad):
         if not ctx.needs_input_grad[0]:
             return None, None, None
-        dx = torch.matmul(grad, ctx.layer.dequantized(grad.dtype, backward=True))
+        layer = ctx.layer
+        if layer.takes_fused_gemm(grad) and layer.out_features % 64 == 0:
+            direct = ctx.x_dtype if ctx.x_dtype in (torch.float16, torch.float32) else torch.float16
+            dx = nf4_linear_dx([grad], [(layer.packed, layer.quant_state)], direct)
+            return dx.to(ctx.x_dtype), None, None
+        dx = torch.matmul(grad, layer.dequantized(grad.dtype, backward=True))
         return dx.to(ctx.x_dtype), None, None
 
 
@@ -248,6 +259,11 @@ class NF4Linear(torch.nn.Module):
     """Frozen, bias-free linear with an NF4 double-quantised weight."""
 
     _soup_nf4_linear = True
+    # SOUP_NF4_GEMM=1 routes the projections through the tcgen05 GEMM that dequantises in its
+    # operand prologue. It is off by default: measured on B200 at the training step's shapes
+    # (1280 rows) it takes 94 us for gate+up against 75 us for this library's dequant kernel plus
+    # cuBLAS, and the 1536 x 1536 / 256 x 1536 projections are bound by its ~13 us of fixed cost.
+    fused_gemm = os.environ.get("SOUP_NF4_GEMM", "0") == "1"
 
     def __init__(self, in_features, out_features, packed, quant_state, compute_dtype=torch.float16,
                  bias=None):
@@ -277,6 +293,12 @@ class NF4Linear(torch.nn.Module):
         if self.group is not None:
             return self.group.weight(self, dtype, backward)
         return dequantize_nf4(self.packed, self.quant_state, dtype)
+
+    def takes_fused_gemm(self, operand):
+        """Whether a product with `operand` (fp16, CUDA) runs on the GEMM that dequantises in its
+        prologue."""
+        return (NF4Linear.fused_gemm and operand.dtype == torch.float16 and operand.is_cuda
+                and gemm_supported(self.quant_state, self.in_features))
 
     def matmul_4bit(self, x_low):
         return _MatMul4Bit.apply(x_low, self)

@@ -13,6 +13,7 @@ RMSNorm is reused.
 import torch
 
 from . import _lib
+from .nf4 import nf4_linear, nf4_linear_dx
 from .rmsnorm import fp16_copy_of
 
 _SUPPORTED = (torch.float16, torch.bfloat16, torch.float32)
@@ -124,6 +125,19 @@ def _four_bit_pair(gate_proj, up_proj, x):
     return gate, up
 
 
+def _fused_pair(gate_proj, up_proj, x_low):
+    """[(packed, state), (packed, state)] when gate_proj and up_proj are this package's NF4 layers
+    and their products with `x_low` can share one launch of the NF4 GEMM (x is then read once and
+    the two input gradients are summed in the accumulator), else None."""
+    if not (getattr(gate_proj, "_soup_nf4_linear", False) and getattr(up_proj, "_soup_nf4_linear", False)):
+        return None
+    if not (gate_proj.takes_fused_gemm(x_low) and up_proj.takes_fused_gemm(x_low)):
+        return None
+    if gate_proj.out_features % 64 or up_proj.out_features % 64:
+        return None
+    return [(gate_proj.packed, gate_proj.quant_state), (up_proj.packed, up_proj.quant_state)]
+
+
 class MLPInputRecompute(torch.autograd.Function):
     """silu(gate_proj(x)) * up_proj(x) for frozen projections, keeping only the MLP input for
     backward (the reference's solution/swiglu_recompute.py:138-215): backward runs the two
@@ -142,7 +156,11 @@ class MLPInputRecompute(torch.autograd.Function):
             kept = fp16_copy_of(x) if compute == torch.float16 else None
             if kept is None:   # usually the norm before the MLP has written exactly this copy
                 kept = x.to(compute)
-            gate, up = pair[0].matmul(kept), pair[1].matmul(kept)
+            fused = _fused_pair(gate_proj, up_proj, kept)
+            if fused is not None:
+                gate, up = nf4_linear(kept, fused)
+            else:
+                gate, up = pair[0].matmul(kept), pair[1].matmul(kept)
             round_silu = x.dtype == compute
             # a 4-bit down_proj casts its input to `compute` anyway: hand it that dtype directly
             out_dtype = compute if down_compute == compute else x.dtype
@@ -157,6 +175,14 @@ class MLPInputRecompute(torch.autograd.Function):
     def backward(ctx, grad):
         (kept,) = ctx.saved_tensors
         on, dtype = ctx.autocast
+        fused = _fused_pair(*ctx.modules, kept) if ctx.pair is not None else None
+        if fused is not None:
+            # one launch recomputes gate and up, one forms dgate * Wg + dup * Wu in the accumulator
+            d_gate, d_up = nf4_linear(kept, fused)
+            _silu_mul_bwd(grad.contiguous(), d_gate, d_up, d_gate, d_up, ctx.round_silu)
+            direct = ctx.x_dtype if ctx.x_dtype in (torch.float16, torch.float32) else torch.float16
+            dx = nf4_linear_dx([d_gate, d_up], fused, direct)
+            return dx.to(ctx.x_dtype), None, None, None
         leaf = kept.detach().requires_grad_(True)
         with torch.enable_grad(), torch.autocast("cuda", dtype=dtype, enabled=on):
             if ctx.pair is None:

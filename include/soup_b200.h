@@ -210,7 +210,7 @@ int64_t soup_nf4_gemm_workspace_bytes(int64_t m, int64_t cols);
  * `workspace` (nullable, fp32 [m, n_0]): with a single weight and a long k the contraction is
  * split over CTA pairs that add into it (the result is then not bit-reproducible from run to
  * run); without it nothing is split. A failed bounded wait reports through soup_device_status
- * (codes 31-35). */
+ * (codes 31-38). */
 int soup_nf4_linear_fwd(const void* x, const soup_nf4_gemm_item* items, int n_items,
                         const float* code, int64_t m, int64_t k, int nested, int blocksize,
                         int blocksize2, void* workspace, int64_t workspace_bytes, void* stream);

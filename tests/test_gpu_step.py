@@ -70,11 +70,24 @@ def _cpu_reference(model_gpu, cfg):
     return ref, refs
 
 
-def test_step_matches_installed_transformers_on_cpu():
+@pytest.mark.parametrize("fused_gemm", [False, True])
+def test_step_matches_installed_transformers_on_cpu(fused_gemm, monkeypatch):
+    """`fused_gemm`: the 4-bit projections as dequantise + cuBLAS (default) or on the tcgen05 GEMM
+    that dequantises in its operand prologue (forward, MLP recompute and every input gradient)."""
     import claudemaxing_b200 as solution
-    from claudemaxing_b200 import qlora
+    from claudemaxing_b200 import nf4 as nf4_mod, qlora
     from claudemaxing_b200.qlora import LoRALinear
 
+    monkeypatch.setattr(qlora.NF4Linear, "fused_gemm", fused_gemm)
+    launches = []
+    real_fwd, real_dx = nf4_mod._lib.call, None
+
+    def counting_call(name, *args):
+        if name.startswith("soup_nf4_linear"):
+            launches.append(name)
+        return real_fwd(name, *args)
+
+    monkeypatch.setattr(nf4_mod._lib, "call", counting_call)
     solution.apply()
     model, lora = qlora.build_qlora_model("cuda", TINY, dropout=1e-6, seed=1)
     # B = 0 would make the adapter output and dA vanish: give B small values
@@ -103,6 +116,11 @@ def test_step_matches_installed_transformers_on_cpu():
     finally:
         lm_head_loss.fused_head_loss = original
     assert calls, "the fused head did not run"
+    if fused_gemm:   # q, k, v, o, gate+up, down forward; gate+up recompute; five input gradients
+        assert launches.count("soup_nf4_linear_fwd") == 7 * TINY["num_hidden_layers"]
+        assert launches.count("soup_nf4_linear_dx") >= 5 * TINY["num_hidden_layers"] - 3
+    else:
+        assert not launches
     assert abs(loss.item() - ref_out.loss.item()) <= 1e-2 * abs(ref_out.loss.item())
     checked = 0
     for m in model.modules():
