@@ -196,7 +196,7 @@ __device__ __forceinline__ void release_accumulator(const GemmSmem& s, int ab, u
   __syncwarp();
   if (lane == 0) {
     if (rank == 0) mbar_arrive(&s.acc_empty[ab]);
-    else mbar_arrive_cluster(mapa_u32(smem_u32(&s.acc_empty[ab]), 0));
+    else mbar_arrive_remote(mapa_u32(smem_u32(&s.acc_empty[ab]), 0));
   }
 }
 

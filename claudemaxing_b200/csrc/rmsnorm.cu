@@ -575,6 +575,142 @@ rmsnorm_bwd_pipe_kernel(const void* __restrict__ dy, const void* __restrict__ xi
   }
 }
 
+// The 4-bit model's backward: fp32 dy, the fp16 copy of the forward's output as the saved tensor,
+// fp32 weight and dx. Only dy travels through the warp's ring; the saved row, half as many bytes,
+// comes through plain 8-byte loads into registers one row ahead (as RoPE's cos/sin rows do). That
+// halves the bulk copies per row (the copy engine has a cost per copy) and leaves the ring two
+// stages where a slot of dy + saved row had room for one. NVX: 4-element vectors per lane.
+template <int NVX>
+__global__ void __launch_bounds__(rowpipe::kMaxWarps * 32, 2)
+rmsnorm_bwd_saved_kernel(const float* __restrict__ dy, const __half* __restrict__ saved,
+                         const float* __restrict__ w, const float* __restrict__ rstd_in,
+                         float* __restrict__ dx, const int32_t* __restrict__ slot,
+                         const __half* __restrict__ small, int64_t n_small, int64_t n_rows,
+                         int n_cols, int stages, int team, int w_offset, int* status) {
+  constexpr int EPV = 4;
+  extern __shared__ __align__(128) char smem[];
+  __shared__ int s_abort;
+  __shared__ float s_part[2 * rowpipe::kMaxWarps];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  const int member = team == 2 ? (warp & 1) : 0;
+  const int n_vec = n_cols / EPV / team, v0 = member * n_vec;
+  const uint32_t y_bytes = (uint32_t)n_cols * 4 / team;
+  const int64_t y_pitch = (int64_t)n_cols * 4;
+  if (threadIdx.x == 0) s_abort = 0;
+  rowpipe::Ring ring;
+  ring.init(smem, y_bytes, stages, warp, lane);
+  __syncthreads();
+  const int64_t row0 = (int64_t)blockIdx.x * (warps / team) + warp / team;
+  const int64_t stride = (int64_t)gridDim.x * (warps / team);
+  const char* yb = reinterpret_cast<const char*>(dy) + (size_t)member * y_bytes;
+  const __half* xb = saved + (size_t)v0 * EPV;
+  int64_t next = row0;
+  if (lane == 0) {
+    for (int s = 0; s < stages && next < n_rows; ++s, next += stride) {
+      umma::mbar_expect_tx(&ring.bars[s], y_bytes);
+      rowpipe::bulk_load(ring.slot_ptr(s), yb + next * y_pitch, y_bytes, &ring.bars[s]);
+    }
+  }
+  next = __shfl_sync(0xffffffffu, next, 0);
+  // The weight and its reciprocal, needed by every row, sit in shared memory behind the ring
+  // (registers are taken by the two saved rows in flight and the normalised values).
+  float* s_w = reinterpret_cast<float*>(smem + w_offset);
+  float* s_winv = s_w + n_cols;
+  for (int c = threadIdx.x; c < n_cols; c += blockDim.x) {
+    const float wc = w[c];
+    s_w[c] = wc;
+    s_winv[c] = 1.0f / wc;
+  }
+  __syncthreads();
+  uint32_t slot_mask = 0;
+#pragma unroll
+  for (int v = 0; v < NVX; ++v) {
+    const int vi = lane + 32 * v;
+    if (vi < n_vec) {
+      int sl[EPV];
+      load_slots<EPV>(slot, (v0 + vi) * EPV, sl);
+#pragma unroll
+      for (int k = 0; k < EPV; ++k)
+        if (sl[k] >= 0) slot_mask |= 1u << v;
+    }
+  }
+  Raw<8> xcur[NVX], xnxt[NVX];
+  auto fetch_saved = [&](int64_t row, Raw<8> (&dst)[NVX]) {
+#pragma unroll
+    for (int v = 0; v < NVX; ++v) {
+      const int vi = lane + 32 * v;
+      if (vi < n_vec) dst[v] = ld_raw<8>(xb, (row * n_cols + (int64_t)vi * EPV) * 2);
+    }
+  };
+  if (row0 < n_rows) fetch_saved(row0, xcur);
+  const float inv_cols = 1.0f / (float)n_cols;
+  int iter = 0;
+  for (int64_t row = row0; row < n_rows; row += stride, ++iter) {
+    if (row + stride < n_rows) fetch_saved(row + stride, xnxt);
+    if (!ring.wait(&s_abort, status, 12)) {
+      ring.drain((int)((next - row) / stride));
+      if (team == 2) asm volatile("bar.arrive %0, 64;" ::"r"((warp >> 1) + 1) : "memory");
+      return;
+    }
+    const char* ysrc = ring.slot_ptr(ring.slot);
+    const float rstd = rstd_in[row];
+    // the normalised value: saved / w, except in the side-buffer columns (|w| tiny)
+    float nrm[NVX][EPV];
+    float dot = 0.f;
+#pragma unroll
+    for (int v = 0; v < NVX; ++v) {
+      const int vi = lane + 32 * v;
+      if (vi < n_vec) {
+        float yv[EPV], xv[EPV];
+        unpack_smem<EPV, 4>(ysrc, vi, SOUP_F32, yv);
+        unpack<EPV, 2>(xcur[v], SOUP_F16, xv);
+        const float4 wq = *reinterpret_cast<const float4*>(s_w + (v0 + vi) * EPV);
+        const float4 iq = *reinterpret_cast<const float4*>(s_winv + (v0 + vi) * EPV);
+        const float wv[EPV] = {wq.x, wq.y, wq.z, wq.w}, winv[EPV] = {iq.x, iq.y, iq.z, iq.w};
+        int sl[EPV];
+#pragma unroll
+        for (int k = 0; k < EPV; ++k) sl[k] = -1;
+        if (slot_mask >> v & 1u) load_slots<EPV>(slot, (v0 + vi) * EPV, sl);
+#pragma unroll
+        for (int k = 0; k < EPV; ++k) {
+          nrm[v][k] = sl[k] >= 0 ? __half2float(small[row * n_small + sl[k]]) : xv[k] * winv[k];
+          dot += yv[k] * wv[k] * nrm[v][k];
+        }
+      }
+    }
+    dot = warp_sum(dot);
+    if (team == 2) dot = rowpipe::team_sum2(dot, s_part, warp, lane, iter);
+    const float mean_dot = dot * inv_cols;
+#pragma unroll
+    for (int v = 0; v < NVX; ++v) {
+      const int vi = lane + 32 * v;
+      if (vi < n_vec) {
+        float yv[EPV];
+        unpack_smem<EPV, 4>(ysrc, vi, SOUP_F32, yv);
+        const float4 wq = *reinterpret_cast<const float4*>(s_w + (v0 + vi) * EPV);
+        float4 o;
+        o.x = (yv[0] * wq.x - nrm[v][0] * mean_dot) * rstd;
+        o.y = (yv[1] * wq.y - nrm[v][1] * mean_dot) * rstd;
+        o.z = (yv[2] * wq.z - nrm[v][2] * mean_dot) * rstd;
+        o.w = (yv[3] * wq.w - nrm[v][3] * mean_dot) * rstd;
+        *reinterpret_cast<float4*>(dx + row * n_cols + (int64_t)(v0 + vi) * EPV) = o;
+      }
+    }
+    __syncwarp();
+    if (next < n_rows) {
+      if (lane == 0) {
+        umma::fence_proxy_async_smem();
+        umma::mbar_expect_tx(&ring.bars[ring.slot], y_bytes);
+        rowpipe::bulk_load(ring.slot_ptr(ring.slot), yb + next * y_pitch, y_bytes, &ring.bars[ring.slot]);
+      }
+      next += stride;
+    }
+    ring.advance();
+#pragma unroll
+    for (int v = 0; v < NVX; ++v) xcur[v] = xnxt[v];
+  }
+}
+
 // YB / XB: bytes per element of dy and of the saved tensor (x, or the fp16 copy of the output).
 template <int NV, int YB, int XB, bool DW>
 __global__ void __launch_bounds__(kWarpsPerCta * 32)
@@ -855,9 +991,34 @@ extern "C" int soup_rmsnorm_bwd(const void* dy, const void* xin, const void* w, 
                                                          status);                                 \
   } while (0)
     const bool same = dy_dtype == xin_dtype && dy_dtype == w_dtype && dy_dtype == dx_dtype;
-    if (saved_output && dy_dtype == SOUP_F32 && xin_dtype == SOUP_F16 && w_dtype == SOUP_F32 &&
-        dx_dtype == SOUP_F32)
-      SOUP_RMS_BWD_P(4, 2, SOUP_F32, SOUP_F16, SOUP_F32, SOUP_F32, 1);   // the 4-bit model's path
+    const bool four_bit = saved_output && dy_dtype == SOUP_F32 && xin_dtype == SOUP_F16 &&
+                          w_dtype == SOUP_F32 && dx_dtype == SOUP_F32;
+    // the 4-bit model's path with the saved row through registers: the ring carries dy only
+    const rowpipe::Plan plan_y = four_bit ? rowpipe::make_plan((size_t)n_cols * 4, 0, (n_cols * 2) % 32 == 0, n_rows)
+                                          : rowpipe::Plan{8, 0, 1, 1, 0, 0};
+    const int per_lane = plan_y.stages ? (int)((n_cols / 4 / plan_y.team + 31) / 32) : 0;
+    // weight and reciprocal behind the ring; two CTAs of this size must still fit an SM
+    const size_t w_off = (plan_y.smem + 15) / 16 * 16;
+    const size_t smem_y = w_off + 2 * (size_t)n_cols * sizeof(float);
+    if (four_bit && plan_y.stages >= 1 && per_lane >= 1 && per_lane <= 8 && smem_y <= 112 * 1024) {
+      grid = plan_y.grid;
+#define SOUP_RMS_BWD_S(NVX_)                                                                     \
+  do {                                                                                            \
+    auto kernel = rmsnorm_bwd_saved_kernel<NVX_>;                                                 \
+    cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_y);       \
+    kernel<<<plan_y.grid, plan_y.warps * 32, smem_y, s>>>(                                        \
+        reinterpret_cast<const float*>(dy), reinterpret_cast<const __half*>(xin),                 \
+        reinterpret_cast<const float*>(w), rstd, reinterpret_cast<float*>(dx), slot,              \
+        reinterpret_cast<const __half*>(small), n_small, n_rows, (int)n_cols, plan_y.stages,      \
+        plan_y.team, (int)w_off, status);                                                         \
+  } while (0)
+      if (per_lane <= 2) SOUP_RMS_BWD_S(2);
+      else if (per_lane <= 4) SOUP_RMS_BWD_S(4);
+      else if (per_lane <= 6) SOUP_RMS_BWD_S(6);
+      else SOUP_RMS_BWD_S(8);
+#undef SOUP_RMS_BWD_S
+    } else if (four_bit)
+      SOUP_RMS_BWD_P(4, 2, SOUP_F32, SOUP_F16, SOUP_F32, SOUP_F32, 1);
     else if (!saved_output && same && dy_dtype == SOUP_F16)
       SOUP_RMS_BWD_P(2, 2, SOUP_F16, SOUP_F16, SOUP_F16, SOUP_F16, 0);
     else if (!saved_output && same && dy_dtype == SOUP_BF16)
