@@ -423,6 +423,21 @@ def kernel_suite(dev, hbm_peak, n_rows=2048, tag="", with_nf4=True):
 
     record("dropout_pack", time_rotating(pack, nD), n_rows * H * (4 + 1 + 2) + n_rows * H // 8)
     record("dropout_unpack", time_rotating(unpack, nD), n_rows * H * (2 + 2 + 2 + 4) + n_rows * H // 8)
+    del xs, ms_, packed_out, x16, dxs, xd2
+
+    if n_rows <= 4096:
+        # metrics from logits that exist anyway (the route for steps that end up building them):
+        # one warp per row over [n_rows, 151936] fp16, 622 MB at 2048 rows (larger than L2)
+        logit_sets = [torch.randn(n_rows, VOCAB, device=dev, dtype=f16) for _ in range(2)]
+        tg = torch.randint(0, VOCAB, (n_rows,), device=dev)
+        o_loss, o_ent = torch.empty(n_rows, device=dev), torch.empty(n_rows, device=dev)
+        o_hit = torch.empty(n_rows, dtype=torch.int32, device=dev)
+
+        def xent(i):
+            _lib.call("soup_xent_rows", logit_sets[i].data_ptr(), tg.data_ptr(), o_loss.data_ptr(),
+                      o_ent.data_ptr(), o_hit.data_ptr(), n_rows, VOCAB, VOCAB, _lib.F16, cur())
+
+        record("xent_rows_from_logits", time_rotating(xent, 2), n_rows * VOCAB * 2 + n_rows * 20)
     return out
 
 
@@ -989,7 +1004,7 @@ def main():
         launches = head_launches(n_tokens, v_local, 1)
     else:
         steps_plan = parallel.plan_exchange_steps(n_local, world,
-                                                  parallel.exchange_rows(n_tokens, HIDDEN, bounds))
+                                                  parallel.step_rows(n_tokens, HIDDEN, bounds))
         launches = sum(head_launches((z - a) * world, v_local, world) for a, z in steps_plan)
 
     # ---- parity against the CPU oracle, outside every timed region, at every N

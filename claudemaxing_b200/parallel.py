@@ -155,6 +155,22 @@ def vocab_parallel_head(h16, w_shard, target, bounds, group=None, want_grad=True
     return dict(token_loss=token_loss, entropy=entropy, correct=correct, grad_raw=grad_raw)
 
 
+STEP_ROWS = 16384   # rows gathered per exchange step of the row-sharded head (all ranks together)
+
+
+def step_rows(n_total, hidden, bounds, chunk_cols=None):
+    """Rows (over all ranks) one exchange step of `vocab_parallel_head_rows` gathers: whole
+    kernel row blocks, up to STEP_ROWS. A step has fixed costs (its first chunk's one-wave
+    launches, a dozen small kernels, four collectives' launch latencies: 0.15-0.2 ms measured), so
+    a job of 2048 rows per GPU runs as one step; a long job (65536 rows) as steps whose gather and
+    reduce-scatter travel beside the neighbouring steps' GEMMs. SOUP_VP_STEP_ROWS overrides."""
+    import os
+
+    block = exchange_rows(n_total, hidden, bounds, chunk_cols)
+    want = int(os.environ.get("SOUP_VP_STEP_ROWS", STEP_ROWS))
+    return max(block, want // block * block)
+
+
 def plan_exchange_steps(n_local, world, block_rows):
     """[(begin, end)] ranges of a rank's local rows, one per exchange step. A step gathers the
     same range from every rank (world * (end - begin) rows, at most `block_rows`, the kernels'
@@ -213,8 +229,7 @@ def vocab_parallel_head_rows(h_local, target_local, w_shard, bounds, group=None,
     dev = h_local.device
     h_local = h_local.contiguous()
     target_local = target_local.contiguous().to(torch.int64)
-    block = exchange_rows(n_local * world, hidden, bounds, chunk_cols)
-    steps = plan_exchange_steps(n_local, world, block)
+    steps = plan_exchange_steps(n_local, world, step_rows(n_local * world, hidden, bounds, chunk_cols))
     f32 = torch.float32
     token_loss = torch.empty(n_local, dtype=f32, device=dev)
     entropy = torch.empty(n_local, dtype=f32, device=dev)

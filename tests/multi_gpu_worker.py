@@ -81,12 +81,14 @@ def check_rows(rank, world, dev, n_local=1100, chunk_cols=4096):
     t = torch.randint(0, vocab, (n,), generator=gen)
     t[torch.rand(n, generator=gen) < 0.1] = -100
     bounds = parallel.shard_bounds(vocab, world)
-    steps = parallel.plan_exchange_steps(n_local, world, parallel.exchange_rows(n, hdim, bounds, chunk_cols))
+    os.environ["SOUP_VP_STEP_ROWS"] = "2048"     # several exchange steps also for this small job
+    steps = parallel.plan_exchange_steps(n_local, world, parallel.step_rows(n, hdim, bounds, chunk_cols))
     assert len(steps) >= 2, steps
     mine = slice(rank * n_local, (rank + 1) * n_local)
     res = parallel.vocab_parallel_head_rows(h[mine].to(dev), t[mine].to(dev),
                                             w[bounds[rank]:bounds[rank + 1]].to(dev), bounds,
                                             chunk_cols=chunk_cols)
+    os.environ.pop("SOUP_VP_STEP_ROWS", None)
     ref = head_ce.head_ce(h.float(), w.float(), t)
     n_lab = int((t != -100).sum())
     grad = res["grad"].float().cpu() / (GRAD_SCALE * n_lab)

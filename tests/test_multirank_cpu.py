@@ -210,6 +210,7 @@ def _rows_worker(rank, world, port, results):
         parallel.head_finish = _cpu_finish
         parallel._rounded = lambda g, dtype: g.to(dtype)
         parallel._row_block = lambda n, hidden, v_shard, chunk_cols: 32
+        os.environ["SOUP_VP_STEP_ROWS"] = "32"              # several exchange steps for a tiny job
         n_local, hidden, vocab = 27, 32, 77                 # 27 rows per rank: ragged last step
         gen = torch.Generator().manual_seed(5)
         h = torch.randn(world * n_local, hidden, generator=gen).half()
@@ -258,3 +259,16 @@ def test_exchange_steps_cover_the_rows_in_near_equal_pieces():
         sizes = [z - a for a, z in steps]
         assert max(sizes) * world <= max(block, 8 * world) and max(sizes) - min(sizes[:-1] or sizes) <= 8
     assert parallel.plan_exchange_steps(0, 4, 4096) == []
+
+
+def test_step_rows_are_whole_row_blocks_and_common_to_all_ranks():
+    from claudemaxing_b200 import parallel
+
+    for world in (2, 4, 8):
+        bounds = parallel.shard_bounds(151936, world)
+        block = parallel.exchange_rows(2048 * world, 1536, bounds)
+        rows = parallel.step_rows(2048 * world, 1536, bounds)
+        assert rows % block == 0 and block <= rows <= max(block, parallel.STEP_ROWS)
+        # the weak-scaling job of 2048 rows per GPU is one exchange step
+        assert len(parallel.plan_exchange_steps(2048, world, rows)) == 1
+        assert len(parallel.plan_exchange_steps(65536 // world, world, rows)) >= 4
