@@ -1,12 +1,46 @@
-"""Grouped-query attention through torch SDPA without repeating k/v.
+"""Attention of the packed training row, and grouped-query attention without repeating k/v.
 
-The hot path keeps torch's SDPA (a library call in the reference too, solution/attention.py:
-332-343): one call per layer with `enable_gqa`, which gives the same products as transformers'
-repeat_kv path without materialising the repeated k and v.
+Attention stays a library call, as in the reference (solution/attention.py:332-343 calls torch
+SDPA). Two routes replace transformers' "sdpa" attention function:
+
+* a packed row whose batch rows are given as segment offsets (`cu_seq_lens_q` / `cu_seq_lens_k`,
+  the keyword names transformers uses for packed sequences) runs torch's variable-length causal
+  attention: work and memory are linear in the packed length times the longest segment, and no
+  [N, N] mask exists. The reference's packed route builds that mask (solution/lm_head_loss.py:
+  300-337); this is the same attention pattern stated as segments.
+* a boolean 4-D mask on a grouped-query model runs one SDPA call with `enable_gqa`, which gives
+  the same products as transformers' repeat_kv path without materialising the repeated k and v.
 """
 
 import torch
 import torch.nn.functional as F
+
+_LOW = (torch.float16, torch.bfloat16)
+
+
+def mask_of_segments(cu_rows, n):
+    """[1, 1, n, n] bool: key in the same segment as the query and not after it. `cu_rows` holds
+    the segments' starts followed by the total."""
+    idx = torch.arange(n, device=cu_rows.device)
+    segment = torch.searchsorted(cu_rows[1:].to(torch.int64), idx, right=True)
+    same = segment.unsqueeze(1).eq(segment.unsqueeze(0))
+    return (same & idx.unsqueeze(0).le(idx.unsqueeze(1))).unsqueeze(0).unsqueeze(0)
+
+
+def _varlen():
+    try:
+        from torch.nn.attention.varlen import varlen_attn
+    except ImportError:
+        return None
+    return varlen_attn
+
+
+def _autocast_dtype():
+    try:
+        on, dtype = torch.is_autocast_enabled("cuda"), torch.get_autocast_dtype("cuda")
+    except (TypeError, AttributeError):
+        on, dtype = torch.is_autocast_enabled(), torch.get_autocast_gpu_dtype()
+    return dtype if on else None
 
 
 def _grouped_sdpa(query, key, value, attention_mask, scaling):
@@ -14,13 +48,52 @@ def _grouped_sdpa(query, key, value, attention_mask, scaling):
     (`enable_gqa`), which is transformers' repeat_kv order. One call per layer matters: at a few
     thousand packed tokens every attention kernel is launch- and latency-bound."""
     out = F.scaled_dot_product_attention(query, key, value, attn_mask=attention_mask, dropout_p=0.0,
-                                         scale=scaling, enable_gqa=True)
+                                         scale=scaling, enable_gqa=query.shape[1] != key.shape[1])
     return out.transpose(1, 2).contiguous()
 
 
+def segment_attention(query, key, value, cu_rows, longest, scaling):
+    """Causal attention inside each segment of one packed row. query [1, Hq, N, D], key and value
+    [1, Hkv, N, D] (any strides with a contiguous last dimension), `cu_rows` int32 [S + 1] on the
+    same device, `longest` >= the longest segment. Returns [1, N, Hq, D], contiguous. Under
+    autocast the operands are cast as SDPA would cast them; operands the variable-length kernel
+    does not take (fp32, CPU, head dimension over 256) go through SDPA with the mask instead."""
+    varlen_attn = _varlen()
+    dtype = _autocast_dtype() or query.dtype
+    if (varlen_attn is None or not query.is_cuda or dtype not in _LOW or query.shape[-1] > 256
+            or query.shape[-1] % 8 or query.shape[1] % key.shape[1]):
+        return _grouped_sdpa(query, key, value, mask_of_segments(cu_rows, query.shape[2]), scaling)
+    q, k, v = (t.transpose(1, 2)[0] if t.dtype == dtype else t.transpose(1, 2)[0].to(dtype)
+               for t in (query, key, value))
+    out = varlen_attn(q, k, v, cu_rows, cu_rows, int(longest), int(longest),
+                      scale=scaling, window_size=(-1, 0))
+    return out.unsqueeze(0)
+
+
+def segments_route_installed():
+    """Whether transformers' "sdpa" attention function is the one that understands segments."""
+    try:
+        from transformers.modeling_utils import AttentionInterface
+    except ImportError:
+        return False
+    return getattr(AttentionInterface._global_mapping.get("sdpa"), "_grouped_sdpa", False)
+
+
+def segment_arguments(cu_rows, longest, n=None):
+    """Keyword arguments that make a transformers decoder attend inside the segments of a packed
+    row: the offsets under transformers' packed-sequence names and no mask at all when the "sdpa"
+    function is this module's, else the [1, 1, N, N] mask."""
+    if segments_route_installed():
+        return {"attention_mask": {"full_attention": None}, "cu_seq_lens_q": cu_rows,
+                "cu_seq_lens_k": cu_rows, "max_length_q": longest, "max_length_k": longest}
+    total = int(cu_rows[-1]) if n is None else n
+    return {"attention_mask": mask_of_segments(cu_rows, total)}
+
+
 def patch_qwen2_grouped_sdpa():
-    """transformers' "sdpa" attention for grouped-query models with a boolean 4-D mask goes
-    through `_grouped_sdpa`; everything else keeps the installed implementation."""
+    """transformers' "sdpa" attention: a packed row given as segment offsets goes through
+    `segment_attention`, a grouped-query model with a boolean 4-D mask through `_grouped_sdpa`;
+    everything else keeps the installed implementation."""
     from transformers.modeling_utils import AttentionInterface
 
     current = AttentionInterface._global_mapping.get("sdpa")
@@ -31,14 +104,22 @@ def patch_qwen2_grouped_sdpa():
     def sdpa_attention_forward(module, query, key, value, attention_mask, dropout=0.0,
                                scaling=None, is_causal=None, **kwargs):
         groups = getattr(module, "num_key_value_groups", 1)
-        tensors_ok = all(isinstance(x, torch.Tensor) and x.dim() == 4 and x.is_cuda
-                         for x in (query, key, value))
-        mask_ok = (isinstance(attention_mask, torch.Tensor)
-                   and attention_mask.dtype == torch.bool and attention_mask.dim() == 4)
+        tensors_ok = all(isinstance(x, torch.Tensor) and x.dim() == 4 for x in (query, key, value))
         plain = (dropout == 0.0 and kwargs.get("sliding_window") is None
                  and kwargs.get("position_bias") is None
                  and not kwargs.get("output_attentions", False))
-        if (groups > 1 and tensors_ok and mask_ok and plain
+        cu = kwargs.get("cu_seq_lens_q")
+        if (attention_mask is None and isinstance(cu, torch.Tensor) and kwargs.get("cu_seq_lens_k") is cu
+                and tensors_ok and plain and query.shape[0] == 1 and key.shape == value.shape
+                and query.shape[2] == key.shape[2]):
+            return segment_attention(query, key, value, cu, kwargs.get("max_length_q", query.shape[2]),
+                                     scaling), None
+        if attention_mask is None and isinstance(cu, torch.Tensor) and tensors_ok:
+            # segments this route does not cover (attention dropout, a cache): state them as a mask
+            attention_mask = mask_of_segments(cu, key.shape[2])[..., -query.shape[2]:, :]
+        mask_ok = (isinstance(attention_mask, torch.Tensor)
+                   and attention_mask.dtype == torch.bool and attention_mask.dim() == 4)
+        if (groups > 1 and tensors_ok and mask_ok and plain and query.is_cuda
                 and query.shape[1] == key.shape[1] * groups and key.shape == value.shape):
             return _grouped_sdpa(query, key, value, attention_mask, scaling), None
         return original(module, query, key, value, attention_mask, dropout=dropout,

@@ -3,9 +3,12 @@
 // A thread owns 8 elements of the first half of a head row and the matching 8 of the second half
 // (two 128-bit loads and two 128-bit stores per head). It loads its cos/sin vectors once and walks
 // its share of the heads with them, kHeadsPerThread at a time, q heads first, then k heads, so
-// cos/sin traffic is amortised over the heads and q and k need a single launch. Inputs are read through their strides (q and k
-// arrive as transposed views of the projection outputs); outputs are contiguous [b, h, t, d].
-// Arithmetic is fp32, as in qwen_rope_kernel of the reference (solution/rope.py:17-43).
+// cos/sin traffic is amortised over the heads and q and k need a single launch. Inputs are read
+// through their strides (q and k arrive as transposed views of the projection outputs) and the
+// outputs are written through theirs ([b, h, t, d] contiguous for the plain entry point). q may
+// come as a sum of two tensors (the frozen projection's output and the adapter's), added in fp32
+// before the rotation. Arithmetic is fp32, as in qwen_rope_kernel of the reference
+// (solution/rope.py:17-43).
 #include "common.cuh"
 #include "rowpipe.cuh"
 
@@ -17,10 +20,13 @@ constexpr int kHeadsPerThread = 4;   // heads whose loads are in flight together
 
 struct RopeArgs {
   const void* x[2];   // q, k
+  const void* add;    // optional second term of q, with strides of its own
+  int64_t asb, ash, ast;
   void* out[2];
   int64_t sb[2], sh[2], st[2];
+  int64_t osb[2], osh[2], ost[2];
   int heads[2];
-  int xdt[2], odt[2];
+  int xdt[2], odt[2], adt;
   const void* cos;
   const void* sin;
   int64_t cs_b, cs_t;
@@ -71,6 +77,17 @@ __global__ void __launch_bounds__(kThreads) rope_vec_kernel(RopeArgs a) {
         const int64_t off = bi * a.sb[which] + hh * a.sh[which] + ti * a.st[which] + (gi << 3);
         load8(a.x[which], off, a.xdt[which], x1[u]);
         load8(a.x[which], off + half, a.xdt[which], x2[u]);
+        if (which == 0 && a.add) {
+          float y1[8], y2[8];
+          const int64_t aoff = bi * a.asb + hh * a.ash + ti * a.ast + (gi << 3);
+          load8(a.add, aoff, a.adt, y1);
+          load8(a.add, aoff + half, a.adt, y2);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            x1[u][k] += y1[k];
+            x2[u][k] += y2[k];
+          }
+        }
       }
     }
 #pragma unroll
@@ -83,7 +100,7 @@ __global__ void __launch_bounds__(kThreads) rope_vec_kernel(RopeArgs a) {
 #pragma unroll
         for (int k = 0; k < 8; ++k)
           rotate(x1[u][k], x2[u][k], c1[k], c2[k], s1[k], s2[k], a.backward, o1[k], o2[k]);
-        const int64_t orow = ((bi * a.heads[which] + hh) * a.t + ti) * a.d + (gi << 3);
+        const int64_t orow = bi * a.osb[which] + hh * a.osh[which] + ti * a.ost[which] + (gi << 3);
         store8(a.out[which], orow, a.odt[which], o1);
         store8(a.out[which], orow + half, a.odt[which], o2);
       }
@@ -111,21 +128,27 @@ rope_pipe_kernel(RopeArgs a, int stages, int* status) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
   const int half = a.d >> 1, chunks = half / EPV;   // chunks divides 32 (checked by the host)
   const uint32_t q_bytes = (uint32_t)(a.heads[0] * a.d) * XB, k_bytes = (uint32_t)(a.heads[1] * a.d) * XB;
+  const uint32_t add_bytes = a.add ? q_bytes : 0;   // the addend has q's element size (host check)
+  const int adt = DT >= 0 ? DT : a.adt;
   if (threadIdx.x == 0) s_abort = 0;
   rowpipe::Ring ring;
-  ring.init(smem, q_bytes + k_bytes, stages, warp, lane);
+  ring.init(smem, q_bytes + k_bytes + add_bytes, stages, warp, lane);
   __syncthreads();
   const int64_t n_rows = a.b * a.t;
   const int64_t row0 = (int64_t)blockIdx.x * warps + warp;
   const int64_t stride = (int64_t)gridDim.x * warps;
-  // Two bulk copies per position (its q heads, its k heads). The copy engine has a cost per copy,
+  // Two bulk copies per position (its q heads, its k heads; a third for q's second term). The copy engine has a cost per copy,
   // so the 256-byte cos and sin rows do not go through it: every lane keeps the cos/sin values of
   // its own chunk in registers (its chunk is the same for all heads, as chunks divides 32) and
   // fetches the next position's with plain loads while it rotates the current one.
   auto request = [&](int s, int64_t row) {   // lane 0 only
     const int64_t bi = row / a.t, ti = row % a.t;
     char* dst = ring.slot_ptr(s);
-    umma::mbar_expect_tx(&ring.bars[s], q_bytes + k_bytes);
+    umma::mbar_expect_tx(&ring.bars[s], q_bytes + k_bytes + add_bytes);
+    if (add_bytes)
+      rowpipe::bulk_load(dst + q_bytes + k_bytes,
+                         reinterpret_cast<const char*>(a.add) + (bi * a.asb + ti * a.ast) * XB,
+                         add_bytes, &ring.bars[s]);
     if (q_bytes)
       rowpipe::bulk_load(dst, reinterpret_cast<const char*>(a.x[0]) + (bi * a.sb[0] + ti * a.st[0]) * XB,
                          q_bytes, &ring.bars[s]);
@@ -166,10 +189,21 @@ rope_pipe_kernel(RopeArgs a, int stages, int* status) {
       const int e = h * a.d + c * EPV;   // q heads and then k heads are adjacent in the slot as well
       unpack<EPV, XB>(ld_raw<EPV * XB>(src, (int64_t)e * XB), which ? xdt_k : xdt_q, x1);
       unpack<EPV, XB>(ld_raw<EPV * XB>(src, (int64_t)(e + half) * XB), which ? xdt_k : xdt_q, x2);
+      if (add_bytes && !which) {   // q heads come first in the slot: the addend's element index is e
+        float y1[EPV], y2[EPV];
+        const char* more = src + q_bytes + k_bytes;
+        unpack<EPV, XB>(ld_raw<EPV * XB>(more, (int64_t)e * XB), adt, y1);
+        unpack<EPV, XB>(ld_raw<EPV * XB>(more, (int64_t)(e + half) * XB), adt, y2);
+#pragma unroll
+        for (int k = 0; k < EPV; ++k) {
+          x1[k] += y1[k];
+          x2[k] += y2[k];
+        }
+      }
 #pragma unroll
       for (int k = 0; k < EPV; ++k)
         rotate(x1[k], x2[k], c1[k], c2[k], s1[k], s2[k], a.backward, o1[k], o2[k]);
-      const int64_t orow = ((bi * (which ? a.heads[1] : a.heads[0]) + hh) * a.t + ti) * a.d + c * EPV;
+      const int64_t orow = bi * a.osb[which] + hh * a.osh[which] + ti * a.ost[which] + c * EPV;
       void* dst = which ? a.out[1] : a.out[0];
       storev<EPV>(dst, orow, which ? odt_k : odt_q, o1);
       storev<EPV>(dst, orow + half, which ? odt_k : odt_q, o2);
@@ -204,10 +238,16 @@ __global__ void __launch_bounds__(kThreads) rope_scalar_kernel(RopeArgs a) {
     const int64_t off = bi * a.sb[which] + hh * a.sh[which] + ti * a.st[which] + i;
     const int64_t cs_row = bi * a.cs_b + ti * a.cs_t + i;
     float o1, o2;
-    rotate(load1(a.x[which], off, a.xdt[which]), load1(a.x[which], off + half, a.xdt[which]),
+    float v1 = load1(a.x[which], off, a.xdt[which]), v2 = load1(a.x[which], off + half, a.xdt[which]);
+    if (which == 0 && a.add) {
+      const int64_t aoff = bi * a.asb + hh * a.ash + ti * a.ast + i;
+      v1 += load1(a.add, aoff, a.adt);
+      v2 += load1(a.add, aoff + half, a.adt);
+    }
+    rotate(v1, v2,
            load1(a.cos, cs_row, a.csdt), load1(a.cos, cs_row + half, a.csdt),
            load1(a.sin, cs_row, a.csdt), load1(a.sin, cs_row + half, a.csdt), a.backward, o1, o2);
-    const int64_t orow = ((bi * a.heads[which] + hh) * a.t + ti) * a.d + i;
+    const int64_t orow = bi * a.osb[which] + hh * a.osh[which] + ti * a.ost[which] + i;
     store1(a.out[which], orow, a.odt[which], o1);
     store1(a.out[which], orow + half, a.odt[which], o2);
   }
@@ -218,15 +258,19 @@ inline bool mult8(int64_t v) { return (v & 7) == 0; }
 }  // namespace
 }  // namespace soup
 
-extern "C" int soup_rope(const void* q, const void* k, const void* cos, const void* sin,
-                         void* q_out, void* k_out, int64_t b, int64_t hq, int64_t hk, int64_t t,
-                         int64_t d, int64_t q_sb, int64_t q_sh, int64_t q_st, int64_t k_sb,
-                         int64_t k_sh, int64_t k_st, int64_t cs_b, int64_t cs_t, int q_dtype,
-                         int k_dtype, int cs_dtype, int q_out_dtype, int k_out_dtype, int backward,
-                         void* stream) {
+extern "C" int soup_rope_sum(const void* q, const void* q_add, const void* k, const void* cos,
+                             const void* sin, void* q_out, void* k_out, int64_t b, int64_t hq,
+                             int64_t hk, int64_t t, int64_t d, int64_t q_sb, int64_t q_sh,
+                             int64_t q_st, int64_t k_sb, int64_t k_sh, int64_t k_st, int64_t cs_b,
+                             int64_t cs_t, int64_t qa_sb, int64_t qa_sh, int64_t qa_st,
+                             int64_t qo_sb, int64_t qo_sh, int64_t qo_st,
+                             int64_t ko_sb, int64_t ko_sh, int64_t ko_st, int q_dtype,
+                             int q_add_dtype, int k_dtype, int cs_dtype, int q_out_dtype,
+                             int k_out_dtype, int backward, void* stream) {
   using namespace soup;
   if (!q) hq = 0;
   if (!k) hk = 0;
+  if (!hq) q_add = nullptr;
   if (b == 0 || t == 0 || hq + hk == 0) return SOUP_OK;
   if (b < 0 || t < 0 || hq < 0 || hk < 0 || d <= 0 || (d & 1))
     SOUP_FAIL(SOUP_ERR_ARG, "rope: bad shape (head_dim must be even)");
@@ -234,32 +278,42 @@ extern "C" int soup_rope(const void* q, const void* k, const void* cos, const vo
   if (!is_float_dtype(cs_dtype) || (hq && !(is_float_dtype(q_dtype) && is_float_dtype(q_out_dtype))) ||
       (hk && !(is_float_dtype(k_dtype) && is_float_dtype(k_out_dtype))))
     SOUP_FAIL(SOUP_ERR_ARG, "rope: unsupported dtype");
+  if (q_add && !is_float_dtype(q_add_dtype)) SOUP_FAIL(SOUP_ERR_ARG, "rope: unsupported dtype of q's second term");
   RopeArgs a;
   a.x[0] = q; a.x[1] = k; a.out[0] = q_out; a.out[1] = k_out;
+  a.add = q_add; a.adt = q_add ? q_add_dtype : q_dtype;
+  a.asb = qa_sb; a.ash = qa_sh; a.ast = qa_st;
   a.sb[0] = q_sb; a.sh[0] = q_sh; a.st[0] = q_st;
   a.sb[1] = k_sb; a.sh[1] = k_sh; a.st[1] = k_st;
+  a.osb[0] = qo_sb; a.osh[0] = qo_sh; a.ost[0] = qo_st;
+  a.osb[1] = ko_sb; a.osh[1] = ko_sh; a.ost[1] = ko_st;
   a.heads[0] = (int)hq; a.heads[1] = (int)hk;
   a.xdt[0] = q_dtype; a.xdt[1] = k_dtype; a.odt[0] = q_out_dtype; a.odt[1] = k_out_dtype;
   a.cos = cos; a.sin = sin; a.cs_b = cs_b; a.cs_t = cs_t; a.csdt = cs_dtype;
   a.b = b; a.t = t; a.d = (int)d; a.backward = backward;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   bool vec = (d % 16 == 0) && aligned16(cos) && aligned16(sin) && mult8(cs_b) && mult8(cs_t);
-  if (hq) vec = vec && aligned16(q) && aligned16(q_out) && mult8(q_sb) && mult8(q_sh) && mult8(q_st);
-  if (hk) vec = vec && aligned16(k) && aligned16(k_out) && mult8(k_sb) && mult8(k_sh) && mult8(k_st);
+  if (hq) vec = vec && aligned16(q) && aligned16(q_out) && mult8(q_sb) && mult8(q_sh) && mult8(q_st) &&
+              mult8(qo_sb) && mult8(qo_sh) && mult8(qo_st) &&
+              (!q_add || (aligned16(q_add) && mult8(qa_sb) && mult8(qa_sh) && mult8(qa_st)));
+  if (hk) vec = vec && aligned16(k) && aligned16(k_out) && mult8(k_sb) && mult8(k_sh) && mult8(k_st) &&
+              mult8(ko_sb) && mult8(ko_sh) && mult8(ko_st);
   // The pipelined kernel: both tensors with a position's heads adjacent (stride d between heads),
   // one element size for q and k, a slot that fits the ring.
   const int xb = dtype_size(hq ? q_dtype : k_dtype);
   const bool adjacent = vec && (!hq || q_sh == d) && (!hk || k_sh == d) &&
-                        (!hq || !hk || dtype_size(q_dtype) == dtype_size(k_dtype));
+                        (!hq || !hk || dtype_size(q_dtype) == dtype_size(k_dtype)) &&
+                        (!q_add || (dtype_size(q_add_dtype) == dtype_size(q_dtype) && qa_sh == d));
   rowpipe::Plan plan = {8, 0, 1, 1, 0, 0};
   const int chunks = (int)(d / 2) / 4;
   if (adjacent && chunks > 0 && 32 % chunks == 0)
-    plan = rowpipe::make_plan((size_t)(hq + hk) * d * xb, 0, false, b * t);
+    plan = rowpipe::make_plan((size_t)(hq + hk + (q_add ? hq : 0)) * d * xb, 0, false, b * t);
   int* status = plan.stages ? rowpipe::status_word() : nullptr;
   if (plan.stages && status) {
     const int dt0 = hq ? q_dtype : k_dtype;
     const bool same = (!hq || (q_dtype == dt0 && q_out_dtype == dt0)) &&
-                      (!hk || (k_dtype == dt0 && k_out_dtype == dt0)) && cs_dtype == dt0;
+                      (!hk || (k_dtype == dt0 && k_out_dtype == dt0)) && cs_dtype == dt0 &&
+                      (!q_add || q_add_dtype == dt0);
 #define SOUP_ROPE_P(XB_, DT_)                                                                    \
   do {                                                                                            \
     auto kernel = rope_pipe_kernel<XB_, DT_>;                                                     \
@@ -291,4 +345,17 @@ extern "C" int soup_rope(const void* q, const void* k, const void* cos, const vo
   }
   SOUP_CHECK_LAUNCH("rope");
   return SOUP_OK;
+}
+
+extern "C" int soup_rope(const void* q, const void* k, const void* cos, const void* sin,
+                         void* q_out, void* k_out, int64_t b, int64_t hq, int64_t hk, int64_t t,
+                         int64_t d, int64_t q_sb, int64_t q_sh, int64_t q_st, int64_t k_sb,
+                         int64_t k_sh, int64_t k_st, int64_t cs_b, int64_t cs_t, int q_dtype,
+                         int k_dtype, int cs_dtype, int q_out_dtype, int k_out_dtype, int backward,
+                         void* stream) {
+  // contiguous [b, h, t, d] outputs, no second term
+  return soup_rope_sum(q, nullptr, k, cos, sin, q_out, k_out, b, hq, hk, t, d, q_sb, q_sh, q_st,
+                       k_sb, k_sh, k_st, cs_b, cs_t, 0, 0, 0, hq * t * d, t * d, d, hk * t * d, t * d, d,
+                       q_dtype, q_dtype, k_dtype, cs_dtype, q_out_dtype, k_out_dtype, backward,
+                       stream);
 }

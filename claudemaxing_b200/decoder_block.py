@@ -1,0 +1,319 @@
+"""One decoder block of the packed 4-bit LoRA training step as a short chain of fused steps.
+
+The per-op patches keep transformers' block as it is: every 4-bit projection returns its fp16
+product cast back to fp32, the adapter output is added in a kernel of its own, q and k are rotated
+in fp32 and cast to fp16 again for the attention, the residual sums are separate mixed-dtype adds,
+and backward mirrors each of those. At a few thousand packed tokens each of these elementwise
+kernels costs a launch and a pass over [tokens, hidden]: about a quarter of the step on B200. This
+module computes the same block with those passes folded into the kernels next to them:
+
+* q, k and v come from one GEMM on the block's dequantised weights (adjacent in the buffer all of
+  a block's projections are dequantised into) and stay fp16; `soup_rope_sum` adds the adapter
+  output to q in fp32, rotates q and k and writes them as fp16 [tokens, heads, head_dim], which
+  are exactly the values the reference chain reaches (fp32 sum, fp32 rotation, one rounding to
+  fp16 at the attention's cast); v + adapter is one fp16 add (fp32 inside, one rounding);
+* attention is causal attention inside the segments of the packed row (attention.py);
+* o_proj and down_proj add the fp32 residual in the GEMM's epilogue and write fp32;
+* backward rotates dq and dk straight into column blocks of one [tokens, q+k+v] fp16 buffer and
+  forms the input gradient of the three projections in one GEMM with fp32 output; the MLP's two
+  input gradients accumulate in one fp32 output as well.
+
+Where a GEMM now writes its fp32 accumulator (+ residual) instead of rounding the product to fp16
+first, results differ from the per-op chain by that rounding, within the tolerance the reference's
+end-to-end test applies (tests_local/test_lm_head_trainer.py:186-188). The order of the dropout
+draws is the per-op chain's (q_proj's adapter, then v_proj's).
+
+It applies to blocks whose projections are this package's NF4Linear / LoRALinear layers sharing
+one NF4Group (qlora.build_qlora_model), called in training under fp16 autocast with the packed
+row's segment offsets; any other call runs the block's installed forward.
+"""
+
+import types
+
+import torch
+
+from . import lora as lora_mod
+from .attention import segment_attention
+from .rmsnorm import fp16_copy_of
+from .rope import rotate_into
+from .swiglu_recompute import _silu_mul_bwd, _silu_mul_fwd
+
+F16, F32 = torch.float16, torch.float32
+
+
+def _plain_precision(fn):
+    """Runs `fn` with autocast off: its GEMMs take fp16 operands and state their output dtype
+    themselves, and autocast would cast the fp32 residual of an `addmm` down to fp16."""
+    import functools
+
+    @functools.wraps(fn)
+    def wrapped(*args, **kwargs):
+        with torch.autocast("cuda", enabled=False):
+            return fn(*args, **kwargs)
+
+    return wrapped
+
+
+def _base(module):
+    return getattr(module, "base_layer", module)
+
+
+class BlockPlan:
+    """What `fused_block_forward` needs to know about one decoder block, checked once."""
+
+    def __init__(self, layer):
+        attn, mlp = layer.self_attn, layer.mlp
+        self.layer = layer
+        self.q, self.k, self.v, self.o = attn.q_proj, attn.k_proj, attn.v_proj, attn.o_proj
+        self.gate, self.up, self.down = mlp.gate_proj, mlp.up_proj, mlp.down_proj
+        self.head_dim = attn.head_dim
+        self.why_not = self._structure()
+        self._bias = None
+
+    def _structure(self):
+        seven = (self.q, self.k, self.v, self.o, self.gate, self.up, self.down)
+        bases = [_base(m) for m in seven]
+        if not all(getattr(b, "_soup_nf4_linear", False) for b in bases):
+            return "a projection is not an NF4Linear"
+        group = bases[0].group
+        if group is None or any(b.group is not group for b in bases):
+            return "the projections do not share one NF4Group"
+        if any(b.compute_dtype != F16 for b in bases):
+            return "a projection computes in another dtype than fp16"
+        if any(m is not b for m, b in zip(seven[3:], bases[3:])):
+            return "an adapter on o_proj or the MLP"
+        if bases[3].bias is not None or any(b.bias is not None for b in bases[4:]):
+            return "a bias on o_proj or the MLP"
+        if group.stacked(bases[:3], F16, probe=True) is None:
+            return "q, k and v weights are not adjacent in the group's buffer"
+        if getattr(getattr(self.layer.mlp, "config", None), "hidden_act", "silu") != "silu":
+            return "another activation than silu"
+        d = self.head_dim
+        if d % 16 or d > 256 or any(b.out_features % d for b in bases[:3]):
+            return "head dimension"
+        if bases[1].out_features != bases[2].out_features:
+            return "k and v widths differ"
+        return ""
+
+    def qkv_bias(self, device):
+        """fp16 [q + k + v] bias of the stacked projection (zeros where a projection has none), or
+        None when none of the three has one."""
+        bases = [_base(m) for m in (self.q, self.k, self.v)]
+        if all(b.bias is None for b in bases):
+            return None
+        if self._bias is None or self._bias.device != device:
+            parts = [(b.bias.detach().to(device=device, dtype=F16) if b.bias is not None
+                      else torch.zeros(b.out_features, dtype=F16, device=device)) for b in bases]
+            self._bias = torch.cat(parts)
+        return self._bias
+
+    def adapter(self, module, x):
+        """(A, B, p, scaling) of a LoRALinear whose adapter LoRABranch reproduces for this input;
+        None for a bare projection; False when the adapter needs the module's own forward."""
+        if module is _base(module):
+            return None
+        if not lora_mod.branch_covers(x, module.p, module.training):
+            return False
+        return module.lora_A.weight, module.lora_B.weight, float(module.p), float(module.scaling)
+
+
+class _QKVRope(torch.autograd.Function):
+    """(x16 @ [Wq; Wk; Wv]^T + bias) split into q (+ adapter), k, v (+ adapter); q and k rotated;
+    all three returned as fp16 [tokens, heads, head_dim]."""
+
+    @staticmethod
+    @_plain_precision
+    def forward(ctx, x, x16, lora_q, lora_v, cos, sin, plan):
+        bases = [_base(m) for m in (plan.q, plan.k, plan.v)]
+        n, d = x16.numel() // x16.shape[-1], plan.head_dim
+        nq, nk = bases[0].out_features, bases[1].out_features
+        rows = x16.reshape(n, x16.shape[-1])
+        w = bases[0].group.stacked(bases, F16)
+        bias = plan.qkv_bias(x16.device)
+        qkv = torch.mm(rows, w.t()) if bias is None else torch.addmm(bias, rows, w.t())
+        hq, hk = nq // d, nk // d
+        q_out = torch.empty(n, hq, d, dtype=F16, device=x16.device)
+        k_out = torch.empty(n, hk, d, dtype=F16, device=x16.device)
+
+        def heads_first(t, h):   # [n, h*d] (any row stride) seen as [1, h, n, d]
+            return t.unflatten(-1, (h, d)).unsqueeze(0).transpose(1, 2)
+
+        rotate_into(heads_first(qkv[:, :nq], hq),
+                    None if lora_q is None else heads_first(lora_q.reshape(n, nq), hq),
+                    heads_first(qkv[:, nq:nq + nk], hk), cos, sin,
+                    q_out.unsqueeze(0).transpose(1, 2), k_out.unsqueeze(0).transpose(1, 2))
+        v_rows = qkv[:, nq + nk:]
+        v_out = v_rows.contiguous() if lora_v is None else v_rows + lora_v.reshape(n, nk)
+        ctx.save_for_backward(cos, sin)
+        ctx.plan, ctx.sizes, ctx.x_shape = plan, (n, d, nq, nk, hq, hk), x.shape
+        ctx.lora_shapes = (None if lora_q is None else lora_q.shape, None if lora_v is None else lora_v.shape)
+        return q_out, k_out, v_out.view(n, hk, d)
+
+    @staticmethod
+    @_plain_precision
+    def backward(ctx, dq, dk, dv):
+        cos, sin = ctx.saved_tensors
+        plan, (n, d, nq, nk, hq, hk) = ctx.plan, ctx.sizes
+        dq, dk = (g if g.stride(-1) == 1 else g.contiguous() for g in (dq, dk))
+        dqkv = torch.empty(n, nq + 2 * nk, dtype=F16, device=dq.device)
+
+        def heads_first(t, h):
+            return t.unflatten(-1, (h, d)).unsqueeze(0).transpose(1, 2)
+
+        rotate_into(dq.unsqueeze(0).transpose(1, 2), None, dk.unsqueeze(0).transpose(1, 2), cos, sin,
+                    heads_first(dqkv[:, :nq], hq), heads_first(dqkv[:, nq:nq + nk], hk), backward=True)
+        dqkv[:, nq + nk:].copy_(dv.reshape(n, nk))
+        dx = None
+        if ctx.needs_input_grad[0]:
+            bases = [_base(m) for m in (plan.q, plan.k, plan.v)]
+            w = bases[0].group.stacked(bases, F16)
+            dx = torch.mm(dqkv, w, out_dtype=F32).view(ctx.x_shape)
+        q_shape, v_shape = ctx.lora_shapes
+        return (dx, None,
+                None if q_shape is None else dqkv[:, :nq].view(q_shape),
+                None if v_shape is None else dqkv[:, nq + nk:].view(v_shape),
+                None, None, None)
+
+
+class _ProjectAddResidual(torch.autograd.Function):
+    """residual + y @ W^T with the sum formed in the GEMM's fp32 epilogue (y fp16 [n, k], residual
+    fp32 [..., h], W the dequantised weight of a frozen bias-free NF4Linear)."""
+
+    @staticmethod
+    @_plain_precision
+    def forward(ctx, y, residual, linear):
+        w = linear.dequantized(F16)
+        h = residual.shape[-1]
+        out = torch.addmm(residual.reshape(-1, h), y, w.t(), out_dtype=F32).view(residual.shape)
+        ctx.linear, ctx.y_shape = linear, y.shape
+        return out
+
+    @staticmethod
+    @_plain_precision
+    def backward(ctx, grad):
+        dy = None
+        if ctx.needs_input_grad[0]:
+            g16 = grad.reshape(-1, grad.shape[-1]).to(F16)
+            dy = torch.mm(g16, ctx.linear.dequantized(F16)).view(ctx.y_shape)
+        return dy, (grad if ctx.needs_input_grad[1] else None), None
+
+
+class _GatedMLPAddResidual(torch.autograd.Function):
+    """residual + down(silu(gate(x)) * up(x)) for frozen 4-bit projections, keeping only the fp16
+    input for backward (the recompute of solution/swiglu_recompute.py:138-215), the residual sum
+    in down_proj's epilogue and the two input gradients in one fp32 accumulator."""
+
+    @staticmethod
+    @_plain_precision
+    def forward(ctx, x, x16, residual, plan):
+        rows = x16.reshape(-1, x16.shape[-1])
+        gate = torch.mm(rows, plan.gate.dequantized(F16).t())
+        up = torch.mm(rows, plan.up.dequantized(F16).t())
+        act = torch.empty_like(gate)
+        _silu_mul_fwd(gate, up, act, False)   # fp32 input, fp16 products: silu is not rounded first
+        del gate, up
+        h = residual.shape[-1]
+        out = torch.addmm(residual.reshape(-1, h), act, plan.down.dequantized(F16).t(),
+                          out_dtype=F32).view(residual.shape)
+        ctx.save_for_backward(x16)
+        ctx.plan, ctx.x_shape = plan, x.shape
+        return out
+
+    @staticmethod
+    @_plain_precision
+    def backward(ctx, grad):
+        (x16,) = ctx.saved_tensors
+        plan = ctx.plan
+        dx = None
+        if ctx.needs_input_grad[0]:
+            rows = x16.reshape(-1, x16.shape[-1])
+            g16 = grad.reshape(-1, grad.shape[-1]).to(F16)
+            d_act = torch.mm(g16, plan.down.dequantized(F16))
+            w_gate, w_up = plan.gate.dequantized(F16), plan.up.dequantized(F16)
+            gate, up = torch.mm(rows, w_gate.t()), torch.mm(rows, w_up.t())
+            _silu_mul_bwd(d_act, gate, up, gate, up, False)   # gradients overwrite the recomputed pair
+            dx = torch.mm(gate, w_gate, out_dtype=F32)
+            dx = torch.addmm(dx, up, w_up, out_dtype=F32).view(ctx.x_shape)
+        return dx, None, (grad if ctx.needs_input_grad[2] else None), None
+
+
+def _why_not(plan, hidden, attention_mask, past_key_values, position_embeddings, kwargs):
+    """Why this call runs the block's installed forward ("" when the fused chain covers it)."""
+    if plan.why_not:
+        return plan.why_not
+    if type(_base(plan.q)).fused_gemm:
+        return "the projections are set to run on the GEMM that dequantises in its prologue"
+    cu = kwargs.get("cu_seq_lens_q")
+    if attention_mask is not None or not isinstance(cu, torch.Tensor) or kwargs.get("cu_seq_lens_k") is not cu:
+        return "not a packed row given as segment offsets"
+    if past_key_values is not None or position_embeddings is None:
+        return "a cache, or no rotary tables"
+    if not (isinstance(hidden, torch.Tensor) and hidden.is_cuda and hidden.dtype == F32
+            and hidden.dim() == 3 and hidden.shape[0] == 1 and hidden.is_contiguous()):
+        return "hidden states are not one contiguous fp32 CUDA row"
+    if not (plan.layer.training and torch.is_grad_enabled() and lora_mod._autocast_fp16()):
+        return "not a training call under fp16 autocast"
+    attn = plan.layer.self_attn
+    if getattr(attn, "sliding_window", None) is not None or (attn.training and attn.attention_dropout):
+        return "sliding window or attention dropout"
+    if kwargs.get("output_attentions", False):
+        return "attention weights are wanted"
+    cos, sin = position_embeddings
+    if cos.dim() != 3 or cos.shape[0] != 1 or cos.shape[-1] != plan.head_dim or cos.requires_grad:
+        return "rotary tables of another shape"
+    return ""
+
+
+def fused_block_forward(layer, hidden_states, attention_mask=None, position_ids=None,
+                        past_key_values=None, use_cache=False, position_embeddings=None, **kwargs):
+    """Qwen2DecoderLayer.forward for the covered case (see the module docstring); same arguments,
+    same return value."""
+    plan = layer._soup_block
+    if _why_not(plan, hidden_states, attention_mask, past_key_values, position_embeddings, kwargs):
+        return plan.installed(hidden_states, attention_mask=attention_mask, position_ids=position_ids,
+                              past_key_values=past_key_values, use_cache=use_cache,
+                              position_embeddings=position_embeddings, **kwargs)
+    x = layer.input_layernorm(hidden_states)
+    adapters = [plan.adapter(m, x) for m in (plan.q, plan.k, plan.v)]
+    if adapters[1] is not None or any(a is False for a in adapters):
+        # an adapter on k_proj, or one LoRABranch does not reproduce: the installed forward (the
+        # norm runs again there; nothing else has happened yet)
+        return plan.installed(hidden_states, attention_mask=attention_mask, position_ids=position_ids,
+                              past_key_values=past_key_values, use_cache=use_cache,
+                              position_embeddings=position_embeddings, **kwargs)
+    x16 = fp16_copy_of(x)
+    if x16 is None:
+        x16 = x.detach().to(F16)
+    branches = [None if a is None else lora_mod.LoRABranch.apply(x, x16, *a) for a in adapters]
+    cos, sin = position_embeddings
+    q, k, v = _QKVRope.apply(x, x16, branches[0], branches[2], cos.contiguous(), sin.contiguous(), plan)
+    n = q.shape[0]
+    cu = kwargs["cu_seq_lens_q"]
+    attended = segment_attention(q.unsqueeze(0).transpose(1, 2), k.unsqueeze(0).transpose(1, 2),
+                                 v.unsqueeze(0).transpose(1, 2), cu, kwargs.get("max_length_q", n),
+                                 layer.self_attn.scaling)
+    hidden_states = _ProjectAddResidual.apply(attended.reshape(n, -1), hidden_states, plan.o)
+    x = layer.post_attention_layernorm(hidden_states)
+    x16 = fp16_copy_of(x)
+    if x16 is None:
+        x16 = x.detach().to(F16)
+    return _GatedMLPAddResidual.apply(x, x16, hidden_states, plan)
+
+
+def install_fused_blocks(model):
+    """Gives every decoder block of `model` whose structure the fused chain covers the fused
+    forward (on the instance: other models keep transformers' class). Returns the number of
+    blocks taken."""
+    taken = 0
+    for layer in model.model.layers:
+        if getattr(layer, "_soup_block", None) is not None:
+            taken += 1
+            continue
+        plan = BlockPlan(layer)
+        if plan.why_not:
+            continue
+        plan.installed = layer.forward
+        layer.__dict__["_soup_block"] = plan
+        layer.forward = types.MethodType(fused_block_forward, layer)
+        taken += 1
+    return taken

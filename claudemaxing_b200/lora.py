@@ -46,6 +46,26 @@ def _unpack(x16, bits, g16, scale, dx_dtype):
     return xd, dx
 
 
+def _fp16_pair(weight_a, weight_b):
+    """fp16 copies of the two adapter weights from one launch (they are 50 KB each: two separate
+    casts are two launches' worth of latency and nothing else)."""
+    if weight_a.dtype == weight_b.dtype == torch.float32 and weight_a.is_cuda:
+        a16 = torch.empty(weight_a.shape, dtype=torch.float16, device=weight_a.device)
+        b16 = torch.empty(weight_b.shape, dtype=torch.float16, device=weight_b.device)
+        torch._foreach_copy_([a16, b16], [weight_a.detach(), weight_b.detach()])
+        return a16, b16
+    return weight_a.to(torch.float16), weight_b.to(torch.float16)
+
+
+def _weight_gradient(grad_rows, input_rows, dtype):
+    """grad_rows^T @ input_rows (both fp16, [rows, out] and [rows, in]) in `dtype`. For an fp32
+    weight the GEMM writes its fp32 accumulator directly: no fp16 rounding (or overflow at a large
+    loss scale) of a sum over thousands of rows, and no cast kernel behind the GEMM."""
+    if dtype == torch.float32 and grad_rows.is_cuda and grad_rows.dtype == input_rows.dtype == torch.float16:
+        return torch.mm(grad_rows.t(), input_rows, out_dtype=torch.float32)
+    return grad_rows.t().mm(input_rows).to(dtype)
+
+
 class LoRABranch(torch.autograd.Function):
     """fp16 `lora_B(lora_A(dropout(x))) * scaling` for fp32 x under fp16 autocast."""
 
@@ -56,7 +76,7 @@ class LoRABranch(torch.autograd.Function):
         scale = 1.0 / (1.0 - p)
         xd, bits = _pack(x, mask, scale)  # from the fp32 x: lora_A's input exactly as peft's
         del mask
-        a16, b16 = weight_a.to(torch.float16), weight_b.to(torch.float16)
+        a16, b16 = _fp16_pair(weight_a, weight_b)
         a = torch.nn.functional.linear(xd, a16)
         out = torch.nn.functional.linear(a, b16) * scaling
         ctx.save_for_backward(x16, bits, a, a16, b16)   # the fp16 adapter copies are 50 KB each
@@ -69,13 +89,13 @@ class LoRABranch(torch.autograd.Function):
         x16, bits, a, a16, b16 = ctx.saved_tensors
         g = grad.to(torch.float16) * ctx.scaling
         g2 = g.reshape(-1, g.shape[-1])
-        grad_b = g2.t().mm(a.reshape(-1, a.shape[-1]))
+        grad_b = _weight_gradient(g2, a.reshape(-1, a.shape[-1]), ctx.weight_dtypes[1])
         grad_a_in = g.matmul(b16)
         ga2 = grad_a_in.reshape(-1, grad_a_in.shape[-1])
         grad_xd = grad_a_in.matmul(a16)
         xd, dx = _unpack(x16, bits, grad_xd.contiguous(), ctx.scale, ctx.x_dtype)
-        grad_a = ga2.t().mm(xd.reshape(-1, xd.shape[-1]))
-        return dx, None, grad_a.to(ctx.weight_dtypes[0]), grad_b.to(ctx.weight_dtypes[1]), None, None
+        grad_a = _weight_gradient(ga2, xd.reshape(-1, xd.shape[-1]), ctx.weight_dtypes[0])
+        return dx, None, grad_a, grad_b, None, None
 
 
 class _SharedCopy:

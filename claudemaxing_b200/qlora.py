@@ -129,27 +129,44 @@ class _MatMul4Bit(torch.autograd.Function):
             direct = ctx.x_dtype if ctx.x_dtype in (torch.float16, torch.float32) else torch.float16
             dx = nf4_linear_dx([grad], [(layer.packed, layer.quant_state)], direct)
             return dx.to(ctx.x_dtype), None, None
-        dx = torch.matmul(grad, layer.dequantized(grad.dtype, backward=True))
+        dx = torch.matmul(grad, layer.dequantized(grad.dtype))
         return dx.to(ctx.x_dtype), None, None
 
 
 class _DequantBuffers:
-    """Two fp16 weight buffers per (device, dtype) shared by all groups of a model: the block in
-    use and the block that is being dequantised ahead on a side stream."""
+    """The fp16 weight buffers of one (device, dtype) that all groups of a model share, each the
+    size of the largest block, kept in order of last use."""
 
     def __init__(self, numel, dtype, device):
-        self.flat = [torch.empty(numel, dtype=dtype, device=device) for _ in range(2)]
-        self.owner = [None, None]      # weakref to the group whose weights the buffer holds
-        self.key = [None, None]
-        self.ready = [None, None]      # event of a prefetch the main stream has not waited for yet
-        self.last = None               # weakref to the group served last
-        self.side = torch.cuda.Stream(device=device)
+        self.numel, self.dtype, self.device = numel, dtype, device
+        self.flat = []                 # allocated on demand, up to NF4Group.resident_blocks(numel)
+        self.owner = []                # weakref to the group whose weights the buffer holds
+        self.key = []
+        self.order = []                # buffer indices, least recently used first
 
     def holds(self, group, key):
-        for i in (0, 1):
-            if self.owner[i] is not None and self.owner[i]() is group and self.key[i] == key:
+        for i, owner in enumerate(self.owner):
+            if owner is not None and owner() is group and self.key[i] == key:
                 return i
         return None
+
+    def touch(self, i):
+        if i in self.order:
+            self.order.remove(i)
+        self.order.append(i)
+
+    def take(self, limit):
+        """Index of a buffer to overwrite: one whose contents are unknown, a new one while fewer
+        than `limit` exist, else the one used longest ago."""
+        for i, owner in enumerate(self.owner):
+            if owner is None:
+                return i
+        if len(self.flat) < limit:
+            self.flat.append(torch.empty(self.numel, dtype=self.dtype, device=self.device))
+            self.owner.append(None)
+            self.key.append(None)
+            return len(self.flat) - 1
+        return self.order[0]
 
 
 class NF4Group:
@@ -157,34 +174,35 @@ class NF4Group:
 
     A block's seven weights are used right after one another (q, k, v, o, gate, up, down forward;
     the reverse in backward), each too small to fill the GPU with its own launch. One batched
-    launch writes all of them into one of two buffers that every group of the model shares (the
-    largest block's fp16 weights each, 94 MB for Qwen2.5-1.5B); a block stays resident until two
-    other blocks have been used, so backward finds the last two blocks of forward still there. Any
-    order of use stays correct: a block that is not in a buffer is dequantised on the spot. The
-    returned weight is a view that a later block overwrites: use it on the current stream at once
-    and do not keep it.
+    launch writes all of them into a buffer of a small pool that every group of the model shares
+    (the largest block's fp16 weights each, 94 MB for Qwen2.5-1.5B). The pool holds as many blocks
+    as fit `SOUP_NF4_RESIDENT_MB` (default 4096, at least two blocks), replaced in order of last
+    use: on a 180 GB part the 2.6 GB of a whole Qwen2.5-1.5B stay resident from forward to
+    backward, so a training step dequantises every block once instead of twice; a larger model
+    keeps the blocks backward reaches first. Any order of use stays correct: a block that is not
+    in a buffer is dequantised on the spot. The returned weight is a view that a later block may
+    overwrite: use it on the current stream at once and do not keep it.
 
-    With `NF4Group.prefetch = True` the neighbour the computation will reach next (`next` going
-    forward, `prev` in backward) is dequantised on a side stream into the other buffer while the
-    current block's GEMMs run. Measured on the Qwen2.5-1.5B step this is slower (24.2 ms against
-    22.5 ms per captured step): the dequant CTAs take SM slots and HBM bandwidth from the GEMMs
-    for longer than the 26 us they would have cost in line. It is off by default.
+    Dequantising the next block ahead on a side stream was tried and removed: on the
+    Qwen2.5-1.5B step it was slower (24.2 ms against 22.5 ms per captured step), the dequant CTAs
+    taking SM slots and HBM bandwidth from the GEMMs for longer than the 26 us they cost in line.
     """
 
     _buffers = {}  # (device, dtype) -> _DequantBuffers
-    prefetch = os.environ.get("SOUP_NF4_PREFETCH", "0") == "1"
+    resident_mb = int(os.environ.get("SOUP_NF4_RESIDENT_MB", "4096"))
+
+    @classmethod
+    def resident_blocks(cls, numel, dtype):
+        per_block = numel * torch.empty((), dtype=dtype).element_size()
+        return max(2, (cls.resident_mb << 20) // max(per_block, 1))
 
     @classmethod
     def forget(cls):
-        """Declares every buffer's contents unknown (after waiting for prefetches still running).
-        A CUDA graph must not start from weights that happen to be resident at capture time, and
-        what a capture "ran" never ran."""
+        """Declares every buffer's contents unknown. A CUDA graph must not start from weights that
+        happen to be resident at capture time, and what a capture "ran" never ran."""
         for bufs in cls._buffers.values():
-            for i in (0, 1):
-                if bufs.ready[i] is not None:
-                    torch.cuda.current_stream(bufs.flat[i].device).wait_event(bufs.ready[i])
-                bufs.owner[i] = bufs.key[i] = bufs.ready[i] = None
-            bufs.last = None
+            bufs.owner = [None] * len(bufs.flat)
+            bufs.key = [None] * len(bufs.flat)
 
     def __init__(self, layers):
         self.layers = list(layers)
@@ -216,42 +234,35 @@ class NF4Group:
                              outs=self._views(bufs.flat[i]))
         bufs.owner[i], bufs.key[i] = weakref.ref(self), self._key()
 
-    def weight(self, layer, dtype, backward=False):
+    def stacked(self, layers, dtype, probe=False):
+        """The dequantised weights of consecutive `layers` of this group as one
+        [sum of out_features, in_features] matrix (they are adjacent in the buffer when each one's
+        element count is a multiple of 128), or None when they are not adjacent or differ in
+        in_features. With `probe` only the answer to that question (True / None): nothing is
+        dequantised."""
+        index = [self.layers.index(l) for l in layers]
+        adjacent = all(j == i + 1 and self.offsets[j] == self.offsets[i] + self.sizes[i]
+                       for i, j in zip(index, index[1:]))
+        if not adjacent or len({l.in_features for l in layers}) != 1:
+            return None
+        if probe:
+            return True
+        first = self.weight(layers[0], dtype)
+        flat = first.reshape(-1)
+        total = sum(l.out_features for l in layers)
+        return torch.as_strided(flat, (total, layers[0].in_features), (layers[0].in_features, 1))
+
+    def weight(self, layer, dtype):
         device = layer.packed.device
         bufs = NF4Group._buffers.get((device, dtype))
-        if bufs is None or bufs.flat[0].numel() < self.offsets[-1]:
+        if bufs is None or bufs.numel < self.offsets[-1]:
             bufs = _DequantBuffers(self.offsets[-1], dtype, device)
             NF4Group._buffers[(device, dtype)] = bufs
-        main = torch.cuda.current_stream(device)
         i = bufs.holds(self, self._key())
         if i is None:
-            # not resident: take the buffer that does not hold the block served last
-            i = 0
-            if bufs.last is not None and bufs.owner[0] is not None and bufs.owner[0]() is bufs.last():
-                i = 1
-            if bufs.ready[i] is not None:       # an unused prefetch is still running into it
-                main.wait_event(bufs.ready[i])
-                bufs.ready[i] = None
+            i = bufs.take(self.resident_blocks(bufs.numel, dtype))
             self._fill(bufs, i, dtype)
-        elif bufs.ready[i] is not None:         # prefetched: the main stream joins the side stream
-            main.wait_event(bufs.ready[i])
-            bufs.ready[i] = None
-        moved_on = bufs.last is None or bufs.last() is not self
-        bufs.last = weakref.ref(self)
-        neighbour = self.prev if backward else self.next
-        if (moved_on and NF4Group.prefetch and neighbour is not None
-                and neighbour.offsets[-1] <= bufs.flat[0].numel()
-                and bufs.holds(neighbour, neighbour._key()) is None):
-            j = 1 - i
-            # everything enqueued so far (the last user of the other buffer included) comes first
-            fence = torch.cuda.Event()
-            fence.record(main)
-            with torch.cuda.stream(bufs.side):
-                bufs.side.wait_event(fence)
-                neighbour._fill(bufs, j, dtype)
-                done = torch.cuda.Event()
-                done.record(bufs.side)
-            bufs.ready[j] = done
+        bufs.touch(i)
         return self._views(bufs.flat[i])[self.layers.index(layer)]
 
 
@@ -287,11 +298,11 @@ class NF4Linear(torch.nn.Module):
         self.quant_state = self.quant_state.to(self.packed.device)
         return self
 
-    def dequantized(self, dtype, backward=False):
+    def dequantized(self, dtype):
         """The [out, in] weight in `dtype`: a fresh tensor, or a short-lived view of the group's
-        buffer (`backward` tells the group which neighbour to dequantise ahead)."""
+        buffer."""
         if self.group is not None:
-            return self.group.weight(self, dtype, backward)
+            return self.group.weight(self, dtype)
         return dequantize_nf4(self.packed, self.quant_state, dtype)
 
     def takes_fused_gemm(self, operand):
@@ -345,13 +356,14 @@ QWEN25_1P5B = dict(hidden_size=1536, intermediate_size=8960, num_hidden_layers=2
 
 
 def build_qlora_model(device, config=None, lora_targets=("q_proj", "v_proj"), r=16, alpha=32,
-                      dropout=0.05, seed=0, group_dequant=True):
+                      dropout=0.05, seed=0, group_dequant=True, fused_blocks=True):
     """A Qwen2 causal LM prepared the way the reference's run prepares it, without its packages:
     random fp16 weights of the given architecture (default Qwen2.5-1.5B), every decoder
     projection NF4-quantised (blocksize 64, double-quantised absmax), norms and the tied
     embedding/head in fp32 and frozen, LoRA (fp32 A Kaiming-uniform, B zero) on q_proj and v_proj.
-    With `group_dequant` each block's seven weights are dequantised by one launch (NF4Group).
-    Returns (model, list of trainable LoRA parameters)."""
+    With `group_dequant` each block's seven weights are dequantised by one launch (NF4Group);
+    with `fused_blocks` as well, the packed training call runs each block as the fused chain of
+    decoder_block.py. Returns (model, list of trainable LoRA parameters)."""
     from transformers import Qwen2Config, Qwen2ForCausalLM
 
     cfg = dict(QWEN25_1P5B)
@@ -392,6 +404,10 @@ def build_qlora_model(device, config=None, lora_targets=("q_proj", "v_proj"), r=
     lora_params = [p for n, p in model.named_parameters() if "lora_" in n]
     for p in lora_params:
         p.requires_grad_(True)
+    if group_dequant and fused_blocks:
+        from .decoder_block import install_fused_blocks
+
+        install_fused_blocks(model)
     torch.cuda.empty_cache() if torch.cuda.is_available() else None
     return model, lora_params
 
@@ -436,15 +452,17 @@ def qlora_step(model, batch, optimizer=None, scaler=None, num_items=None):
 class CapturedStep:
     """One QLoRA training step replayed from CUDA graphs instead of ~3000 eager launches.
 
-    The packed real tokens of a batch are padded up to `bucket_tokens` (padding tokens attend to
-    nothing but themselves and carry ignore labels, so loss and gradients are those of the real
-    tokens) and copied into fixed device buffers. Forward, backward and the loss-scaled gradient
+    The packed real tokens of a batch are padded up to `bucket_tokens` (the padding tokens are
+    an attention segment of their own and carry ignore labels, so loss and gradients are those of
+    the real tokens) and copied into fixed device buffers, with the offsets of the batch rows in
+    the packed row for the attention (a later batch may have at most as many rows as the one the
+    step was captured on). Forward, backward and the loss-scaled gradient
     clean-up are one graph; the optimizer step is a second one, so a data-parallel job can
     all-reduce the LoRA gradients (one flat fp32 buffer that every `.grad` is a view of) between
     the two. The eager launch sequence it replaces is the trainer's compute_loss → backward →
     optimizer.step of the reference (solution/lm_head_loss.py:375-430 wraps the first).
 
-    `load()` takes a host or device batch and moves 4 × bucket_tokens int64 values; `run()` replays
+    `load()` takes a host or device batch and moves 3 × bucket_tokens int64 values and the row offsets; `run()` replays
     and returns the (device) loss of the step. Construction runs `warmup` eager steps and the
     capture on `batch`, then puts the parameters, the optimizer state and the loss scale back to
     what they were, so the first `run()` is the first training step. The optimizer must be built
@@ -469,7 +487,9 @@ class CapturedStep:
         self.bucket = n
         self.ids = torch.zeros(1, n, dtype=torch.int64, device=dev)
         self.col = torch.zeros(1, n, dtype=torch.int64, device=dev)
-        self.row = torch.arange(n, dtype=torch.int64, device=dev)[None].clone()
+        # segment offsets of the packed row: the batch rows, then the padding tokens as one segment
+        self.max_rows = int(batch["input_ids"].shape[0])
+        self.cu_rows = torch.zeros(self.max_rows + 2, dtype=torch.int32, device=dev)
         self.target = torch.full((1, n), -100, dtype=torch.int64, device=dev)
         self.index = torch.arange(n, dtype=torch.int64, device=dev)
         # divisor of the loss: the labelled tokens of the whole job divided by the ranks, so that
@@ -490,7 +510,7 @@ class CapturedStep:
     # ------------------------------------------------------------------ host side of a step
     def load(self, batch):
         """Packs `batch` (input_ids, attention_mask, labels of shape [B, T], host or device) and
-        copies ids / positions / row ids / shifted labels into the graph's buffers."""
+        copies ids / positions / shifted labels / row offsets into the graph's buffers."""
         L = self._L
         ids, mask, labels = batch["input_ids"], batch["attention_mask"], batch["labels"]
         B, T = ids.shape
@@ -498,23 +518,25 @@ class CapturedStep:
         n = keep.numel()
         if n > self.bucket:
             raise ValueError(f"batch has {n} real tokens, the captured step holds {self.bucket}")
+        if B > self.max_rows:
+            raise ValueError(f"batch has {B} rows, the captured step holds {self.max_rows}")
         target = L.shift_labels_left(labels).reshape(-1)[keep]
-        stage = torch.empty(4, self.bucket, dtype=torch.int64, device=ids.device,
+        stage = torch.empty(3, self.bucket, dtype=torch.int64, device=ids.device,
                             pin_memory=not ids.is_cuda)
         stage[0, :n] = ids.reshape(-1)[keep]
         stage[1, :n] = keep % T
-        stage[2, :n] = keep // T
-        stage[3, :n] = target
-        if n < self.bucket:
-            pad = torch.arange(self.bucket - n, dtype=torch.int64, device=ids.device)
-            stage[0, n:] = 0
-            stage[1, n:] = 0
-            stage[2, n:] = B + pad      # a row of its own per padding token
-            stage[3, n:] = -100
+        stage[2, :n] = target
+        stage[0:2, n:] = 0
+        stage[2, n:] = -100
+        ends = torch.bincount(keep // T, minlength=B).cumsum(0)
+        cu = torch.full((self.max_rows + 2,), n, dtype=torch.int32, device=ids.device)
+        cu[0] = 0
+        cu[1:B + 1] = ends
+        cu[-1] = self.bucket
         self.ids.copy_(stage[0:1], non_blocking=True)
         self.col.copy_(stage[1:2], non_blocking=True)
-        self.row.copy_(stage[2:3], non_blocking=True)
-        self.target.copy_(stage[3:4], non_blocking=True)
+        self.target.copy_(stage[2:3], non_blocking=True)
+        self.cu_rows.copy_(cu.pin_memory() if not cu.is_cuda else cu, non_blocking=True)
         labelled = (self.target != -100).sum().to(torch.float32)
         if self.world > 1:
             torch.distributed.all_reduce(labelled, group=self.group)
@@ -524,6 +546,7 @@ class CapturedStep:
 
     def run(self):
         self.graph_fb.replay()
+        NF4Group.forget()           # the replay rewrote the shared weight buffers behind Python's back
         if self.world > 1:
             torch.distributed.all_reduce(self.flat_grad, group=self.group)
             self.flat_grad.div_(self.world)
@@ -533,10 +556,8 @@ class CapturedStep:
     # ------------------------------------------------------------------ captured bodies
     def _forward_backward(self):
         L = self._L
-        row, col = self.row[0], self.col[0]
-        allowed = (row[:, None] == row[None, :]) & (col[None, :] <= col[:, None])
         packed = SimpleNamespace(B=1, T=self.bucket, index=self.index, ids=self.ids, pos=self.col,
-                                 mask=allowed[None, None], target=self.target)
+                                 target=self.target, cu_rows=self.cu_rows, longest=self.bucket)
         self.flat_grad.zero_()
         with torch.autocast("cuda", dtype=torch.float16):
             out = L._packed_forward(self.model, {"use_cache": False,

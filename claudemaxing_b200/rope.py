@@ -47,6 +47,30 @@ def _rotate_pair(q, k, cos, sin, q_dtype, k_dtype, backward):
     return q_out, k_out
 
 
+def rotate_into(q, q_add, k, cos, sin, q_out, k_out, backward=False):
+    """Rotates `q` (+ `q_add`, summed in fp32 first, when given) and `k` into `q_out` and `k_out`.
+    Every tensor is a [batch, heads, seq, head_dim] view with a unit last stride; the outputs are
+    written through their strides, so they may be [batch, seq, heads, head_dim] buffers seen
+    transposed, or column blocks of a wider matrix. One launch (csrc/rope.cu, soup_rope_sum)."""
+    _lib.require_cuda(q, k, cos, sin, q_out, k_out)
+    b, hq, t, d = q.shape
+    if q_add is not None and q_add.shape != q.shape:
+        raise ValueError("q's second term must have q's shape")
+    for x in (q, k, q_out, k_out) + (() if q_add is None else (q_add,)):
+        if x.stride(-1) != 1:
+            raise ValueError("rotate_into needs a unit last stride")
+    cs_b = cos.stride(0) if cos.shape[0] > 1 else 0
+    _lib.call(
+        "soup_rope_sum", _lib.ptr(q), _lib.ptr(q_add), _lib.ptr(k), _lib.ptr(cos), _lib.ptr(sin),
+        _lib.ptr(q_out), _lib.ptr(k_out), b, hq, k.shape[1], t, d,
+        *q.stride()[:3], *k.stride()[:3], cs_b, cos.stride(1),
+        *((0, 0, 0) if q_add is None else q_add.stride()[:3]),
+        *q_out.stride()[:3], *k_out.stride()[:3],
+        _lib.dtype_code(q.dtype), _lib.dtype_code((q_add if q_add is not None else q).dtype),
+        _lib.dtype_code(k.dtype), _lib.dtype_code(cos.dtype), _lib.dtype_code(q_out.dtype),
+        _lib.dtype_code(k_out.dtype), int(backward), _lib.stream_of(q))
+
+
 class RoPE(torch.autograd.Function):
     """`RoPE.apply(q, k, cos, sin) -> (q', k')`; the gradient of a rotation is the rotation by the
     opposite angle, so backward is the same kernel with its `backward` flag set."""

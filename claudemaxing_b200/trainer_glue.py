@@ -15,6 +15,7 @@ import functools
 import torch
 
 from . import lm_head_loss as head
+from .attention import segment_arguments
 from .embedding import shrink_tied_embedding
 
 
@@ -23,15 +24,26 @@ StepTerms = head.StepTerms
 
 @dataclasses.dataclass
 class PackedRow:
-    """A padded batch `[B, T]` reduced to its real tokens as one row `[1, N]`."""
+    """A padded batch `[B, T]` reduced to its real tokens as one row `[1, N]`. The tokens of a
+    batch row stay together and in order, so attention over the packed row is causal attention
+    inside each of the `B` segments that `cu_rows` delimits."""
 
     B: int
     T: int
     index: torch.Tensor     # [N] flat positions of the real tokens in the [B*T] batch
     ids: torch.Tensor       # [1, N]
     pos: torch.Tensor       # [1, N] position ids (restart in every batch row)
-    mask: torch.Tensor      # [1, 1, N, N] bool: same batch row and key not after the query
     target: torch.Tensor    # [1, N] labels shifted left inside their batch row
+    cu_rows: torch.Tensor   # [B + 1] int32: where each batch row's tokens start in the packed row
+    longest: int            # an upper bound of the tokens of one batch row
+
+    @property
+    def mask(self):
+        """[1, 1, N, N] bool, same batch row and key not after the query: the O(N^2) form of
+        `cu_rows`, built only for an attention that cannot take the segments."""
+        from .attention import mask_of_segments
+
+        return mask_of_segments(self.cu_rows, self.ids.shape[1])
 
 
 # --------------------------------------------------------------------------------- packing
@@ -44,19 +56,19 @@ def pack_tokens(ids, mask, labels, position_ids=None):
     if n_real == 0 or n_real == n_rows * width:
         return None
     batch_row = torch.div(real, width, rounding_mode="floor")
-    column = real - batch_row * width
     if position_ids is None:
-        positions = column
+        positions = real - batch_row * width
     elif isinstance(position_ids, torch.Tensor) and position_ids.shape == ids.shape:
         positions = position_ids.reshape(-1).index_select(0, real)
     else:
         return None
-    visible = batch_row.unsqueeze(1).eq(batch_row.unsqueeze(0)) & column.unsqueeze(0).le(column.unsqueeze(1))
+    cu_rows = torch.zeros(n_rows + 1, dtype=torch.int32, device=ids.device)
+    cu_rows[1:] = torch.bincount(batch_row, minlength=n_rows).cumsum(0)
     shifted = head.shift_labels_left(labels.to(ids.device)).reshape(-1).index_select(0, real)
     return PackedRow(B=n_rows, T=width, index=real,
                      ids=ids.reshape(-1).index_select(0, real).unsqueeze(0),
-                     pos=positions.unsqueeze(0), mask=visible.unsqueeze(0).unsqueeze(0),
-                     target=shifted.unsqueeze(0))
+                     pos=positions.unsqueeze(0), target=shifted.unsqueeze(0),
+                     cu_rows=cu_rows, longest=width)
 
 
 def _plain_frozen_linear(module):
@@ -128,8 +140,9 @@ def _packed_forward(lm, kwargs, packed):
     passthrough = dict(kwargs)
     for replaced in ("input_ids", "attention_mask", "position_ids"):
         passthrough.pop(replaced, None)
-    decoded = lm.model(input_ids=packed.ids, attention_mask=packed.mask, position_ids=packed.pos,
-                       **passthrough)
+    for name, value in segment_arguments(packed.cu_rows, packed.longest, packed.ids.shape[1]).items():
+        passthrough.setdefault(name, value)
+    decoded = lm.model(input_ids=packed.ids, position_ids=packed.pos, **passthrough)
     hidden, weight = decoded.last_hidden_state, lm.lm_head.weight
     if head.head_compute_dtype(hidden, weight) == torch.float16:
         loss, terms = head.fused_head_loss(hidden, weight, None,

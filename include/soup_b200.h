@@ -157,6 +157,24 @@ int soup_rope(const void* q, const void* k, const void* cos, const void* sin, vo
               int64_t cs_t, int q_dtype, int k_dtype, int cs_dtype, int q_out_dtype,
               int k_out_dtype, int backward, void* stream);
 
+/* The same rotation with q given as a sum of two tensors and with strided outputs, for a decoder
+ * block that keeps q, k and v in half precision between the projections and the attention:
+ *   q_add  NULL, or q's second term (the adapter branch's output), read through
+ *          (qa_sb, qa_sh, qa_st, 1) and added in fp32 before the rotation, so the result equals rotating the fp32 sum the reference's
+ *          layer forms (base output + adapter output, then solution/rope.py:54-56 on the sum)
+ *   q_out, k_out  written through (qo_sb, qo_sh, qo_st, 1) / (ko_sb, ko_sh, ko_st, 1): any layout
+ *          with a contiguous head row, e.g. [b, t, h, d] for a variable-length attention kernel,
+ *          or a column block of a wider [b*t, n] gradient buffer in backward
+ * No counterpart of its own in the reference (its RoPE.apply takes and returns whole tensors). */
+int soup_rope_sum(const void* q, const void* q_add, const void* k, const void* cos,
+                  const void* sin, void* q_out, void* k_out, int64_t b, int64_t hq, int64_t hk,
+                  int64_t t, int64_t d, int64_t q_sb, int64_t q_sh, int64_t q_st, int64_t k_sb,
+                  int64_t k_sh, int64_t k_st, int64_t cs_b, int64_t cs_t, int64_t qa_sb,
+                  int64_t qa_sh, int64_t qa_st, int64_t qo_sb, int64_t qo_sh, int64_t qo_st,
+                  int64_t ko_sb, int64_t ko_sh, int64_t ko_st,
+                  int q_dtype, int q_add_dtype, int k_dtype, int cs_dtype, int q_out_dtype,
+                  int k_out_dtype, int backward, void* stream);
+
 /* out = round_out(round_gate?(silu(gate)) * up). Replaces silu_mul_fwd_persistent at
  * solution/swiglu_recompute.py:98-100 and :176-178 (kernel :36-48). */
 int soup_silu_mul_fwd(const void* gate, const void* up, void* out, int64_t n, int gate_dtype,

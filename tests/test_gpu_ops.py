@@ -239,6 +239,51 @@ def test_rope_packed_positions_restart_per_row():
     assert abs(oq.float().norm().item() / q.float().norm().item() - 1) < 1e-3
 
 
+@pytest.mark.parametrize("dims", [(1280, 12, 2, 128), (37, 4, 4, 64), (5, 3, 1, 24)])
+@pytest.mark.parametrize("with_term", [True, False])
+def test_rope_of_a_sum_into_strided_outputs_is_the_chain_it_replaces(dims, with_term):
+    """`rotate_into`: fp16 q (a column block of a wider projection output) + fp16 second term,
+    fp32 tables, fp16 [tokens, heads, head_dim] outputs: bit-identical to what the per-op chain
+    reaches (fp32 sum, rotation in fp32 through `rope`, one cast to fp16); and the transposed
+    rotation written into column blocks of a wider gradient buffer."""
+    from claudemaxing_b200.rope import rope, rotate_into
+
+    t, h, kv, d = dims
+    gen = torch.Generator().manual_seed(3)
+    wide = torch.randn(t, (h + 2 * kv) * d, generator=gen).half().to(DEV)   # [q | k | v] columns
+    term = torch.randn(1, t, h * d, generator=gen).half().to(DEV) if with_term else None
+    pos = torch.arange(t, dtype=F32)[None]
+    inv = 1.0 / (1e6 ** (torch.arange(0, d, 2, dtype=F32) / d))
+    emb = torch.cat((pos[..., None] * inv,) * 2, -1)
+    cos, sin = emb.cos().to(DEV), emb.sin().to(DEV)
+
+    def heads_first(x, heads):
+        return x.unflatten(-1, (heads, d)).unsqueeze(0).transpose(1, 2)
+
+    q_in, k_in = heads_first(wide[:, :h * d], h), heads_first(wide[:, h * d:(h + kv) * d], kv)
+    q_out = torch.empty(t, h, d, dtype=F16, device=DEV)
+    k_out = torch.empty(t, kv, d, dtype=F16, device=DEV)
+    rotate_into(q_in, None if term is None else heads_first(term[0], h), k_in, cos, sin,
+                q_out.unsqueeze(0).transpose(1, 2), k_out.unsqueeze(0).transpose(1, 2))
+    q_sum = q_in.float() if term is None else q_in.float() + heads_first(term[0], h).float()
+    want_q, want_k = rope(q_sum, k_in.float(), cos, sin)
+    assert torch.equal(q_out, want_q.half().transpose(1, 2)[0])
+    assert torch.equal(k_out, want_k.half().transpose(1, 2)[0])
+    # backward: fp16 gradients in, fp16 column blocks out; the chain casts the fp32 result once
+    gq = torch.randn(t, h, d, generator=gen).half().to(DEV)
+    gk = torch.randn(t, kv, d, generator=gen).half().to(DEV)
+    buf = torch.full((t, (h + 2 * kv) * d), 7.0, dtype=F16, device=DEV)
+    rotate_into(gq.unsqueeze(0).transpose(1, 2), None, gk.unsqueeze(0).transpose(1, 2), cos, sin,
+                heads_first(buf[:, :h * d], h), heads_first(buf[:, h * d:(h + kv) * d], kv), backward=True)
+    q_leaf = q_sum.clone().requires_grad_()
+    k_leaf = k_in.float().clone().requires_grad_()
+    oq, ok = rope(q_leaf, k_leaf, cos, sin)
+    torch.autograd.backward((oq, ok), (gq.float().unsqueeze(0).transpose(1, 2), gk.float().unsqueeze(0).transpose(1, 2)))
+    assert torch.equal(buf[:, :h * d], q_leaf.grad.half().transpose(1, 2)[0].reshape(t, h * d))
+    assert torch.equal(buf[:, h * d:(h + kv) * d], k_leaf.grad.half().transpose(1, 2)[0].reshape(t, kv * d))
+    assert (buf[:, (h + kv) * d:] == 7.0).all()    # the v block is not this kernel's to write
+
+
 # ----------------------------------------------------------------------------------- SwiGLU
 @pytest.mark.parametrize("tag", ["f16", "f32", "mix", "noround"])
 def test_swiglu_golden(tag):

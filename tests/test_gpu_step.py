@@ -132,6 +132,36 @@ def test_step_matches_installed_transformers_on_cpu(fused_gemm, monkeypatch):
     assert checked == 2 * TINY["num_hidden_layers"]
 
 
+def test_fused_blocks_give_the_per_op_chain_s_step():
+    """The same model with its decoder blocks run as the fused chain (decoder_block.py) and as
+    transformers' block through the per-op patches: same dropout draws (same seed, same order),
+    loss and LoRA gradients equal to fp16 rounding of the few intermediate results the fused
+    GEMMs keep in fp32."""
+    import claudemaxing_b200 as solution
+    from claudemaxing_b200 import qlora
+    from claudemaxing_b200.qlora import LoRALinear
+
+    solution.apply()
+    results = []
+    for fused in (True, False):
+        model, lora = qlora.build_qlora_model("cuda", TINY, dropout=0.1, seed=1, fused_blocks=fused)
+        taken = sum(1 for l in model.model.layers if getattr(l, "_soup_block", None) is not None)
+        assert taken == (TINY["num_hidden_layers"] if fused else 0)
+        torch.manual_seed(2)
+        for m in model.modules():
+            if isinstance(m, LoRALinear):
+                m.lora_B.weight.data.normal_(0, 0.02)
+        batch = qlora.synthetic_batch(batch=4, min_len=16, max_len=96, vocab=TINY["vocab_size"],
+                                      seed=5, device="cuda")
+        torch.manual_seed(11)
+        loss = qlora.qlora_step(model, batch)
+        results.append((loss.item(), [p.grad.detach().float().cpu() for p in lora]))
+    (loss_f, grads_f), (loss_p, grads_p) = results
+    assert abs(loss_f - loss_p) < 1e-3 * abs(loss_p)
+    for a, b in zip(grads_f, grads_p):
+        assert rel_norm(a, b) < 2e-2
+
+
 def test_step_trains():
     import claudemaxing_b200 as solution
     from claudemaxing_b200 import qlora
@@ -165,22 +195,69 @@ def test_single_call_grouped_attention_matches_repeat_kv():
     assert rel_norm(out.cpu(), ref.cpu()) < 2e-3
 
 
-def test_group_dequant_equals_per_weight_dequant():
+@pytest.mark.parametrize("dtype,autocast", [(torch.float16, False), (torch.float32, True), (torch.float32, False)])
+def test_segment_attention_matches_the_masked_formula(dtype, autocast):
+    """Causal attention inside the segments of a packed row (variable-length kernel, no mask)
+    against softmax(mask(q k^T)) v in fp32: fp16 operands, fp32 operands under fp16 autocast (cast
+    as SDPA casts them), and fp32 operands without autocast (the masked SDPA route). An empty
+    segment and a segment of one token are among the rows."""
+    from claudemaxing_b200.attention import mask_of_segments, segment_attention
+
+    torch.manual_seed(0)
+    lens = [77, 0, 130, 1, 92]
+    n, hq, hk, d = sum(lens), 12, 2, 128
+    cu = torch.tensor([0] + torch.tensor(lens).cumsum(0).tolist(), dtype=torch.int32, device="cuda")
+    q = torch.randn(1, n, hq, d, device="cuda").to(dtype).transpose(1, 2).requires_grad_()
+    k = torch.randn(1, n, hk, d, device="cuda").to(dtype).transpose(1, 2).requires_grad_()
+    v = torch.randn(1, n, hk, d, device="cuda").to(dtype).transpose(1, 2).requires_grad_()
+    go = torch.randn(1, n, hq, d, device="cuda")
+    with torch.autocast("cuda", dtype=torch.float16, enabled=autocast):
+        out = segment_attention(q, k, v, cu, max(lens), d ** -0.5)
+    assert out.shape == (1, n, hq, d) and out.is_contiguous()
+    assert out.dtype == (torch.float16 if autocast else dtype)
+    out.backward(go.to(out.dtype))
+    got = [out.detach().float().cpu()] + [t.grad.float().cpu() for t in (q, k, v)]
+    assert all(t.grad.dtype == dtype for t in (q, k, v))
+    q2, k2, v2 = (t.detach().double().requires_grad_() for t in (q, k, v))
+    mask = mask_of_segments(cu, n)
+    s = (q2 @ k2.repeat_interleave(hq // hk, 1).transpose(-1, -2)) * d ** -0.5
+    ref = (s.masked_fill(~mask, float("-inf")).softmax(-1) @ v2.repeat_interleave(hq // hk, 1)).transpose(1, 2)
+    ref.backward(go.double())
+    want = [ref.detach().float().cpu()] + [t.grad.float().cpu() for t in (q2, k2, v2)]
+    for name, a, b in zip(("out", "dq", "dk", "dv"), got, want):
+        assert rel_norm(a, b) < 3e-3, name
+
+
+@pytest.mark.parametrize("resident_mb", [0, 4096])
+def test_group_dequant_equals_per_weight_dequant(resident_mb, monkeypatch):
+    """The shared pool of dequantised blocks returns each weight's own numbers whether a block is
+    found resident or has been replaced (a pool of two blocks under three in turn), and a block
+    that stays resident is dequantised once."""
     from claudemaxing_b200 import qlora
     from claudemaxing_b200.nf4 import dequantize_nf4
 
-    model, _ = qlora.build_qlora_model("cuda", TINY, seed=4)
+    monkeypatch.setattr(qlora.NF4Group, "resident_mb", resident_mb)
+    monkeypatch.setattr(qlora.NF4Group, "_buffers", {})
+    model, _ = qlora.build_qlora_model("cuda", dict(TINY, num_hidden_layers=3), seed=4)
     layers = model.model.layers
-    for layer in (layers[0], layers[1], layers[0]):      # ownership moves between blocks and back
+    fills = []
+    real_fill = qlora.NF4Group._fill
+    monkeypatch.setattr(qlora.NF4Group, "_fill",
+                        lambda self, bufs, i, dtype: (fills.append(i), real_fill(self, bufs, i, dtype))[1])
+    for layer in (layers[0], layers[1], layers[2], layers[0], layers[2], layers[1]):
         for mod in (layer.self_attn.o_proj, layer.mlp.down_proj, layer.self_attn.k_proj):
             got = mod.dequantized(torch.float16).clone()
             want = dequantize_nf4(mod.packed, mod.quant_state, torch.float16)
             assert torch.equal(got, want)
+    # two buffers: 0 1 0(evicts block 0) then block 0 again into 1, block 2 resident, block 1 into 1
+    assert fills == ([0, 1, 0, 1, 1] if resident_mb == 0 else [0, 1, 2])
+    qlora.NF4Group.forget()
+    assert layers[2].mlp.down_proj.dequantized(torch.float16) is not None and len(fills) == (6 if resident_mb == 0 else 4)
 
 
 def test_captured_step_equals_the_eager_step_and_trains():
     """The CUDA-graph step on the padded packed bucket gives the eager step's loss (padding tokens
-    attend only to themselves and carry ignore labels), leaves the adapters untouched by its own
+    are a segment of their own and carry ignore labels), leaves the adapters untouched by its own
     warm-up, and its replays train."""
     import claudemaxing_b200 as solution
     from claudemaxing_b200 import qlora

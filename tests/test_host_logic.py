@@ -61,11 +61,33 @@ def test_pack_tokens_layout():
     p = L.pack_tokens(ids, mask, labels)
     assert p.ids.tolist() == [[5, 6, 7, 8, 9]] and p.pos.tolist() == [[0, 1, 2, 0, 1]]
     assert p.target.tolist() == [[6, 7, 0, 9, 0]]
-    allowed = p.mask[0, 0]
+    assert p.cu_rows.tolist() == [0, 3, 5] and p.cu_rows.dtype == torch.int32 and p.longest == 4
+    allowed = p.mask[0, 0]   # the O(N^2) statement of the same segments, built on request
     assert allowed.shape == (5, 5) and allowed[2, :3].all() and not allowed[3, :3].any()
     assert allowed[4, 3] and not allowed[3, 4]
     assert L.pack_tokens(ids, torch.ones_like(mask), labels) is None  # nothing to drop
     assert L._chunk_tiles(None) == 0 and L._chunk_tiles(7) == 1 and L._chunk_tiles(8192) == 32
+
+
+def test_segment_mask_is_the_row_and_column_rule_of_the_packed_batch():
+    """`mask_of_segments` on the packed row's offsets is "same batch row and key column not after
+    the query's" (the mask the reference's packing builds, solution/lm_head_loss.py:300-337), for
+    ragged rows, left padding and a row without real tokens."""
+    from claudemaxing_b200.attention import mask_of_segments, segment_arguments
+
+    mask = torch.tensor([[1, 1, 1, 0, 0], [0, 0, 0, 0, 0], [0, 0, 1, 1, 1], [1, 0, 1, 0, 1]])
+    ids = torch.arange(20).reshape(4, 5)
+    p = L.pack_tokens(ids, mask, ids.clone())
+    assert p.cu_rows.tolist() == [0, 3, 3, 6, 9]
+    real = mask.reshape(-1).nonzero().reshape(-1)
+    row, col = real // 5, real % 5
+    want = (row[:, None] == row[None, :]) & (col[None, :] <= col[:, None])
+    assert torch.equal(mask_of_segments(p.cu_rows, 9)[0, 0], want) and torch.equal(p.mask[0, 0], want)
+    # without this package's attention function installed the decoder is given the mask itself
+    from transformers.modeling_utils import AttentionInterface
+    if not getattr(AttentionInterface._global_mapping.get("sdpa"), "_grouped_sdpa", False):
+        args = segment_arguments(p.cu_rows, p.longest, 9)
+        assert set(args) == {"attention_mask"} and torch.equal(args["attention_mask"][0, 0], want)
 
 
 def test_shard_bounds_cover_the_vocabulary_in_whole_tiles():
