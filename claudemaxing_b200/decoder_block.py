@@ -28,6 +28,7 @@ one NF4Group (qlora.build_qlora_model), called in training under fp16 autocast w
 row's segment offsets; any other call runs the block's installed forward.
 """
 
+import os
 import types
 
 import torch
@@ -69,6 +70,8 @@ class BlockPlan:
         self.head_dim = attn.head_dim
         self.why_not = self._structure()
         self._bias = None
+        self.casts = None
+        self.keep_products = os.environ.get("SOUP_MLP_RECOMPUTE", "0") != "1"
 
     def _structure(self):
         seven = (self.q, self.k, self.v, self.o, self.gate, self.up, self.down)
@@ -108,13 +111,58 @@ class BlockPlan:
         return self._bias
 
     def adapter(self, module, x):
-        """(A, B, p, scaling) of a LoRALinear whose adapter LoRABranch reproduces for this input;
-        None for a bare projection; False when the adapter needs the module's own forward."""
+        """(A, B, p, scaling, A fp16, B fp16) of a LoRALinear whose adapter LoRABranch reproduces
+        for this input (the fp16 copies None unless the model cast them for this forward); None
+        for a bare projection; False when the adapter needs the module's own forward."""
         if module is _base(module):
             return None
         if not lora_mod.branch_covers(x, module.p, module.training):
             return False
-        return module.lora_A.weight, module.lora_B.weight, float(module.p), float(module.scaling)
+        a16 = b16 = None
+        if self.casts is not None and self.casts.armed:
+            a16, b16 = self.casts.of(module)
+        return (module.lora_A.weight, module.lora_B.weight, float(module.p), float(module.scaling),
+                a16, b16)
+
+
+class AdapterCasts:
+    """fp16 copies of the adapter weights of a model's fused blocks, refreshed by one multi-tensor
+    launch at the start of every forward of the decoder (112 weights of 50 KB and less would
+    otherwise be 112 launches). The copies are handed out only while that forward runs (`armed`);
+    a block called on its own casts its weights itself."""
+
+    def __init__(self):
+        self.sources, self.copies, self.where = [], [], {}
+        self.armed = False
+
+    def add(self, module):
+        if id(module) in self.where:
+            return
+        self.where[id(module)] = len(self.sources)
+        for weight in (module.lora_A.weight, module.lora_B.weight):
+            self.sources.append(weight)
+            self.copies.append(None)
+
+    def of(self, module):
+        i = self.where[id(module)]
+        return self.copies[i], self.copies[i + 1]
+
+    def refresh(self, *_):
+        self.armed = False
+        if not self.sources or not torch.is_grad_enabled():
+            return
+        ok = all(w.is_cuda and w.dtype == F32 for w in self.sources)
+        if not ok:
+            return
+        for i, w in enumerate(self.sources):
+            c = self.copies[i]
+            if c is None or c.device != w.device or c.shape != w.shape:
+                self.copies[i] = torch.empty(w.shape, dtype=F16, device=w.device)
+        torch._foreach_copy_(self.copies, [w.detach() for w in self.sources])
+        self.armed = True
+
+    def disarm(self, *_):
+        self.armed = False
 
 
 class _QKVRope(torch.autograd.Function):
@@ -199,9 +247,14 @@ class _ProjectAddResidual(torch.autograd.Function):
 
 
 class _GatedMLPAddResidual(torch.autograd.Function):
-    """residual + down(silu(gate(x)) * up(x)) for frozen 4-bit projections, keeping only the fp16
-    input for backward (the recompute of solution/swiglu_recompute.py:138-215), the residual sum
-    in down_proj's epilogue and the two input gradients in one fp32 accumulator."""
+    """residual + down(silu(gate(x)) * up(x)) for frozen 4-bit projections, with the residual sum
+    in down_proj's epilogue and the two input gradients in one fp32 accumulator. silu(gate) * up
+    is never kept: backward rebuilds it from gate and up inside the gradient kernel, as
+    SwiGLURecompute does (solution/swiglu_recompute.py:60-100). What is kept besides depends on
+    `BlockPlan.keep_products`: the two fp16 products gate and up (the default here: 2 x tokens x
+    intermediate x 2 bytes per block, 1.3 GB for the whole Qwen2.5-1.5B step at 1280 tokens, on a
+    180 GB part), or only the fp16 input, the two projections being run again in backward (the
+    reference's MLPInputRecompute, solution/swiglu_recompute.py:138-215, made for a 16 GB part)."""
 
     @staticmethod
     @_plain_precision
@@ -211,29 +264,37 @@ class _GatedMLPAddResidual(torch.autograd.Function):
         up = torch.mm(rows, plan.up.dequantized(F16).t())
         act = torch.empty_like(gate)
         _silu_mul_fwd(gate, up, act, False)   # fp32 input, fp16 products: silu is not rounded first
-        del gate, up
         h = residual.shape[-1]
         out = torch.addmm(residual.reshape(-1, h), act, plan.down.dequantized(F16).t(),
                           out_dtype=F32).view(residual.shape)
-        ctx.save_for_backward(x16)
+        ctx.kept = plan.keep_products
+        if ctx.kept:
+            ctx.save_for_backward(gate, up)
+        else:
+            ctx.save_for_backward(x16)
         ctx.plan, ctx.x_shape = plan, x.shape
         return out
 
     @staticmethod
     @_plain_precision
     def backward(ctx, grad):
-        (x16,) = ctx.saved_tensors
         plan = ctx.plan
         dx = None
         if ctx.needs_input_grad[0]:
-            rows = x16.reshape(-1, x16.shape[-1])
             g16 = grad.reshape(-1, grad.shape[-1]).to(F16)
             d_act = torch.mm(g16, plan.down.dequantized(F16))
             w_gate, w_up = plan.gate.dequantized(F16), plan.up.dequantized(F16)
-            gate, up = torch.mm(rows, w_gate.t()), torch.mm(rows, w_up.t())
-            _silu_mul_bwd(d_act, gate, up, gate, up, False)   # gradients overwrite the recomputed pair
-            dx = torch.mm(gate, w_gate, out_dtype=F32)
-            dx = torch.addmm(dx, up, w_up, out_dtype=F32).view(ctx.x_shape)
+            if ctx.kept:
+                gate, up = ctx.saved_tensors
+                d_gate, d_up = torch.empty_like(gate), torch.empty_like(up)
+                _silu_mul_bwd(d_act, gate, up, d_gate, d_up, False)
+            else:
+                (x16,) = ctx.saved_tensors
+                rows = x16.reshape(-1, x16.shape[-1])
+                d_gate, d_up = torch.mm(rows, w_gate.t()), torch.mm(rows, w_up.t())
+                _silu_mul_bwd(d_act, d_gate, d_up, d_gate, d_up, False)   # over the recomputed pair
+            dx = torch.mm(d_gate, w_gate, out_dtype=F32)
+            dx = torch.addmm(dx, d_up, w_up, out_dtype=F32).view(ctx.x_shape)
         return dx, None, (grad if ctx.needs_input_grad[2] else None), None
 
 
@@ -305,7 +366,14 @@ def install_fused_blocks(model):
     forward (on the instance: other models keep transformers' class). Returns the number of
     blocks taken."""
     taken = 0
-    for layer in model.model.layers:
+    decoder = model.model
+    casts = decoder.__dict__.get("_soup_adapter_casts")
+    if casts is None:
+        casts = AdapterCasts()
+        decoder.__dict__["_soup_adapter_casts"] = casts
+        decoder.register_forward_pre_hook(casts.refresh)
+        decoder.register_forward_hook(casts.disarm, always_call=True)
+    for layer in decoder.layers:
         if getattr(layer, "_soup_block", None) is not None:
             taken += 1
             continue
@@ -313,6 +381,10 @@ def install_fused_blocks(model):
         if plan.why_not:
             continue
         plan.installed = layer.forward
+        plan.casts = casts
+        for module in (plan.q, plan.k, plan.v):
+            if module is not _base(module):
+                casts.add(module)
         layer.__dict__["_soup_block"] = plan
         layer.forward = types.MethodType(fused_block_forward, layer)
         taken += 1

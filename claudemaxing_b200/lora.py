@@ -46,17 +46,6 @@ def _unpack(x16, bits, g16, scale, dx_dtype):
     return xd, dx
 
 
-def _fp16_pair(weight_a, weight_b):
-    """fp16 copies of the two adapter weights from one launch (they are 50 KB each: two separate
-    casts are two launches' worth of latency and nothing else)."""
-    if weight_a.dtype == weight_b.dtype == torch.float32 and weight_a.is_cuda:
-        a16 = torch.empty(weight_a.shape, dtype=torch.float16, device=weight_a.device)
-        b16 = torch.empty(weight_b.shape, dtype=torch.float16, device=weight_b.device)
-        torch._foreach_copy_([a16, b16], [weight_a.detach(), weight_b.detach()])
-        return a16, b16
-    return weight_a.to(torch.float16), weight_b.to(torch.float16)
-
-
 def _weight_gradient(grad_rows, input_rows, dtype):
     """grad_rows^T @ input_rows (both fp16, [rows, out] and [rows, in]) in `dtype`. For an fp32
     weight the GEMM writes its fp32 accumulator directly: no fp16 rounding (or overflow at a large
@@ -70,13 +59,16 @@ class LoRABranch(torch.autograd.Function):
     """fp16 `lora_B(lora_A(dropout(x))) * scaling` for fp32 x under fp16 autocast."""
 
     @staticmethod
-    def forward(ctx, x, x16, weight_a, weight_b, p, scaling):
+    def forward(ctx, x, x16, weight_a, weight_b, p, scaling, a16=None, b16=None):
+        """`a16`, `b16`: fp16 copies of the two weights when the caller has made them already (a
+        model that casts all its adapters in one launch per forward); cast here otherwise."""
         dropped, mask = torch.native_dropout(x, p, True)
         del dropped  # only the mask is used
         scale = 1.0 / (1.0 - p)
         xd, bits = _pack(x, mask, scale)  # from the fp32 x: lora_A's input exactly as peft's
         del mask
-        a16, b16 = _fp16_pair(weight_a, weight_b)
+        if a16 is None or b16 is None:
+            a16, b16 = weight_a.to(torch.float16), weight_b.to(torch.float16)
         a = torch.nn.functional.linear(xd, a16)
         out = torch.nn.functional.linear(a, b16) * scaling
         ctx.save_for_backward(x16, bits, a, a16, b16)   # the fp16 adapter copies are 50 KB each
@@ -95,7 +87,7 @@ class LoRABranch(torch.autograd.Function):
         grad_xd = grad_a_in.matmul(a16)
         xd, dx = _unpack(x16, bits, grad_xd.contiguous(), ctx.scale, ctx.x_dtype)
         grad_a = _weight_gradient(ga2, xd.reshape(-1, xd.shape[-1]), ctx.weight_dtypes[0])
-        return dx, None, grad_a, grad_b, None, None
+        return dx, None, grad_a, grad_b, None, None, None, None
 
 
 class _SharedCopy:

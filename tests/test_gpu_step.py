@@ -143,10 +143,12 @@ def test_fused_blocks_give_the_per_op_chain_s_step():
 
     solution.apply()
     results = []
-    for fused in (True, False):
+    for fused, keep in ((True, True), (False, None), (True, False)):
         model, lora = qlora.build_qlora_model("cuda", TINY, dropout=0.1, seed=1, fused_blocks=fused)
-        taken = sum(1 for l in model.model.layers if getattr(l, "_soup_block", None) is not None)
-        assert taken == (TINY["num_hidden_layers"] if fused else 0)
+        taken = [l._soup_block for l in model.model.layers if getattr(l, "_soup_block", None) is not None]
+        assert len(taken) == (TINY["num_hidden_layers"] if fused else 0)
+        for plan in taken:     # keep gate and up for backward, or run the two projections again
+            plan.keep_products = keep
         torch.manual_seed(2)
         for m in model.modules():
             if isinstance(m, LoRALinear):
@@ -156,10 +158,15 @@ def test_fused_blocks_give_the_per_op_chain_s_step():
         torch.manual_seed(11)
         loss = qlora.qlora_step(model, batch)
         results.append((loss.item(), [p.grad.detach().float().cpu() for p in lora]))
-    (loss_f, grads_f), (loss_p, grads_p) = results
+    (loss_f, grads_f), (loss_p, grads_p), (loss_r, grads_r) = results
     assert abs(loss_f - loss_p) < 1e-3 * abs(loss_p)
     for a, b in zip(grads_f, grads_p):
         assert rel_norm(a, b) < 2e-2
+    # recomputing the two products gives the numbers that were kept: same loss to the bit, and
+    # gradients equal up to the order of the attention backward's atomic sums
+    assert loss_r == loss_f
+    for a, b in zip(grads_r, grads_f):
+        assert rel_norm(a, b) < 1e-3
 
 
 def test_step_trains():
