@@ -649,7 +649,7 @@ def qlora_step_leg(dev, rank, world, steps, warmup, timed):
         "aggregate_tokens_per_s": round(n_real / (ms * 1e-3), 1), "ms_per_step": round(ms, 4),
         "real_tokens_per_step": n_real, "bucket_tokens_per_gpu": captured.bucket,
         "e2e": {"value": round(n_real / world / (e2e_ms * 1e-3), 1), "ms_per_step": round(e2e_ms, 4),
-                "h2d_bytes_per_step": 4 * captured.bucket * 8, "d2h_bytes_per_step": 4},
+                "h2d_bytes_per_step": 3 * captured.bucket * 8 + captured.cu_rows.numel() * 4, "d2h_bytes_per_step": 4},
         "eager_ms_per_step": round(eager_ms, 4),
         "nf4_gemm_in_prologue_ms_per_step": None if fused_ms is None else round(fused_ms, 4),
         "loss_first": round(first, 5), "loss_last": round(float(last), 5),
