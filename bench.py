@@ -559,6 +559,36 @@ def cpu_oracle_suite(cores):
 
 
 # ------------------------------------------------------------------------------------------
+def step_only(dev, steps):
+    """The captured Qwen2.5-1.5B-architecture QLoRA step alone (same model, batch and optimizer as
+    `qlora_step_leg` on one GPU): five warm replays, one replay inside the NVTX range 'soup_step',
+    then `steps` timed replays."""
+    import claudemaxing_b200 as solution
+    from claudemaxing_b200 import qlora
+
+    solution.apply()
+    model, lora = qlora.build_qlora_model(dev, seed=0)
+    batch = qlora.synthetic_batch(seed=3)
+    optimizer = torch.optim.AdamW(lora, lr=1e-4, fused=True, capturable=True)
+    scaler = torch.amp.GradScaler("cuda", init_scale=65536.0)
+    captured = qlora.CapturedStep(model, lora, optimizer, batch, scaler=scaler)
+    for _ in range(5):
+        captured.run()
+    torch.cuda.synchronize()
+    torch.cuda.nvtx.range_push("soup_step")
+    captured.run()
+    torch.cuda.synchronize()
+    torch.cuda.nvtx.range_pop()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(steps):
+        loss = captured.run()
+    b.record()
+    torch.cuda.synchronize()
+    return {"qlora_step_ms": round(a.elapsed_time(b) / steps, 4), "loss": float(loss),
+            "bucket_tokens": captured.bucket, "real_tokens": batch["n_tokens"]}
+
+
 def qlora_step_leg(dev, rank, world, steps, warmup, timed):
     """BASELINE config 4 (and 5b at N>1): the full Qwen2.5-1.5B-architecture QLoRA step, batch 4 per
     GPU with lengths uniform in [64, 512], packed; forward, backward, LoRA-gradient all-reduce at
@@ -799,6 +829,9 @@ def main():
     ap.add_argument("--suite-rows", type=int, default=32768)
     ap.add_argument("--gemm-only", action="store_true",
                     help="run only the NF4 GEMM comparison and print its JSON")
+    ap.add_argument("--step-only", action="store_true",
+                    help="run only the captured QLoRA step: warm replays, then one replay inside the "
+                         "NVTX range 'soup_step' (for a profiler's range filter), then a timed region")
     ap.add_argument("--plain-launches", action="store_true",
                     help="with --suite-only: up to three direct launches per case instead of graph replays")
     args = ap.parse_args()
@@ -829,6 +862,9 @@ def main():
     if args.gemm_only:
         PLAIN_LAUNCHES = args.plain_launches
         print(json.dumps({"kernels": nf4_gemm_suite(dev, peaks()[0]["bf16_tflops"])}), flush=True)
+        return
+    if args.step_only:
+        print(json.dumps(step_only(dev, max(args.steps, 1))), flush=True)
         return
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
