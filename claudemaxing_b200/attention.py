@@ -12,10 +12,16 @@ SDPA). Two routes replace transformers' "sdpa" attention function:
   the same products as transformers' repeat_kv path without materialising the repeated k and v.
 """
 
+import os
+
 import torch
 import torch.nn.functional as F
 
+from . import _lib
+
 _LOW = (torch.float16, torch.bfloat16)
+# SOUP_ATTN_KERNEL=0 keeps torch's variable-length kernel for the forward as well
+OWN_FORWARD = os.environ.get("SOUP_ATTN_KERNEL", "1") != "0"
 
 
 def mask_of_segments(cu_rows, n):
@@ -52,6 +58,51 @@ def _grouped_sdpa(query, key, value, attention_mask, scaling):
     return out.transpose(1, 2).contiguous()
 
 
+def _token_major(t):
+    """[tokens, heads, 128] view of a [1, heads, tokens, 128] tensor if its heads are adjacent in
+    memory (a transposed view of a [tokens, heads * 128] matrix), else None."""
+    x = t.transpose(1, 2)[0]
+    if x.stride(2) == 1 and x.stride(1) == x.shape[2] and x.stride(0) >= x.shape[1] * x.shape[2] \
+            and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0:
+        return x
+    return None
+
+
+class SegmentAttention(torch.autograd.Function):
+    """Causal attention inside the segments of a packed row on fp16 [tokens, heads, 128] tensors:
+    forward by this library's tcgen05 kernel (csrc/attention.cu), which also returns the row
+    log-sum-exps; backward by torch's variable-length flash-attention backward, which takes
+    exactly those (output, log-sum-exp [heads, tokens])."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, cu_rows, longest, scale):
+        n, hq, d = q.shape
+        out = torch.empty((n, hq, d), dtype=q.dtype, device=q.device)
+        lse = torch.empty((hq, n), dtype=torch.float32, device=q.device)
+        _lib.call("soup_attn_fwd", _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(cu_rows),
+                  _lib.ptr(out), _lib.ptr(lse), n, cu_rows.numel() - 1, hq, k.shape[1], d,
+                  q.stride(0), k.stride(0), v.stride(0), float(scale), _lib.stream_of(q))
+        ctx.save_for_backward(q, k, v, cu_rows, out, lse)
+        ctx.longest, ctx.scale = int(longest), float(scale)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad):
+        q, k, v, cu_rows, out, lse = ctx.saved_tensors
+        rng_state = torch.empty(2, dtype=torch.uint64, device=q.device)   # no dropout: never read
+        dq, dk, dv = torch.ops.torch_attn._varlen_attn_backward(
+            grad.contiguous(), q, k, v, out, lse, cu_rows, cu_rows, ctx.longest, ctx.longest, True,
+            rng_state, ctx.scale, [-1, 0])
+        return dq, dk, dv, None, None, None
+
+
+def _own_forward_covers(q, k, v, cu_rows):
+    return (OWN_FORWARD and q is not None and k is not None and v is not None
+            and q.dtype == torch.float16 and k.dtype == v.dtype == torch.float16
+            and q.shape[2] == 128 and cu_rows.dtype == torch.int32 and cu_rows.is_cuda
+            and hasattr(torch.ops, "torch_attn") and hasattr(torch.ops.torch_attn, "_varlen_attn_backward"))
+
+
 def segment_attention(query, key, value, cu_rows, longest, scaling):
     """Causal attention inside each segment of one packed row. query [1, Hq, N, D], key and value
     [1, Hkv, N, D] (any strides with a contiguous last dimension), `cu_rows` int32 [S + 1] on the
@@ -63,6 +114,11 @@ def segment_attention(query, key, value, cu_rows, longest, scaling):
     if (varlen_attn is None or not query.is_cuda or dtype not in _LOW or query.shape[-1] > 256
             or query.shape[-1] % 8 or query.shape[1] % key.shape[1]):
         return _grouped_sdpa(query, key, value, mask_of_segments(cu_rows, query.shape[2]), scaling)
+    if dtype == torch.float16 and all(t.dtype == dtype for t in (query, key, value)):
+        rows = [_token_major(t) for t in (query, key, value)]
+        if _own_forward_covers(*rows, cu_rows):
+            scale = query.shape[-1] ** -0.5 if scaling is None else scaling
+            return SegmentAttention.apply(*rows, cu_rows, longest, scale).unsqueeze(0)
     q, k, v = (t.transpose(1, 2)[0] if t.dtype == dtype else t.transpose(1, 2)[0].to(dtype)
                for t in (query, key, value))
     out = varlen_attn(q, k, v, cu_rows, cu_rows, int(longest), int(longest),

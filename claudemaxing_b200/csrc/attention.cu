@@ -1,0 +1,356 @@
+// Causal attention inside the segments of one packed row (the batch rows of a packed training
+// batch), forward, for head_dim 128 and fp16 q/k/v with grouped-query heads.
+//
+// One CTA owns 128 consecutive query tokens of one segment and one query head. The keys and
+// values it may see (its segment, up to its last token) arrive in tiles of 64 tokens by TMA into
+// a two-stage ring. S = Q K^T of a tile is one tcgen05 product (M 128, N 64, K 128) into one of two
+// 64-column accumulators in tensor memory; the four softmax warps read it (thread = query row).
+// The softmax is done in two passes over the key tiles, so that the output accumulator never has
+// to be rescaled: the first pass only reduces the row maximum and the sum of exponentials; the
+// second forms S again, writes P = exp(S - max) as fp16 into a 128-byte-swizzled shared-memory
+// tile (the A operand) and accumulates O += P V in tensor memory (V as MN-major B operand). At
+// segment lengths of a few hundred tokens the second QK^T is cheap next to the latency of a
+// rescale round trip through tensor memory. The epilogue divides by the sum and writes fp16 rows
+// and the log-sum-exp (natural log, of the scaled scores) per row and head.
+//
+// Shared memory (96 KB) and tensor memory (256 columns) allow two CTAs per SM, which is what a
+// latency-bound problem of ~150 CTAs wants. Every wait is bounded (umma::mbar_wait).
+//
+// The reference calls torch SDPA here (solution/attention.py:332-343) on a [1, 1, N, N] mask
+// built by its packing (solution/lm_head_loss.py:300-337); this kernel takes the segment offsets.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "rowpipe.cuh"
+#include "umma.cuh"
+
+namespace soup {
+namespace {
+
+using namespace umma;
+
+constexpr int kD = 128;          // head dimension
+constexpr int kBQ = 128;         // query rows per CTA
+constexpr int kBKV = 64;         // key/value rows per tile
+constexpr int kStages = 2;       // key tiles in flight (the value tile has one buffer)
+constexpr int kQBytes = kBQ * kD * 2;          // 32 KB: two boxes of [128 rows x 64 cols]
+constexpr int kQBox = kBQ * 128;               // 16 KB
+constexpr int kKBytes = kBKV * kD * 2;         // 16 KB: two boxes of [64 rows x 64 cols]
+constexpr int kKVBox = kBKV * 128;             // 8 KB
+constexpr int kPBytes = kBQ * kBKV * 2;        // 16 KB: one box of [128 rows x 64 cols]
+constexpr int kThreads = 224;                  // warps 0-3 softmax, 4 key TMA, 5 MMA, 6 value TMA
+constexpr uint32_t kTmemCols = 256;            // S0 [0,64) S1 [64,128) O [128,256)
+
+struct __align__(1024) Smem {
+  uint8_t q[kQBytes];
+  uint8_t k[kStages][kKBytes];
+  uint8_t v[kKBytes];
+  uint8_t p[kPBytes];
+  uint64_t q_full, k_full[kStages], k_empty[kStages], v_full, v_empty, s_full[2], s_empty[2], p_full,
+      p_empty, o_full;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+struct AttnArgs {
+  const int32_t* cu;     // [segments + 1]
+  __half* out;           // [n, hq, 128]
+  float* lse;            // [hq, n]
+  int n, segments, hq, group;
+  float scale_log2;      // softmax scale * log2(e)
+  float scale;
+  int* status;
+};
+
+// Which (segment, first query token) a tile slot is: slots enumerate the 128-row tiles of the
+// segments in order. Returns false for a slot past the last tile.
+__device__ __forceinline__ bool locate(const int32_t* cu, int segments, int slot, int& seg_begin,
+                                       int& seg_end, int& q0) {
+  int base = 0;
+  for (int s = 0; s < segments; ++s) {
+    const int b = cu[s], e = cu[s + 1];
+    const int tiles = (e - b + kBQ - 1) / kBQ;
+    if (slot < base + tiles) {
+      seg_begin = b;
+      seg_end = e;
+      q0 = b + (slot - base) * kBQ;
+      return true;
+    }
+    base += tiles;
+  }
+  return false;
+}
+
+
+__global__ void __launch_bounds__(kThreads, 2)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                const __grid_constant__ CUtensorMap map_v, AttnArgs a) {
+  extern __shared__ uint8_t raw[];
+  int seg_begin, seg_end, q0;
+  if (!locate(a.cu, a.segments, blockIdx.x, seg_begin, seg_end, q0)) return;   // the whole CTA leaves
+  Smem& s = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int h = blockIdx.y, hk = h / a.group;
+  const int q_end = min(seg_end, q0 + kBQ);                      // one past this tile's last token
+  const int n_kv = (q_end - seg_begin + kBKV - 1) / kBKV;        // key tiles it may see (>= 1)
+  if (threadIdx.x == 0) {
+    mbar_init(&s.q_full, 1);
+    for (int i = 0; i < kStages; ++i) {
+      mbar_init(&s.k_full[i], 1);
+      mbar_init(&s.k_empty[i], 1);
+    }
+    mbar_init(&s.v_full, 1);
+    mbar_init(&s.v_empty, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&s.s_full[i], 1);
+      mbar_init(&s.s_empty[i], 4);
+    }
+    mbar_init(&s.p_full, 4);
+    mbar_init(&s.p_empty, 1);
+    mbar_init(&s.o_full, 1);
+    s.abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 4) {
+    tmem_alloc(&s.tmem_base, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = s.tmem_base;
+  volatile int* abort_flag = &s.abort_flag;
+
+  if (warp == 4) {
+    // ---------------------------------------------------------------- Q and the key tiles
+    if (lane == 0) {
+      prefetch_tensormap(&map_q);
+      prefetch_tensormap(&map_k);
+      mbar_expect_tx(&s.q_full, kQBytes);
+      tma_load_2d(s.q, &map_q, h * kD, q0, &s.q_full);
+      tma_load_2d(s.q + kQBox, &map_q, h * kD + 64, q0, &s.q_full);
+      for (int g = 0; g < 2 * n_kv; ++g) {
+        const int st = g % kStages;
+        if (g >= kStages &&
+            !mbar_wait(&s.k_empty[st], ((g / kStages) & 1) ^ 1, abort_flag, a.status, 41))
+          break;
+        const int row = seg_begin + (g < n_kv ? g : g - n_kv) * kBKV;
+        mbar_expect_tx(&s.k_full[st], kKBytes);
+        tma_load_2d(s.k[st], &map_k, hk * kD, row, &s.k_full[st]);
+        tma_load_2d(s.k[st] + kKVBox, &map_k, hk * kD + 64, row, &s.k_full[st]);
+      }
+    }
+  } else if (warp == 6) {
+    // ---------------------------------------------------------------- the value tiles (pass 2)
+    if (lane == 0) {
+      prefetch_tensormap(&map_v);
+      for (int t = 0; t < n_kv; ++t) {
+        if (t > 0 && !mbar_wait(&s.v_empty, (t - 1) & 1, abort_flag, a.status, 42)) break;
+        const int row = seg_begin + t * kBKV;
+        mbar_expect_tx(&s.v_full, kKBytes);
+        tma_load_2d(s.v, &map_v, hk * kD, row, &s.v_full);
+        tma_load_2d(s.v + kKVBox, &map_v, hk * kD + 64, row, &s.v_full);
+      }
+    }
+  } else if (warp == 5) {
+    // ---------------------------------------------------------------- MMA issue
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = make_idesc_f16(kBQ, kBKV, kFmtF16, kFmtF16, false, false);
+      constexpr uint32_t idesc_o = make_idesc_f16(kBQ, kD, kFmtF16, kFmtF16, false, true);
+      const uint64_t dq = make_smem_desc(smem_u32(s.q), 16, 1024);
+      bool ok = mbar_wait(&s.q_full, 0, abort_flag, a.status, 43);
+      // S_g = Q K_g^T into accumulator g & 1: 8 steps of 16 along the head dimension
+      auto issue_s = [&](int g) -> bool {
+        const int st = g % kStages, sb = g & 1;
+        if (!mbar_wait(&s.k_full[st], (g / kStages) & 1, abort_flag, a.status, 44)) return false;
+        if (g >= 2 && !mbar_wait(&s.s_empty[sb], ((g >> 1) & 1) ^ 1, abort_flag, a.status, 45))
+          return false;
+        tc_fence_after_sync();
+        const uint64_t dk = make_smem_desc(smem_u32(s.k[st]), 16, 1024);
+#pragma unroll
+        for (int k8 = 0; k8 < kD / 16; ++k8) {
+          const uint32_t qa = (uint32_t)(k8 >> 2) * (kQBox >> 4) + (uint32_t)(k8 & 3) * 2;
+          const uint32_t kb = (uint32_t)(k8 >> 2) * (kKVBox >> 4) + (uint32_t)(k8 & 3) * 2;
+          mma_f16_ss(tmem + sb * kBKV, dq + qa, dk + kb, idesc_s, k8 != 0);
+        }
+        tc_commit(&s.s_full[sb]);
+        return true;
+      };
+      for (int g = 0; g < n_kv && ok; ++g) {   // pass 1: scores only
+        ok = issue_s(g);
+        if (ok) tc_commit(&s.k_empty[g % kStages]);
+      }
+      if (ok) ok = issue_s(n_kv);
+      const uint64_t dp = make_smem_desc(smem_u32(s.p), 16, 1024);
+      const uint64_t dv = make_smem_desc(smem_u32(s.v), kKVBox, 1024);   // MN-major: boxes kKVBox apart
+      for (int t = 0; t < n_kv && ok; ++t) {   // pass 2: scores of the next tile, then O += P V
+        const int g = n_kv + t;
+        if (t + 1 < n_kv) ok = issue_s(g + 1);
+        if (ok) ok = mbar_wait(&s.v_full, t & 1, abort_flag, a.status, 46);
+        if (ok) ok = mbar_wait(&s.p_full, t & 1, abort_flag, a.status, 47);
+        if (!ok) break;
+        tc_fence_after_sync();
+#pragma unroll
+        for (int k4 = 0; k4 < kBKV / 16; ++k4)
+          mma_f16_ss(tmem + 2 * kBKV, dp + k4 * 2, dv + k4 * (2048 >> 4), idesc_o, (t | k4) != 0);
+        tc_commit(&s.k_empty[g % kStages]);
+        tc_commit(&s.v_empty);
+        tc_commit(&s.p_empty);
+      }
+      if (ok) tc_commit(&s.o_full);
+    }
+  } else {
+    // ---------------------------------------------------------------- softmax: thread = query row
+    const int r = threadIdx.x;
+    const int q_idx = q0 + r;
+    const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
+    const float sl = a.scale_log2;
+    float m = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int g = 0; g < 2 * n_kv && ok; ++g) {
+      const int sb = g & 1;
+      ok = mbar_wait(&s.s_full[sb], (g >> 1) & 1, abort_flag, a.status, 48);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after_sync();
+      uint32_t x0[32], x1[32];
+      tmem_ld_32x32(lane_base + sb * kBKV, x0);
+      tmem_ld_32x32(lane_base + sb * kBKV + 32, x1);
+      tmem_ld_wait_on(x0);
+      tmem_ld_wait_on(x1);
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s.s_empty[sb]);
+      const int t = g < n_kv ? g : g - n_kv;
+      const int limit = q_idx - (seg_begin + t * kBKV);   // columns 0..limit are visible
+      if (g < n_kv) {
+        float tile_max = -INFINITY;
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          if (c <= limit) tile_max = fmaxf(tile_max, __uint_as_float(x0[c]));
+          if (c + 32 <= limit) tile_max = fmaxf(tile_max, __uint_as_float(x1[c]));
+        }
+        if (tile_max > -INFINITY) {
+          const float m_new = fmaxf(m, tile_max);
+          float sum = 0.f;
+#pragma unroll
+          for (int c = 0; c < 32; ++c) {
+            if (c <= limit) sum += exp2f((__uint_as_float(x0[c]) - m_new) * sl);
+            if (c + 32 <= limit) sum += exp2f((__uint_as_float(x1[c]) - m_new) * sl);
+          }
+          l = l * exp2f((m - m_new) * sl) + sum;   // m = -inf the first time: exp2(-inf) = 0
+          m = m_new;
+        }
+      } else {
+        uint32_t packed[32];
+#pragma unroll
+        for (int c = 0; c < 32; c += 2) {
+          const float p0 = c <= limit ? exp2f((__uint_as_float(x0[c]) - m) * sl) : 0.f;
+          const float p1 = c + 1 <= limit ? exp2f((__uint_as_float(x0[c + 1]) - m) * sl) : 0.f;
+          const float p2 = c + 32 <= limit ? exp2f((__uint_as_float(x1[c]) - m) * sl) : 0.f;
+          const float p3 = c + 33 <= limit ? exp2f((__uint_as_float(x1[c + 1]) - m) * sl) : 0.f;
+          __half2 lo = __floats2half2_rn(p0, p1), hi = __floats2half2_rn(p2, p3);
+          packed[c >> 1] = *reinterpret_cast<uint32_t*>(&lo);
+          packed[16 + (c >> 1)] = *reinterpret_cast<uint32_t*>(&hi);
+        }
+        if (t > 0) {
+          ok = mbar_wait(&s.p_empty, (t - 1) & 1, abort_flag, a.status, 49);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+        }
+        // row r of the [128 x 64] fp16 tile: eight 16-byte chunks, chunk j at position j ^ (r & 7)
+        uint8_t* row = s.p + r * 128;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const uint4 chunk = make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+          *reinterpret_cast<uint4*>(row + ((j ^ (r & 7)) << 4)) = chunk;
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&s.p_full);
+      }
+    }
+    if (ok) {
+      ok = mbar_wait(&s.o_full, 0, abort_flag, a.status, 50);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (ok) {
+      tc_fence_after_sync();
+      const float inv = 1.f / l;
+      const bool valid = q_idx < seg_end;
+      __half* dst = a.out + ((size_t)q_idx * a.hq + h) * kD;
+#pragma unroll
+      for (int c0 = 0; c0 < kD; c0 += 32) {
+        uint32_t o[32];
+        tmem_ld_32x32(lane_base + 2 * kBKV + c0, o);
+        tmem_ld_wait_on(o);
+        if (valid) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint32_t w[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              __half2 hh = __floats2half2_rn(__uint_as_float(o[8 * j + 2 * e]) * inv,
+                                             __uint_as_float(o[8 * j + 2 * e + 1]) * inv);
+              w[e] = *reinterpret_cast<uint32_t*>(&hh);
+            }
+            *reinterpret_cast<uint4*>(dst + c0 + 8 * j) = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        }
+      }
+      if (valid) a.lse[(size_t)h * a.n + q_idx] = m * a.scale + logf(l);
+      tc_fence_before_sync();
+    }
+  }
+  __syncthreads();
+  if (warp == 4) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem, kTmemCols);
+  }
+}
+
+}  // namespace
+}  // namespace soup
+
+extern "C" int soup_attn_fwd(const void* q, const void* k, const void* v, const int32_t* cu_rows,
+                             void* out, float* lse, int64_t n_tokens, int64_t n_segments,
+                             int64_t hq, int64_t hk, int64_t head_dim, int64_t q_pitch,
+                             int64_t k_pitch, int64_t v_pitch, float scale, void* stream) {
+  using namespace soup;
+  if (n_tokens == 0 || n_segments == 0) return SOUP_OK;
+  if (!q || !k || !v || !cu_rows || !out || !lse) SOUP_FAIL(SOUP_ERR_ARG, "attn_fwd: null pointer");
+  if (head_dim != kD) SOUP_FAIL(SOUP_ERR_ARG, "attn_fwd: head_dim must be 128");
+  if (n_tokens < 0 || n_segments < 0 || hq <= 0 || hk <= 0 || hq % hk)
+    SOUP_FAIL(SOUP_ERR_ARG, "attn_fwd: bad sizes (query heads must be a multiple of key heads)");
+  if (n_tokens > (1 << 30) || n_segments > 65535 || hq > 65535)
+    SOUP_FAIL(SOUP_ERR_ARG, "attn_fwd: too many tokens, segments or heads");
+  if (q_pitch < hq * kD || k_pitch < hk * kD || v_pitch < hk * kD || (q_pitch | k_pitch | v_pitch) & 7)
+    SOUP_FAIL(SOUP_ERR_ARG, "attn_fwd: row pitches must cover the heads and be multiples of 8 elements");
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(out))
+    SOUP_FAIL(SOUP_ERR_ARG, "attn_fwd: pointers must be 16-byte aligned");
+  CUtensorMap mq, mk, mv;
+  if (umma::encode_map_2d_16bit(&mq, q, (uint64_t)n_tokens, (uint64_t)(hq * kD), (uint64_t)q_pitch, kBQ, 64, false) ||
+      umma::encode_map_2d_16bit(&mk, k, (uint64_t)n_tokens, (uint64_t)(hk * kD), (uint64_t)k_pitch, kBKV, 64, false) ||
+      umma::encode_map_2d_16bit(&mv, v, (uint64_t)n_tokens, (uint64_t)(hk * kD), (uint64_t)v_pitch, kBKV, 64, false))
+    SOUP_FAIL(SOUP_ERR_LAUNCH, "attn_fwd: cuTensorMapEncodeTiled failed");
+  AttnArgs a;
+  a.cu = cu_rows;
+  a.out = reinterpret_cast<__half*>(out);
+  a.lse = lse;
+  a.n = (int)n_tokens;
+  a.segments = (int)n_segments;
+  a.hq = (int)hq;
+  a.group = (int)(hq / hk);
+  a.scale = scale;
+  a.scale_log2 = scale * 1.4426950408889634f;
+  a.status = rowpipe::status_word();
+  const size_t smem = sizeof(Smem) + 1024;
+  if (cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+    SOUP_FAIL(SOUP_ERR_LAUNCH, "attn_fwd: shared memory attribute");
+  // every segment adds at most one partial tile to the tiles of the packed row
+  const unsigned slots = (unsigned)((n_tokens + kBQ - 1) / kBQ + n_segments);
+  dim3 grid(slots, (unsigned)hq);
+  attn_fwd_kernel<<<grid, kThreads, smem, reinterpret_cast<cudaStream_t>(stream)>>>(mq, mk, mv, a);
+  SOUP_CHECK_LAUNCH("attn_fwd");
+  return SOUP_OK;
+}

@@ -175,6 +175,20 @@ int soup_rope_sum(const void* q, const void* q_add, const void* k, const void* c
                   int q_dtype, int q_add_dtype, int k_dtype, int cs_dtype, int q_out_dtype,
                   int k_out_dtype, int backward, void* stream);
 
+/* Causal attention inside the segments of one packed row, forward: for every token i of segment s,
+ * out[i, h] = softmax_j(scale * q[i, h] . k[j, h / (hq/hk)]) v[j, h / (hq/hk)] over the tokens j <= i
+ * of the same segment. Stands where the reference calls torch SDPA on the [1, 1, N, N] mask of its
+ * packed batch (solution/attention.py:332-343, mask from solution/lm_head_loss.py:300-337); the
+ * segments are given as offsets instead of a mask.
+ *   q [n_tokens, hq, 128] fp16, row pitch q_pitch elements (heads adjacent); k, v [n_tokens, hk, 128]
+ *   cu_rows int32 [n_segments + 1] on the device: segment s is tokens cu_rows[s] .. cu_rows[s+1]-1
+ *   out [n_tokens, hq, 128] fp16 contiguous; lse fp32 [hq, n_tokens]: log(sum_j exp(scale * s_ij))
+ * head_dim must be 128; pointers 16-byte aligned, pitches multiples of 8. tcgen05 / TMEM / TMA. */
+int soup_attn_fwd(const void* q, const void* k, const void* v, const int32_t* cu_rows, void* out,
+                  float* lse, int64_t n_tokens, int64_t n_segments, int64_t hq, int64_t hk,
+                  int64_t head_dim, int64_t q_pitch, int64_t k_pitch, int64_t v_pitch, float scale,
+                  void* stream);
+
 /* out = round_out(round_gate?(silu(gate)) * up). Replaces silu_mul_fwd_persistent at
  * solution/swiglu_recompute.py:98-100 and :176-178 (kernel :36-48). */
 int soup_silu_mul_fwd(const void* gate, const void* up, void* out, int64_t n, int gate_dtype,

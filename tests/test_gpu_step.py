@@ -202,16 +202,21 @@ def test_single_call_grouped_attention_matches_repeat_kv():
     assert rel_norm(out.cpu(), ref.cpu()) < 2e-3
 
 
+@pytest.mark.parametrize("lens", [[77, 0, 130, 1, 92], [300, 280, 296, 292, 112], [640, 5, 128, 64, 129]])
 @pytest.mark.parametrize("dtype,autocast", [(torch.float16, False), (torch.float32, True), (torch.float32, False)])
-def test_segment_attention_matches_the_masked_formula(dtype, autocast):
+def test_segment_attention_matches_the_masked_formula(dtype, autocast, lens, monkeypatch):
     """Causal attention inside the segments of a packed row (variable-length kernel, no mask)
     against softmax(mask(q k^T)) v in fp32: fp16 operands, fp32 operands under fp16 autocast (cast
     as SDPA casts them), and fp32 operands without autocast (the masked SDPA route). An empty
     segment and a segment of one token are among the rows."""
+    from claudemaxing_b200 import attention as attention_mod
     from claudemaxing_b200.attention import mask_of_segments, segment_attention
 
+    launches = []
+    real_call = attention_mod._lib.call
+    monkeypatch.setattr(attention_mod._lib, "call",
+                        lambda name, *args: (launches.append(name), real_call(name, *args))[1])
     torch.manual_seed(0)
-    lens = [77, 0, 130, 1, 92]
     n, hq, hk, d = sum(lens), 12, 2, 128
     cu = torch.tensor([0] + torch.tensor(lens).cumsum(0).tolist(), dtype=torch.int32, device="cuda")
     q = torch.randn(1, n, hq, d, device="cuda").to(dtype).transpose(1, 2).requires_grad_()
@@ -222,6 +227,8 @@ def test_segment_attention_matches_the_masked_formula(dtype, autocast):
         out = segment_attention(q, k, v, cu, max(lens), d ** -0.5)
     assert out.shape == (1, n, hq, d) and out.is_contiguous()
     assert out.dtype == (torch.float16 if autocast else dtype)
+    # fp16 operands with adjacent heads: the forward is this library's kernel
+    assert ("soup_attn_fwd" in launches) == (dtype == torch.float16)
     out.backward(go.to(out.dtype))
     got = [out.detach().float().cpu()] + [t.grad.float().cpu() for t in (q, k, v)]
     assert all(t.grad.dtype == dtype for t in (q, k, v))
