@@ -32,6 +32,7 @@ SIGNATURES = {
     "soup_rope": [_P, _P, _P, _P, _P, _P] + [_L] * 13 + [_I] * 6 + [_P],
     "soup_rope_sum": [_P, _P, _P, _P, _P, _P, _P] + [_L] * 22 + [_I] * 7 + [_P],
     "soup_attn_fwd": [_P, _P, _P, _P, _P, _P] + [_L] * 8 + [_F, _P],
+    "soup_attn_bwd": [_P] * 10 + [_L] * 8 + [_F, _P],
     "soup_row_status": [_P, _P],
     "soup_device_status": [_P, _I, _P],
     "soup_wait_selftest": [_L, _P, _P, _P],

@@ -20,8 +20,25 @@ import torch.nn.functional as F
 from . import _lib
 
 _LOW = (torch.float16, torch.bfloat16)
-# SOUP_ATTN_KERNEL=0 keeps torch's variable-length kernel for the forward as well
+# SOUP_ATTN_KERNEL=0 keeps torch's variable-length kernel for forward and backward;
+# SOUP_ATTN_BACKWARD=0 keeps it for the backward only
 OWN_FORWARD = os.environ.get("SOUP_ATTN_KERNEL", "1") != "0"
+OWN_BACKWARD = os.environ.get("SOUP_ATTN_BACKWARD", "1") != "0"
+
+
+def attention_gradients(q, k, v, out, lse, grad, cu_rows, scale):
+    """(dq fp16 [n, hq, 128], dk fp32 [n, hk, 128], dv fp32 [n, hk, 128]) of the segment attention
+    from this library's backward kernel (csrc/attention.cu)."""
+    n, hq, d = q.shape
+    grad = grad if grad.is_contiguous() else grad.contiguous()
+    dq = torch.empty((n, hq, d), dtype=q.dtype, device=q.device)
+    dk = torch.empty((n, k.shape[1], d), dtype=torch.float32, device=q.device)
+    dv = torch.empty((n, k.shape[1], d), dtype=torch.float32, device=q.device)
+    _lib.call("soup_attn_bwd", _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(out), _lib.ptr(grad),
+              _lib.ptr(lse), _lib.ptr(cu_rows), _lib.ptr(dq), _lib.ptr(dk), _lib.ptr(dv), n,
+              cu_rows.numel() - 1, hq, k.shape[1], d, q.stride(0), k.stride(0), v.stride(0),
+              float(scale), _lib.stream_of(q))
+    return dq, dk, dv
 
 
 def mask_of_segments(cu_rows, n):
@@ -70,9 +87,9 @@ def _token_major(t):
 
 class SegmentAttention(torch.autograd.Function):
     """Causal attention inside the segments of a packed row on fp16 [tokens, heads, 128] tensors:
-    forward by this library's tcgen05 kernel (csrc/attention.cu), which also returns the row
-    log-sum-exps; backward by torch's variable-length flash-attention backward, which takes
-    exactly those (output, log-sum-exp [heads, tokens])."""
+    forward and backward by this library's tcgen05 kernels (csrc/attention.cu). The forward also
+    returns the row log-sum-exps in the layout torch's variable-length flash-attention backward
+    takes ([heads, tokens]), which `SOUP_ATTN_BACKWARD=0` uses instead of this library's."""
 
     @staticmethod
     def forward(ctx, q, k, v, cu_rows, longest, scale):
@@ -89,6 +106,9 @@ class SegmentAttention(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad):
         q, k, v, cu_rows, out, lse = ctx.saved_tensors
+        if OWN_BACKWARD:
+            dq, dk, dv = attention_gradients(q, k, v, out, lse, grad, cu_rows, ctx.scale)
+            return dq, dk.to(k.dtype), dv.to(v.dtype), None, None, None
         rng_state = torch.empty(2, dtype=torch.uint64, device=q.device)   # no dropout: never read
         dq, dk, dv = torch.ops.torch_attn._varlen_attn_backward(
             grad.contiguous(), q, k, v, out, lse, cu_rows, cu_rows, ctx.longest, ctx.longest, True,

@@ -312,6 +312,319 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 }  // namespace
 }  // namespace soup
 
+namespace soup {
+namespace {
+
+// ------------------------------------------------------------------------------------------
+// Backward. Same decomposition as forward: a CTA owns 128 query tokens of one segment and one
+// query head and walks the key tiles it may see. Per key tile (64 tokens):
+//   S = Q K^T and dP = dO V^T            (two products into tensor-memory columns 0-63 / 64-127)
+//   P = exp(scale S - lse), dS = P (dP - D)   by the four row warps (D = rowsum(dO o O), formed
+//                                         by the same threads when the kernel starts)
+//   dV^T = dO^T P, dK^T = Q^T dS          (A and B both MN-major; into the columns S and dP left)
+//   dQ  += dS K                            (accumulates over the key tiles in columns 128-255)
+// dV^T and dK^T come out with the head dimension on the tensor-memory lanes; the row warps stage
+// them in shared memory as [key row][head dim] fp32 and bulk reductions (cp.reduce.async.bulk)
+// add each key row to the fp32 dK / dV buffers: the query heads of a group and the query tiles
+// of a segment all add into the same rows. dQ needs
+// no atomics; it is scaled, rounded to fp16 and stored when the walk ends. dS is written over
+// the value tile (dead once dP exists), which keeps shared memory at 112 KB: two CTAs per SM.
+struct BwdSmem {          // 112 KB of tiles: the dynamic shared memory itself must start on a 1 KB
+  uint8_t q[kQBytes];    // boundary (checked by the kernel), there is no room for alignment slack
+  uint8_t d_o[kQBytes];
+  uint8_t k[kKBytes];
+  uint8_t v[kKBytes];     // V_t, then dS_t
+  uint8_t p[kPBytes];
+  uint64_t q_full, k_full, k_empty, v_full, v_empty, sdp_full, pds_full, grads_full, acc_free;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+struct AttnBwdArgs {
+  const int32_t* cu;
+  const __half* out;     // [n, hq, 128]
+  const __half* d_out;   // [n, hq, 128]
+  const float* lse;      // [hq, n]
+  __half* dq;            // [n, hq, 128]
+  float* dk;             // [n, hk, 128] fp32, zero on entry
+  float* dv;             // [n, hk, 128] fp32, zero on entry
+  int n, segments, hq, hk, group;
+  float scale_log2, scale;
+  int* status;
+};
+
+// Adds `bytes` of fp32 values in shared memory to global memory (both 16-byte aligned, bytes a
+// multiple of 16) by one bulk asynchronous reduction; part of the thread's current bulk group.
+__device__ __forceinline__ void bulk_red_add_f32(float* gdst, const void* ssrc, uint32_t bytes) {
+  asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;"
+               ::"l"(gdst), "r"(smem_u32(ssrc)), "r"(bytes)
+               : "memory");
+}
+
+__device__ __forceinline__ void row_warps_sync() {   // the four row warps, named barrier 1
+  asm volatile("bar.sync 1, 128;" ::: "memory");
+}
+
+__device__ __forceinline__ void write_tile_row(uint8_t* tile, int r, const uint32_t (&packed)[32]) {
+  // row r of a [128 x 64] fp16 tile in the 128-byte swizzle: chunk j at position j ^ (r & 7)
+  uint8_t* row = tile + r * 128;
+#pragma unroll
+  for (int j = 0; j < 8; ++j)
+    *reinterpret_cast<uint4*>(row + ((j ^ (r & 7)) << 4)) =
+        make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+}
+
+__global__ void __launch_bounds__(kThreads, 2)
+attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_do,
+                const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                AttnBwdArgs a) {
+  extern __shared__ __align__(1024) uint8_t raw[];
+  int seg_begin, seg_end, q0;
+  if (!locate(a.cu, a.segments, blockIdx.x, seg_begin, seg_end, q0)) return;
+  if (smem_u32(raw) & 1023u) {   // the swizzled tiles need 1 KB alignment
+    if (threadIdx.x == 0 && a.status) atomicCAS(a.status, 0, 60);
+    return;
+  }
+  BwdSmem& s = *reinterpret_cast<BwdSmem*>(raw);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int h = blockIdx.y, hk = h / a.group;
+  const int q_end = min(seg_end, q0 + kBQ);
+  const int n_kv = (q_end - seg_begin + kBKV - 1) / kBKV;
+  if (threadIdx.x == 0) {
+    mbar_init(&s.q_full, 1);
+    mbar_init(&s.k_full, 1);
+    mbar_init(&s.k_empty, 1);
+    mbar_init(&s.v_full, 1);
+    mbar_init(&s.v_empty, 1);
+    mbar_init(&s.sdp_full, 1);
+    mbar_init(&s.pds_full, 4);
+    mbar_init(&s.grads_full, 1);
+    mbar_init(&s.acc_free, 4);
+    s.abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 4) {
+    tmem_alloc(&s.tmem_base, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = s.tmem_base;
+  volatile int* abort_flag = &s.abort_flag;
+
+  if (warp == 4) {
+    if (lane == 0) {   // Q, dO, then the key tiles
+      prefetch_tensormap(&map_q);
+      prefetch_tensormap(&map_do);
+      prefetch_tensormap(&map_k);
+      mbar_expect_tx(&s.q_full, 2 * kQBytes);
+      tma_load_2d(s.q, &map_q, h * kD, q0, &s.q_full);
+      tma_load_2d(s.q + kQBox, &map_q, h * kD + 64, q0, &s.q_full);
+      tma_load_2d(s.d_o, &map_do, h * kD, q0, &s.q_full);
+      tma_load_2d(s.d_o + kQBox, &map_do, h * kD + 64, q0, &s.q_full);
+      for (int t = 0; t < n_kv; ++t) {
+        if (t > 0 && !mbar_wait(&s.k_empty, (t - 1) & 1, abort_flag, a.status, 51)) break;
+        const int row = seg_begin + t * kBKV;
+        mbar_expect_tx(&s.k_full, kKBytes);
+        tma_load_2d(s.k, &map_k, hk * kD, row, &s.k_full);
+        tma_load_2d(s.k + kKVBox, &map_k, hk * kD + 64, row, &s.k_full);
+      }
+    }
+  } else if (warp == 6) {
+    if (lane == 0) {   // the value tiles (their buffer is dS's afterwards)
+      prefetch_tensormap(&map_v);
+      for (int t = 0; t < n_kv; ++t) {
+        if (t > 0 && !mbar_wait(&s.v_empty, (t - 1) & 1, abort_flag, a.status, 52)) break;
+        const int row = seg_begin + t * kBKV;
+        mbar_expect_tx(&s.v_full, kKBytes);
+        tma_load_2d(s.v, &map_v, hk * kD, row, &s.v_full);
+        tma_load_2d(s.v + kKVBox, &map_v, hk * kD + 64, row, &s.v_full);
+      }
+    }
+  } else if (warp == 5) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = make_idesc_f16(kBQ, kBKV, kFmtF16, kFmtF16, false, false);
+      constexpr uint32_t idesc_t = make_idesc_f16(kD, kBKV, kFmtF16, kFmtF16, true, true);
+      constexpr uint32_t idesc_q = make_idesc_f16(kBQ, kD, kFmtF16, kFmtF16, false, true);
+      const uint64_t dq_k = make_smem_desc(smem_u32(s.q), 16, 1024);          // Q, K-major
+      const uint64_t ddo_k = make_smem_desc(smem_u32(s.d_o), 16, 1024);       // dO, K-major
+      const uint64_t dq_mn = make_smem_desc(smem_u32(s.q), kQBox, 1024);      // Q^T: MN-major A
+      const uint64_t ddo_mn = make_smem_desc(smem_u32(s.d_o), kQBox, 1024);   // dO^T: MN-major A
+      const uint64_t dk_k = make_smem_desc(smem_u32(s.k), 16, 1024);          // K, K-major B
+      const uint64_t dk_mn = make_smem_desc(smem_u32(s.k), kKVBox, 1024);     // K, MN-major B
+      const uint64_t dv_k = make_smem_desc(smem_u32(s.v), 16, 1024);          // V, K-major B
+      const uint64_t dds_k = make_smem_desc(smem_u32(s.v), 16, 1024);         // dS, K-major A
+      const uint64_t dds_mn = make_smem_desc(smem_u32(s.v), kPBytes, 1024);   // dS, MN-major B
+      const uint64_t dp_mn = make_smem_desc(smem_u32(s.p), kPBytes, 1024);    // P, MN-major B
+      bool ok = mbar_wait(&s.q_full, 0, abort_flag, a.status, 53);
+      for (int t = 0; t < n_kv && ok; ++t) {
+        ok = mbar_wait(&s.k_full, t & 1, abort_flag, a.status, 54);
+        if (ok) ok = mbar_wait(&s.v_full, t & 1, abort_flag, a.status, 55);
+        if (ok && t > 0) ok = mbar_wait(&s.acc_free, (t - 1) & 1, abort_flag, a.status, 56);
+        if (!ok) break;
+        tc_fence_after_sync();
+#pragma unroll
+        for (int k8 = 0; k8 < kD / 16; ++k8) {   // along the head dimension
+          const uint32_t qa = (uint32_t)(k8 >> 2) * (kQBox >> 4) + (uint32_t)(k8 & 3) * 2;
+          const uint32_t kb = (uint32_t)(k8 >> 2) * (kKVBox >> 4) + (uint32_t)(k8 & 3) * 2;
+          mma_f16_ss(tmem, dq_k + qa, dk_k + kb, idesc_s, k8 != 0);
+        }
+#pragma unroll
+        for (int k8 = 0; k8 < kD / 16; ++k8) {
+          const uint32_t qa = (uint32_t)(k8 >> 2) * (kQBox >> 4) + (uint32_t)(k8 & 3) * 2;
+          const uint32_t kb = (uint32_t)(k8 >> 2) * (kKVBox >> 4) + (uint32_t)(k8 & 3) * 2;
+          mma_f16_ss(tmem + kBKV, ddo_k + qa, dv_k + kb, idesc_s, k8 != 0);
+        }
+        tc_commit(&s.sdp_full);
+        ok = mbar_wait(&s.pds_full, t & 1, abort_flag, a.status, 57);
+        if (!ok) break;
+        tc_fence_after_sync();
+#pragma unroll
+        for (int k8 = 0; k8 < kBQ / 16; ++k8) {   // along the query rows: 16 rows = 2048 bytes
+          mma_f16_ss(tmem, ddo_mn + k8 * (2048 >> 4), dp_mn + k8 * (2048 >> 4), idesc_t, k8 != 0);
+        }
+#pragma unroll
+        for (int k8 = 0; k8 < kBQ / 16; ++k8) {
+          mma_f16_ss(tmem + kBKV, dq_mn + k8 * (2048 >> 4), dds_mn + k8 * (2048 >> 4), idesc_t, k8 != 0);
+        }
+#pragma unroll
+        for (int k4 = 0; k4 < kBKV / 16; ++k4)    // along the key rows of the tile
+          mma_f16_ss(tmem + 2 * kBKV, dds_k + k4 * 2, dk_mn + k4 * (2048 >> 4), idesc_q, (t | k4) != 0);
+        tc_commit(&s.grads_full);
+        tc_commit(&s.k_empty);
+      }
+    }
+  } else {
+    const int r = threadIdx.x;
+    const int q_idx = q0 + r;
+    const bool valid = q_idx < seg_end;
+    const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
+    // D = rowsum(dO o O) and the row's log-sum-exp (in log2 units)
+    float delta = 0.f, lse2 = 0.f;
+    if (valid) {
+      const uint4* po = reinterpret_cast<const uint4*>(a.out + ((size_t)q_idx * a.hq + h) * kD);
+      const uint4* pg = reinterpret_cast<const uint4*>(a.d_out + ((size_t)q_idx * a.hq + h) * kD);
+#pragma unroll
+      for (int i = 0; i < kD / 8; ++i) {
+        const uint4 x = po[i], y = pg[i];
+        const __half2* xh = reinterpret_cast<const __half2*>(&x);
+        const __half2* yh = reinterpret_cast<const __half2*>(&y);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 xf = __half22float2(xh[e]), yf = __half22float2(yh[e]);
+          delta = fmaf(xf.x, yf.x, fmaf(xf.y, yf.y, delta));
+        }
+      }
+      lse2 = a.lse[(size_t)h * a.n + q_idx] * 1.4426950408889634f;
+    }
+    const float sl = a.scale_log2;
+    const int d_idx = warp * 32 + lane;          // this thread's row of dV^T / dK^T
+    bool ok = true;
+    for (int t = 0; t < n_kv && ok; ++t) {
+      const int kv0 = seg_begin + t * kBKV;
+      ok = mbar_wait(&s.sdp_full, t & 1, abort_flag, a.status, 58);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const int limit = valid ? q_idx - kv0 : -1;    // columns 0..limit are visible
+      uint32_t pp[32], ds[32];
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t x[32], y[32];
+        tmem_ld_32x32(lane_base + half * 32, x);
+        tmem_ld_32x32(lane_base + kBKV + half * 32, y);
+        tmem_ld_wait_on(x);
+        tmem_ld_wait_on(y);
+#pragma unroll
+        for (int c = 0; c < 32; c += 2) {
+          float p0 = 0.f, p1 = 0.f;
+          if (c + half * 32 <= limit) p0 = exp2f(fmaf(__uint_as_float(x[c]), sl, -lse2));
+          if (c + 1 + half * 32 <= limit) p1 = exp2f(fmaf(__uint_as_float(x[c + 1]), sl, -lse2));
+          const float g0 = p0 * (__uint_as_float(y[c]) - delta);
+          const float g1 = p1 * (__uint_as_float(y[c + 1]) - delta);
+          __half2 ph = __floats2half2_rn(p0, p1), gh = __floats2half2_rn(g0, g1);
+          pp[half * 16 + (c >> 1)] = *reinterpret_cast<uint32_t*>(&ph);
+          ds[half * 16 + (c >> 1)] = *reinterpret_cast<uint32_t*>(&gh);
+        }
+      }
+      write_tile_row(s.p, r, pp);
+      write_tile_row(s.v, r, ds);    // V is dead: dP has been formed
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s.pds_full);
+      ok = mbar_wait(&s.grads_full, t & 1, abort_flag, a.status, 59);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after_sync();
+      // dV^T and dK^T leave through shared memory: thread d writes its 64 values as column d of a
+      // [64 key rows x 128] fp32 tile (the value and probability buffers, both dead by now), and
+      // the first 64 threads each add one 512-byte key row to global memory with a bulk
+      // reduction: the copy engine does the atomic adds, not 128 red instructions per thread.
+      const int rows_here = min(kBKV, q_end - kv0);   // key rows of this tile that exist for this CTA
+      float* stage = reinterpret_cast<float*>(s.v);
+#pragma unroll
+      for (int which = 0; which < 2; ++which) {
+        const float mul = which ? a.scale : 1.f;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t x[32];
+          tmem_ld_32x32(lane_base + which * kBKV + half * 32, x);
+          tmem_ld_wait_on(x);
+#pragma unroll
+          for (int c = 0; c < 32; ++c) stage[(c + half * 32) * kD + d_idx] = __uint_as_float(x[c]) * mul;
+        }
+        fence_proxy_async_smem();
+        row_warps_sync();
+        if (r < rows_here) {
+          float* dst = (which ? a.dk : a.dv) + ((size_t)(kv0 + r) * a.hk + hk) * kD;
+          bulk_red_add_f32(dst, stage + r * kD, kD * sizeof(float));
+        }
+        tma_store_commit();
+        tma_store_wait_read<0>();    // the staged rows have been read: the tile can be rewritten
+        row_warps_sync();
+      }
+      tc_fence_before_sync();
+      if (r == 0) mbar_arrive(&s.v_empty);     // the value buffer is free for the next tile
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s.acc_free);
+    }
+    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // this thread's reductions have landed
+    if (ok) {   // dQ: complete once the last tile's products are (grads_full of the last step)
+      __half* dst = a.dq + ((size_t)q_idx * a.hq + h) * kD;
+#pragma unroll
+      for (int c0 = 0; c0 < kD; c0 += 32) {
+        uint32_t o[32];
+        tmem_ld_32x32(lane_base + 2 * kBKV + c0, o);
+        tmem_ld_wait_on(o);
+        if (valid) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint32_t w[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              __half2 hh = __floats2half2_rn(__uint_as_float(o[8 * j + 2 * e]) * a.scale,
+                                             __uint_as_float(o[8 * j + 2 * e + 1]) * a.scale);
+              w[e] = *reinterpret_cast<uint32_t*>(&hh);
+            }
+            *reinterpret_cast<uint4*>(dst + c0 + 8 * j) = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        }
+      }
+      tc_fence_before_sync();
+    }
+  }
+  __syncthreads();
+  if (warp == 4) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem, kTmemCols);
+  }
+}
+
+}  // namespace
+}  // namespace soup
+
 extern "C" int soup_attn_fwd(const void* q, const void* k, const void* v, const int32_t* cu_rows,
                              void* out, float* lse, int64_t n_tokens, int64_t n_segments,
                              int64_t hq, int64_t hk, int64_t head_dim, int64_t q_pitch,
@@ -328,6 +641,11 @@ extern "C" int soup_attn_fwd(const void* q, const void* k, const void* v, const 
     SOUP_FAIL(SOUP_ERR_ARG, "attn_fwd: row pitches must cover the heads and be multiples of 8 elements");
   if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(out))
     SOUP_FAIL(SOUP_ERR_ARG, "attn_fwd: pointers must be 16-byte aligned");
+  // a runtime call first: it makes the device's context current on this thread (autograd runs
+  // backward on threads of its own), which the driver's tensor-map encoder needs
+  const size_t smem = sizeof(Smem) + 1024;
+  if (cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+    SOUP_FAIL(SOUP_ERR_LAUNCH, "attn_fwd: shared memory attribute");
   CUtensorMap mq, mk, mv;
   if (umma::encode_map_2d_16bit(&mq, q, (uint64_t)n_tokens, (uint64_t)(hq * kD), (uint64_t)q_pitch, kBQ, 64, false) ||
       umma::encode_map_2d_16bit(&mk, k, (uint64_t)n_tokens, (uint64_t)(hk * kD), (uint64_t)k_pitch, kBKV, 64, false) ||
@@ -344,13 +662,66 @@ extern "C" int soup_attn_fwd(const void* q, const void* k, const void* v, const 
   a.scale = scale;
   a.scale_log2 = scale * 1.4426950408889634f;
   a.status = rowpipe::status_word();
-  const size_t smem = sizeof(Smem) + 1024;
-  if (cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-    SOUP_FAIL(SOUP_ERR_LAUNCH, "attn_fwd: shared memory attribute");
   // every segment adds at most one partial tile to the tiles of the packed row
   const unsigned slots = (unsigned)((n_tokens + kBQ - 1) / kBQ + n_segments);
   dim3 grid(slots, (unsigned)hq);
   attn_fwd_kernel<<<grid, kThreads, smem, reinterpret_cast<cudaStream_t>(stream)>>>(mq, mk, mv, a);
   SOUP_CHECK_LAUNCH("attn_fwd");
+  return SOUP_OK;
+}
+
+extern "C" int soup_attn_bwd(const void* q, const void* k, const void* v, const void* out,
+                             const void* d_out, const float* lse, const int32_t* cu_rows, void* dq,
+                             float* dk, float* dv, int64_t n_tokens, int64_t n_segments, int64_t hq,
+                             int64_t hk, int64_t head_dim, int64_t q_pitch, int64_t k_pitch,
+                             int64_t v_pitch, float scale, void* stream) {
+  using namespace soup;
+  if (n_tokens == 0 || n_segments == 0) return SOUP_OK;
+  if (!q || !k || !v || !out || !d_out || !lse || !cu_rows || !dq || !dk || !dv)
+    SOUP_FAIL(SOUP_ERR_ARG, "attn_bwd: null pointer");
+  if (head_dim != kD) SOUP_FAIL(SOUP_ERR_ARG, "attn_bwd: head_dim must be 128");
+  if (n_tokens < 0 || n_segments < 0 || hq <= 0 || hk <= 0 || hq % hk)
+    SOUP_FAIL(SOUP_ERR_ARG, "attn_bwd: bad sizes (query heads must be a multiple of key heads)");
+  if (n_tokens > (1 << 30) || n_segments > 65535 || hq > 65535)
+    SOUP_FAIL(SOUP_ERR_ARG, "attn_bwd: too many tokens, segments or heads");
+  if (q_pitch < hq * kD || k_pitch < hk * kD || v_pitch < hk * kD || (q_pitch | k_pitch | v_pitch) & 7)
+    SOUP_FAIL(SOUP_ERR_ARG, "attn_bwd: row pitches must cover the heads and be multiples of 8 elements");
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(out) || !aligned16(d_out) || !aligned16(dq))
+    SOUP_FAIL(SOUP_ERR_ARG, "attn_bwd: pointers must be 16-byte aligned");
+  // a runtime call first (see soup_attn_fwd): backward usually runs on an autograd thread
+  const size_t smem = sizeof(BwdSmem);
+  if (cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+    SOUP_FAIL(SOUP_ERR_LAUNCH, "attn_bwd: shared memory attribute");
+  CUtensorMap mq, mdo, mk, mv;
+  const int e_q = umma::encode_map_2d_16bit(&mq, q, (uint64_t)n_tokens, (uint64_t)(hq * kD), (uint64_t)q_pitch, kBQ, 64, false);
+  const int e_do = umma::encode_map_2d_16bit(&mdo, d_out, (uint64_t)n_tokens, (uint64_t)(hq * kD), (uint64_t)(hq * kD), kBQ, 64, false);
+  const int e_k = umma::encode_map_2d_16bit(&mk, k, (uint64_t)n_tokens, (uint64_t)(hk * kD), (uint64_t)k_pitch, kBKV, 64, false);
+  const int e_v = umma::encode_map_2d_16bit(&mv, v, (uint64_t)n_tokens, (uint64_t)(hk * kD), (uint64_t)v_pitch, kBKV, 64, false);
+  if (e_q || e_do || e_k || e_v)
+    SOUP_FAIL(SOUP_ERR_LAUNCH, "attn_bwd: cuTensorMapEncodeTiled failed (q %d, d_out %d, k %d, v %d)", e_q, e_do, e_k, e_v);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const size_t kv_bytes = (size_t)n_tokens * hk * kD * sizeof(float);
+  if (cudaMemsetAsync(dk, 0, kv_bytes, st) != cudaSuccess || cudaMemsetAsync(dv, 0, kv_bytes, st) != cudaSuccess)
+    SOUP_FAIL(SOUP_ERR_LAUNCH, "attn_bwd: clearing dk / dv failed");
+  AttnBwdArgs a;
+  a.cu = cu_rows;
+  a.out = reinterpret_cast<const __half*>(out);
+  a.d_out = reinterpret_cast<const __half*>(d_out);
+  a.lse = lse;
+  a.dq = reinterpret_cast<__half*>(dq);
+  a.dk = dk;
+  a.dv = dv;
+  a.n = (int)n_tokens;
+  a.segments = (int)n_segments;
+  a.hq = (int)hq;
+  a.hk = (int)hk;
+  a.group = (int)(hq / hk);
+  a.scale = scale;
+  a.scale_log2 = scale * 1.4426950408889634f;
+  a.status = rowpipe::status_word();
+  const unsigned slots = (unsigned)((n_tokens + kBQ - 1) / kBQ + n_segments);
+  dim3 grid(slots, (unsigned)hq);
+  attn_bwd_kernel<<<grid, kThreads, smem, st>>>(mq, mdo, mk, mv, a);
+  SOUP_CHECK_LAUNCH("attn_bwd");
   return SOUP_OK;
 }

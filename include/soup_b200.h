@@ -189,6 +189,18 @@ int soup_attn_fwd(const void* q, const void* k, const void* v, const int32_t* cu
                   int64_t head_dim, int64_t q_pitch, int64_t k_pitch, int64_t v_pitch, float scale,
                   void* stream);
 
+/* Backward of soup_attn_fwd: from q, k, v, the forward's out and lse, and d_out, the gradients
+ *   dq [n_tokens, hq, 128] fp16 contiguous (every token inside a segment is written),
+ *   dk, dv [n_tokens, hk, 128] fp32 contiguous: cleared here, then accumulated with atomic adds over
+ *   the query heads of a group and the query tiles of a segment (their last bits can differ
+ *   between runs).
+ * out and d_out are [n_tokens, hq, 128] fp16 contiguous; the rest as in soup_attn_fwd. In the
+ * reference this is the backward of torch SDPA (solution/attention.py:332-343). */
+int soup_attn_bwd(const void* q, const void* k, const void* v, const void* out, const void* d_out,
+                  const float* lse, const int32_t* cu_rows, void* dq, float* dk, float* dv,
+                  int64_t n_tokens, int64_t n_segments, int64_t hq, int64_t hk, int64_t head_dim,
+                  int64_t q_pitch, int64_t k_pitch, int64_t v_pitch, float scale, void* stream);
+
 /* out = round_out(round_gate?(silu(gate)) * up). Replaces silu_mul_fwd_persistent at
  * solution/swiglu_recompute.py:98-100 and :176-178 (kernel :36-48). */
 int soup_silu_mul_fwd(const void* gate, const void* up, void* out, int64_t n, int gate_dtype,

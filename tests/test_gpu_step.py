@@ -227,9 +227,10 @@ def test_segment_attention_matches_the_masked_formula(dtype, autocast, lens, mon
         out = segment_attention(q, k, v, cu, max(lens), d ** -0.5)
     assert out.shape == (1, n, hq, d) and out.is_contiguous()
     assert out.dtype == (torch.float16 if autocast else dtype)
-    # fp16 operands with adjacent heads: the forward is this library's kernel
+    # fp16 operands with adjacent heads: forward and backward are this library's kernels
     assert ("soup_attn_fwd" in launches) == (dtype == torch.float16)
     out.backward(go.to(out.dtype))
+    assert ("soup_attn_bwd" in launches) == (dtype == torch.float16)
     got = [out.detach().float().cpu()] + [t.grad.float().cpu() for t in (q, k, v)]
     assert all(t.grad.dtype == dtype for t in (q, k, v))
     q2, k2, v2 = (t.detach().double().requires_grad_() for t in (q, k, v))
