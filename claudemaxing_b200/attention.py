@@ -32,8 +32,7 @@ def attention_gradients(q, k, v, out, lse, grad, cu_rows, scale):
     n, hq, d = q.shape
     grad = grad if grad.is_contiguous() else grad.contiguous()
     dq = torch.empty((n, hq, d), dtype=q.dtype, device=q.device)
-    dk = torch.empty((n, k.shape[1], d), dtype=torch.float32, device=q.device)
-    dv = torch.empty((n, k.shape[1], d), dtype=torch.float32, device=q.device)
+    dk, dv = torch.empty((2, n, k.shape[1], d), dtype=torch.float32, device=q.device)   # one clear
     _lib.call("soup_attn_bwd", _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(out), _lib.ptr(grad),
               _lib.ptr(lse), _lib.ptr(cu_rows), _lib.ptr(dq), _lib.ptr(dk), _lib.ptr(dv), n,
               cu_rows.numel() - 1, hq, k.shape[1], d, q.stride(0), k.stride(0), v.stride(0),

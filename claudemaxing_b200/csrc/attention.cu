@@ -316,25 +316,33 @@ namespace soup {
 namespace {
 
 // ------------------------------------------------------------------------------------------
-// Backward. Same decomposition as forward: a CTA owns 128 query tokens of one segment and one
-// query head and walks the key tiles it may see. Per key tile (64 tokens):
-//   S = Q K^T and dP = dO V^T            (two products into tensor-memory columns 0-63 / 64-127)
+// Backward. Same decomposition as forward (a CTA owns 128 query tokens of one segment and one
+// query head and walks the key tiles it may see), but with key tiles of 128 tokens and one CTA
+// per SM: the walk is a chain of dependent steps, so fewer and larger steps are what shorten it.
+// Per key tile:
+//   S = Q K^T and dP = dO V^T            (two products into tensor-memory columns 0-127 / 128-255)
 //   P = exp(scale S - lse), dS = P (dP - D)   by the four row warps (D = rowsum(dO o O), formed
 //                                         by the same threads when the kernel starts)
 //   dV^T = dO^T P, dK^T = Q^T dS          (A and B both MN-major; into the columns S and dP left)
-//   dQ  += dS K                            (accumulates over the key tiles in columns 128-255)
+//   dQ  += dS K                            (accumulates over the key tiles in columns 256-383)
 // dV^T and dK^T come out with the head dimension on the tensor-memory lanes; the row warps stage
-// them in shared memory as [key row][head dim] fp32 and bulk reductions (cp.reduce.async.bulk)
-// add each key row to the fp32 dK / dV buffers: the query heads of a group and the query tiles
-// of a segment all add into the same rows. dQ needs
-// no atomics; it is scaled, rounded to fp16 and stored when the walk ends. dS is written over
-// the value tile (dead once dP exists), which keeps shared memory at 112 KB: two CTAs per SM.
-struct BwdSmem {          // 112 KB of tiles: the dynamic shared memory itself must start on a 1 KB
-  uint8_t q[kQBytes];    // boundary (checked by the kernel), there is no room for alignment slack
-  uint8_t d_o[kQBytes];
-  uint8_t k[kKBytes];
-  uint8_t v[kKBytes];     // V_t, then dS_t
-  uint8_t p[kPBytes];
+// them in shared memory as [key row][head dim] fp32 (over the V, P, dS and K tiles, all dead by
+// then) and bulk reductions (cp.reduce.async.bulk) add each key row to the fp32 dK / dV buffers:
+// the query heads of a group and the query tiles of a segment all add into the same rows. dQ
+// needs no atomics; it is scaled, rounded to fp16 and stored when the walk ends. CTAs take the
+// tiles with the longest walks first (`locate_heavy_first`), so that the few CTAs beyond one per
+// SM are short ones.
+constexpr int kBKVb = 128;                     // key rows per tile in backward
+constexpr int kTileBytes = kBKVb * kD * 2;     // 32 KB: every fp16 tile here is [128 x 128]
+constexpr uint32_t kTmemColsBwd = 512;         // S/dV^T [0,128) dP/dK^T [128,256) dQ [256,384)
+
+struct BwdSmem {
+  uint8_t q[kTileBytes];
+  uint8_t d_o[kTileBytes];
+  uint8_t v[kTileBytes];     // V_t; with p: the fp32 staging tile of dV
+  uint8_t p[kTileBytes];
+  uint8_t ds[kTileBytes];    // dS_t; with k: the fp32 staging tile of dK
+  uint8_t k[kTileBytes];
   uint64_t q_full, k_full, k_empty, v_full, v_empty, sdp_full, pds_full, grads_full, acc_free;
   uint32_t tmem_base;
   int abort_flag;
@@ -365,31 +373,53 @@ __device__ __forceinline__ void row_warps_sync() {   // the four row warps, name
   asm volatile("bar.sync 1, 128;" ::: "memory");
 }
 
-__device__ __forceinline__ void write_tile_row(uint8_t* tile, int r, const uint32_t (&packed)[32]) {
-  // row r of a [128 x 64] fp16 tile in the 128-byte swizzle: chunk j at position j ^ (r & 7)
-  uint8_t* row = tile + r * 128;
+// Four 16-byte chunks (32 fp16 columns starting at column `col0`, a multiple of 32) of row r of a
+// [128 x 128] fp16 tile stored as two 128-byte-swizzled boxes of 64 columns.
+__device__ __forceinline__ void write_tile_chunks(uint8_t* tile, int r, int col0, const uint32_t (&w)[16]) {
+  uint8_t* row = tile + (col0 >> 6) * (kTileBytes / 2) + r * 128;
+  const int j0 = (col0 & 63) >> 3;
 #pragma unroll
-  for (int j = 0; j < 8; ++j)
-    *reinterpret_cast<uint4*>(row + ((j ^ (r & 7)) << 4)) =
-        make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+  for (int j = 0; j < 4; ++j)
+    *reinterpret_cast<uint4*>(row + (((j0 + j) ^ (r & 7)) << 4)) =
+        make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
 }
 
-__global__ void __launch_bounds__(kThreads, 2)
+// Like `locate`, but the slots go through the tiles in the order of their walks' lengths: the
+// last tile of every segment first, then the ones before them, and so on.
+__device__ __forceinline__ bool locate_heavy_first(const int32_t* cu, int segments, int slot,
+                                                   int& seg_begin, int& seg_end, int& q0) {
+  if (segments > 64) return locate(cu, segments, slot, seg_begin, seg_end, q0);
+  int deepest = 0;
+  for (int s = 0; s < segments; ++s) deepest = max(deepest, (cu[s + 1] - cu[s] + kBQ - 1) / kBQ);
+  int base = 0;
+  for (int level = deepest - 1; level >= 0; --level)
+    for (int s = 0; s < segments; ++s) {
+      const int b = cu[s], e = cu[s + 1];
+      if ((e - b + kBQ - 1) / kBQ > level) {
+        if (slot == base) {
+          seg_begin = b;
+          seg_end = e;
+          q0 = b + level * kBQ;
+          return true;
+        }
+        ++base;
+      }
+    }
+  return false;
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_do,
                 const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                 AttnBwdArgs a) {
-  extern __shared__ __align__(1024) uint8_t raw[];
+  extern __shared__ uint8_t raw[];
   int seg_begin, seg_end, q0;
-  if (!locate(a.cu, a.segments, blockIdx.x, seg_begin, seg_end, q0)) return;
-  if (smem_u32(raw) & 1023u) {   // the swizzled tiles need 1 KB alignment
-    if (threadIdx.x == 0 && a.status) atomicCAS(a.status, 0, 60);
-    return;
-  }
-  BwdSmem& s = *reinterpret_cast<BwdSmem*>(raw);
+  if (!locate_heavy_first(a.cu, a.segments, blockIdx.x, seg_begin, seg_end, q0)) return;
+  BwdSmem& s = *reinterpret_cast<BwdSmem*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int h = blockIdx.y, hk = h / a.group;
   const int q_end = min(seg_end, q0 + kBQ);
-  const int n_kv = (q_end - seg_begin + kBKV - 1) / kBKV;
+  const int n_kv = (q_end - seg_begin + kBKVb - 1) / kBKVb;
   if (threadIdx.x == 0) {
     mbar_init(&s.q_full, 1);
     mbar_init(&s.k_full, 1);
@@ -404,7 +434,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     fence_barrier_init();
   }
   if (warp == 4) {
-    tmem_alloc(&s.tmem_base, kTmemCols);
+    tmem_alloc(&s.tmem_base, kTmemColsBwd);
     tmem_relinquish();
   }
   tc_fence_before_sync();
@@ -412,87 +442,85 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   tc_fence_after_sync();
   const uint32_t tmem = s.tmem_base;
   volatile int* abort_flag = &s.abort_flag;
+  constexpr int kBox = kTileBytes / 2;   // one [128 rows x 64 cols] box
 
   if (warp == 4) {
     if (lane == 0) {   // Q, dO, then the key tiles
       prefetch_tensormap(&map_q);
       prefetch_tensormap(&map_do);
       prefetch_tensormap(&map_k);
-      mbar_expect_tx(&s.q_full, 2 * kQBytes);
+      mbar_expect_tx(&s.q_full, 2 * kTileBytes);
       tma_load_2d(s.q, &map_q, h * kD, q0, &s.q_full);
-      tma_load_2d(s.q + kQBox, &map_q, h * kD + 64, q0, &s.q_full);
+      tma_load_2d(s.q + kBox, &map_q, h * kD + 64, q0, &s.q_full);
       tma_load_2d(s.d_o, &map_do, h * kD, q0, &s.q_full);
-      tma_load_2d(s.d_o + kQBox, &map_do, h * kD + 64, q0, &s.q_full);
+      tma_load_2d(s.d_o + kBox, &map_do, h * kD + 64, q0, &s.q_full);
       for (int t = 0; t < n_kv; ++t) {
         if (t > 0 && !mbar_wait(&s.k_empty, (t - 1) & 1, abort_flag, a.status, 51)) break;
-        const int row = seg_begin + t * kBKV;
-        mbar_expect_tx(&s.k_full, kKBytes);
+        const int row = seg_begin + t * kBKVb;
+        mbar_expect_tx(&s.k_full, kTileBytes);
         tma_load_2d(s.k, &map_k, hk * kD, row, &s.k_full);
-        tma_load_2d(s.k + kKVBox, &map_k, hk * kD + 64, row, &s.k_full);
+        tma_load_2d(s.k + kBox, &map_k, hk * kD + 64, row, &s.k_full);
       }
     }
   } else if (warp == 6) {
-    if (lane == 0) {   // the value tiles (their buffer is dS's afterwards)
+    if (lane == 0) {   // the value tiles
       prefetch_tensormap(&map_v);
       for (int t = 0; t < n_kv; ++t) {
         if (t > 0 && !mbar_wait(&s.v_empty, (t - 1) & 1, abort_flag, a.status, 52)) break;
-        const int row = seg_begin + t * kBKV;
-        mbar_expect_tx(&s.v_full, kKBytes);
+        const int row = seg_begin + t * kBKVb;
+        mbar_expect_tx(&s.v_full, kTileBytes);
         tma_load_2d(s.v, &map_v, hk * kD, row, &s.v_full);
-        tma_load_2d(s.v + kKVBox, &map_v, hk * kD + 64, row, &s.v_full);
+        tma_load_2d(s.v + kBox, &map_v, hk * kD + 64, row, &s.v_full);
       }
     }
   } else if (warp == 5) {
     if (lane == 0) {
-      constexpr uint32_t idesc_s = make_idesc_f16(kBQ, kBKV, kFmtF16, kFmtF16, false, false);
-      constexpr uint32_t idesc_t = make_idesc_f16(kD, kBKV, kFmtF16, kFmtF16, true, true);
+      // every operand is a [128 x 128] fp16 tile of two swizzled boxes: K-major steps of 16
+      // columns advance 32 bytes inside a box (4 per box); MN-major steps of 16 rows advance
+      // 2048 bytes, the two boxes being the leading-dimension offset apart
+      constexpr uint32_t idesc_s = make_idesc_f16(kBQ, kBKVb, kFmtF16, kFmtF16, false, false);
+      constexpr uint32_t idesc_t = make_idesc_f16(kD, kBKVb, kFmtF16, kFmtF16, true, true);
       constexpr uint32_t idesc_q = make_idesc_f16(kBQ, kD, kFmtF16, kFmtF16, false, true);
-      const uint64_t dq_k = make_smem_desc(smem_u32(s.q), 16, 1024);          // Q, K-major
-      const uint64_t ddo_k = make_smem_desc(smem_u32(s.d_o), 16, 1024);       // dO, K-major
-      const uint64_t dq_mn = make_smem_desc(smem_u32(s.q), kQBox, 1024);      // Q^T: MN-major A
-      const uint64_t ddo_mn = make_smem_desc(smem_u32(s.d_o), kQBox, 1024);   // dO^T: MN-major A
-      const uint64_t dk_k = make_smem_desc(smem_u32(s.k), 16, 1024);          // K, K-major B
-      const uint64_t dk_mn = make_smem_desc(smem_u32(s.k), kKVBox, 1024);     // K, MN-major B
-      const uint64_t dv_k = make_smem_desc(smem_u32(s.v), 16, 1024);          // V, K-major B
-      const uint64_t dds_k = make_smem_desc(smem_u32(s.v), 16, 1024);         // dS, K-major A
-      const uint64_t dds_mn = make_smem_desc(smem_u32(s.v), kPBytes, 1024);   // dS, MN-major B
-      const uint64_t dp_mn = make_smem_desc(smem_u32(s.p), kPBytes, 1024);    // P, MN-major B
+      const uint64_t q_k = make_smem_desc(smem_u32(s.q), 16, 1024);
+      const uint64_t do_k = make_smem_desc(smem_u32(s.d_o), 16, 1024);
+      const uint64_t k_k = make_smem_desc(smem_u32(s.k), 16, 1024);
+      const uint64_t v_k = make_smem_desc(smem_u32(s.v), 16, 1024);
+      const uint64_t ds_k = make_smem_desc(smem_u32(s.ds), 16, 1024);
+      const uint64_t q_mn = make_smem_desc(smem_u32(s.q), kBox, 1024);
+      const uint64_t do_mn = make_smem_desc(smem_u32(s.d_o), kBox, 1024);
+      const uint64_t k_mn = make_smem_desc(smem_u32(s.k), kBox, 1024);
+      const uint64_t p_mn = make_smem_desc(smem_u32(s.p), kBox, 1024);
+      const uint64_t ds_mn = make_smem_desc(smem_u32(s.ds), kBox, 1024);
+      auto kstep = [](int k8) { return (uint32_t)(k8 >> 2) * (uint32_t)(kBox >> 4) + (uint32_t)(k8 & 3) * 2u; };
       bool ok = mbar_wait(&s.q_full, 0, abort_flag, a.status, 53);
       for (int t = 0; t < n_kv && ok; ++t) {
         ok = mbar_wait(&s.k_full, t & 1, abort_flag, a.status, 54);
-        if (ok) ok = mbar_wait(&s.v_full, t & 1, abort_flag, a.status, 55);
         if (ok && t > 0) ok = mbar_wait(&s.acc_free, (t - 1) & 1, abort_flag, a.status, 56);
         if (!ok) break;
         tc_fence_after_sync();
 #pragma unroll
-        for (int k8 = 0; k8 < kD / 16; ++k8) {   // along the head dimension
-          const uint32_t qa = (uint32_t)(k8 >> 2) * (kQBox >> 4) + (uint32_t)(k8 & 3) * 2;
-          const uint32_t kb = (uint32_t)(k8 >> 2) * (kKVBox >> 4) + (uint32_t)(k8 & 3) * 2;
-          mma_f16_ss(tmem, dq_k + qa, dk_k + kb, idesc_s, k8 != 0);
-        }
+        for (int k8 = 0; k8 < kD / 16; ++k8)
+          mma_f16_ss(tmem, q_k + kstep(k8), k_k + kstep(k8), idesc_s, k8 != 0);
+        ok = mbar_wait(&s.v_full, t & 1, abort_flag, a.status, 55);
+        if (!ok) break;
+        tc_fence_after_sync();
 #pragma unroll
-        for (int k8 = 0; k8 < kD / 16; ++k8) {
-          const uint32_t qa = (uint32_t)(k8 >> 2) * (kQBox >> 4) + (uint32_t)(k8 & 3) * 2;
-          const uint32_t kb = (uint32_t)(k8 >> 2) * (kKVBox >> 4) + (uint32_t)(k8 & 3) * 2;
-          mma_f16_ss(tmem + kBKV, ddo_k + qa, dv_k + kb, idesc_s, k8 != 0);
-        }
+        for (int k8 = 0; k8 < kD / 16; ++k8)
+          mma_f16_ss(tmem + 128, do_k + kstep(k8), v_k + kstep(k8), idesc_s, k8 != 0);
         tc_commit(&s.sdp_full);
         ok = mbar_wait(&s.pds_full, t & 1, abort_flag, a.status, 57);
         if (!ok) break;
         tc_fence_after_sync();
 #pragma unroll
-        for (int k8 = 0; k8 < kBQ / 16; ++k8) {   // along the query rows: 16 rows = 2048 bytes
-          mma_f16_ss(tmem, ddo_mn + k8 * (2048 >> 4), dp_mn + k8 * (2048 >> 4), idesc_t, k8 != 0);
-        }
+        for (int k8 = 0; k8 < kBQ / 16; ++k8)   // along the query rows
+          mma_f16_ss(tmem, do_mn + k8 * (2048 >> 4), p_mn + k8 * (2048 >> 4), idesc_t, k8 != 0);
 #pragma unroll
-        for (int k8 = 0; k8 < kBQ / 16; ++k8) {
-          mma_f16_ss(tmem + kBKV, dq_mn + k8 * (2048 >> 4), dds_mn + k8 * (2048 >> 4), idesc_t, k8 != 0);
-        }
+        for (int k8 = 0; k8 < kBQ / 16; ++k8)
+          mma_f16_ss(tmem + 128, q_mn + k8 * (2048 >> 4), ds_mn + k8 * (2048 >> 4), idesc_t, k8 != 0);
 #pragma unroll
-        for (int k4 = 0; k4 < kBKV / 16; ++k4)    // along the key rows of the tile
-          mma_f16_ss(tmem + 2 * kBKV, dds_k + k4 * 2, dk_mn + k4 * (2048 >> 4), idesc_q, (t | k4) != 0);
+        for (int k8 = 0; k8 < kBKVb / 16; ++k8)  // along the key rows of the tile
+          mma_f16_ss(tmem + 256, ds_k + kstep(k8), k_mn + k8 * (2048 >> 4), idesc_q, (t | k8) != 0);
         tc_commit(&s.grads_full);
-        tc_commit(&s.k_empty);
       }
     }
   } else {
@@ -522,34 +550,33 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     const int d_idx = warp * 32 + lane;          // this thread's row of dV^T / dK^T
     bool ok = true;
     for (int t = 0; t < n_kv && ok; ++t) {
-      const int kv0 = seg_begin + t * kBKV;
+      const int kv0 = seg_begin + t * kBKVb;
       ok = mbar_wait(&s.sdp_full, t & 1, abort_flag, a.status, 58);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after_sync();
       const int limit = valid ? q_idx - kv0 : -1;    // columns 0..limit are visible
-      uint32_t pp[32], ds[32];
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        uint32_t x[32], y[32];
-        tmem_ld_32x32(lane_base + half * 32, x);
-        tmem_ld_32x32(lane_base + kBKV + half * 32, y);
+#pragma unroll 1
+      for (int c0 = 0; c0 < kBKVb; c0 += 32) {
+        uint32_t x[32], y[32], pp[16], ds[16];
+        tmem_ld_32x32(lane_base + c0, x);
+        tmem_ld_32x32(lane_base + 128 + c0, y);
         tmem_ld_wait_on(x);
         tmem_ld_wait_on(y);
 #pragma unroll
         for (int c = 0; c < 32; c += 2) {
           float p0 = 0.f, p1 = 0.f;
-          if (c + half * 32 <= limit) p0 = exp2f(fmaf(__uint_as_float(x[c]), sl, -lse2));
-          if (c + 1 + half * 32 <= limit) p1 = exp2f(fmaf(__uint_as_float(x[c + 1]), sl, -lse2));
+          if (c0 + c <= limit) p0 = exp2f(fmaf(__uint_as_float(x[c]), sl, -lse2));
+          if (c0 + c + 1 <= limit) p1 = exp2f(fmaf(__uint_as_float(x[c + 1]), sl, -lse2));
           const float g0 = p0 * (__uint_as_float(y[c]) - delta);
           const float g1 = p1 * (__uint_as_float(y[c + 1]) - delta);
           __half2 ph = __floats2half2_rn(p0, p1), gh = __floats2half2_rn(g0, g1);
-          pp[half * 16 + (c >> 1)] = *reinterpret_cast<uint32_t*>(&ph);
-          ds[half * 16 + (c >> 1)] = *reinterpret_cast<uint32_t*>(&gh);
+          pp[c >> 1] = *reinterpret_cast<uint32_t*>(&ph);
+          ds[c >> 1] = *reinterpret_cast<uint32_t*>(&gh);
         }
+        write_tile_chunks(s.p, r, c0, pp);
+        write_tile_chunks(s.ds, r, c0, ds);
       }
-      write_tile_row(s.p, r, pp);
-      write_tile_row(s.v, r, ds);    // V is dead: dP has been formed
       fence_proxy_async_smem();
       tc_fence_before_sync();
       __syncwarp();
@@ -558,37 +585,41 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after_sync();
-      // dV^T and dK^T leave through shared memory: thread d writes its 64 values as column d of a
-      // [64 key rows x 128] fp32 tile (the value and probability buffers, both dead by now), and
-      // the first 64 threads each add one 512-byte key row to global memory with a bulk
-      // reduction: the copy engine does the atomic adds, not 128 red instructions per thread.
-      const int rows_here = min(kBKV, q_end - kv0);   // key rows of this tile that exist for this CTA
-      float* stage = reinterpret_cast<float*>(s.v);
+      // dV^T and dK^T leave through shared memory: thread d writes its values as column d of a
+      // [128 key rows x 128] fp32 tile (dV over the V and P tiles, dK over the dS and K tiles, all
+      // four dead now), and thread r adds key row r of both to global memory with two bulk
+      // reductions: the copy engine does the atomic adds.
+      float* stage_v = reinterpret_cast<float*>(s.v);
+      float* stage_k = reinterpret_cast<float*>(s.ds);
+#pragma unroll 1
+      for (int c0 = 0; c0 < kBKVb; c0 += 32) {
+        uint32_t x[32], y[32];
+        tmem_ld_32x32(lane_base + c0, x);
+        tmem_ld_32x32(lane_base + 128 + c0, y);
+        tmem_ld_wait_on(x);
+        tmem_ld_wait_on(y);
 #pragma unroll
-      for (int which = 0; which < 2; ++which) {
-        const float mul = which ? a.scale : 1.f;
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          uint32_t x[32];
-          tmem_ld_32x32(lane_base + which * kBKV + half * 32, x);
-          tmem_ld_wait_on(x);
-#pragma unroll
-          for (int c = 0; c < 32; ++c) stage[(c + half * 32) * kD + d_idx] = __uint_as_float(x[c]) * mul;
+        for (int c = 0; c < 32; ++c) {
+          stage_v[(c0 + c) * kD + d_idx] = __uint_as_float(x[c]);
+          stage_k[(c0 + c) * kD + d_idx] = __uint_as_float(y[c]) * a.scale;
         }
-        fence_proxy_async_smem();
-        row_warps_sync();
-        if (r < rows_here) {
-          float* dst = (which ? a.dk : a.dv) + ((size_t)(kv0 + r) * a.hk + hk) * kD;
-          bulk_red_add_f32(dst, stage + r * kD, kD * sizeof(float));
-        }
-        tma_store_commit();
-        tma_store_wait_read<0>();    // the staged rows have been read: the tile can be rewritten
-        row_warps_sync();
       }
       tc_fence_before_sync();
-      if (r == 0) mbar_arrive(&s.v_empty);     // the value buffer is free for the next tile
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&s.acc_free);
+      fence_proxy_async_smem();
+      row_warps_sync();
+      if (lane == 0) mbar_arrive(&s.acc_free);        // the accumulators have been read
+      if (kv0 + r < q_end) {                          // key row r of this tile exists for this CTA
+        const size_t row = ((size_t)(kv0 + r) * a.hk + hk) * kD;
+        bulk_red_add_f32(a.dv + row, stage_v + r * kD, kD * sizeof(float));
+        bulk_red_add_f32(a.dk + row, stage_k + r * kD, kD * sizeof(float));
+      }
+      tma_store_commit();
+      tma_store_wait_read<0>();    // the staged rows have been read: the tiles can be reloaded
+      row_warps_sync();
+      if (r == 0) {
+        mbar_arrive(&s.k_empty);
+        mbar_arrive(&s.v_empty);
+      }
     }
     asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // this thread's reductions have landed
     if (ok) {   // dQ: complete once the last tile's products are (grads_full of the last step)
@@ -596,7 +627,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 #pragma unroll
       for (int c0 = 0; c0 < kD; c0 += 32) {
         uint32_t o[32];
-        tmem_ld_32x32(lane_base + 2 * kBKV + c0, o);
+        tmem_ld_32x32(lane_base + 256 + c0, o);
         tmem_ld_wait_on(o);
         if (valid) {
 #pragma unroll
@@ -618,10 +649,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   __syncthreads();
   if (warp == 4) {
     tc_fence_after_sync();
-    tmem_dealloc(tmem, kTmemCols);
+    tmem_dealloc(tmem, kTmemColsBwd);
   }
 }
-
 }  // namespace
 }  // namespace soup
 
@@ -689,19 +719,21 @@ extern "C" int soup_attn_bwd(const void* q, const void* k, const void* v, const 
   if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(out) || !aligned16(d_out) || !aligned16(dq))
     SOUP_FAIL(SOUP_ERR_ARG, "attn_bwd: pointers must be 16-byte aligned");
   // a runtime call first (see soup_attn_fwd): backward usually runs on an autograd thread
-  const size_t smem = sizeof(BwdSmem);
+  const size_t smem = sizeof(BwdSmem) + 1024;
   if (cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
     SOUP_FAIL(SOUP_ERR_LAUNCH, "attn_bwd: shared memory attribute");
   CUtensorMap mq, mdo, mk, mv;
   const int e_q = umma::encode_map_2d_16bit(&mq, q, (uint64_t)n_tokens, (uint64_t)(hq * kD), (uint64_t)q_pitch, kBQ, 64, false);
   const int e_do = umma::encode_map_2d_16bit(&mdo, d_out, (uint64_t)n_tokens, (uint64_t)(hq * kD), (uint64_t)(hq * kD), kBQ, 64, false);
-  const int e_k = umma::encode_map_2d_16bit(&mk, k, (uint64_t)n_tokens, (uint64_t)(hk * kD), (uint64_t)k_pitch, kBKV, 64, false);
-  const int e_v = umma::encode_map_2d_16bit(&mv, v, (uint64_t)n_tokens, (uint64_t)(hk * kD), (uint64_t)v_pitch, kBKV, 64, false);
+  const int e_k = umma::encode_map_2d_16bit(&mk, k, (uint64_t)n_tokens, (uint64_t)(hk * kD), (uint64_t)k_pitch, kBKVb, 64, false);
+  const int e_v = umma::encode_map_2d_16bit(&mv, v, (uint64_t)n_tokens, (uint64_t)(hk * kD), (uint64_t)v_pitch, kBKVb, 64, false);
   if (e_q || e_do || e_k || e_v)
     SOUP_FAIL(SOUP_ERR_LAUNCH, "attn_bwd: cuTensorMapEncodeTiled failed (q %d, d_out %d, k %d, v %d)", e_q, e_do, e_k, e_v);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const size_t kv_bytes = (size_t)n_tokens * hk * kD * sizeof(float);
-  if (cudaMemsetAsync(dk, 0, kv_bytes, st) != cudaSuccess || cudaMemsetAsync(dv, 0, kv_bytes, st) != cudaSuccess)
+  const bool adjacent = reinterpret_cast<char*>(dk) + kv_bytes == reinterpret_cast<char*>(dv);
+  if (cudaMemsetAsync(dk, 0, adjacent ? 2 * kv_bytes : kv_bytes, st) != cudaSuccess ||
+      (!adjacent && cudaMemsetAsync(dv, 0, kv_bytes, st) != cudaSuccess))
     SOUP_FAIL(SOUP_ERR_LAUNCH, "attn_bwd: clearing dk / dv failed");
   AttnBwdArgs a;
   a.cu = cu_rows;
