@@ -2,9 +2,9 @@
 // batch), forward, for head_dim 128 and fp16 q/k/v with grouped-query heads.
 //
 // One CTA owns 128 consecutive query tokens of one segment and one query head. The keys and
-// values it may see (its segment, up to its last token) arrive in tiles of 64 tokens by TMA into
-// a two-stage ring. S = Q K^T of a tile is one tcgen05 product (M 128, N 64, K 128) into one of two
-// 64-column accumulators in tensor memory; the four softmax warps read it (thread = query row).
+// values it may see (its segment, up to its last token) arrive in tiles of 128 tokens by TMA into
+// a two-stage ring. S = Q K^T of a tile is one tcgen05 product (M 128, N 128, K 128) into one of two
+// 128-column accumulators in tensor memory; the four softmax warps read it (thread = query row).
 // The softmax is done in two passes over the key tiles, so that the output accumulator never has
 // to be rescaled: the first pass only reduces the row maximum and the sum of exponentials; the
 // second forms S again, writes P = exp(S - max) as fp16 into a 128-byte-swizzled shared-memory
@@ -13,8 +13,9 @@
 // rescale round trip through tensor memory. The epilogue divides by the sum and writes fp16 rows
 // and the log-sum-exp (natural log, of the scaled scores) per row and head.
 //
-// Shared memory (96 KB) and tensor memory (256 columns) allow two CTAs per SM, which is what a
-// latency-bound problem of ~150 CTAs wants. Every wait is bounded (umma::mbar_wait).
+// One CTA per SM (160 KB of shared memory, 384 columns of tensor memory): a CTA's walk is a chain
+// of dependent steps, so few large steps beat many small ones; CTAs take the tiles with the
+// longest walks first. Every wait is bounded (umma::mbar_wait).
 //
 // The reference calls torch SDPA here (solution/attention.py:332-343) on a [1, 1, N, N] mask
 // built by its packing (solution/lm_head_loss.py:300-337); this kernel takes the segment offsets.
@@ -31,15 +32,16 @@ using namespace umma;
 
 constexpr int kD = 128;          // head dimension
 constexpr int kBQ = 128;         // query rows per CTA
-constexpr int kBKV = 64;         // key/value rows per tile
+constexpr int kBKV = 128;        // key/value rows per tile
 constexpr int kStages = 2;       // key tiles in flight (the value tile has one buffer)
+constexpr int kTileBytes = 128 * kD * 2;       // 32 KB: a [128 x 128] fp16 tile, two swizzled boxes
 constexpr int kQBytes = kBQ * kD * 2;          // 32 KB: two boxes of [128 rows x 64 cols]
 constexpr int kQBox = kBQ * 128;               // 16 KB
-constexpr int kKBytes = kBKV * kD * 2;         // 16 KB: two boxes of [64 rows x 64 cols]
-constexpr int kKVBox = kBKV * 128;             // 8 KB
-constexpr int kPBytes = kBQ * kBKV * 2;        // 16 KB: one box of [128 rows x 64 cols]
+constexpr int kKBytes = kBKV * kD * 2;         // 32 KB: two boxes of [128 rows x 64 cols]
+constexpr int kKVBox = kBKV * 128;             // 16 KB
+constexpr int kPBytes = kBQ * kBKV * 2;        // 32 KB: two boxes of [128 rows x 64 cols]
 constexpr int kThreads = 224;                  // warps 0-3 softmax, 4 key TMA, 5 MMA, 6 value TMA
-constexpr uint32_t kTmemCols = 256;            // S0 [0,64) S1 [64,128) O [128,256)
+constexpr uint32_t kTmemCols = 512;            // S0 [0,128) S1 [128,256) O [256,384)
 
 struct __align__(1024) Smem {
   uint8_t q[kQBytes];
@@ -82,12 +84,47 @@ __device__ __forceinline__ bool locate(const int32_t* cu, int segments, int slot
 }
 
 
-__global__ void __launch_bounds__(kThreads, 2)
+// Four 16-byte chunks (32 fp16 columns starting at column `col0`, a multiple of 32) of row r of a
+// [128 x 128] fp16 tile stored as two 128-byte-swizzled boxes of 64 columns.
+__device__ __forceinline__ void write_tile_chunks(uint8_t* tile, int r, int col0, const uint32_t (&w)[16]) {
+  uint8_t* row = tile + (col0 >> 6) * (kTileBytes / 2) + r * 128;
+  const int j0 = (col0 & 63) >> 3;
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+    *reinterpret_cast<uint4*>(row + (((j0 + j) ^ (r & 7)) << 4)) =
+        make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+}
+
+// Like `locate`, but the slots go through the tiles in the order of their walks' lengths: the
+// last tile of every segment first, then the ones before them, and so on.
+__device__ __forceinline__ bool locate_heavy_first(const int32_t* cu, int segments, int slot,
+                                                   int& seg_begin, int& seg_end, int& q0) {
+  if (segments > 64) return locate(cu, segments, slot, seg_begin, seg_end, q0);
+  int deepest = 0;
+  for (int s = 0; s < segments; ++s) deepest = max(deepest, (cu[s + 1] - cu[s] + kBQ - 1) / kBQ);
+  int base = 0;
+  for (int level = deepest - 1; level >= 0; --level)
+    for (int s = 0; s < segments; ++s) {
+      const int b = cu[s], e = cu[s + 1];
+      if ((e - b + kBQ - 1) / kBQ > level) {
+        if (slot == base) {
+          seg_begin = b;
+          seg_end = e;
+          q0 = b + level * kBQ;
+          return true;
+        }
+        ++base;
+      }
+    }
+  return false;
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                 const __grid_constant__ CUtensorMap map_v, AttnArgs a) {
   extern __shared__ uint8_t raw[];
   int seg_begin, seg_end, q0;
-  if (!locate(a.cu, a.segments, blockIdx.x, seg_begin, seg_end, q0)) return;   // the whole CTA leaves
+  if (!locate_heavy_first(a.cu, a.segments, blockIdx.x, seg_begin, seg_end, q0)) return;   // the whole CTA leaves
   Smem& s = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int h = blockIdx.y, hk = h / a.group;
@@ -191,8 +228,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         if (!ok) break;
         tc_fence_after_sync();
 #pragma unroll
-        for (int k4 = 0; k4 < kBKV / 16; ++k4)
-          mma_f16_ss(tmem + 2 * kBKV, dp + k4 * 2, dv + k4 * (2048 >> 4), idesc_o, (t | k4) != 0);
+        for (int k8 = 0; k8 < kBKV / 16; ++k8) {   // along the key rows: P K-major, V MN-major
+          const uint32_t pa = (uint32_t)(k8 >> 2) * (kQBox >> 4) + (uint32_t)(k8 & 3) * 2;
+          mma_f16_ss(tmem + 2 * kBKV, dp + pa, dv + k8 * (2048 >> 4), idesc_o, (t | k8) != 0);
+        }
         tc_commit(&s.k_empty[g % kStages]);
         tc_commit(&s.v_empty);
         tc_commit(&s.p_empty);
@@ -213,61 +252,58 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after_sync();
-      uint32_t x0[32], x1[32];
-      tmem_ld_32x32(lane_base + sb * kBKV, x0);
-      tmem_ld_32x32(lane_base + sb * kBKV + 32, x1);
-      tmem_ld_wait_on(x0);
-      tmem_ld_wait_on(x1);
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&s.s_empty[sb]);
       const int t = g < n_kv ? g : g - n_kv;
       const int limit = q_idx - (seg_begin + t * kBKV);   // columns 0..limit are visible
-      if (g < n_kv) {
-        float tile_max = -INFINITY;
+      if (g < n_kv) {   // pass 1: running maximum and sum of exponentials
+#pragma unroll 1
+        for (int c0 = 0; c0 < kBKV; c0 += 32) {
+          uint32_t x[32];
+          tmem_ld_32x32(lane_base + sb * kBKV + c0, x);
+          tmem_ld_wait_on(x);
+          float tile_max = -INFINITY;
 #pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          if (c <= limit) tile_max = fmaxf(tile_max, __uint_as_float(x0[c]));
-          if (c + 32 <= limit) tile_max = fmaxf(tile_max, __uint_as_float(x1[c]));
-        }
-        if (tile_max > -INFINITY) {
-          const float m_new = fmaxf(m, tile_max);
-          float sum = 0.f;
+          for (int c = 0; c < 32; ++c)
+            if (c0 + c <= limit) tile_max = fmaxf(tile_max, __uint_as_float(x[c]));
+          if (tile_max > -INFINITY) {
+            const float m_new = fmaxf(m, tile_max);
+            float sum = 0.f;
 #pragma unroll
-          for (int c = 0; c < 32; ++c) {
-            if (c <= limit) sum += exp2f((__uint_as_float(x0[c]) - m_new) * sl);
-            if (c + 32 <= limit) sum += exp2f((__uint_as_float(x1[c]) - m_new) * sl);
+            for (int c = 0; c < 32; ++c)
+              if (c0 + c <= limit) sum += exp2f((__uint_as_float(x[c]) - m_new) * sl);
+            l = l * exp2f((m - m_new) * sl) + sum;   // m = -inf the first time: exp2(-inf) = 0
+            m = m_new;
           }
-          l = l * exp2f((m - m_new) * sl) + sum;   // m = -inf the first time: exp2(-inf) = 0
-          m = m_new;
         }
-      } else {
-        uint32_t packed[32];
-#pragma unroll
-        for (int c = 0; c < 32; c += 2) {
-          const float p0 = c <= limit ? exp2f((__uint_as_float(x0[c]) - m) * sl) : 0.f;
-          const float p1 = c + 1 <= limit ? exp2f((__uint_as_float(x0[c + 1]) - m) * sl) : 0.f;
-          const float p2 = c + 32 <= limit ? exp2f((__uint_as_float(x1[c]) - m) * sl) : 0.f;
-          const float p3 = c + 33 <= limit ? exp2f((__uint_as_float(x1[c + 1]) - m) * sl) : 0.f;
-          __half2 lo = __floats2half2_rn(p0, p1), hi = __floats2half2_rn(p2, p3);
-          packed[c >> 1] = *reinterpret_cast<uint32_t*>(&lo);
-          packed[16 + (c >> 1)] = *reinterpret_cast<uint32_t*>(&hi);
-        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&s.s_empty[sb]);
+      } else {          // pass 2: P = exp(S - max) as the fp16 A operand of O += P V
         if (t > 0) {
           ok = mbar_wait(&s.p_empty, (t - 1) & 1, abort_flag, a.status, 49);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
         }
-        // row r of the [128 x 64] fp16 tile: eight 16-byte chunks, chunk j at position j ^ (r & 7)
-        uint8_t* row = s.p + r * 128;
+#pragma unroll 1
+        for (int c0 = 0; c0 < kBKV; c0 += 32) {
+          uint32_t x[32], packed[16];
+          tmem_ld_32x32(lane_base + sb * kBKV + c0, x);
+          tmem_ld_wait_on(x);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const uint4 chunk = make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
-          *reinterpret_cast<uint4*>(row + ((j ^ (r & 7)) << 4)) = chunk;
+          for (int c = 0; c < 32; c += 2) {
+            const float p0 = c0 + c <= limit ? exp2f((__uint_as_float(x[c]) - m) * sl) : 0.f;
+            const float p1 = c0 + c + 1 <= limit ? exp2f((__uint_as_float(x[c + 1]) - m) * sl) : 0.f;
+            __half2 hh = __floats2half2_rn(p0, p1);
+            packed[c >> 1] = *reinterpret_cast<uint32_t*>(&hh);
+          }
+          write_tile_chunks(s.p, r, c0, packed);
         }
+        tc_fence_before_sync();
         fence_proxy_async_smem();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&s.p_full);
+        if (lane == 0) {
+          mbar_arrive(&s.s_empty[sb]);
+          mbar_arrive(&s.p_full);
+        }
       }
     }
     if (ok) {
@@ -333,7 +369,6 @@ namespace {
 // tiles with the longest walks first (`locate_heavy_first`), so that the few CTAs beyond one per
 // SM are short ones.
 constexpr int kBKVb = 128;                     // key rows per tile in backward
-constexpr int kTileBytes = kBKVb * kD * 2;     // 32 KB: every fp16 tile here is [128 x 128]
 constexpr uint32_t kTmemColsBwd = 512;         // S/dV^T [0,128) dP/dK^T [128,256) dQ [256,384)
 
 struct BwdSmem {
@@ -371,41 +406,6 @@ __device__ __forceinline__ void bulk_red_add_f32(float* gdst, const void* ssrc, 
 
 __device__ __forceinline__ void row_warps_sync() {   // the four row warps, named barrier 1
   asm volatile("bar.sync 1, 128;" ::: "memory");
-}
-
-// Four 16-byte chunks (32 fp16 columns starting at column `col0`, a multiple of 32) of row r of a
-// [128 x 128] fp16 tile stored as two 128-byte-swizzled boxes of 64 columns.
-__device__ __forceinline__ void write_tile_chunks(uint8_t* tile, int r, int col0, const uint32_t (&w)[16]) {
-  uint8_t* row = tile + (col0 >> 6) * (kTileBytes / 2) + r * 128;
-  const int j0 = (col0 & 63) >> 3;
-#pragma unroll
-  for (int j = 0; j < 4; ++j)
-    *reinterpret_cast<uint4*>(row + (((j0 + j) ^ (r & 7)) << 4)) =
-        make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
-}
-
-// Like `locate`, but the slots go through the tiles in the order of their walks' lengths: the
-// last tile of every segment first, then the ones before them, and so on.
-__device__ __forceinline__ bool locate_heavy_first(const int32_t* cu, int segments, int slot,
-                                                   int& seg_begin, int& seg_end, int& q0) {
-  if (segments > 64) return locate(cu, segments, slot, seg_begin, seg_end, q0);
-  int deepest = 0;
-  for (int s = 0; s < segments; ++s) deepest = max(deepest, (cu[s + 1] - cu[s] + kBQ - 1) / kBQ);
-  int base = 0;
-  for (int level = deepest - 1; level >= 0; --level)
-    for (int s = 0; s < segments; ++s) {
-      const int b = cu[s], e = cu[s + 1];
-      if ((e - b + kBQ - 1) / kBQ > level) {
-        if (slot == base) {
-          seg_begin = b;
-          seg_end = e;
-          q0 = b + level * kBQ;
-          return true;
-        }
-        ++base;
-      }
-    }
-  return false;
 }
 
 __global__ void __launch_bounds__(kThreads, 1)

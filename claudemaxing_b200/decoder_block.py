@@ -33,8 +33,10 @@ import types
 
 import torch
 
+from . import _lib
+from . import attention as attention_mod
 from . import lora as lora_mod
-from .attention import segment_attention
+from .attention import attention_gradients, segment_attention
 from .rmsnorm import fp16_copy_of
 from .rope import rotate_into
 from .swiglu_recompute import _silu_mul_bwd, _silu_mul_fwd
@@ -167,11 +169,14 @@ class AdapterCasts:
 
 class _QKVRope(torch.autograd.Function):
     """(x16 @ [Wq; Wk; Wv]^T + bias) split into q (+ adapter), k, v (+ adapter); q and k rotated;
-    all three returned as fp16 [tokens, heads, head_dim]."""
+    all three returned as fp16 [tokens, heads, head_dim]. With `cu_rows` (segment offsets of the
+    packed row) the causal attention inside the segments runs here as well, on this library's
+    kernels, and its output [tokens, heads, head_dim] is what is returned: backward then hands the
+    attention kernel's fp32 dV straight to the copy into the projection's gradient buffer."""
 
     @staticmethod
     @_plain_precision
-    def forward(ctx, x, x16, lora_q, lora_v, cos, sin, plan):
+    def forward(ctx, x, x16, lora_q, lora_v, cos, sin, plan, cu_rows=None, scale=None):
         bases = [_base(m) for m in (plan.q, plan.k, plan.v)]
         n, d = x16.numel() // x16.shape[-1], plan.head_dim
         nq, nk = bases[0].out_features, bases[1].out_features
@@ -192,16 +197,34 @@ class _QKVRope(torch.autograd.Function):
                     q_out.unsqueeze(0).transpose(1, 2), k_out.unsqueeze(0).transpose(1, 2))
         v_rows = qkv[:, nq + nk:]
         v_out = v_rows.contiguous() if lora_v is None else v_rows + lora_v.reshape(n, nk)
-        ctx.save_for_backward(cos, sin)
         ctx.plan, ctx.sizes, ctx.x_shape = plan, (n, d, nq, nk, hq, hk), x.shape
         ctx.lora_shapes = (None if lora_q is None else lora_q.shape, None if lora_v is None else lora_v.shape)
-        return q_out, k_out, v_out.view(n, hk, d)
+        ctx.attends = cu_rows is not None
+        v_out = v_out.view(n, hk, d)
+        if not ctx.attends:
+            ctx.save_for_backward(cos, sin)
+            return q_out, k_out, v_out
+        attended = torch.empty(n, hq, d, dtype=F16, device=x16.device)
+        lse = torch.empty(hq, n, dtype=F32, device=x16.device)
+        _lib.call("soup_attn_fwd", _lib.ptr(q_out), _lib.ptr(k_out), _lib.ptr(v_out), _lib.ptr(cu_rows),
+                  _lib.ptr(attended), _lib.ptr(lse), n, cu_rows.numel() - 1, hq, hk, d,
+                  q_out.stride(0), k_out.stride(0), v_out.stride(0), float(scale), _lib.stream_of(q_out))
+        ctx.save_for_backward(cos, sin, q_out, k_out, v_out, attended, lse, cu_rows)
+        ctx.scale = float(scale)
+        return attended
 
     @staticmethod
     @_plain_precision
-    def backward(ctx, dq, dk, dv):
-        cos, sin = ctx.saved_tensors
+    def backward(ctx, *grads):
         plan, (n, d, nq, nk, hq, hk) = ctx.plan, ctx.sizes
+        if ctx.attends:
+            cos, sin, q_out, k_out, v_out, attended, lse, cu_rows = ctx.saved_tensors
+            dq, dk, dv = attention_gradients(q_out, k_out, v_out, attended, lse,
+                                             grads[0].reshape(n, hq, d), cu_rows, ctx.scale)
+            dk = dk.to(F16)   # the pipelined rotation wants q and k of one element size
+        else:
+            cos, sin = ctx.saved_tensors
+            dq, dk, dv = grads
         dq, dk = (g if g.stride(-1) == 1 else g.contiguous() for g in (dq, dk))
         dqkv = torch.empty(n, nq + 2 * nk, dtype=F16, device=dq.device)
 
@@ -220,7 +243,7 @@ class _QKVRope(torch.autograd.Function):
         return (dx, None,
                 None if q_shape is None else dqkv[:, :nq].view(q_shape),
                 None if v_shape is None else dqkv[:, nq + nk:].view(v_shape),
-                None, None, None)
+                None, None, None, None, None)
 
 
 class _ProjectAddResidual(torch.autograd.Function):
@@ -347,12 +370,19 @@ def fused_block_forward(layer, hidden_states, attention_mask=None, position_ids=
         x16 = x.detach().to(F16)
     branches = [None if a is None else lora_mod.LoRABranch.apply(x, x16, *a) for a in adapters]
     cos, sin = position_embeddings
-    q, k, v = _QKVRope.apply(x, x16, branches[0], branches[2], cos.contiguous(), sin.contiguous(), plan)
-    n = q.shape[0]
     cu = kwargs["cu_seq_lens_q"]
-    attended = segment_attention(q.unsqueeze(0).transpose(1, 2), k.unsqueeze(0).transpose(1, 2),
-                                 v.unsqueeze(0).transpose(1, 2), cu, kwargs.get("max_length_q", n),
-                                 layer.self_attn.scaling)
+    scale = layer.self_attn.scaling
+    if (plan.head_dim == 128 and attention_mod.OWN_FORWARD and attention_mod.OWN_BACKWARD
+            and cu.dtype == torch.int32 and cu.is_cuda):
+        attended = _QKVRope.apply(x, x16, branches[0], branches[2], cos.contiguous(), sin.contiguous(),
+                                  plan, cu, plan.head_dim ** -0.5 if scale is None else scale)
+        n = attended.shape[0]
+    else:
+        q, k, v = _QKVRope.apply(x, x16, branches[0], branches[2], cos.contiguous(), sin.contiguous(), plan)
+        n = q.shape[0]
+        attended = segment_attention(q.unsqueeze(0).transpose(1, 2), k.unsqueeze(0).transpose(1, 2),
+                                     v.unsqueeze(0).transpose(1, 2), cu, kwargs.get("max_length_q", n),
+                                     scale)
     hidden_states = _ProjectAddResidual.apply(attended.reshape(n, -1), hidden_states, plan.o)
     x = layer.post_attention_layernorm(hidden_states)
     x16 = fp16_copy_of(x)
