@@ -203,10 +203,36 @@ def golden_head():
              logits=logits, rows_loss=tl_, rows_entropy=en_, rows_correct=co_)
 
 
+def golden_attention():
+    """The reference's own (unused) Triton attention, solution/attention.py:27-246, on a padded
+    batch: causal attention inside the valid keys of each batch row, grouped-query heads, fp16
+    output and the gradients of q, k and v. The packed row of this repository is the same
+    attention with the batch rows as segments."""
+    from solution import attention as ref
+
+    for tag, (B, H, KVH, T, D), lengths in (("a", (3, 6, 2, 40, 128), [40, 23, 1]),
+                                            ("b", (2, 4, 4, 70, 128), [70, 33])):
+        torch.manual_seed(5)
+        q = torch.randn(B, T, H, D).transpose(1, 2).requires_grad_(True)
+        k = torch.randn(B, T, KVH, D).transpose(1, 2).requires_grad_(True)
+        v = torch.randn(B, T, KVH, D).transpose(1, 2).requires_grad_(True)
+        pad = torch.arange(T)[None, :] < torch.tensor(lengths)[:, None]
+        key_ok = pad.to(torch.int8).contiguous()
+        g = torch.randn(B, T, H, D) * pad[:, :, None, None]
+        out = ref.qwen_attention(q, k, v, key_ok, None, torch.float16)
+        out.float().backward(g)
+        save(f"attention_{tag}", q=q.detach(), k=k.detach(), v=v.detach(), lengths=torch.tensor(lengths),
+             grad=g, out=out.detach(), dq=q.grad, dk=k.grad, dv=v.grad)
+
+
 if __name__ == "__main__":
+    if len(sys.argv) > 2 and sys.argv[2] == "attention":
+        golden_attention()
+        sys.exit(0)
     golden_nf4()
     golden_rmsnorm()
     golden_rope()
     golden_swiglu()
     golden_dropout()
     golden_head()
+    golden_attention()
