@@ -442,6 +442,67 @@ def kernel_suite(dev, hbm_peak, n_rows=2048, tag="", with_nf4=True):
 
 
 
+def attention_suite(dev, tensor_peak):
+    """The packed row's attention at the training step's shape (the synthetic batch's four rows
+    plus the padding segment: 1280 tokens, 12 query / 2 key heads x 128), forward and backward:
+    this library's tcgen05 kernels against torch's variable-length flash attention on the same
+    tensors. 28 rotating sets of q, k, v (as in the 28 layers of a step). flops: 4 L^2 D per head
+    and segment forward (QK^T and PV, causal half), 10 L^2 D backward (five products)."""
+    from torch.nn.attention.varlen import varlen_attn
+
+    from claudemaxing_b200 import _lib
+    from claudemaxing_b200.attention import attention_gradients
+
+    lens = [300, 280, 296, 292, 112]
+    n, hq, hk, d = sum(lens), 12, 2, 128
+    cu = torch.tensor([0] + torch.tensor(lens).cumsum(0).tolist(), dtype=torch.int32, device=dev)
+    scale = d ** -0.5
+    gen = torch.Generator(device=dev).manual_seed(6)
+    sets = [[torch.randn(n, h, d, device=dev, dtype=torch.float16, generator=gen) for h in (hq, hk, hk, hq)]
+            for _ in range(28)]
+    outs = [torch.empty(n, hq, d, device=dev, dtype=torch.float16) for _ in range(28)]
+    lses = [torch.empty(hq, n, device=dev, dtype=torch.float32) for _ in range(28)]
+    causal_pairs = sum(l * l / 2 for l in lens)
+
+    def own_fwd(j):
+        q, k, v, _ = sets[j]
+        _lib.call("soup_attn_fwd", _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(cu), _lib.ptr(outs[j]),
+                  _lib.ptr(lses[j]), n, cu.numel() - 1, hq, hk, d, q.stride(0), k.stride(0), v.stride(0),
+                  scale, _lib.stream_of(q))
+
+    def own_bwd(j):
+        q, k, v, g = sets[j]
+        attention_gradients(q, k, v, outs[j], lses[j], g, cu, scale)
+
+    def lib_fwd(j):
+        q, k, v, _ = sets[j]
+        varlen_attn(q, k, v, cu, cu, n, n, scale=scale, window_size=(-1, 0))
+
+    rng = torch.empty(2, dtype=torch.uint64, device=dev)
+
+    def lib_bwd(j):
+        q, k, v, g = sets[j]
+        torch.ops.torch_attn._varlen_attn_backward(g, q, k, v, outs[j], lses[j], cu, cu, n, n, True,
+                                                   rng, scale, [-1, 0])
+
+    for j in range(28):
+        own_fwd(j)
+    out = {}
+    for leg, own, lib, products in (("fwd", own_fwd, lib_fwd, 2), ("bwd", own_bwd, lib_bwd, 5)):
+        flops = products * 2.0 * causal_pairs * d * hq
+        ms_own = time_rotating(own, 28, reps=5)
+        ms_lib = time_rotating(lib, 28, reps=5)
+        out[f"segment_attention_{leg}@1280tokens"] = {
+            "ms": round(ms_own, 5), "tflops": round(flops / (ms_own * 1e-3) / 1e12, 1),
+            "frac_of_measured_bf16_peak": round(flops / (ms_own * 1e-3) / 1e12 / tensor_peak, 4),
+            "torch_varlen_flash_ms": round(ms_lib, 5), "launches": 1 if leg == "fwd" else 2,
+            "note": "latency-bound: ~150 CTAs each walking at most three key tiles; the backward "
+                    "launch count includes clearing the fp32 dK / dV buffers" if leg == "bwd" else
+                    "latency-bound: ~150 CTAs each walking at most three key tiles twice"}
+    _lib.check_device_status()
+    return out
+
+
 def nf4_gemm_suite(dev, tensor_peak, rows=1280):
     """The projections of one Qwen2.5-1.5B decoder block at the training step's row count, forward
     and input gradient: the tcgen05 GEMM that dequantises NF4 in its operand prologue against the
@@ -829,6 +890,8 @@ def main():
     ap.add_argument("--suite-rows", type=int, default=32768)
     ap.add_argument("--gemm-only", action="store_true",
                     help="run only the NF4 GEMM comparison and print its JSON")
+    ap.add_argument("--attention-only", action="store_true",
+                    help="run only the packed-row attention comparison and print its JSON")
     ap.add_argument("--step-only", action="store_true",
                     help="run only the captured QLoRA step: warm replays, then one replay inside the "
                          "NVTX range 'soup_step' (for a profiler's range filter), then a timed region")
@@ -861,10 +924,16 @@ def main():
         return
     if args.gemm_only:
         PLAIN_LAUNCHES = args.plain_launches
-        print(json.dumps({"kernels": nf4_gemm_suite(dev, peaks()[0]["bf16_tflops"])}), flush=True)
+        suite = nf4_gemm_suite(dev, peaks()[0]["bf16_tflops"])
+        suite.update(attention_suite(dev, peaks()[0]["bf16_tflops"]))
+        print(json.dumps({"kernels": suite}), flush=True)
         return
     if args.step_only:
         print(json.dumps(step_only(dev, max(args.steps, 1))), flush=True)
+        return
+    if args.attention_only:
+        PLAIN_LAUNCHES = args.plain_launches
+        print(json.dumps({"kernels": attention_suite(dev, peaks()[0]["bf16_tflops"])}), flush=True)
         return
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
@@ -1094,6 +1163,7 @@ def main():
             kernels.update(kernel_suite(dev, peak["hbm_gbs"], n_rows=65536, tag="@65536rows",
                                         with_nf4=False))
             kernels.update(nf4_gemm_suite(dev, tensor_peak))
+            kernels.update(attention_suite(dev, tensor_peak))
         if not args.no_cpu and kernels is not None:
             cpu_ms = cpu_oracle_suite(cores)
             for key, ms in cpu_ms.items():
