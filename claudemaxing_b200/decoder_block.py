@@ -113,8 +113,9 @@ class BlockPlan:
         return self._bias
 
     def adapter(self, module, x):
-        """(A, B, p, scaling, A fp16, B fp16) of a LoRALinear whose adapter LoRABranch reproduces
-        for this input (the fp16 copies None unless the model cast them for this forward); None
+        """(A, B, p, scaling, A fp16, scaling * B fp16, True) of a LoRALinear whose adapter
+        LoRABranch reproduces for this input (the copies None / False unless the model cast them
+        for this forward); None
         for a bare projection; False when the adapter needs the module's own forward."""
         if module is _base(module):
             return None
@@ -124,43 +125,44 @@ class BlockPlan:
         if self.casts is not None and self.casts.armed:
             a16, b16 = self.casts.of(module)
         return (module.lora_A.weight, module.lora_B.weight, float(module.p), float(module.scaling),
-                a16, b16)
+                a16, b16, b16 is not None)
 
 
 class AdapterCasts:
-    """fp16 copies of the adapter weights of a model's fused blocks, refreshed by one multi-tensor
-    launch at the start of every forward of the decoder (112 weights of 50 KB and less would
-    otherwise be 112 launches). The copies are handed out only while that forward runs (`armed`);
-    a block called on its own casts its weights itself."""
+    """fp16 copies of the adapter weights of a model's fused blocks, refreshed by three
+    multi-tensor launches at the start of every forward of the decoder (112 weights of 50 KB and
+    less would otherwise be 112 launches): A as it is, B multiplied by its layer's scaling first
+    (`LoRABranch`'s `b16_scaled`). The copies are handed out only while that forward runs
+    (`armed`); a block called on its own casts its weights itself."""
 
     def __init__(self):
-        self.sources, self.copies, self.where = [], [], {}
+        self.modules, self.where = [], {}
+        self.a16, self.b16 = [], []
         self.armed = False
 
     def add(self, module):
-        if id(module) in self.where:
-            return
-        self.where[id(module)] = len(self.sources)
-        for weight in (module.lora_A.weight, module.lora_B.weight):
-            self.sources.append(weight)
-            self.copies.append(None)
+        if id(module) not in self.where:
+            self.where[id(module)] = len(self.modules)
+            self.modules.append(module)
 
     def of(self, module):
         i = self.where[id(module)]
-        return self.copies[i], self.copies[i + 1]
+        return self.a16[i], self.b16[i]
 
     def refresh(self, *_):
         self.armed = False
-        if not self.sources or not torch.is_grad_enabled():
+        if not self.modules or not torch.is_grad_enabled():
             return
-        ok = all(w.is_cuda and w.dtype == F32 for w in self.sources)
-        if not ok:
+        a32 = [m.lora_A.weight.detach() for m in self.modules]
+        b32 = [m.lora_B.weight.detach() for m in self.modules]
+        if not all(w.is_cuda and w.dtype == F32 for w in a32 + b32):
             return
-        for i, w in enumerate(self.sources):
-            c = self.copies[i]
-            if c is None or c.device != w.device or c.shape != w.shape:
-                self.copies[i] = torch.empty(w.shape, dtype=F16, device=w.device)
-        torch._foreach_copy_(self.copies, [w.detach() for w in self.sources])
+        if len(self.a16) != len(a32) or any(c.device != w.device or c.shape != w.shape
+                                            for c, w in zip(self.a16 + self.b16, a32 + b32)):
+            self.a16 = [torch.empty(w.shape, dtype=F16, device=w.device) for w in a32]
+            self.b16 = [torch.empty(w.shape, dtype=F16, device=w.device) for w in b32]
+        torch._foreach_copy_(self.a16, a32)
+        torch._foreach_copy_(self.b16, torch._foreach_mul(b32, [float(m.scaling) for m in self.modules]))
         self.armed = True
 
     def disarm(self, *_):

@@ -59,9 +59,13 @@ class LoRABranch(torch.autograd.Function):
     """fp16 `lora_B(lora_A(dropout(x))) * scaling` for fp32 x under fp16 autocast."""
 
     @staticmethod
-    def forward(ctx, x, x16, weight_a, weight_b, p, scaling, a16=None, b16=None):
+    def forward(ctx, x, x16, weight_a, weight_b, p, scaling, a16=None, b16=None, b16_scaled=False):
         """`a16`, `b16`: fp16 copies of the two weights when the caller has made them already (a
-        model that casts all its adapters in one launch per forward); cast here otherwise."""
+        model that casts all its adapters in one launch per forward); cast here otherwise. With
+        `b16_scaled`, b16 is fp16(scaling * B): the branch output and the gradient that goes back
+        through B then need no scaling pass over [tokens, out] (two of the branch's larger
+        kernels); only B's own gradient, [out, r], is multiplied. For a power-of-two scaling the
+        numbers are the same; otherwise B is rounded after the scaling instead of before."""
         dropped, mask = torch.native_dropout(x, p, True)
         del dropped  # only the mask is used
         scale = 1.0 / (1.0 - p)
@@ -70,24 +74,30 @@ class LoRABranch(torch.autograd.Function):
         if a16 is None or b16 is None:
             a16, b16 = weight_a.to(torch.float16), weight_b.to(torch.float16)
         a = torch.nn.functional.linear(xd, a16)
-        out = torch.nn.functional.linear(a, b16) * scaling
+        out = torch.nn.functional.linear(a, b16)
+        if not b16_scaled:
+            out = out * scaling
         ctx.save_for_backward(x16, bits, a, a16, b16)   # the fp16 adapter copies are 50 KB each
-        ctx.scale, ctx.scaling, ctx.x_dtype = scale, scaling, x.dtype
+        ctx.scale, ctx.scaling, ctx.x_dtype, ctx.b16_scaled = scale, scaling, x.dtype, b16_scaled
         ctx.weight_dtypes = (weight_a.dtype, weight_b.dtype)
         return out
 
     @staticmethod
     def backward(ctx, grad):
         x16, bits, a, a16, b16 = ctx.saved_tensors
-        g = grad.to(torch.float16) * ctx.scaling
+        g = grad.to(torch.float16)
+        if not ctx.b16_scaled:
+            g = g * ctx.scaling
         g2 = g.reshape(-1, g.shape[-1])
         grad_b = _weight_gradient(g2, a.reshape(-1, a.shape[-1]), ctx.weight_dtypes[1])
+        if ctx.b16_scaled:
+            grad_b = grad_b * ctx.scaling
         grad_a_in = g.matmul(b16)
         ga2 = grad_a_in.reshape(-1, grad_a_in.shape[-1])
         grad_xd = grad_a_in.matmul(a16)
         xd, dx = _unpack(x16, bits, grad_xd.contiguous(), ctx.scale, ctx.x_dtype)
         grad_a = _weight_gradient(ga2, xd.reshape(-1, xd.shape[-1]), ctx.weight_dtypes[0])
-        return dx, None, grad_a, grad_b, None, None, None, None
+        return dx, None, grad_a, grad_b, None, None, None, None, None
 
 
 class _SharedCopy:
