@@ -55,8 +55,28 @@ def _weight_gradient(grad_rows, input_rows, dtype):
     return grad_rows.t().mm(input_rows).to(dtype)
 
 
+def _add_weight_gradient(weight, grad_rows, input_rows, alpha):
+    """weight.grad += alpha * grad_rows^T @ input_rows inside the GEMM (fp32 accumulator added to
+    the fp32 gradient in its epilogue): True when done, False when the caller has to return the
+    gradient to autograd instead (no gradient tensor yet, or operands this form does not take)."""
+    grad = weight.grad
+    if (grad is None or grad.dtype != torch.float32 or not grad.is_cuda or not grad.is_contiguous()
+            or grad_rows.dtype != torch.float16 or input_rows.dtype != torch.float16):
+        return False
+    torch.addmm(grad, grad_rows.t(), input_rows, out_dtype=torch.float32, alpha=alpha, out=grad)
+    return True
+
+
 class LoRABranch(torch.autograd.Function):
-    """fp16 `lora_B(lora_A(dropout(x))) * scaling` for fp32 x under fp16 autocast."""
+    """fp16 `lora_B(lora_A(dropout(x))) * scaling` for fp32 x under fp16 autocast.
+
+    `LoRABranch.accumulate_in_place` (off by default; `CapturedStep` turns it on for the step it
+    captures): backward adds the two weight gradients to `weight.grad` itself, in the epilogue of
+    the GEMM that forms them, and returns None for them, so autograd launches no separate
+    accumulation (and runs no hooks of those parameters: not for a model wrapped in
+    DistributedDataParallel)."""
+
+    accumulate_in_place = False
 
     @staticmethod
     def forward(ctx, x, x16, weight_a, weight_b, p, scaling, a16=None, b16=None, b16_scaled=False):
@@ -80,6 +100,7 @@ class LoRABranch(torch.autograd.Function):
         ctx.save_for_backward(x16, bits, a, a16, b16)   # the fp16 adapter copies are 50 KB each
         ctx.scale, ctx.scaling, ctx.x_dtype, ctx.b16_scaled = scale, scaling, x.dtype, b16_scaled
         ctx.weight_dtypes = (weight_a.dtype, weight_b.dtype)
+        ctx.weights = (weight_a, weight_b) if LoRABranch.accumulate_in_place else None
         return out
 
     @staticmethod
@@ -89,14 +110,22 @@ class LoRABranch(torch.autograd.Function):
         if not ctx.b16_scaled:
             g = g * ctx.scaling
         g2 = g.reshape(-1, g.shape[-1])
-        grad_b = _weight_gradient(g2, a.reshape(-1, a.shape[-1]), ctx.weight_dtypes[1])
-        if ctx.b16_scaled:
-            grad_b = grad_b * ctx.scaling
+        a2 = a.reshape(-1, a.shape[-1])
+        in_place = ctx.weights is not None and ctx.needs_input_grad[2] and ctx.needs_input_grad[3]
+        grad_b = None
+        if not (in_place and _add_weight_gradient(ctx.weights[1], g2, a2,
+                                                  ctx.scaling if ctx.b16_scaled else 1.0)):
+            grad_b = _weight_gradient(g2, a2, ctx.weight_dtypes[1])
+            if ctx.b16_scaled:
+                grad_b = grad_b * ctx.scaling
         grad_a_in = g.matmul(b16)
         ga2 = grad_a_in.reshape(-1, grad_a_in.shape[-1])
         grad_xd = grad_a_in.matmul(a16)
         xd, dx = _unpack(x16, bits, grad_xd.contiguous(), ctx.scale, ctx.x_dtype)
-        grad_a = _weight_gradient(ga2, xd.reshape(-1, xd.shape[-1]), ctx.weight_dtypes[0])
+        xd2 = xd.reshape(-1, xd.shape[-1])
+        grad_a = None
+        if not (in_place and _add_weight_gradient(ctx.weights[0], ga2, xd2, 1.0)):
+            grad_a = _weight_gradient(ga2, xd2, ctx.weight_dtypes[0])
         return dx, None, grad_a, grad_b, None, None, None, None, None
 
 

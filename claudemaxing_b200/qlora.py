@@ -559,11 +559,17 @@ class CapturedStep:
         packed = SimpleNamespace(B=1, T=self.bucket, index=self.index, ids=self.ids, pos=self.col,
                                  target=self.target, cu_rows=self.cu_rows, longest=self.bucket)
         self.flat_grad.zero_()
-        with torch.autocast("cuda", dtype=torch.float16):
-            out = L._packed_forward(self.model, {"use_cache": False,
-                                                 "num_items_in_batch": self.denominator}, packed)
-        scaled = self.scaler.scale(out.loss) if self.scaler is not None else out.loss * self.loss_scale
-        scaled.backward()
+        # every adapter gradient is a view of the zeroed flat buffer: the GEMMs that form them add
+        # into it directly (no hooks hang on these parameters here)
+        was, LoRABranch.accumulate_in_place = LoRABranch.accumulate_in_place, True
+        try:
+            with torch.autocast("cuda", dtype=torch.float16):
+                out = L._packed_forward(self.model, {"use_cache": False,
+                                                     "num_items_in_batch": self.denominator}, packed)
+            scaled = self.scaler.scale(out.loss) if self.scaler is not None else out.loss * self.loss_scale
+            scaled.backward()
+        finally:
+            LoRABranch.accumulate_in_place = was
         return out.loss.detach()
 
     def _optimizer_step(self):

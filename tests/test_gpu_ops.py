@@ -401,6 +401,36 @@ def test_lora_branch_matches_plain_formula():
     assert rel_norm(b.grad.cpu(), b2.grad.cpu()) < 5e-3
 
 
+@pytest.mark.parametrize("scaling", [2.0, 1.7])
+def test_lora_branch_with_cast_scaled_weights_and_in_place_gradients(scaling, monkeypatch):
+    """The branch given fp16 A and fp16(scaling * B) copies (no scaling pass over its output or
+    the incoming gradient), adding its weight gradients into existing `.grad` tensors inside the
+    GEMMs: the plain call's numbers (identical for a power-of-two scaling)."""
+    from claudemaxing_b200.lora import LoRABranch
+
+    torch.manual_seed(0)
+    x = torch.randn(3, 40, 256, device=DEV)
+    a = (torch.randn(16, 256, device=DEV) * 0.1).requires_grad_()
+    b = (torch.randn(64, 16, device=DEV) * 0.1).requires_grad_()
+    g = torch.randn(3, 40, 64, device=DEV).half()
+    results = []
+    for fast in (False, True):
+        xx = x.clone().requires_grad_()
+        a.grad, b.grad = torch.full_like(a, 0.5), torch.full_like(b, -0.25)   # something to add to
+        kept = (a.grad, b.grad)
+        monkeypatch.setattr(LoRABranch, "accumulate_in_place", fast)
+        torch.manual_seed(7)
+        extra = (a.detach().half(), (b.detach() * scaling).half(), True) if fast else ()
+        out = LoRABranch.apply(xx, xx.detach().half(), a, b, 0.1, scaling, *extra)
+        out.backward(g)
+        assert (a.grad is kept[0] and b.grad is kept[1]) or not fast
+        results.append((out.detach(), xx.grad, a.grad.clone(), b.grad.clone()))
+    for name, plain, fast in zip(("out", "dx", "dA", "dB"), *results):
+        if scaling == 2.0 and name in ("out", "dx"):
+            assert torch.equal(plain, fast), name
+        assert rel_norm(fast.float().cpu(), plain.float().cpu()) < 2e-3, name
+
+
 def test_ops_refuse_cpu_tensors():
     from claudemaxing_b200.rmsnorm import rmsnorm
     from claudemaxing_b200.swiglu_recompute import swiglu_recompute
