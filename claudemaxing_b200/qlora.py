@@ -604,7 +604,14 @@ class CapturedStep:
             self.scaler.load_state_dict(scaler)
 
     def _capture(self, warmup):
+        from .embedding import shrink_tied_embedding
+
         self.model.train()
+        # what the patched forward does on its first training call: decided here, before the
+        # capture, because it replaces the tied weight's storage (a graph captured on the fp32
+        # storage would read freed memory once an eager step shrank it)
+        with torch.autocast("cuda", dtype=torch.float16):
+            shrink_tied_embedding(self.model)
         snapshot = self._snapshot()
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())

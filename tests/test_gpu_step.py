@@ -299,6 +299,14 @@ def test_captured_step_equals_the_eager_step_and_trains():
     if other["n_tokens"] <= step.bucket:
         step.load(other)
         assert torch.isfinite(step.run()).item()
+    # an eager step through the patched forward after the capture (it is what decides the tied
+    # embedding's storage dtype on its first call) leaves everything the graphs read in place
+    step.load(batch)
+    before_eager = float(step.run())
+    eager_now = float(qlora.qlora_step(model, dev_batch))
+    after_eager = float(step.run())
+    assert abs(eager_now - before_eager) < 0.05 * abs(before_eager)
+    assert abs(after_eager - before_eager) < 0.05 * abs(before_eager)
 
 
 @pytest.mark.parametrize("autocast_dtype", [torch.bfloat16, None])
