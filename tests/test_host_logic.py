@@ -123,3 +123,39 @@ def test_nf4_supported_guard():
     p, s = qlora.quantize_nf4(w)
     assert not _supported(p, s, torch.float16)  # CPU tensors are not for the kernel
     assert not _supported(p, None, torch.float16)
+
+
+def test_fused_block_plan_accepts_this_package_s_layers_and_says_why_not_otherwise():
+    """Host logic of decoder_block.py on a CPU model (no kernel runs): the structure check takes a
+    block built by build_qlora_model, the q/k/v weights are adjacent in the group's buffer, and a
+    call that is not the packed fp16-autocast training call is sent to the installed forward."""
+    from claudemaxing_b200 import decoder_block as D
+    from claudemaxing_b200 import qlora
+
+    tiny = dict(hidden_size=256, intermediate_size=512, num_hidden_layers=2, num_attention_heads=2,
+                num_key_value_heads=1, vocab_size=500, max_position_embeddings=128)
+    model, lora = qlora.build_qlora_model("cpu", tiny, seed=0)
+    layer = model.model.layers[0]
+    plan = layer._soup_block
+    assert plan.why_not == "" and plan.head_dim == 128 and plan.keep_products
+    group = layer.self_attn.k_proj.group
+    bases = [layer.self_attn.q_proj.base_layer, layer.self_attn.k_proj, layer.self_attn.v_proj.base_layer]
+    assert group.stacked(bases, torch.float16, probe=True) is True
+    assert group.stacked([bases[0], bases[2]], torch.float16, probe=True) is None     # not consecutive
+    assert group.stacked([layer.mlp.up_proj, layer.mlp.down_proj], torch.float16, probe=True) is None   # other width
+    casts = model.model.__dict__["_soup_adapter_casts"]
+    assert len(casts.modules) == 2 * tiny["num_hidden_layers"] and not casts.armed
+    casts.refresh()                      # CPU weights: nothing is cast, nothing is handed out
+    assert not casts.armed and plan.adapter(layer.self_attn.k_proj, None) is None
+    hidden = torch.zeros(1, 8, 256)
+    cu = torch.tensor([0, 8], dtype=torch.int32)
+    rope = (torch.zeros(1, 8, 128), torch.zeros(1, 8, 128))
+    reason = D._why_not(plan, hidden, None, None, rope, {"cu_seq_lens_q": cu, "cu_seq_lens_k": cu})
+    assert reason == "hidden states are not one contiguous fp32 CUDA row"
+    assert "segment offsets" in D._why_not(plan, hidden, torch.ones(1, 1, 8, 8, dtype=torch.bool), None, rope, {})
+    # a model whose blocks are not this package's layers is left alone
+    from transformers import Qwen2Config, Qwen2ForCausalLM
+    plain = Qwen2ForCausalLM(Qwen2Config(**tiny))
+    assert D.install_fused_blocks(plain) == 0
+    assert "NF4Linear" in D.BlockPlan(plain.model.layers[0]).why_not
+    assert len(lora) == 4 * tiny["num_hidden_layers"]
