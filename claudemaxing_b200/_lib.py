@@ -29,6 +29,7 @@ SIGNATURES = {
     "soup_rmsnorm_fwd": [_P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _F, _I, _I, _I, _P],
     "soup_rmsnorm_bwd": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _I, _I, _I, _I, _I, _P],
     "soup_rmsnorm_bwd_noalloc": [_P, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _I, _I, _I, _I, _I, _P],
+    "soup_rmsnorm_bwd_residual": [_P] * 9 + [_L] * 3 + [_P],
     "soup_rope": [_P, _P, _P, _P, _P, _P] + [_L] * 13 + [_I] * 6 + [_P],
     "soup_rope_sum": [_P, _P, _P, _P, _P, _P, _P] + [_L] * 22 + [_I] * 7 + [_P],
     "soup_attn_fwd": [_P, _P, _P, _P, _P, _P] + [_L] * 8 + [_F, _P],

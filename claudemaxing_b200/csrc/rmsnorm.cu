@@ -584,7 +584,8 @@ template <int NVX>
 __global__ void __launch_bounds__(rowpipe::kMaxWarps * 32, 2)
 rmsnorm_bwd_saved_kernel(const float* __restrict__ dy, const __half* __restrict__ saved,
                          const float* __restrict__ w, const float* __restrict__ rstd_in,
-                         float* __restrict__ dx, const int32_t* __restrict__ slot,
+                         const float* __restrict__ add, float* __restrict__ dx,
+                         __half* __restrict__ dx16, const int32_t* __restrict__ slot,
                          const __half* __restrict__ small, int64_t n_small, int64_t n_rows,
                          int n_cols, int stages, int team, int w_offset, int* status) {
   constexpr int EPV = 4;
@@ -693,7 +694,19 @@ rmsnorm_bwd_saved_kernel(const float* __restrict__ dy, const __half* __restrict_
         o.y = (yv[1] * wq.y - nrm[v][1] * mean_dot) * rstd;
         o.z = (yv[2] * wq.z - nrm[v][2] * mean_dot) * rstd;
         o.w = (yv[3] * wq.w - nrm[v][3] * mean_dot) * rstd;
-        *reinterpret_cast<float4*>(dx + row * n_cols + (int64_t)(v0 + vi) * EPV) = o;
+        const int64_t at = row * n_cols + (int64_t)(v0 + vi) * EPV;
+        if (add) {   // the gradient that reaches the same tensor along the residual connection
+          const float4 r = *reinterpret_cast<const float4*>(add + at);
+          o.x += r.x; o.y += r.y; o.z += r.z; o.w += r.w;
+        }
+        *reinterpret_cast<float4*>(dx + at) = o;
+        if (dx16) {  // and its fp16 copy, for the projection backward that receives it next
+          __half2 lo = __floats2half2_rn(o.x, o.y), hi = __floats2half2_rn(o.z, o.w);
+          uint2 packed;
+          packed.x = *reinterpret_cast<uint32_t*>(&lo);
+          packed.y = *reinterpret_cast<uint32_t*>(&hi);
+          *reinterpret_cast<uint2*>(dx16 + at) = packed;
+        }
       }
     }
     __syncwarp();
@@ -930,12 +943,46 @@ extern "C" int64_t soup_rmsnorm_bwd_partials(int64_t n_rows, int64_t n_cols) {
   return soup::bwd_ctas(n_rows);
 }
 
+namespace soup {
+namespace {
+int rmsnorm_bwd_any(const void* dy, const void* xin, const void* w, const float* rstd, void* dx,
+                    float* dw_partial, void* dw, const int32_t* slot, const void* small,
+                    int64_t n_small, int64_t n_rows, int64_t n_cols, int dy_dtype, int xin_dtype,
+                    int w_dtype, int dx_dtype, int saved_output, const float* add, __half* dx16,
+                    void* stream);
+}  // namespace
+}  // namespace soup
+
 extern "C" int soup_rmsnorm_bwd(const void* dy, const void* xin, const void* w, const float* rstd,
                                 void* dx, float* dw_partial, void* dw, const int32_t* slot,
                                 const void* small, int64_t n_small, int64_t n_rows, int64_t n_cols,
                                 int dy_dtype, int xin_dtype, int w_dtype, int dx_dtype,
                                 int saved_output, void* stream) {
-  using namespace soup;
+  return soup::rmsnorm_bwd_any(dy, xin, w, rstd, dx, dw_partial, dw, slot, small, n_small, n_rows,
+                               n_cols, dy_dtype, xin_dtype, w_dtype, dx_dtype, saved_output, nullptr,
+                               nullptr, stream);
+}
+
+extern "C" int soup_rmsnorm_bwd_residual(const float* dy, const void* low, const float* w,
+                                         const float* rstd, const float* add, float* dx, void* dx16,
+                                         const int32_t* slot, const void* small, int64_t n_small,
+                                         int64_t n_rows, int64_t n_cols, void* stream) {
+  if (add && (reinterpret_cast<uintptr_t>(add) & 15u))
+    SOUP_FAIL(SOUP_ERR_ARG, "rmsnorm_bwd_residual: the residual gradient must be 16-byte aligned");
+  if (dx16 && (reinterpret_cast<uintptr_t>(dx16) & 7u))
+    SOUP_FAIL(SOUP_ERR_ARG, "rmsnorm_bwd_residual: the fp16 copy must be 8-byte aligned");
+  return soup::rmsnorm_bwd_any(dy, low, w, rstd, dx, nullptr, nullptr, slot, small, n_small, n_rows,
+                               n_cols, SOUP_F32, SOUP_F16, SOUP_F32, SOUP_F32, 1, add,
+                               reinterpret_cast<__half*>(dx16), stream);
+}
+
+namespace soup {
+namespace {
+int rmsnorm_bwd_any(const void* dy, const void* xin, const void* w, const float* rstd, void* dx,
+                    float* dw_partial, void* dw, const int32_t* slot, const void* small,
+                    int64_t n_small, int64_t n_rows, int64_t n_cols, int dy_dtype, int xin_dtype,
+                    int w_dtype, int dx_dtype, int saved_output, const float* add, __half* dx16,
+                    void* stream) {
   if (n_rows < 0 || n_cols <= 0 || n_cols > 16384)
     SOUP_FAIL(SOUP_ERR_ARG, "rmsnorm_bwd: need 0 < n_cols <= 16384 (got %lld)", (long long)n_cols);
   const bool want_dw = dw != nullptr;
@@ -967,6 +1014,8 @@ extern "C" int soup_rmsnorm_bwd(const void* dy, const void* xin, const void* w, 
                                  : rowpipe::Plan{8, 0, 1, 1, 0, 0};
   int* status = plan.stages ? rowpipe::status_word() : nullptr;
   unsigned grid = (unsigned)(want_dw ? bwd_ctas(n_rows) : n_rows);
+  if ((add || dx16) && !(vec && plan.stages && status))
+    SOUP_FAIL(SOUP_ERR_ARG, "rmsnorm_bwd_residual: this shape does not take the residual form");
   if (!vec) {
     if (want_dw)
       rmsnorm_bwd_scalar_kernel<true><<<grid, 256, 0, s>>>(dy, xin, w, rstd, dx, dw_partial, slot,
@@ -1000,7 +1049,11 @@ extern "C" int soup_rmsnorm_bwd(const void* dy, const void* xin, const void* w, 
     // weight and reciprocal behind the ring; two CTAs of this size must still fit an SM
     const size_t w_off = (plan_y.smem + 15) / 16 * 16;
     const size_t smem_y = w_off + 2 * (size_t)n_cols * sizeof(float);
-    if (four_bit && plan_y.stages >= 1 && per_lane >= 1 && per_lane <= 8 && smem_y <= 112 * 1024) {
+    const bool saved_kernel = four_bit && plan_y.stages >= 1 && per_lane >= 1 && per_lane <= 8 &&
+                              smem_y <= 112 * 1024;
+    if ((add || dx16) && !saved_kernel)
+      SOUP_FAIL(SOUP_ERR_ARG, "rmsnorm_bwd_residual: this shape does not take the residual form");
+    if (saved_kernel) {
       grid = plan_y.grid;
 #define SOUP_RMS_BWD_S(NVX_)                                                                     \
   do {                                                                                            \
@@ -1008,7 +1061,7 @@ extern "C" int soup_rmsnorm_bwd(const void* dy, const void* xin, const void* w, 
     cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_y);       \
     kernel<<<plan_y.grid, plan_y.warps * 32, smem_y, s>>>(                                        \
         reinterpret_cast<const float*>(dy), reinterpret_cast<const __half*>(xin),                 \
-        reinterpret_cast<const float*>(w), rstd, reinterpret_cast<float*>(dx), slot,              \
+        reinterpret_cast<const float*>(w), rstd, add, reinterpret_cast<float*>(dx), dx16, slot,   \
         reinterpret_cast<const __half*>(small), n_small, n_rows, (int)n_cols, plan_y.stages,      \
         plan_y.team, (int)w_off, status);                                                         \
   } while (0)
@@ -1081,6 +1134,8 @@ extern "C" int soup_rmsnorm_bwd(const void* dy, const void* xin, const void* w, 
   }
   return SOUP_OK;
 }
+}  // namespace
+}  // namespace soup
 
 
 // ------------------------------------------------------------------------------------------

@@ -28,6 +28,7 @@ one NF4Group (qlora.build_qlora_model), called in training under fp16 autocast w
 row's segment offsets; any other call runs the block's installed forward.
 """
 
+import importlib
 import os
 import types
 
@@ -42,6 +43,8 @@ from .rope import rotate_into
 from .swiglu_recompute import _silu_mul_bwd, _silu_mul_fwd
 
 F16, F32 = torch.float16, torch.float32
+# the package exports a function of the same name as this module: fetch the module itself
+rmsnorm_mod = importlib.import_module(__package__ + ".rmsnorm")
 
 
 def _plain_precision(fn):
@@ -169,6 +172,86 @@ class AdapterCasts:
         self.armed = False
 
 
+class _GradCopies:
+    """The fp16 copy of the hidden-state gradient `_NormResidual.backward` has just written, found
+    again by the fp32 gradient's storage and version when the projection backward one block
+    earlier receives that gradient."""
+
+    key = copy = None
+
+    @classmethod
+    def record(cls, grad, copy):
+        cls.key, cls.copy = (grad.data_ptr(), grad._version, tuple(grad.shape)), copy
+
+    @classmethod
+    def take(cls, grad):
+        if cls.key != (grad.data_ptr(), grad._version, tuple(grad.shape)):
+            return None
+        copy, cls.key, cls.copy = cls.copy, None, None
+        return copy
+
+
+def _fp16_gradient_rows(grad):
+    """[rows, hidden] fp16 of an fp32 hidden-state gradient: the copy the norm backward wrote
+    beside it, else a cast."""
+    copy = _GradCopies.take(grad)
+    if copy is None:
+        return grad.reshape(-1, grad.shape[-1]).to(F16)
+    return copy.view(-1, grad.shape[-1])
+
+
+class _NormResidual(torch.autograd.Function):
+    """(RMSNorm(h), h): the norm of a block and the residual connection that leaves the same
+    tensor, as one autograd node, so that backward sees the norm's output gradient and the
+    residual gradient together: one kernel (`soup_rmsnorm_bwd_residual`) forms
+    rmsnorm_backward(dy) + residual gradient and the fp16 copy of the sum, where autograd would
+    launch the norm backward, an add and, in the projection backward that receives the sum, a
+    cast. For the frozen fp32 norm weights of the 4-bit model (the forward's saved-output form)."""
+
+    @staticmethod
+    def forward(ctx, h, weight, eps):
+        rows = h.view(-1, h.shape[-1])
+        out, rstd, low, slots, small = rmsnorm_mod._forward_launch(rows, weight, eps, F32, True)
+        ctx.save_for_backward(low, weight, rstd, slots, small)
+        result = out.view(h.shape)
+        rmsnorm_mod._LastCopy.record(result, low)
+        return result, h
+
+    @staticmethod
+    def backward(ctx, dy, residual_grad):
+        low, weight, rstd, slots, small = ctx.saved_tensors
+        n, cols = low.shape
+        if dy is None:
+            return residual_grad, None, None
+        dy = dy.contiguous()
+        add = None if residual_grad is None else residual_grad.contiguous()
+        dx = torch.empty(dy.shape, dtype=F32, device=dy.device)
+        dx16 = torch.empty(dy.shape, dtype=F16, device=dy.device)
+        try:
+            _lib.call("soup_rmsnorm_bwd_residual", _lib.ptr(dy), _lib.ptr(low), _lib.ptr(weight),
+                      _lib.ptr(rstd), _lib.ptr(add), _lib.ptr(dx), _lib.ptr(dx16), _lib.ptr(slots),
+                      _lib.ptr(small), small.shape[-1], n, cols, _lib.stream_of(dy))
+        except RuntimeError:   # a shape the residual form does not take: the three separate steps
+            _lib.call("soup_rmsnorm_bwd", _lib.ptr(dy), _lib.ptr(low), _lib.ptr(weight), _lib.ptr(rstd),
+                      _lib.ptr(dx), None, None, _lib.ptr(slots), _lib.ptr(small), small.shape[-1], n,
+                      cols, _lib.F32, _lib.F16, _lib.F32, _lib.F32, 1, _lib.stream_of(dy))
+            return (dx if add is None else dx + add), None, None
+        _GradCopies.record(dx, dx16)
+        return dx, None, None
+
+
+def _norm_and_residual(norm, hidden):
+    """(norm(hidden), hidden as the residual branch sees it) through `_NormResidual` when the norm
+    is a frozen fp32 RMSNorm whose forward keeps the fp16 copy, else through the module."""
+    weight = norm.weight
+    if (hidden.requires_grad and weight.dtype == F32 and not weight.requires_grad and weight.is_cuda
+            and weight.dim() == 1 and hidden.shape[-1] == weight.shape[0]
+            and hidden.shape[-1] <= rmsnorm_mod.MAX_COLS and hidden.shape[-1] % 8 == 0
+            and rmsnorm_mod._small_columns(weight) is not None):
+        return _NormResidual.apply(hidden, weight, norm.variance_epsilon)
+    return norm(hidden), hidden
+
+
 class _QKVRope(torch.autograd.Function):
     """(x16 @ [Wq; Wk; Wv]^T + bias) split into q (+ adapter), k, v (+ adapter); q and k rotated;
     all three returned as fp16 [tokens, heads, head_dim]. With `cu_rows` (segment offsets of the
@@ -266,7 +349,7 @@ class _ProjectAddResidual(torch.autograd.Function):
     def backward(ctx, grad):
         dy = None
         if ctx.needs_input_grad[0]:
-            g16 = grad.reshape(-1, grad.shape[-1]).to(F16)
+            g16 = _fp16_gradient_rows(grad)
             dy = torch.mm(g16, ctx.linear.dequantized(F16)).view(ctx.y_shape)
         return dy, (grad if ctx.needs_input_grad[1] else None), None
 
@@ -306,7 +389,7 @@ class _GatedMLPAddResidual(torch.autograd.Function):
         plan = ctx.plan
         dx = None
         if ctx.needs_input_grad[0]:
-            g16 = grad.reshape(-1, grad.shape[-1]).to(F16)
+            g16 = _fp16_gradient_rows(grad)
             d_act = torch.mm(g16, plan.down.dequantized(F16))
             w_gate, w_up = plan.gate.dequantized(F16), plan.up.dequantized(F16)
             if ctx.kept:
@@ -359,7 +442,7 @@ def fused_block_forward(layer, hidden_states, attention_mask=None, position_ids=
         return plan.installed(hidden_states, attention_mask=attention_mask, position_ids=position_ids,
                               past_key_values=past_key_values, use_cache=use_cache,
                               position_embeddings=position_embeddings, **kwargs)
-    x = layer.input_layernorm(hidden_states)
+    x, residual = _norm_and_residual(layer.input_layernorm, hidden_states)
     adapters = [plan.adapter(m, x) for m in (plan.q, plan.k, plan.v)]
     if adapters[1] is not None or any(a is False for a in adapters):
         # an adapter on k_proj, or one LoRABranch does not reproduce: the installed forward (the
@@ -385,12 +468,12 @@ def fused_block_forward(layer, hidden_states, attention_mask=None, position_ids=
         attended = segment_attention(q.unsqueeze(0).transpose(1, 2), k.unsqueeze(0).transpose(1, 2),
                                      v.unsqueeze(0).transpose(1, 2), cu, kwargs.get("max_length_q", n),
                                      scale)
-    hidden_states = _ProjectAddResidual.apply(attended.reshape(n, -1), hidden_states, plan.o)
-    x = layer.post_attention_layernorm(hidden_states)
+    hidden_states = _ProjectAddResidual.apply(attended.reshape(n, -1), residual, plan.o)
+    x, residual = _norm_and_residual(layer.post_attention_layernorm, hidden_states)
     x16 = fp16_copy_of(x)
     if x16 is None:
         x16 = x.detach().to(F16)
-    return _GatedMLPAddResidual.apply(x, x16, hidden_states, plan)
+    return _GatedMLPAddResidual.apply(x, x16, residual, plan)
 
 
 def install_fused_blocks(model):

@@ -144,6 +144,19 @@ int soup_rmsnorm_bwd_noalloc(const void* dy, const void* xin, const void* w, con
                              int xin_dtype, int w_dtype, int dx_dtype, int saved_output,
                              void* stream);
 
+/* The 4-bit model's RMSNorm backward (fp32 dy, the forward's fp16 copy `low` as the saved tensor,
+ * fp32 weight and dx; the saved-output form of soup_rmsnorm_bwd) with the residual connection
+ * folded in: dx = rmsnorm_backward(dy) + add, where `add` (nullable, fp32 [n_rows, n_cols]) is the
+ * gradient that reaches the norm's input along the residual branch, and dx16 (nullable) receives
+ * the fp16 copy of dx that the projection backward one block earlier wants. Two elementwise
+ * kernels (an add and a cast over [tokens, hidden]) per norm disappear. Returns SOUP_ERR_ARG for
+ * shapes the saved-output kernel does not take; the caller then adds and casts itself. No
+ * counterpart of its own in the reference (its block leaves both to autograd). */
+int soup_rmsnorm_bwd_residual(const float* dy, const void* low, const float* w, const float* rstd,
+                              const float* add, float* dx, void* dx16, const int32_t* slot,
+                              const void* small, int64_t n_small, int64_t n_rows, int64_t n_cols,
+                              void* stream);
+
 /* Rotary embedding of q and k in one launch (forward, or the transposed rotation for backward).
  * Replaces the two qwen_rope_kernel launches of RoPE.forward / RoPE.backward at
  * solution/rope.py:54-56 (kernel :17-43). Either of q / k may be NULL (skipped).

@@ -284,6 +284,46 @@ def test_rope_of_a_sum_into_strided_outputs_is_the_chain_it_replaces(dims, with_
     assert (buf[:, (h + kv) * d:] == 7.0).all()    # the v block is not this kernel's to write
 
 
+@pytest.mark.parametrize("rows,cols", [(1280, 1536), (37, 256), (5, 4096)])
+@pytest.mark.parametrize("with_residual", [True, False])
+def test_rmsnorm_backward_with_the_residual_gradient_folded_in(rows, cols, with_residual):
+    """`soup_rmsnorm_bwd_residual` = the saved-output RMSNorm backward, plus the residual branch's
+    gradient, plus the fp16 copy of the sum: bit-identical to the backward kernel followed by
+    torch's add and cast; and the autograd node `_NormResidual` gives the gradients of
+    norm(h) and h + f(norm(h)) composed the plain way."""
+    import importlib
+
+    from claudemaxing_b200 import _lib
+
+    rms = importlib.import_module("claudemaxing_b200.rmsnorm")
+    block = importlib.import_module("claudemaxing_b200.decoder_block")
+    gen = torch.Generator().manual_seed(8)
+    h = torch.randn(1, rows, cols, generator=gen).to(DEV).requires_grad_()
+    w = (torch.randn(cols, generator=gen) * 0.3 + 1.0).to(DEV)
+    w[3] = 1e-5                                   # a tiny-|w| column goes through the side buffer
+    dy = torch.randn(1, rows, cols, generator=gen).to(DEV)
+    res = torch.randn(1, rows, cols, generator=gen).to(DEV) if with_residual else None
+    out, rstd, low, slots, small = rms._forward_launch(h.detach().view(rows, cols), w, 1e-6, F32, True)
+    plain = torch.empty(rows, cols, device=DEV)
+    _lib.call("soup_rmsnorm_bwd", _lib.ptr(dy), _lib.ptr(low), _lib.ptr(w), _lib.ptr(rstd), _lib.ptr(plain),
+              None, None, _lib.ptr(slots), _lib.ptr(small), small.shape[-1], rows, cols, _lib.F32,
+              _lib.F16, _lib.F32, _lib.F32, 1, _lib.stream_of(dy))
+    want = plain if res is None else plain + res.view(rows, cols)
+    dx, dx16 = torch.empty(rows, cols, device=DEV), torch.empty(rows, cols, dtype=F16, device=DEV)
+    _lib.call("soup_rmsnorm_bwd_residual", _lib.ptr(dy), _lib.ptr(low), _lib.ptr(w), _lib.ptr(rstd),
+              _lib.ptr(res), _lib.ptr(dx), _lib.ptr(dx16), _lib.ptr(slots), _lib.ptr(small),
+              small.shape[-1], rows, cols, _lib.stream_of(dy))
+    assert torch.equal(dx, want) and torch.equal(dx16, want.half())
+    # the autograd node: y = norm(h) * 2 + h (a branch on the norm and the residual connection)
+    x, h_res = block._NormResidual.apply(h, w, 1e-6)
+    (x * 2.0 + h_res).backward(dy)
+    h2 = h.detach().clone().requires_grad_()
+    (rms.rmsnorm(h2, w, 1e-6) * 2.0 + h2).backward(dy)
+    assert_close_rel_max(h.grad.cpu(), h2.grad.cpu(), 1e-5, "gradient through norm and residual")
+    copy = block._GradCopies.take(h.grad)
+    assert copy is None or torch.equal(copy.view_as(h.grad), h.grad.half())
+
+
 # ----------------------------------------------------------------------------------- SwiGLU
 @pytest.mark.parametrize("tag", ["f16", "f32", "mix", "noround"])
 def test_swiglu_golden(tag):
