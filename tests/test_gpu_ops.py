@@ -310,10 +310,15 @@ def test_rmsnorm_backward_with_the_residual_gradient_folded_in(rows, cols, with_
               _lib.F16, _lib.F32, _lib.F32, 1, _lib.stream_of(dy))
     want = plain if res is None else plain + res.view(rows, cols)
     dx, dx16 = torch.empty(rows, cols, device=DEV), torch.empty(rows, cols, dtype=F16, device=DEV)
-    _lib.call("soup_rmsnorm_bwd_residual", _lib.ptr(dy), _lib.ptr(low), _lib.ptr(w), _lib.ptr(rstd),
-              _lib.ptr(res), _lib.ptr(dx), _lib.ptr(dx16), _lib.ptr(slots), _lib.ptr(small),
-              small.shape[-1], rows, cols, _lib.stream_of(dy))
-    assert torch.equal(dx, want) and torch.equal(dx16, want.half())
+    try:
+        _lib.call("soup_rmsnorm_bwd_residual", _lib.ptr(dy), _lib.ptr(low), _lib.ptr(w), _lib.ptr(rstd),
+                  _lib.ptr(res), _lib.ptr(dx), _lib.ptr(dx16), _lib.ptr(slots), _lib.ptr(small),
+                  small.shape[-1], rows, cols, _lib.stream_of(dy))
+    except RuntimeError as err:     # rows too wide for the saved-output kernel: said so, not guessed
+        assert cols > 1024 * 3 and "does not take the residual form" in str(err)
+    else:
+        assert cols <= 1024 * 3
+        assert torch.equal(dx, want) and torch.equal(dx16, want.half())
     # the autograd node: y = norm(h) * 2 + h (a branch on the norm and the residual connection)
     x, h_res = block._NormResidual.apply(h, w, 1e-6)
     (x * 2.0 + h_res).backward(dy)
