@@ -53,6 +53,8 @@ def test_attention_kernels_on_the_reference_kernels_golden_vectors(tag):
     (4, 4, [70]),
     (12, 2, [300, 0, 280, 296, 292, 112]),
     (6, 1, [1000, 3]),
+    (4, 2, [40] * 100 + [3]),        # more than 64 segments: the plain tile order
+    (2, 1, [2500]),                  # twenty key tiles: many turns of every barrier
 ])
 def test_attention_kernels_against_fp32_with_the_fp16_sdpa_error_as_the_bar(hq, hk, lens):
     from oracle import attention as oat
