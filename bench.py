@@ -5,7 +5,7 @@
 
 One "step" is one pass of the hot path over one batch of synthetic input: fused_head_loss forward
 plus backward through the public API (loss, per-row loss/entropy/accuracy, dHidden). The workload
-at N=1 is BASELINE config 1 (2048 packed tokens, hidden 1536, tied fp16 head 151936 x 1536, 10 %
+at N=1 is benchmark config 1 (2048 packed tokens, hidden 1536, tied fp16 head 151936 x 1536, 10 %
 ignored targets). At N>1 the head is vocabulary-parallel with 2048 tokens per GPU (weak scaling:
 per-GPU GEMM work is constant, the exchange is one all-gather of the per-row states and one
 all-reduce of dHidden). `--workload c5a` selects the fixed 65536-token job instead.
@@ -52,7 +52,7 @@ SLAB = 2048   # rows of hidden states generated from one seed
 
 
 def make_weight():
-    """The tied head weight of BASELINE config 1: [151936, 1536] ~N(0, 0.02) fp16, generated on the
+    """The tied head weight of benchmark config 1: [151936, 1536] ~N(0, 0.02) fp16, generated on the
     CPU slab by slab (no 900 MB fp32 temporary) so that oracle and kernels see identical bits."""
     gen = torch.Generator().manual_seed(1000)
     weight = torch.empty(VOCAB, HIDDEN, dtype=torch.float16)
@@ -64,7 +64,7 @@ def make_weight():
 
 def make_rows(slab):
     """Slab `slab` of the token rows: hidden [2048, 1536] ~N(0,1) fp16 and targets uniform over the
-    vocabulary with 10 % set to ignore_index (BASELINE config 1 recipe). Every slab has its own
+    vocabulary with 10 % set to ignore_index (benchmark config 1 recipe). Every slab has its own
     seed, so a rank generates only the rows it feeds and any rank can regenerate any row."""
     gen = torch.Generator().manual_seed(2000 + slab)
     hidden = torch.randn(SLAB, HIDDEN, generator=gen).half()
@@ -651,7 +651,7 @@ def step_only(dev, steps):
 
 
 def qlora_step_leg(dev, rank, world, steps, warmup, timed):
-    """BASELINE config 4 (and 5b at N>1): the full Qwen2.5-1.5B-architecture QLoRA step, batch 4 per
+    """benchmark config 4 (and 5b at N>1): the full Qwen2.5-1.5B-architecture QLoRA step, batch 4 per
     GPU with lengths uniform in [64, 512], packed; forward, backward, LoRA-gradient all-reduce at
     N>1, fused AdamW. Timed as CUDA-graph replays (CapturedStep) and, for comparison, eagerly."""
     import torch.distributed as dist
@@ -1129,7 +1129,7 @@ def main():
                          "matmul + log_softmax + autograd (oracle/head_ce.py); its output is the "
                          "reference of `parity`"}
 
-    # ---- BASELINE configs[4](a): the fixed 65536-token job, vocabulary-parallel over N
+    # ---- benchmark configs[4](a): the fixed 65536-token job, vocabulary-parallel over N
     c5a = None
     if args.workload == "c1" and not args.no_c5a and c5a_slabs:
         del job

@@ -1,4 +1,4 @@
-"""LM head + cross-entropy oracle: fp32 matmul + log_softmax, as BASELINE config 1 prescribes and
+"""LM head + cross-entropy oracle: fp32 matmul + log_softmax, as benchmark config 1 prescribes and
 as the reference's own test computes its expectation (tests_local/test_lm_head_loss.py:66-86, with
 the autocast removed so that everything is fp32)."""
 

@@ -1,5 +1,5 @@
 """Parity of the fused LM head + cross-entropy (tcgen05 kernels, through the C ABI) with the fp32
-CPU oracle. Tolerances are BASELINE's: per-row loss and entropy within 1e-3 absolute, dHidden
+CPU oracle. Tolerances are those of the benchmark definition: per-row loss and entropy within 1e-3 absolute, dHidden
 within 1e-2 of max |ref|; argmax accuracy within max(1, 1%) rows (near ties), as the reference's
 own test allows (tests_local/test_lm_head_loss.py:134-142)."""
 
@@ -206,7 +206,7 @@ def test_vocab_parallel_partials_merge_to_the_single_pass(n_shards):
 
 
 def test_full_size_linearity_property():
-    # BASELINE config 1 size (N=2048, H=1536, V=151936): no CPU oracle in seconds at this size, so
+    # benchmark config 1 size (N=2048, H=1536, V=151936): no CPU oracle in seconds at this size, so
     # check properties: sum_v softmax = 1 means dHidden of a row is orthogonal to nothing cheap,
     # but the loss must equal lse - label logit recomputed for a sample of rows in fp64, and rows
     # with identical hidden states must get identical results wherever they sit in the tiles.

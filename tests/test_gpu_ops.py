@@ -222,7 +222,7 @@ def test_rope_vs_oracle(dims, dtype, cos_batch_one):
 
 
 def test_rope_packed_positions_restart_per_row():
-    # BASELINE config 3: one packed row of lengths {512,384,640,512}, positions restart at 0
+    # benchmark config 3: one packed row of lengths {512,384,640,512}, positions restart at 0
     from claudemaxing_b200.rope import rope
     from oracle import elementwise as ew
 
