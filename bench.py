@@ -498,7 +498,7 @@ def attention_suite(dev, tensor_peak):
             "torch_varlen_flash_ms": round(ms_lib, 5), "launches": 1 if leg == "fwd" else 2,
             "note": "latency-bound: ~150 CTAs each walking at most three key tiles; the backward "
                     "launch count includes clearing the fp32 dK / dV buffers" if leg == "bwd" else
-                    "latency-bound: ~150 CTAs each walking at most three key tiles twice"}
+                    "latency-bound: ~150 CTAs each walking at most three key tiles (score tiles resident in tensor memory between the two softmax passes)"}
     _lib.check_device_status()
     return out
 

@@ -6,8 +6,8 @@
 // a two-stage ring. S = Q K^T of a tile is one tcgen05 product (M 128, N 128, K 128) into one of two
 // 128-column accumulators in tensor memory; the four softmax warps read it (thread = query row).
 // The softmax is done in two passes over the key tiles, so that the output accumulator never has
-// to be rescaled: the first pass only reduces the row maximum and the sum of exponentials; the
-// second forms S again, writes P = exp(S - max) as fp16 into a 128-byte-swizzled shared-memory
+// to be rescaled: the first pass only reduces the row maximum; the second forms S again, sums
+// the exponentials, writes P = exp(S - max) as fp16 into a 128-byte-swizzled shared-memory
 // tile (the A operand) and accumulates O += P V in tensor memory (V as MN-major B operand). At
 // segment lengths of a few hundred tokens the second QK^T is cheap next to the latency of a
 // rescale round trip through tensor memory. The epilogue divides by the sum and writes fp16 rows
@@ -41,14 +41,14 @@ constexpr int kKBytes = kBKV * kD * 2;         // 32 KB: two boxes of [128 rows 
 constexpr int kKVBox = kBKV * 128;             // 16 KB
 constexpr int kPBytes = kBQ * kBKV * 2;        // 32 KB: two boxes of [128 rows x 64 cols]
 constexpr int kThreads = 224;                  // warps 0-3 softmax, 4 key TMA, 5 MMA, 6 value TMA
-constexpr uint32_t kTmemCols = 512;            // S0 [0,128) S1 [128,256) O [256,384)
+constexpr uint32_t kTmemCols = 512;            // score tiles from column 0, O behind them
 
 struct __align__(1024) Smem {
   uint8_t q[kQBytes];
   uint8_t k[kStages][kKBytes];
   uint8_t v[kKBytes];
   uint8_t p[kPBytes];
-  uint64_t q_full, k_full[kStages], k_empty[kStages], v_full, v_empty, s_full[2], s_empty[2], p_full,
+  uint64_t q_full, k_full[kStages], k_empty[kStages], v_full, v_empty, s_full[3], s_empty[2], p_full,
       p_empty, o_full;
   uint32_t tmem_base;
   int abort_flag;
@@ -138,10 +138,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     }
     mbar_init(&s.v_full, 1);
     mbar_init(&s.v_empty, 1);
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&s.s_full[i], 1);
-      mbar_init(&s.s_empty[i], 4);
-    }
+    for (int i = 0; i < 3; ++i) mbar_init(&s.s_full[i], 1);
+    for (int i = 0; i < 2; ++i) mbar_init(&s.s_empty[i], 4);
     mbar_init(&s.p_full, 4);
     mbar_init(&s.p_empty, 1);
     mbar_init(&s.o_full, 1);
@@ -157,6 +155,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   tc_fence_after_sync();
   const uint32_t tmem = s.tmem_base;
   volatile int* abort_flag = &s.abort_flag;
+  // Up to three key tiles (segments of up to 384 tokens): all score tiles stay in tensor memory
+  // (columns 0-383, O in 384-511), so the second pass reads them again instead of forming them
+  // again and the keys are loaded once. Longer walks alternate two score accumulators and form
+  // every tile twice (O in columns 256-383).
+  const bool resident = n_kv <= 3;
+  const uint32_t o_col = resident ? 3 * kBKV : 2 * kBKV;
 
   if (warp == 4) {
     // ---------------------------------------------------------------- Q and the key tiles
@@ -166,7 +170,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       mbar_expect_tx(&s.q_full, kQBytes);
       tma_load_2d(s.q, &map_q, h * kD, q0, &s.q_full);
       tma_load_2d(s.q + kQBox, &map_q, h * kD + 64, q0, &s.q_full);
-      for (int g = 0; g < 2 * n_kv; ++g) {
+      for (int g = 0; g < (resident ? n_kv : 2 * n_kv); ++g) {
         const int st = g % kStages;
         if (g >= kStages &&
             !mbar_wait(&s.k_empty[st], ((g / kStages) & 1) ^ 1, abort_flag, a.status, 41))
@@ -196,45 +200,73 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       constexpr uint32_t idesc_o = make_idesc_f16(kBQ, kD, kFmtF16, kFmtF16, false, true);
       const uint64_t dq = make_smem_desc(smem_u32(s.q), 16, 1024);
       bool ok = mbar_wait(&s.q_full, 0, abort_flag, a.status, 43);
-      // S_g = Q K_g^T into accumulator g & 1: 8 steps of 16 along the head dimension
-      auto issue_s = [&](int g) -> bool {
-        const int st = g % kStages, sb = g & 1;
-        if (!mbar_wait(&s.k_full[st], (g / kStages) & 1, abort_flag, a.status, 44)) return false;
-        if (g >= 2 && !mbar_wait(&s.s_empty[sb], ((g >> 1) & 1) ^ 1, abort_flag, a.status, 45))
-          return false;
-        tc_fence_after_sync();
+      const uint64_t dp = make_smem_desc(smem_u32(s.p), 16, 1024);
+      const uint64_t dv = make_smem_desc(smem_u32(s.v), kKVBox, 1024);   // MN-major: boxes kKVBox apart
+      // S = Q K^T of the key tile in stage `st` into the accumulator at column `col`: 8 steps of
+      // 16 along the head dimension
+      auto mma_s = [&](int st, uint32_t col) {
         const uint64_t dk = make_smem_desc(smem_u32(s.k[st]), 16, 1024);
 #pragma unroll
         for (int k8 = 0; k8 < kD / 16; ++k8) {
           const uint32_t qa = (uint32_t)(k8 >> 2) * (kQBox >> 4) + (uint32_t)(k8 & 3) * 2;
           const uint32_t kb = (uint32_t)(k8 >> 2) * (kKVBox >> 4) + (uint32_t)(k8 & 3) * 2;
-          mma_f16_ss(tmem + sb * kBKV, dq + qa, dk + kb, idesc_s, k8 != 0);
+          mma_f16_ss(tmem + col, dq + qa, dk + kb, idesc_s, k8 != 0);
         }
+      };
+      // O (+)= P V along the key rows of the tile: P K-major, V MN-major
+      auto mma_pv = [&](int t) {
+#pragma unroll
+        for (int k8 = 0; k8 < kBKV / 16; ++k8) {
+          const uint32_t pa = (uint32_t)(k8 >> 2) * (kQBox >> 4) + (uint32_t)(k8 & 3) * 2;
+          mma_f16_ss(tmem + o_col, dp + pa, dv + k8 * (2048 >> 4), idesc_o, (t | k8) != 0);
+        }
+      };
+      auto issue_s = [&](int g) -> bool {   // the two-accumulator walk: tile g into accumulator g & 1
+        const int st = g % kStages, sb = g & 1;
+        if (!mbar_wait(&s.k_full[st], (g / kStages) & 1, abort_flag, a.status, 44)) return false;
+        if (g >= 2 && !mbar_wait(&s.s_empty[sb], ((g >> 1) & 1) ^ 1, abort_flag, a.status, 45))
+          return false;
+        tc_fence_after_sync();
+        mma_s(st, sb * kBKV);
         tc_commit(&s.s_full[sb]);
         return true;
       };
-      for (int g = 0; g < n_kv && ok; ++g) {   // pass 1: scores only
-        ok = issue_s(g);
-        if (ok) tc_commit(&s.k_empty[g % kStages]);
-      }
-      if (ok) ok = issue_s(n_kv);
-      const uint64_t dp = make_smem_desc(smem_u32(s.p), 16, 1024);
-      const uint64_t dv = make_smem_desc(smem_u32(s.v), kKVBox, 1024);   // MN-major: boxes kKVBox apart
-      for (int t = 0; t < n_kv && ok; ++t) {   // pass 2: scores of the next tile, then O += P V
-        const int g = n_kv + t;
-        if (t + 1 < n_kv) ok = issue_s(g + 1);
-        if (ok) ok = mbar_wait(&s.v_full, t & 1, abort_flag, a.status, 46);
-        if (ok) ok = mbar_wait(&s.p_full, t & 1, abort_flag, a.status, 47);
-        if (!ok) break;
-        tc_fence_after_sync();
-#pragma unroll
-        for (int k8 = 0; k8 < kBKV / 16; ++k8) {   // along the key rows: P K-major, V MN-major
-          const uint32_t pa = (uint32_t)(k8 >> 2) * (kQBox >> 4) + (uint32_t)(k8 & 3) * 2;
-          mma_f16_ss(tmem + 2 * kBKV, dp + pa, dv + k8 * (2048 >> 4), idesc_o, (t | k8) != 0);
+      if (resident) {
+        for (int t = 0; t < n_kv && ok; ++t) {
+          ok = mbar_wait(&s.k_full[t % kStages], (t / kStages) & 1, abort_flag, a.status, 44);
+          if (!ok) break;
+          tc_fence_after_sync();
+          mma_s(t % kStages, t * kBKV);
+          tc_commit(&s.s_full[t]);
+          tc_commit(&s.k_empty[t % kStages]);
         }
-        tc_commit(&s.k_empty[g % kStages]);
-        tc_commit(&s.v_empty);
-        tc_commit(&s.p_empty);
+        for (int t = 0; t < n_kv && ok; ++t) {
+          ok = mbar_wait(&s.v_full, t & 1, abort_flag, a.status, 46);
+          if (ok) ok = mbar_wait(&s.p_full, t & 1, abort_flag, a.status, 47);
+          if (!ok) break;
+          tc_fence_after_sync();
+          mma_pv(t);
+          tc_commit(&s.v_empty);
+          tc_commit(&s.p_empty);
+        }
+      } else {
+        for (int g = 0; g < n_kv && ok; ++g) {   // pass 1: scores only
+          ok = issue_s(g);
+          if (ok) tc_commit(&s.k_empty[g % kStages]);
+        }
+        if (ok) ok = issue_s(n_kv);
+        for (int t = 0; t < n_kv && ok; ++t) {   // pass 2: scores of the next tile, then O += P V
+          const int g = n_kv + t;
+          if (t + 1 < n_kv) ok = issue_s(g + 1);
+          if (ok) ok = mbar_wait(&s.v_full, t & 1, abort_flag, a.status, 46);
+          if (ok) ok = mbar_wait(&s.p_full, t & 1, abort_flag, a.status, 47);
+          if (!ok) break;
+          tc_fence_after_sync();
+          mma_pv(t);
+          tc_commit(&s.k_empty[g % kStages]);
+          tc_commit(&s.v_empty);
+          tc_commit(&s.p_empty);
+        }
       }
       if (ok) tc_commit(&s.o_full);
     }
@@ -248,35 +280,30 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     bool ok = true;
     for (int g = 0; g < 2 * n_kv && ok; ++g) {
       const int sb = g & 1;
-      ok = mbar_wait(&s.s_full[sb], (g >> 1) & 1, abort_flag, a.status, 48);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
+      const int tile = g < n_kv ? g : g - n_kv;
+      const uint32_t s_col = resident ? tile * kBKV : sb * kBKV;
+      if (!resident || g < n_kv) {   // resident tiles are complete once pass 1 has seen them
+        ok = resident ? mbar_wait(&s.s_full[tile], 0, abort_flag, a.status, 48)
+                      : mbar_wait(&s.s_full[sb], (g >> 1) & 1, abort_flag, a.status, 48);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+      }
       tc_fence_after_sync();
       const int t = g < n_kv ? g : g - n_kv;
       const int limit = q_idx - (seg_begin + t * kBKV);   // columns 0..limit are visible
-      if (g < n_kv) {   // pass 1: running maximum and sum of exponentials
+      if (g < n_kv) {   // pass 1: the row maximum only
 #pragma unroll 1
         for (int c0 = 0; c0 < kBKV; c0 += 32) {
           uint32_t x[32];
-          tmem_ld_32x32(lane_base + sb * kBKV + c0, x);
+          tmem_ld_32x32(lane_base + s_col + c0, x);
           tmem_ld_wait_on(x);
-          float tile_max = -INFINITY;
 #pragma unroll
           for (int c = 0; c < 32; ++c)
-            if (c0 + c <= limit) tile_max = fmaxf(tile_max, __uint_as_float(x[c]));
-          if (tile_max > -INFINITY) {
-            const float m_new = fmaxf(m, tile_max);
-            float sum = 0.f;
-#pragma unroll
-            for (int c = 0; c < 32; ++c)
-              if (c0 + c <= limit) sum += exp2f((__uint_as_float(x[c]) - m_new) * sl);
-            l = l * exp2f((m - m_new) * sl) + sum;   // m = -inf the first time: exp2(-inf) = 0
-            m = m_new;
-          }
+            if (c0 + c <= limit) m = fmaxf(m, __uint_as_float(x[c]));
         }
         tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&s.s_empty[sb]);
+        if (lane == 0 && !resident) mbar_arrive(&s.s_empty[sb]);
       } else {          // pass 2: P = exp(S - max) as the fp16 A operand of O += P V
         if (t > 0) {
           ok = mbar_wait(&s.p_empty, (t - 1) & 1, abort_flag, a.status, 49);
@@ -286,12 +313,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 #pragma unroll 1
         for (int c0 = 0; c0 < kBKV; c0 += 32) {
           uint32_t x[32], packed[16];
-          tmem_ld_32x32(lane_base + sb * kBKV + c0, x);
+          tmem_ld_32x32(lane_base + s_col + c0, x);
           tmem_ld_wait_on(x);
 #pragma unroll
           for (int c = 0; c < 32; c += 2) {
             const float p0 = c0 + c <= limit ? exp2f((__uint_as_float(x[c]) - m) * sl) : 0.f;
             const float p1 = c0 + c + 1 <= limit ? exp2f((__uint_as_float(x[c + 1]) - m) * sl) : 0.f;
+            l += p0 + p1;       // the sum of exponentials, from the values before rounding
             __half2 hh = __floats2half2_rn(p0, p1);
             packed[c >> 1] = *reinterpret_cast<uint32_t*>(&hh);
           }
@@ -301,7 +329,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
-          mbar_arrive(&s.s_empty[sb]);
+          if (!resident) mbar_arrive(&s.s_empty[sb]);
           mbar_arrive(&s.p_full);
         }
       }
@@ -318,7 +346,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 #pragma unroll
       for (int c0 = 0; c0 < kD; c0 += 32) {
         uint32_t o[32];
-        tmem_ld_32x32(lane_base + 2 * kBKV + c0, o);
+        tmem_ld_32x32(lane_base + o_col + c0, o);
         tmem_ld_wait_on(o);
         if (valid) {
 #pragma unroll
