@@ -41,6 +41,8 @@ SIGNATURES = {
     "soup_silu_mul_bwd": [_P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _P],
     "soup_dropout_pack": [_P, _P, _P, _P, _L, _F, _I, _P],
     "soup_dropout_unpack": [_P, _P, _P, _P, _P, _L, _F, _I, _P],
+    "soup_dropout_pack2": [_P] * 7 + [_L, _F, _F, _I, _P],
+    "soup_dropout_unpack2": [_P] * 8 + [_L, _F, _F, _P],
     "soup_lmhead_workspace_bytes": [_L, _L, _L, _L],
     "soup_lmhead_ce": [_P] * 13 + [_L] * 6 + [_I, _P],
     "soup_lmhead_set_timing": [_P],

@@ -141,12 +141,25 @@ class AdapterCasts:
     def __init__(self):
         self.modules, self.where = [], {}
         self.a16, self.b16 = [], []
+        self.pairs, self.stacked = {}, {}
         self.armed = False
 
     def add(self, module):
         if id(module) not in self.where:
             self.where[id(module)] = len(self.modules)
             self.modules.append(module)
+
+    def add_pair(self, first, second):
+        """The two adapters of a block whose A weights have one shape: their fp16 copies are the
+        two halves of one [2, r, in] tensor (`pair_of`), ready for a batched product."""
+        self.add(first)
+        self.add(second)
+        if first.lora_A.weight.shape == second.lora_A.weight.shape:
+            self.pairs[id(first)] = (self.where[id(first)], self.where[id(second)])
+
+    def pair_of(self, first):
+        at = self.pairs.get(id(first))
+        return None if at is None or not self.stacked else self.stacked.get(at)
 
     def of(self, module):
         i = self.where[id(module)]
@@ -164,6 +177,11 @@ class AdapterCasts:
                                             for c, w in zip(self.a16 + self.b16, a32 + b32)):
             self.a16 = [torch.empty(w.shape, dtype=F16, device=w.device) for w in a32]
             self.b16 = [torch.empty(w.shape, dtype=F16, device=w.device) for w in b32]
+            self.stacked = {}
+            for i, j in self.pairs.values():     # the pair's two A copies as halves of one tensor
+                both = torch.empty((2,) + tuple(a32[i].shape), dtype=F16, device=a32[i].device)
+                self.a16[i], self.a16[j] = both[0], both[1]
+                self.stacked[(i, j)] = both
         torch._foreach_copy_(self.a16, a32)
         torch._foreach_copy_(self.b16, torch._foreach_mul(b32, [float(m.scaling) for m in self.modules]))
         self.armed = True
@@ -453,7 +471,15 @@ def fused_block_forward(layer, hidden_states, attention_mask=None, position_ids=
     x16 = fp16_copy_of(x)
     if x16 is None:
         x16 = x.detach().to(F16)
-    branches = [None if a is None else lora_mod.LoRABranch.apply(x, x16, *a) for a in adapters]
+    pair = plan.casts.pair_of(plan.q) if (plan.casts is not None and plan.casts.armed) else None
+    if (pair is not None and adapters[0] is not None and adapters[2] is not None
+            and lora_mod.pair_covers(x, x16, plan.q, plan.v)):
+        (a_q, b_q, p_q, s_q, _, bq16, _), (a_v, b_v, p_v, s_v, _, bv16, _) = adapters[0], adapters[2]
+        out_q, out_v = lora_mod.LoRABranchPair.apply(x, x16, a_q, b_q, a_v, b_v, p_q, p_v, s_q, s_v,
+                                                     pair, bq16, bv16)
+        branches = [out_q, None, out_v]
+    else:
+        branches = [None if a is None else lora_mod.LoRABranch.apply(x, x16, *a) for a in adapters]
     cos, sin = position_embeddings
     cu = kwargs["cu_seq_lens_q"]
     scale = layer.self_attn.scaling
@@ -497,6 +523,8 @@ def install_fused_blocks(model):
             continue
         plan.installed = layer.forward
         plan.casts = casts
+        if plan.q is not _base(plan.q) and plan.v is not _base(plan.v):
+            casts.add_pair(plan.q, plan.v)
         for module in (plan.q, plan.k, plan.v):
             if module is not _base(module):
                 casts.add(module)

@@ -129,6 +129,77 @@ class LoRABranch(torch.autograd.Function):
         return dx, None, grad_a, grad_b, None, None, None, None, None
 
 
+class LoRABranchPair(torch.autograd.Function):
+    """Two LoRA branches on the same x (q_proj's and v_proj's adapters of a block), each with its
+    own dropout draw, as one autograd node: one launch packs both dropped inputs (x read once),
+    the two rank-r products with A are one batched GEMM, and backward unpacks both in one launch
+    that also sums the two input gradients. Per adapter the numbers are LoRABranch's with
+    `b16_scaled`; the dropout draws come in the same order (first adapter, then second).
+
+    `a16_pair` is fp16 [2, r, in] (both A weights), `b16s_first` / `b16s_second` fp16
+    scaling * B. Returns the two branch outputs."""
+
+    @staticmethod
+    def forward(ctx, x, x16, a_first, b_first, a_second, b_second, p_first, p_second,
+                scaling_first, scaling_second, a16_pair, b16s_first, b16s_second):
+        _lib.require_cuda(x, x16, a16_pair)
+        n, hidden = x.numel(), x.shape[-1]
+        rows = n // hidden
+        mask_first = torch.native_dropout(x, p_first, True)[1]
+        mask_second = torch.native_dropout(x, p_second, True)[1]
+        scales = (1.0 / (1.0 - p_first), 1.0 / (1.0 - p_second))
+        x = x.contiguous()
+        xd = torch.empty((2, rows, hidden), dtype=torch.float16, device=x.device)
+        bits = torch.empty((2, n // 8), dtype=torch.uint8, device=x.device)
+        _lib.call("soup_dropout_pack2", _lib.ptr(x), _lib.ptr(mask_first), _lib.ptr(mask_second),
+                  _lib.ptr(xd[0]), _lib.ptr(xd[1]), _lib.ptr(bits[0]), _lib.ptr(bits[1]), n,
+                  scales[0], scales[1], _lib.dtype_code(x.dtype), _lib.stream_of(x))
+        del mask_first, mask_second
+        a = torch.bmm(xd, a16_pair.transpose(1, 2))          # [2, rows, r]
+        out_first = torch.mm(a[0], b16s_first.t())
+        out_second = torch.mm(a[1], b16s_second.t())
+        ctx.save_for_backward(x16, bits, a, a16_pair, b16s_first, b16s_second)
+        ctx.scales, ctx.scalings = scales, (scaling_first, scaling_second)
+        ctx.x_shape, ctx.weight_dtypes = x.shape, (a_first.dtype, b_first.dtype, a_second.dtype, b_second.dtype)
+        ctx.weights = ((a_first, b_first, a_second, b_second) if LoRABranch.accumulate_in_place else None)
+        lead = x.shape[:-1]
+        return out_first.view(*lead, -1), out_second.view(*lead, -1)
+
+    @staticmethod
+    def backward(ctx, grad_first, grad_second):
+        x16, bits, a, a16_pair, b16s_first, b16s_second = ctx.saved_tensors
+        rows, hidden = a.shape[1], x16.shape[-1]
+        grads = [g.to(torch.float16).reshape(rows, -1) for g in (grad_first, grad_second)]
+        b16s = (b16s_first, b16s_second)
+        in_place = ctx.weights is not None and all(ctx.needs_input_grad[2:6])
+        out = [None] * 4                                     # dA1, dB1, dA2, dB2
+        gain = torch.empty((2, rows, a.shape[-1]), dtype=torch.float16, device=a.device)
+        for i in (0, 1):
+            if not (in_place and _add_weight_gradient(ctx.weights[2 * i + 1], grads[i], a[i], ctx.scalings[i])):
+                out[2 * i + 1] = _weight_gradient(grads[i], a[i], ctx.weight_dtypes[2 * i + 1]) * ctx.scalings[i]
+            torch.mm(grads[i], b16s[i], out=gain[i])
+        grad_xd = torch.bmm(gain, a16_pair)                  # [2, rows, hidden]
+        xd = torch.empty((2, rows, hidden), dtype=torch.float16, device=a.device)
+        dx = torch.empty(ctx.x_shape, dtype=torch.float32, device=a.device)
+        _lib.call("soup_dropout_unpack2", _lib.ptr(x16), _lib.ptr(bits[0]), _lib.ptr(bits[1]),
+                  _lib.ptr(grad_xd[0]), _lib.ptr(grad_xd[1]), _lib.ptr(xd[0]), _lib.ptr(xd[1]),
+                  _lib.ptr(dx), rows * hidden, ctx.scales[0], ctx.scales[1], _lib.stream_of(x16))
+        for i in (0, 1):
+            if not (in_place and _add_weight_gradient(ctx.weights[2 * i], gain[i], xd[i], 1.0)):
+                out[2 * i] = _weight_gradient(gain[i], xd[i], ctx.weight_dtypes[2 * i])
+        return (dx, None, out[0], out[1], out[2], out[3]) + (None,) * 7
+
+
+def pair_covers(x, x16, first, second):
+    """Whether LoRABranchPair takes these two adapter modules (LoRALinear-like: lora_A, lora_B, p,
+    scaling) on this x: what LoRABranch needs, the same rank and input width, whole 16-element
+    groups and an fp16 copy of x that is contiguous."""
+    return (x.dtype == torch.float32 and x.numel() % 16 == 0 and x16 is not None
+            and x16.dtype == torch.float16 and x16.is_contiguous()
+            and first.lora_A.weight.shape == second.lora_A.weight.shape
+            and 0.0 < first.p < 1.0 and 0.0 < second.p < 1.0)
+
+
 class _SharedCopy:
     """The fp16 copy of the tensor the adapter layers of a block all see (q_proj and v_proj get the
     same hidden states): made once, found again by identity, version and storage of the source."""

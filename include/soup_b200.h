@@ -238,6 +238,18 @@ int soup_dropout_pack(const void* x, const uint8_t* mask, void* xd, uint8_t* bit
 int soup_dropout_unpack(const void* x16, const uint8_t* bits, const void* g16, void* xd, void* dx,
                         int64_t n, float scale, int dx_dtype, void* stream);
 
+/* The two adapters of a block (same x, two masks) in one launch each: soup_dropout_pack and
+ * soup_dropout_unpack for both, x read once, and the two input gradients summed:
+ * dx = keep_a*g_a*scale_a + keep_b*g_b*scale_b (fp32). n a multiple of 16; 16-byte aligned
+ * pointers. Per adapter the values and bits are those of the single entries (which replace the
+ * launches of solution/lora.py:64-65 and :73-74). */
+int soup_dropout_pack2(const void* x, const uint8_t* mask_a, const uint8_t* mask_b, void* xd_a,
+                       void* xd_b, uint8_t* bits_a, uint8_t* bits_b, int64_t n, float scale_a,
+                       float scale_b, int x_dtype, void* stream);
+int soup_dropout_unpack2(const void* x16, const uint8_t* bits_a, const uint8_t* bits_b,
+                         const void* g_a, const void* g_b, void* xd_a, void* xd_b, float* dx,
+                         int64_t n, float scale_a, float scale_b, void* stream);
+
 /* ---- linear layers on NF4 weights: tcgen05 GEMM with the dequantisation in its operand prologue --
  * One weight of a launch. `packed`, `absmax`, `code2`, `absmax2`, `offset` as in soup_nf4_dequant
  * (blocksize 64 only: one block is one 128-byte row of the operand tile). Forward reads `bias`

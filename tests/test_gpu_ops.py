@@ -476,6 +476,38 @@ def test_lora_branch_with_cast_scaled_weights_and_in_place_gradients(scaling, mo
         assert rel_norm(fast.float().cpu(), plain.float().cpu()) < 2e-3, name
 
 
+def test_paired_lora_branches_are_the_two_single_branches():
+    """LoRABranchPair (one packing launch, one batched product with A, one unpacking launch that
+    sums the input gradients) against two LoRABranch calls with the same dropout draws: outputs
+    and weight gradients per adapter and the summed input gradient, bit for bit."""
+    from claudemaxing_b200.lora import LoRABranch, LoRABranchPair
+
+    torch.manual_seed(0)
+    x = torch.randn(1, 80, 256, device=DEV)
+    weights = [(torch.randn(16, 256, device=DEV) * 0.1).requires_grad_(),
+               (torch.randn(96, 16, device=DEV) * 0.1).requires_grad_(),
+               (torch.randn(16, 256, device=DEV) * 0.1).requires_grad_(),
+               (torch.randn(32, 16, device=DEV) * 0.1).requires_grad_()]
+    g1, g2 = torch.randn(1, 80, 96, device=DEV).half(), torch.randn(1, 80, 32, device=DEV).half()
+    a16 = torch.stack([weights[0].detach().half(), weights[2].detach().half()])
+    b1, b2 = (weights[1].detach() * 2.0).half(), (weights[3].detach() * 2.0).half()
+    results = []
+    for paired in (False, True):
+        xx = x.clone().requires_grad_()
+        for w in weights:
+            w.grad = None
+        torch.manual_seed(5)
+        if paired:
+            o1, o2 = LoRABranchPair.apply(xx, xx.detach().half(), *weights, 0.1, 0.1, 2.0, 2.0, a16, b1, b2)
+        else:
+            o1 = LoRABranch.apply(xx, xx.detach().half(), weights[0], weights[1], 0.1, 2.0, a16[0], b1, True)
+            o2 = LoRABranch.apply(xx, xx.detach().half(), weights[2], weights[3], 0.1, 2.0, a16[1], b2, True)
+        torch.autograd.backward((o1, o2), (g1, g2))
+        results.append([o1.detach(), o2.detach(), xx.grad] + [w.grad.clone() for w in weights])
+    for name, single, pair in zip(("out1", "out2", "dx", "dA1", "dB1", "dA2", "dB2"), *results):
+        assert torch.equal(single, pair), name
+
+
 def test_ops_refuse_cpu_tensors():
     from claudemaxing_b200.rmsnorm import rmsnorm
     from claudemaxing_b200.swiglu_recompute import swiglu_recompute
