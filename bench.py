@@ -362,6 +362,14 @@ def kernel_suite(dev, hbm_peak, n_rows=2048, tag="", with_nf4=True):
                   _lib.F32, code_f16, _lib.F32, _lib.F32, 1, torch.cuda.current_stream().cuda_stream)
 
     record("rmsnorm_bwd_from_f16_copy", time_rotating(rms_bwd_b, nB), 10 * n_rows * H + 4 * n_rows)
+    d16 = torch.empty(n_rows, H, device=dev, dtype=f16)
+
+    def rms_bwd_res(i):  # the same with the residual gradient added and the fp16 copy of the sum written
+        _lib.call("soup_rmsnorm_bwd_residual", xb[i].data_ptr(), lb[i].data_ptr(), wb.data_ptr(),
+                  rstd.data_ptr(), xb[(i + 1) % nB].data_ptr(), ob[i].data_ptr(), d16.data_ptr(),
+                  slots.data_ptr(), small.data_ptr(), 15, n_rows, H, torch.cuda.current_stream().cuda_stream)
+
+    record("rmsnorm_bwd_residual_from_f16_copy", time_rotating(rms_bwd_res, nB), 16 * n_rows * H + 4 * n_rows)
     del xb, ob, lb
 
     # RoPE: packed row [1, n_rows], 12 q heads / 2 kv heads, head_dim 128
@@ -388,6 +396,23 @@ def kernel_suite(dev, hbm_peak, n_rows=2048, tag="", with_nf4=True):
 
     record("rope_fwd_q_and_k", time_rotating(lambda i: rope_call(i, False), nR), rope_bytes)
     record("rope_bwd_q_and_k", time_rotating(lambda i: rope_call(i, True), nR), rope_bytes)
+    cos32, sin32 = cos.float(), sin.float()
+    term = torch.randn(n_rows, 12 * 128, device=dev, dtype=f16).view(1, n_rows, 12, 128).transpose(1, 2)
+    qt = [torch.empty(n_rows, 12, 128, device=dev, dtype=f16) for _ in range(nR)]
+    kt = [torch.empty(n_rows, 2, 128, device=dev, dtype=f16) for _ in range(nR)]
+
+    def rope_sum_call(i):   # the fused block's form: q + adapter term, fp32 tables, token-major fp16 out
+        q, k = qs[i], ks[i]
+        qv, kv = qt[i].unsqueeze(0).transpose(1, 2), kt[i].unsqueeze(0).transpose(1, 2)
+        _lib.call("soup_rope_sum", q.data_ptr(), term.data_ptr(), k.data_ptr(), cos32.data_ptr(),
+                  sin32.data_ptr(), qt[i].data_ptr(), kt[i].data_ptr(), 1, 12, 2, n_rows, 128,
+                  *q.stride()[:3], *k.stride()[:3], 0, cos32.stride(1), *term.stride()[:3],
+                  *qv.stride()[:3], *kv.stride()[:3], _lib.F16, _lib.F16, _lib.F16, _lib.F32, _lib.F16,
+                  _lib.F16, 0, torch.cuda.current_stream().cuda_stream)
+
+    record("rope_sum_fwd_q_plus_term_and_k", time_rotating(rope_sum_call, nR),
+           rope_bytes + 12 * n_rows * 128 * 2 + 2 * n_rows * 128 * 2)
+    del term, qt, kt
     del qo, ko
     del qs, ks
 
@@ -423,7 +448,25 @@ def kernel_suite(dev, hbm_peak, n_rows=2048, tag="", with_nf4=True):
 
     record("dropout_pack", time_rotating(pack, nD), n_rows * H * (4 + 1 + 2) + n_rows * H // 8)
     record("dropout_unpack", time_rotating(unpack, nD), n_rows * H * (2 + 2 + 2 + 4) + n_rows * H // 8)
-    del xs, ms_, packed_out, x16, dxs, xd2
+    xd_pair = torch.empty(2, n_rows, H, device=dev, dtype=f16)
+    bits_pair = torch.empty(2, n_rows * H // 8, device=dev, dtype=torch.uint8)
+
+    def pack2(i):
+        _lib.call("soup_dropout_pack2", xs[i].data_ptr(), ms_[i].data_ptr(), ms_[(i + 1) % nD].data_ptr(),
+                  xd_pair[0].data_ptr(), xd_pair[1].data_ptr(), bits_pair[0].data_ptr(),
+                  bits_pair[1].data_ptr(), n_rows * H, 1 / 0.95, 1 / 0.95, _lib.F32, cur())
+
+    def unpack2(i):
+        _lib.call("soup_dropout_unpack2", x16[i].data_ptr(), bits_pair[0].data_ptr(), bits_pair[1].data_ptr(),
+                  packed_out[i][0].data_ptr(), packed_out[(i + 1) % nD][0].data_ptr(),
+                  xd_pair[0].data_ptr(), xd_pair[1].data_ptr(), dxs[i].data_ptr(), n_rows * H,
+                  1 / 0.95, 1 / 0.95, cur())
+
+    record("dropout_pack_two_adapters", time_rotating(pack2, nD),
+           n_rows * H * (4 + 2 * 1 + 2 * 2) + 2 * n_rows * H // 8)
+    record("dropout_unpack_two_adapters", time_rotating(unpack2, nD),
+           n_rows * H * (2 + 2 * 2 + 2 * 2 + 4) + 2 * n_rows * H // 8)
+    del xs, ms_, packed_out, x16, dxs, xd2, xd_pair, bits_pair
 
     if n_rows <= 4096:
         # metrics from logits that exist anyway (the route for steps that end up building them):
