@@ -12,11 +12,17 @@ module computes the same block with those passes folded into the kernels next to
   output to q in fp32, rotates q and k and writes them as fp16 [tokens, heads, head_dim], which
   are exactly the values the reference chain reaches (fp32 sum, fp32 rotation, one rounding to
   fp16 at the attention's cast); v + adapter is one fp16 add (fp32 inside, one rounding);
-* attention is causal attention inside the segments of the packed row (attention.py);
+* attention is causal attention inside the segments of the packed row (attention.py; for heads
+  of 128 this library's kernels, called from the same autograd node as the projection);
+* the block's two adapters are one node (lora.LoRABranchPair: both packed and unpacked by one
+  launch each, one batched product with A), their weights cast once per decoder forward;
 * o_proj and down_proj add the fp32 residual in the GEMM's epilogue and write fp32;
 * backward rotates dq and dk straight into column blocks of one [tokens, q+k+v] fp16 buffer and
   forms the input gradient of the three projections in one GEMM with fp32 output; the MLP's two
-  input gradients accumulate in one fp32 output as well.
+  input gradients accumulate in one fp32 output as well;
+* each norm and the residual connection that leaves the same tensor are one node (`_NormResidual`):
+  its backward kernel adds the residual gradient and writes the fp16 copy the projection backward
+  one block earlier wants.
 
 Where a GEMM now writes its fp32 accumulator (+ residual) instead of rounding the product to fp16
 first, results differ from the per-op chain by that rounding, within the tolerance the reference's
