@@ -115,21 +115,26 @@ __global__ void __launch_bounds__(kThreads) rope_vec_kernel(RopeArgs a) {
 // registers. Lanes walk the (head, 16-byte chunk) pairs of the position; stores go straight to
 // the [b, h, t, d] outputs, 128 contiguous bytes per quarter warp.
 // DT: the one dtype code of q, k, cos, sin and both outputs when they all agree (the hot cases:
-// all fp16, all bf16, all fp32), or -1 to read the codes from the arguments.
+// all fp16, all bf16, all fp32), -2 for fp16 rows with fp32 tables, or -1 to read the codes from
+// the arguments.
 template <int XB, int DT>
 __global__ void __launch_bounds__(rowpipe::kMaxWarps * 32, 2)
 rope_pipe_kernel(RopeArgs a, int stages, int* status) {
   constexpr int EPV = 4;   // elements per lane and half: 8- or 16-byte vectors, 16 cos/sin registers
-  const int xdt_q = DT >= 0 ? DT : a.xdt[0], xdt_k = DT >= 0 ? DT : a.xdt[1];
-  const int odt_q = DT >= 0 ? DT : a.odt[0], odt_k = DT >= 0 ? DT : a.odt[1];
-  const int csdt = DT >= 0 ? DT : a.csdt;
+  // DT == -2: fp16 rows (q, k, q's second term, both outputs) with fp32 tables, the fused block's case
+  constexpr bool kHalfRows = DT == -2;
+  const int xdt_q = DT >= 0 ? DT : kHalfRows ? SOUP_F16 : a.xdt[0];
+  const int xdt_k = DT >= 0 ? DT : kHalfRows ? SOUP_F16 : a.xdt[1];
+  const int odt_q = DT >= 0 ? DT : kHalfRows ? SOUP_F16 : a.odt[0];
+  const int odt_k = DT >= 0 ? DT : kHalfRows ? SOUP_F16 : a.odt[1];
+  const int csdt = DT >= 0 ? DT : kHalfRows ? SOUP_F32 : a.csdt;
   extern __shared__ __align__(128) char smem[];
   __shared__ int s_abort;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
   const int half = a.d >> 1, chunks = half / EPV;   // chunks divides 32 (checked by the host)
   const uint32_t q_bytes = (uint32_t)(a.heads[0] * a.d) * XB, k_bytes = (uint32_t)(a.heads[1] * a.d) * XB;
   const uint32_t add_bytes = a.add ? q_bytes : 0;   // the addend has q's element size (host check)
-  const int adt = DT >= 0 ? DT : a.adt;
+  const int adt = DT >= 0 ? DT : kHalfRows ? SOUP_F16 : a.adt;
   if (threadIdx.x == 0) s_abort = 0;
   rowpipe::Ring ring;
   ring.init(smem, q_bytes + k_bytes + add_bytes, stages, warp, lane);
@@ -320,7 +325,12 @@ extern "C" int soup_rope_sum(const void* q, const void* q_add, const void* k, co
     cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plan.smem);    \
     kernel<<<plan.grid, plan.warps * 32, plan.smem, s>>>(a, plan.stages, status);                 \
   } while (0)
+    const bool half_rows = cs_dtype == SOUP_F32 &&
+                           (!hq || (q_dtype == SOUP_F16 && q_out_dtype == SOUP_F16)) &&
+                           (!hk || (k_dtype == SOUP_F16 && k_out_dtype == SOUP_F16)) &&
+                           (!q_add || q_add_dtype == SOUP_F16);
     if (same && dt0 == SOUP_F16) SOUP_ROPE_P(2, SOUP_F16);
+    else if (half_rows) SOUP_ROPE_P(2, -2);
     else if (same && dt0 == SOUP_BF16) SOUP_ROPE_P(2, SOUP_BF16);
     else if (same && dt0 == SOUP_F32) SOUP_ROPE_P(4, SOUP_F32);
     else if (xb == 4) SOUP_ROPE_P(4, -1);
