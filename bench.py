@@ -979,8 +979,9 @@ def main():
         print(json.dumps({"kernels": attention_suite(dev, peaks()[0]["bf16_tflops"])}), flush=True)
         return
     if world > 1:
-        # stdout carries one JSON line: keep NCCL's version banner (NCCL_DEBUG=VERSION) off it
-        if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
+        # stdout carries one JSON line: keep NCCL's version banner (NCCL_DEBUG=VERSION, from the
+        # environment or from a system-wide nccl.conf, which the environment overrides) off it
+        if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
             os.environ["NCCL_DEBUG"] = "WARN"
         dist.init_process_group("nccl", device_id=dev)
     peak, peak_source = peaks()

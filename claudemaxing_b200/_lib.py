@@ -50,6 +50,7 @@ SIGNATURES = {
     "soup_lmhead_status": [_P, _L, _L, _L, _P, _P],
     "soup_lmhead_merge": [_P] * 15 + [_L, _I, _P],
     "soup_lmhead_finish": [_P] * 12 + [_L] * 4 + [_P],
+    "soup_lmhead_finish_to": [_P] * 13 + [_I] + [_L] * 4 + [_P],
     "soup_lmhead_grad_scale": [_P, _P, _P, _L, _I, _P],
     "soup_xent_rows": [_P] * 5 + [_L, _L, _L, _I, _P],
     "soup_nf4_gemm_workspace_bytes": [_L, _L],

@@ -973,6 +973,8 @@ struct FinishArgs {
   int* correct;
   float* dh;                // nullable
   int n_rows, k_dim, v_shard, col_offset;
+  void* dh_out;             // nullable: the finished gradient goes here (dh_out_dtype), dh stays as it is
+  int dh_out_dtype;
 };
 
 __global__ void __launch_bounds__(256) lmhead_finish_kernel(const FinishArgs a) {
@@ -997,7 +999,8 @@ __global__ void __launch_bounds__(256) lmhead_finish_kernel(const FinishArgs a) 
   for (int c = threadIdx.x; c < a.k_dim; c += blockDim.x) {
     float v = labelled ? dh_row[c] * scale : 0.f;
     if (mine) v = fmaf(__half2float(w_row[c]), label_term, v);
-    dh_row[c] = v;
+    if (a.dh_out) store1(a.dh_out, (int64_t)row * a.k_dim + c, a.dh_out_dtype, v);
+    else dh_row[c] = v;
   }
 }
 
@@ -1410,11 +1413,12 @@ extern "C" int soup_lmhead_merge(const float* g_max, const float* g_sum, const f
   return SOUP_OK;
 }
 
-extern "C" int soup_lmhead_finish(const float* run_max, const float* run_sum, const float* run_dot,
-                                  const int* best, const float* label_logit, const float* grad_ref,
-                                  const int64_t* target, const void* weight, float* token_loss,
-                                  float* entropy, int* correct, float* dh, int64_t n, int64_t h,
-                                  int64_t v_shard, int64_t col_offset, void* stream) {
+extern "C" int soup_lmhead_finish_to(const float* run_max, const float* run_sum, const float* run_dot,
+                                     const int* best, const float* label_logit, const float* grad_ref,
+                                     const int64_t* target, const void* weight, float* token_loss,
+                                     float* entropy, int* correct, float* dh, void* dh_out,
+                                     int dh_out_dtype, int64_t n, int64_t h, int64_t v_shard,
+                                     int64_t col_offset, void* stream) {
   using namespace soup;
   if (n == 0) return SOUP_OK;
   if (n < 0 || h <= 0) SOUP_FAIL(SOUP_ERR_ARG, "lmhead_finish: bad shape");
@@ -1423,16 +1427,29 @@ extern "C" int soup_lmhead_finish(const float* run_max, const float* run_sum, co
   if (dh && (!weight || !grad_ref))
     SOUP_FAIL(SOUP_ERR_ARG, "lmhead_finish: dH needs the weight shard and grad_ref");
   if (token_loss && (!entropy || !correct)) SOUP_FAIL(SOUP_ERR_ARG, "lmhead_finish: null output");
+  if (dh_out && (!dh || !is_float_dtype(dh_out_dtype)))
+    SOUP_FAIL(SOUP_ERR_ARG, "lmhead_finish: a separate output needs dh and a floating dtype");
   FinishArgs a;
   a.run_max = run_max; a.run_sum = run_sum; a.run_dot = run_dot; a.best = best;
   a.label_logit = label_logit; a.grad_ref = grad_ref;
   a.target = target; a.weight = reinterpret_cast<const __half*>(weight);
   a.token_loss = token_loss; a.entropy = entropy; a.correct = correct; a.dh = dh;
+  a.dh_out = dh_out; a.dh_out_dtype = dh_out_dtype;
   a.n_rows = (int)n; a.k_dim = (int)h; a.v_shard = (int)v_shard; a.col_offset = (int)col_offset;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   lmhead_finish_kernel<<<(unsigned)n, 256, 0, s>>>(a);
   SOUP_CHECK_LAUNCH("lmhead_finish");
   return SOUP_OK;
+}
+
+extern "C" int soup_lmhead_finish(const float* run_max, const float* run_sum, const float* run_dot,
+                                  const int* best, const float* label_logit, const float* grad_ref,
+                                  const int64_t* target, const void* weight, float* token_loss,
+                                  float* entropy, int* correct, float* dh, int64_t n, int64_t h,
+                                  int64_t v_shard, int64_t col_offset, void* stream) {
+  return soup_lmhead_finish_to(run_max, run_sum, run_dot, best, label_logit, grad_ref, target, weight,
+                               token_loss, entropy, correct, dh, nullptr, SOUP_F32, n, h, v_shard,
+                               col_offset, stream);
 }
 
 extern "C" int soup_lmhead_grad_scale(const float* dh, void* out, const float* scale, int64_t n,

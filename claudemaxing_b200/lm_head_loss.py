@@ -152,11 +152,13 @@ def head_partial(h16, w16, target, col_offset=0, chunk_cols=None, want_grad=True
 
 
 def head_finish(state, target, w16, grad_raw=None, col_offset=0, grad_ref=None,
-                want_metrics=True):
+                want_metrics=True, grad_out=None):
     """Turns a (merged) state into token_loss / entropy / correct and completes `grad_raw` in
     place: GRAD_SCALE * (exp(grad_ref - lse) * grad_raw + (p_label - 1) * W[label]), the label
     term where the label falls in `w16`'s range. `grad_ref` is the array of the state that
-    `head_partial` returned together with `grad_raw` (default: `state.grad_ref`)."""
+    `head_partial` returned together with `grad_raw` (default: `state.grad_ref`). With `grad_out`
+    (same shape, any floating dtype) the completed gradient is written there, rounded once, and
+    `grad_raw` is left as it was."""
     n = target.numel()
     dev = target.device
     token_loss = entropy = correct = None
@@ -166,7 +168,14 @@ def head_finish(state, target, w16, grad_raw=None, col_offset=0, grad_ref=None,
         correct = torch.empty(n, dtype=torch.int32, device=dev)
     if grad_ref is None:
         grad_ref = state.grad_ref
-    if n:
+    if n and grad_out is not None:
+        _lib.call("soup_lmhead_finish_to", _lib.ptr(state.run_max), _lib.ptr(state.run_sum),
+                  _lib.ptr(state.run_dot), _lib.ptr(state.best), _lib.ptr(state.label_logit),
+                  _lib.ptr(grad_ref), _lib.ptr(target), _lib.ptr(w16), _lib.ptr(token_loss),
+                  _lib.ptr(entropy), _lib.ptr(correct), _lib.ptr(grad_raw), _lib.ptr(grad_out),
+                  _lib.dtype_code(grad_out.dtype), n, w16.shape[1], w16.shape[0], int(col_offset),
+                  _lib.stream_of(target))
+    elif n:
         _lib.call("soup_lmhead_finish", _lib.ptr(state.run_max), _lib.ptr(state.run_sum),
                   _lib.ptr(state.run_dot), _lib.ptr(state.best), _lib.ptr(state.label_logit),
                   _lib.ptr(grad_ref), _lib.ptr(target), _lib.ptr(w16), _lib.ptr(token_loss),

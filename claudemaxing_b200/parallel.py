@@ -264,14 +264,18 @@ def vocab_parallel_head_rows(h_local, target_local, w_shard, bounds, group=None,
         gathered = torch.empty((world * mine.shape[0], mine.shape[1]), dtype=mine.dtype, device=dev)
         dist.all_gather_into_tensor(gathered, mine, group=group)
         merged, _ = merge_states(gathered.view(world, *mine.shape), tg, bounds)
-        tl, en, co = head_finish(merged, tg, w_shard, grad_raw, bounds[rank], grad_ref=state.grad_ref)
+        low = (torch.empty(grad_raw.shape, dtype=grad_dtype, device=dev)
+               if want_grad and grad_dtype != torch.float32 else None)
+        tl, en, co = head_finish(merged, tg, w_shard, grad_raw, bounds[rank], grad_ref=state.grad_ref,
+                                 grad_out=low)   # the gradient leaves rounded to `grad_dtype`, in one pass
         own = slice(rank * rows, (rank + 1) * rows)
         token_loss[a:z], entropy[a:z], correct[a:z] = tl[own], en[own], co[own]
         loss_sum += tl.sum()
         labelled += tg.ne(-100).sum()
         hits += co.sum()
         if want_grad:
-            low = _rounded(grad_raw, grad_dtype)
+            if low is None:
+                low = grad_raw if grad_raw.dtype == grad_dtype else _rounded(grad_raw, grad_dtype)
             pending.append(dist.reduce_scatter_tensor(grad[a:z], low, group=group, async_op=True))
             keep.append(low)
     for work in pending:

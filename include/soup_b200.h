@@ -360,6 +360,16 @@ int soup_lmhead_finish(const float* run_max, const float* run_sum, const float* 
                        float* entropy, int* correct, float* dh, int64_t n, int64_t h,
                        int64_t v_shard, int64_t col_offset, void* stream);
 
+/* The same finalisation with the finished gradient written to a buffer of its own in
+ * `dh_out_dtype` (dh is then only read): the vocabulary-parallel head sends fp16 partial
+ * gradients over NVLink, and writing them here saves rewriting the fp32 buffer and a separate
+ * rounding pass over [rows, hidden]. dh_out NULL: exactly soup_lmhead_finish. */
+int soup_lmhead_finish_to(const float* run_max, const float* run_sum, const float* run_dot,
+                          const int* best, const float* label_logit, const float* grad_ref,
+                          const int64_t* target, const void* weight, float* token_loss,
+                          float* entropy, int* correct, float* dh, void* dh_out, int dh_out_dtype,
+                          int64_t n, int64_t h, int64_t v_shard, int64_t col_offset, void* stream);
+
 /* out = out_dtype(dh * scale[0]) — _FusedHeadLoss.backward, solution/lm_head_loss.py:248-254. */
 int soup_lmhead_grad_scale(const float* dh, void* out, const float* scale, int64_t n,
                            int out_dtype, void* stream);

@@ -262,3 +262,27 @@ def test_more_rows_than_a_row_block(dims):
     assert_close_rel_max(dh[idx], ref["dhidden"], 1e-2, "dhidden")
     assert step.labelled.item() == n_lab
     assert abs(loss.item() - step.token_loss.sum().item() / n_lab) <= 1e-4 * max(1.0, abs(loss.item()))
+
+
+@pytest.mark.parametrize("out_dtype", [torch.float16, torch.bfloat16, torch.float32])
+def test_finish_into_a_separate_typed_buffer_is_finish_then_one_rounding(out_dtype):
+    """`head_finish(..., grad_out=)` (soup_lmhead_finish_to): the completed gradient written to a
+    buffer of its own in the wanted dtype equals the in-place finalisation rounded once, and the
+    fp32 partial gradient is left untouched."""
+    from claudemaxing_b200.lm_head_loss import head_finish, head_partial
+
+    torch.manual_seed(3)
+    n, hidden, vocab = 300, 256, 5000
+    h = torch.randn(n, hidden, device="cuda").half()
+    w = (torch.randn(vocab, hidden, device="cuda") * hidden ** -0.5).half()
+    t = torch.randint(0, vocab, (n,), device="cuda")
+    t[::7] = -100
+    state, raw = head_partial(h, w, t, 0, None, True)
+    before = raw.clone()
+    out = torch.empty(n, hidden, dtype=out_dtype, device="cuda")
+    terms_a = head_finish(state, t, w, raw, 0, grad_out=out)
+    assert torch.equal(raw, before)
+    terms_b = head_finish(state, t, w, raw, 0)            # in place
+    assert torch.equal(out, raw.to(out_dtype))
+    for a, b in zip(terms_a, terms_b):
+        assert torch.equal(a, b)

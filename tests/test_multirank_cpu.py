@@ -117,7 +117,8 @@ def _cpu_merge(gathered, target, bounds):
     return out, out.grad_ref.clone()
 
 
-def _cpu_finish(state, target, w, grad_raw=None, col_offset=0, grad_ref=None, want_metrics=True):
+def _cpu_finish(state, target, w, grad_raw=None, col_offset=0, grad_ref=None, want_metrics=True,
+                grad_out=None):
     lse = state.run_max + torch.log(state.run_sum)
     labelled = target >= 0
     loss = torch.where(labelled, lse - state.label_logit, torch.zeros_like(lse))
@@ -130,6 +131,8 @@ def _cpu_finish(state, target, w, grad_raw=None, col_offset=0, grad_ref=None, wa
         p_label = torch.exp(state.label_logit - lse)
         grad_raw[inside] += (p_label[inside] - 1.0)[:, None] * w.float()[local[inside]]
         grad_raw.mul_(1024.0)
+        if grad_out is not None:
+            grad_out.copy_(grad_raw)
     return loss, entropy, correct
 
 
