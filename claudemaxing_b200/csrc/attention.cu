@@ -1,19 +1,21 @@
 // Causal attention inside the segments of one packed row (the batch rows of a packed training
-// batch), forward, for head_dim 128 and fp16 q/k/v with grouped-query heads.
+// batch), forward and backward, for head_dim 128 and fp16 q/k/v with grouped-query heads.
 //
-// One CTA owns 128 consecutive query tokens of one segment and one query head. The keys and
-// values it may see (its segment, up to its last token) arrive in tiles of 128 tokens by TMA into
-// a two-stage ring. S = Q K^T of a tile is one tcgen05 product (M 128, N 128, K 128) into one of two
-// 128-column accumulators in tensor memory; the four softmax warps read it (thread = query row).
-// The softmax is done in two passes over the key tiles, so that the output accumulator never has
-// to be rescaled: the first pass only reduces the row maximum; the second forms S again, sums
-// the exponentials, writes P = exp(S - max) as fp16 into a 128-byte-swizzled shared-memory
-// tile (the A operand) and accumulates O += P V in tensor memory (V as MN-major B operand). At
-// segment lengths of a few hundred tokens the second QK^T is cheap next to the latency of a
-// rescale round trip through tensor memory. The epilogue divides by the sum and writes fp16 rows
-// and the log-sum-exp (natural log, of the scaled scores) per row and head.
+// Forward. One CTA owns 128 consecutive query tokens of one segment and one query head. The keys
+// and values it may see (its segment, up to its last token) arrive in tiles of 128 tokens by TMA
+// (keys through a two-stage ring). S = Q K^T of a tile is one tcgen05 product (M 128, N 128,
+// K 128) into a 128-column accumulator in tensor memory; the four softmax warps read it (thread =
+// query row). The softmax is done in two passes over the key tiles, so that the output
+// accumulator never has to be rescaled: the first pass only reduces the row maximum; the second
+// sums the exponentials, writes P = exp(S - max) as fp16 into a 128-byte-swizzled shared-memory
+// tile (the A operand) and accumulates O += P V in tensor memory (V as MN-major B operand). A
+// walk of up to three key tiles keeps all its score tiles in tensor memory between the passes
+// (S is formed once); a longer walk alternates two accumulators and forms every tile twice,
+// which at these sizes is cheap next to the latency of a rescale round trip through tensor
+// memory. The epilogue divides by the sum and writes fp16 rows and the log-sum-exp (natural log,
+// of the scaled scores) per row and head. The backward kernel is described where it starts.
 //
-// One CTA per SM (160 KB of shared memory, 384 columns of tensor memory): a CTA's walk is a chain
+// One CTA per SM (160 KB of shared memory, 512 columns of tensor memory): a CTA's walk is a chain
 // of dependent steps, so few large steps beat many small ones; CTAs take the tiles with the
 // longest walks first. Every wait is bounded (umma::mbar_wait).
 //
